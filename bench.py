@@ -1,0 +1,335 @@
+"""Benchmark of the Matmul hot path: Q8_0 GEMV (decode) at the Phi-2 MLP shapes.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload ("phi2_mlp_q8_0_gemv_decode"): one decode step through the MLPs of Phi-2's 32 layers
+reduced to its Matmul nodes: 32 x [fc1: W Q8_0H [10240,2560] . x f16 [2560] -> f16 [10240];
+fc2: W Q8_0H [2560,10240] . h f16 [10240] -> f16 [2560]], chained, every layer with its own
+weights, each node built as W.gemm(x, None, false, true, true) like nn::Linear.  64 GEMV
+launches per step, 27,878,400 algorithmic bytes each (codes + f16 scales + x + y); the weights
+(1.78 GB) exceed the 126 MB L2, so every launch streams from HBM.  Synthetic data: weights
+N(0, 0.02) (fc2: N(0, 0.01), see make_weights) quantised with sint8_quantize, input N(0, 1), seeded.
+
+Legs, all in one JSON line printed by rank 0:
+  value         device-timed GB/s, operands resident, one Executable dispatch per step
+  e2e           the same step through the public host API (Tensor.to / gemm / resolve / to):
+                host->device copy of the step's input vector from pinned memory and
+                device->host read of the step's output inside the timed region
+  roofline      algorithmic bytes per launch / average launch time, against the measured HBM peak
+  cpu_baseline  the shader-faithful CPU oracle on all host cores, bounded sample (rank 0, N=1)
+`--impl reference` times that CPU oracle alone (the reference has no CPU Matmul and its WebGPU
+backend cannot run on this box; the oracle is the restated reference arithmetic).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "Q8_0 GEMV effective bandwidth (Phi-2 MLP shapes, decode)"
+UNIT = "GB/s"
+LAYERS = 32
+D_MODEL, D_FF = 2560, 10240
+BYTES_PER_GEMV = D_FF * D_MODEL + 2 * (D_FF * D_MODEL // 32) + 2 * D_MODEL + 2 * D_FF  # 27,878,400
+WORKLOAD = "phi2_mlp_q8_0_gemv_decode"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=LAYERS, help="MLP blocks per step (default: Phi-2's 32)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="dispatch node by node instead of one CUDA graph")
+    return ap.parse_args()
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+UNIQUE_LAYERS = 4
+
+
+def make_weights(layers: int, seed: int):
+    """Per layer (fc1 [D_FF, D_MODEL], fc2 [D_MODEL, D_FF]) Q8_0H host tensors, built with the library's
+    quantiser.  Four distinct layers are generated and repeated: every layer still gets its own device
+    buffer, and bandwidth does not depend on the values.  fc1 ~ N(0, 0.02); fc2 ~ N(0, 0.01) so that the
+    chained activations keep a constant scale and stay inside the f16 range over 32 layers."""
+    import ratchet_b200 as rb
+    qz = rb.Quantizer(rb.Quantization.SInt8)
+    uniq = []
+    for l in range(min(layers, UNIQUE_LAYERS)):
+        rng = np.random.default_rng(seed + 1000 + l)
+        w1 = (rng.standard_normal((D_FF, D_MODEL), dtype=np.float32) * np.float32(0.02))
+        w2 = (rng.standard_normal((D_MODEL, D_FF), dtype=np.float32) * np.float32(0.01))
+        uniq.append((qz.sint8_quantize(rb.Tensor.from_data(w1), rb.DType.Q8_0H),
+                     qz.sint8_quantize(rb.Tensor.from_data(w2), rb.DType.Q8_0H)))
+    return [uniq[l % len(uniq)] for l in range(layers)]
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-i", str(self.index), "-lms", "100"], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, smax, reasons = [], [], set()
+        for line in self.f.read().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.f.name)
+        # the busiest samples are the ones under load
+        sm_sorted = sorted(sm)
+        load = sm_sorted[len(sm_sorted) // 2:] if sm_sorted else []
+        return {"sm_mhz": float(np.median(load)) if load else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_step(weights_raw, x16, layers):
+    """One decode step on the CPU oracle (shader-faithful arithmetic, OpenMP)."""
+    import oracle
+    h = x16
+    for l in range(layers):
+        w1, w2 = weights_raw[l]
+        h = oracle.q8h_gemv_packed(w1, D_FF, D_MODEL, h)
+        h = oracle.q8h_gemv_packed(w2, D_MODEL, D_FF, h)
+    return h
+
+
+def time_cpu(weights_raw, x16, budget_s: float, max_layers: int):
+    """Times a bounded sample: as many whole layers as fit the budget, at least one."""
+    import oracle
+    oracle.lib()
+    t0 = time.perf_counter()
+    cpu_step(weights_raw, x16, 1)  # warm-up, and a cost estimate per layer
+    per_layer = time.perf_counter() - t0
+    layers = int(max(1, min(max_layers, budget_s / max(per_layer, 1e-6))))
+    t0 = time.perf_counter()
+    cpu_step(weights_raw, x16, layers)
+    dt = time.perf_counter() - t0
+    gbs = layers * 2 * BYTES_PER_GEMV / dt / 1e9
+    return gbs, layers, dt
+
+
+def run_reference(args, rank):
+    """The reference arm: the restated reference arithmetic on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    import oracle
+    raw = [(t1.to_numpy(), t2.to_numpy()) for t1, t2 in make_weights(args.layers, 102)]
+    x16 = np.random.default_rng(102).standard_normal(D_MODEL).astype(np.float16)
+    t0 = time.perf_counter()
+    cpu_step(raw, x16, 1)
+    per_layer = time.perf_counter() - t0
+    # a bounded sample of the step: as many of its layers as keep the whole run near two minutes
+    layers = int(max(1, min(args.layers, 120.0 / max(args.steps + min(args.warmup, 2), 1) / max(per_layer, 1e-6))))
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_step(raw, x16, layers)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(raw, x16, layers)
+    dt = time.perf_counter() - t0
+    ms = dt / args.steps * 1e3
+    gbs = layers * 2 * BYTES_PER_GEMV / (dt / args.steps) / 1e9
+    sample = f"{layers} of {args.layers} layers per step ({2 * layers} GEMVs), C oracle with OpenMP"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers": layers, "note": "reference has no CPU Matmul and its WebGPU backend is unavailable on this box; this is the CPU restatement of its shader arithmetic"},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import ratchet_b200 as rb
+    from ratchet_b200 import DType, Device, DeviceRequest, Executable, PinnedArray, Tensor
+
+    if world > 1:
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    gpu = Device.request_device(DeviceRequest.GPU, local_rank)
+    stream = torch.cuda.ExternalStream(gpu.stream, device=torch.device("cuda", local_rank))
+    layers = args.layers
+
+    # ---- operands: weights resident on the device (model state), one pinned input vector, one pinned output
+    host_w = make_weights(layers, 102 + 7919 * rank)
+    dev_w = [(a.to(gpu), b.to(gpu)) for a, b in host_w]
+    rng = np.random.default_rng(102)
+    x_pin = PinnedArray((1, 1, D_MODEL), np.float16)
+    x_pin.array[...] = rng.standard_normal((1, 1, D_MODEL)).astype(np.float16)
+    y_pin = PinnedArray((1, 1, D_MODEL), np.float16)
+
+    def build_graph(x_dev):
+        h, nodes = x_dev, []
+        for w1, w2 in dev_w:
+            h = w1.gemm(h, None, False, True, True)
+            nodes.append(h)
+            h = w2.gemm(h, None, False, True, True)
+            nodes.append(h)
+        return h, nodes
+
+    # ---- device-timed leg: buffers bound once, one dispatch per step
+    x_dev = Tensor.from_data(x_pin.array, gpu)
+    y, nodes = build_graph(x_dev)
+    y.resolve()
+    kernel_names = sorted({rb._lib.load().rt_plan_kernel(gpu.plan_for(t.op.desc)).decode() for t in nodes})
+    exe = Executable(gpu, nodes, use_graph=not args.no_graph)
+    launches_per_step = exe.launches
+
+    def barrier():
+        gpu.sync()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        exe.dispatch()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        exe.dispatch()
+    ev1.record(stream)
+    barrier()
+    dev_ms = ev0.elapsed_time(ev1)
+
+    # ---- end-to-end leg: the public host API, H2D of the input and D2H of the result every step
+    def e2e_step():
+        xd = Tensor.from_data(x_pin.array, gpu)               # H2D from pinned memory
+        out, _ = build_graph(xd)                              # 2*layers lazy Matmul nodes
+        out.resolve(sync=False)                               # plan lookup + dispatch
+        out.to(Device.CPU, out=y_pin.array)                   # D2H of the step's result (waits)
+
+    for _ in range(max(args.warmup, 3)):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev2.record(stream)
+    for _ in range(args.steps):
+        e2e_step()
+    ev3.record(stream)
+    barrier()
+    e2e_ms = ev2.elapsed_time(ev3)                 # device timeline, host gaps included
+    e2e_wall_ms = (time.perf_counter() - t0) * 1e3  # the host's view of the same region
+    clocks = sampler.stop() if rank == 0 else None
+
+    # the step's output must be the same through both legs, and finite
+    y_dev = y.to(Device.CPU).to_numpy().reshape(-1)
+    assert np.all(np.isfinite(y_dev.astype(np.float32))), "non-finite benchmark output"
+    assert np.array_equal(y_dev.view(np.uint16), y_pin.array.reshape(-1).view(np.uint16)), "legs disagree"
+
+    if world > 1:
+        t = torch.tensor([dev_ms, e2e_ms, e2e_wall_ms], device=f"cuda:{local_rank}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_ms, e2e_wall_ms = (float(v) for v in t.tolist())
+
+    if rank == 0:
+        peak, peak_kind = peaks()
+        gemvs = 2 * layers
+        step_bytes = gemvs * BYTES_PER_GEMV
+        ms_per_step = dev_ms / args.steps
+        value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+        launch_us = ms_per_step * 1e3 / gemvs
+        achieved = BYTES_PER_GEMV / (launch_us * 1e-6) / 1e9
+        e2e_ms_step = max(e2e_ms, e2e_wall_ms) / args.steps
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layers": layers, "gemv_per_step": gemvs,
+                       "shapes": "W Q8_0H [10240,2560] and [2560,10240], x f16, M=1",
+                       "l2": f"inputs larger than L2: {gemvs * BYTES_PER_GEMV / 1e6:.0f} MB of distinct weights per step vs 126 MB L2",
+                       "dispatch": "node by node" if args.no_graph else "one CUDA graph per step",
+                       "parallelism": "replicas only (independent decode streams)" if world > 1 else "single GPU",
+                       "kernels": kernel_names},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": f"of {peak_kind}", "launch_us": launch_us, "bytes_per_launch": BYTES_PER_GEMV,
+                         "traffic": None},
+            "e2e": {"value": world * step_bytes / (e2e_ms_step * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms_step,
+                    "h2d_bytes_per_step": int(x_pin.nbytes), "d2h_bytes_per_step": int(y_pin.nbytes)},
+            "gpu_launches": args.steps * launches_per_step,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            import oracle
+            raw = [(a.to_numpy(), b.to_numpy()) for a, b in host_w]
+            gbs, l_used, dt = time_cpu(raw, x_pin.array.reshape(-1).copy(), budget_s=15.0, max_layers=layers)
+            line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+                                    "sample": f"{l_used} of {layers} layers ({2 * l_used} GEMVs) in {dt:.2f} s, C oracle with OpenMP"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

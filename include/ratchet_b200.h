@@ -1,0 +1,231 @@
+/*
+ * ratchet_b200 — C ABI of the B200 (sm_100a) implementation of ratchet-core's Matmul path.
+ *
+ * The reference (FL33TW00D/ratchet) is Rust + WebGPU and has no FFI of its own; each entry
+ * point below names the Rust item whose role it takes, so that a `-sys` crate can bind these
+ * symbols and ratchet-core's `Tensor::gemm -> LazyOp::Matmul -> compile -> dispatch` path
+ * can call them instead of building WGSL.  Paths are relative to the reference project.
+ *
+ * Conventions
+ *  - every function returns an rt_status; on failure `rt_last_error()` gives a thread-local
+ *    message.  Where the reference panics (invariant violations) this library returns
+ *    RT_ERR_INVARIANT / RT_ERR_DTYPE instead of aborting; where it returns an error
+ *    (`anyhow::bail!`) this library returns RT_ERR_SHAPE.
+ *  - shapes are row-major, at most RT_MAX_RANK dimensions, int64 extents.
+ *  - device pointers are plain `void*` obtained from rt_buffer_ptr() or from any other
+ *    CUDA allocator in the same process (cudaMalloc, a framework's caching allocator).
+ *  - nothing on the launch path allocates, synchronises the device, or falls back to the CPU.
+ */
+#ifndef RATCHET_B200_H
+#define RATCHET_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RT_MAX_RANK 8
+
+typedef enum rt_status {
+    RT_OK = 0,
+    RT_ERR_SHAPE = 1,       /* reference: anyhow error from Matmul::compute_c_shape (ops/matmul.rs:284-361) */
+    RT_ERR_DTYPE = 2,       /* reference: panic in OpGuards::check_dtypes (ops/matmul.rs:454-477) */
+    RT_ERR_INVARIANT = 3,   /* reference: panic in Matmul::new / GEMMSpec::new (ops/matmul.rs:258-282, 67-94) */
+    RT_ERR_ARG = 4,         /* null pointer, bad enum, size mismatch */
+    RT_ERR_CUDA = 5,        /* a CUDA runtime call failed; message holds cudaGetErrorString */
+    RT_ERR_UNSUPPORTED = 6, /* legal request this build has no kernel for */
+    RT_ERR_NOMEM = 7,
+    RT_ERR_COMM = 8,        /* NCCL failure in the sharded path */
+    RT_ERR_COMM_TIMEOUT = 9
+} rt_status;
+
+/* crates/ratchet-core/src/dtype/mod.rs:10-20 (DType).  RT_BF16 as a matmul operand and
+ * RT_Q4_K are extensions the reference declares but does not implement
+ * (dtype/mod.rs:12, crates/ratchet-loader/src/k_quants.rs:95-103). */
+typedef enum rt_dtype {
+    RT_F32 = 0,
+    RT_F16 = 1,
+    RT_BF16 = 2,
+    RT_I32 = 3,
+    RT_U32 = 4,
+    RT_Q8_0H = 5, /* GGUF Q8_0 split into codes | f16 scales */
+    RT_Q8_0F = 6, /* GGUF Q8_0 split into codes | f32 scales */
+    RT_Q4_K = 7   /* raw GGUF Q4_K super-blocks, 144 bytes per 256 values */
+} rt_dtype;
+
+typedef enum rt_epilogue {
+    RT_EPILOGUE_NONE = 0,
+    /* bias add, then the tanh GELU of crates/ratchet-core/src/ops/unary.rs:97-119 evaluated
+     * in f32 on the value rounded to the output dtype, then rounded again: the chain
+     * fc1 -> full() -> gelu() -> cast() of crates/ratchet-models/src/whisper/mlp.rs:18-22
+     * fused into the producing kernel. */
+    RT_EPILOGUE_GELU_TANH = 1
+} rt_epilogue;
+
+typedef struct rt_shape {
+    int32_t rank;
+    int64_t dims[RT_MAX_RANK];
+} rt_shape;
+
+typedef struct rt_segment {
+    uint64_t offset;
+    uint64_t size;
+} rt_segment;
+
+/* One Matmul node: the fields of `Matmul` (ops/matmul.rs:248-255) plus the operand views. */
+typedef struct rt_matmul_desc {
+    rt_dtype lhs_dt;
+    rt_dtype rhs_dt;
+    rt_dtype bias_dt;      /* ignored unless has_bias */
+    rt_shape lhs_shape;
+    rt_shape rhs_shape;
+    rt_shape bias_shape;   /* ignored unless has_bias; must be a vector */
+    int32_t has_bias;
+    int32_t trans_lhs;
+    int32_t trans_rhs;
+    int32_t trans_out;
+    int32_t epilogue;      /* rt_epilogue; the reference has only RT_EPILOGUE_NONE */
+} rt_matmul_desc;
+
+/* What GEMMSpec exposes (ops/matmul.rs:31-245), for callers and tests. */
+typedef struct rt_gemm_spec {
+    rt_shape out_shape;     /* compute_c_shape */
+    rt_dtype out_dt;        /* = rhs dtype (ops/matmul.rs:438) */
+    int64_t lhs_stack, rhs_stack, out_stack, stacks;
+    int64_t dim_lhs_outer;  /* M: rows of op(lhs) */
+    int64_t dim_rhs_outer;  /* N: columns of op(rhs) */
+    int64_t dim_inner;      /* K */
+    int32_t is_gemv;        /* rhs is a vector and lhs is not transposed (ops/matmul.rs:221-223) */
+} rt_gemm_spec;
+
+typedef struct rt_device rt_device;
+typedef struct rt_buffer rt_buffer;
+typedef struct rt_plan rt_plan;
+typedef struct rt_executable rt_executable;
+
+/* ------------------------------------------------------------------ errors, version */
+
+/* thiserror / anyhow messages of the reference (ops/op.rs:131-144, tensor.rs:26-38). */
+const char *rt_last_error(void);
+const char *rt_status_name(rt_status s);
+/* "ratchet_b200 <semver> sm_100a"; lets a binding check what it loaded. */
+const char *rt_version(void);
+
+/* ------------------------------------------------------------------ dtypes and layouts (host) */
+
+/* DType::size_of for the plain types (dtype/mod.rs:54-64); 0 for block formats. */
+size_t rt_dtype_size(rt_dtype dt);
+int32_t rt_dtype_is_quantized(rt_dtype dt);          /* dtype/mod.rs:66-68 */
+rt_status rt_dtype_activation(rt_dtype dt, rt_dtype *out); /* dtype/mod.rs:77-83 */
+
+/* DType::segments (dtype/mod.rs:85-95) / Q8_0<T>::segments (dtype/blocks.rs:61-74):
+ * the byte ranges of one tensor's buffer.  Q8_0: codes then scales, each padded to 256 B.
+ * Plain types: one segment of max(numel*size, 16) rounded up to 4 B.  Q4_K: one segment of
+ * numel/256*144 bytes.  `segs` has room for *n_segs entries; *n_segs is set to the count. */
+rt_status rt_dtype_segments(rt_dtype dt, uint64_t numel, rt_segment *segs, int32_t *n_segs);
+/* Sum of the segment sizes: the bytes a tensor of this dtype occupies on the device. */
+rt_status rt_dtype_nbytes(rt_dtype dt, uint64_t numel, uint64_t *nbytes);
+
+/* Quantizer::sint8_quantize (quant.rs:26-79): f32 -> Q8_0F buffer; with RT_Q8_0H the same
+ * codes with the scale rounded to f16 (what the loader holds, gguf/dtype.rs:80-109).
+ * `out` must hold rt_dtype_nbytes(dt, numel).  numel % 32 == 0. */
+rt_status rt_quantize_q8_0(const float *src, uint64_t numel, rt_dtype dt, void *out);
+/* Quantizer::sint8_dequantize (quant.rs:81-124): (i8)q * d in f32; for RT_Q8_0H the f16
+ * product f16(q)*d widened to f32. */
+rt_status rt_dequantize_q8_0(const void *src, uint64_t numel, rt_dtype dt, float *out);
+/* GGUFInterop::transcode for Q8_0H / Q8_0F (crates/ratchet-loader/src/gguf/dtype.rs:44-110):
+ * n_blocks GGUF blocks {f16 d; i8 qs[32]} -> codes | pad | scales | pad. */
+rt_status rt_transcode_gguf_q8_0(const void *blocks, uint64_t n_blocks, rt_dtype dt, void *out);
+/* Q4_K encode / decode of raw GGUF super-blocks (format: k_quants.rs:95-103; no reference
+ * counterpart for the arithmetic, which follows the published GGUF format). */
+rt_status rt_quantize_q4_k(const float *src, uint64_t numel, void *out);
+rt_status rt_dequantize_q4_k(const void *src, uint64_t numel, float *out);
+
+/* ------------------------------------------------------------------ Matmul rules (host) */
+
+/* Matmul::new guards + OpGuards::check_dtypes + compute_c_shape + GEMMSpec::new
+ * (ops/matmul.rs:258-361, 442-478, 53-134).  Fills *spec on success. */
+rt_status rt_matmul_spec(const rt_matmul_desc *desc, rt_gemm_spec *spec);
+/* Matmul::compute_c_shape alone (ops/matmul.rs:284-361). */
+rt_status rt_matmul_out_shape(const rt_matmul_desc *desc, rt_shape *out);
+
+/* ------------------------------------------------------------------ device and storage */
+
+/* Device::request_device(DeviceRequest::GPU) / WgpuDevice::new
+ * (crates/ratchet-core/src/device.rs:71-80, gpu/device.rs:47-118): one CUDA device + one
+ * stream.  Fails with RT_ERR_CUDA when no sm_100 device is present: there is no CPU path. */
+rt_status rt_device_create(int32_t ordinal, rt_device **dev);
+rt_status rt_device_destroy(rt_device *dev);
+/* device.poll(WaitForSubmissionIndex) (tensor.rs:785): wait for the device's stream. */
+rt_status rt_device_sync(rt_device *dev);
+/* The device's cudaStream_t, as a void*. */
+void *rt_device_stream(rt_device *dev);
+int32_t rt_device_sm_count(rt_device *dev);
+
+/* GPUBuffer::from_bytes / BufferPool allocation (storage/gpu_buffer.rs:46-61,
+ * gpu/pools/buffer_pool.rs:82-95): sizes are rounded up to 4 B, minimum 16 B. */
+rt_status rt_buffer_alloc(rt_device *dev, uint64_t nbytes, rt_buffer **buf);
+rt_status rt_buffer_free(rt_buffer *buf);
+void *rt_buffer_ptr(rt_buffer *buf);
+uint64_t rt_buffer_size(rt_buffer *buf);
+/* queue.write_buffer + submit (gpu_buffer.rs:51-61) and DownloadBuffer (gpu_buffer.rs:155-178).
+ * Both are ordered on the device's stream; `sync` != 0 waits for completion.  For a copy to
+ * overlap anything the host memory must be page-locked (rt_host_alloc). */
+rt_status rt_upload(rt_device *dev, rt_buffer *dst, uint64_t dst_off, const void *host, uint64_t n, int32_t sync);
+rt_status rt_download(rt_device *dev, const rt_buffer *src, uint64_t src_off, void *host, uint64_t n, int32_t sync);
+/* Page-locked host memory for the two calls above. */
+rt_status rt_host_alloc(uint64_t nbytes, void **ptr);
+rt_status rt_host_free(void *ptr);
+
+/* ------------------------------------------------------------------ compile + dispatch */
+
+/* MetaOperation::compile for Matmul (op.rs:304-362, ops/matmul.rs:480-647): validates the
+ * node, routes GEMV vs GEMM (ops/matmul.rs:540-592), picks the kernel and its launch shape
+ * and allocates whatever scratch the kernel needs.  Plans are immutable and may be launched
+ * any number of times; creating plans is thread-safe. */
+rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **plan);
+rt_status rt_plan_destroy(rt_plan *plan);
+/* GEMMSpec of the planned node. */
+rt_status rt_plan_spec(const rt_plan *plan, rt_gemm_spec *spec);
+/* Name of the kernel the plan launches (the role of KernelKey, ops/matmul.rs:485-524). */
+const char *rt_plan_kernel(const rt_plan *plan);
+/* Number of kernel launches one rt_matmul_launch issues. */
+int32_t rt_plan_launches(const rt_plan *plan);
+
+/* CompiledOp dispatch (compiled_op.rs:13-19, executable.rs:25-54): enqueue the node on
+ * `stream` (a cudaStream_t; NULL = the device's stream).  Asynchronous.  `lhs`, `rhs`,
+ * `bias` are read-only device pointers to buffers laid out as rt_dtype_segments says;
+ * `out` must not alias them and holds rt_dtype_nbytes(spec.out_dt, numel(out_shape)). */
+rt_status rt_matmul_launch(rt_plan *plan, const void *lhs, const void *rhs, const void *bias, void *out, void *stream);
+
+/* One dispatch: the operands of one planned node. */
+typedef struct rt_dispatch {
+    rt_plan *plan;
+    const void *lhs;
+    const void *rhs;
+    const void *bias; /* NULL when the node has no bias */
+    void *out;
+} rt_dispatch;
+
+/* Executable (executable.rs:13-54): an ordered list of compiled nodes with their buffers bound,
+ * dispatched in one call in list order on one stream (the reference records them into one
+ * compute pass and submits once).  With `use_graph` != 0 the list is captured once into a CUDA
+ * graph at creation (on a private stream; capturing executes nothing) and each dispatch is one
+ * graph launch.  Plans and buffers must outlive the executable. */
+rt_status rt_executable_create(rt_device *dev, const rt_dispatch *nodes, int32_t n_nodes, int32_t use_graph, rt_executable **exe);
+rt_status rt_executable_dispatch(rt_executable *exe, void *stream);
+rt_status rt_executable_destroy(rt_executable *exe);
+/* Kernel launches one dispatch issues (graph or not). */
+int32_t rt_executable_launches(const rt_executable *exe);
+
+/* Debug / parity helper: dequantise a device tensor into f32 (RT_Q8_0F, RT_Q4_K) or f16
+ * (RT_Q8_0H) exactly as the kernels decode it, so "bit-exact dequantised weights" can be
+ * checked on the device.  Arithmetic: quant.rs:114-120; gemm.rs:400-406 for the f16 form. */
+rt_status rt_dequantize_device(rt_device *dev, rt_dtype dt, uint64_t numel, const void *src, void *dst, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RATCHET_B200_H */

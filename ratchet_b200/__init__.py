@@ -1,0 +1,16 @@
+"""ratchet_b200: B200 (sm_100a) implementation of ratchet-core's Matmul path.
+
+CUDA kernels + C ABI in `csrc/` (built into libratchet_b200.so by `ratchet_b200.build`), and a
+host-side mirror of the reference's Tensor / Matmul / Quantizer / Linear interface in
+`tensor.py`.  There is no CPU or PyTorch fallback: without the built library, or without an
+sm_100 device, the calls raise.
+"""
+from ._lib import InvariantError, RatchetError, ShapeError
+from ._lib import RT_EPILOGUE_GELU_TANH as EPILOGUE_GELU_TANH
+from ._lib import RT_EPILOGUE_NONE as EPILOGUE_NONE
+from .tensor import (Device, DeviceRequest, DType, Executable, GpuBuffer, Linear, Matmul, PinnedArray, Quantization, Quantizer,
+                     Tensor, bf16_bits_to_f32, f32_to_bf16_bits, transcode_gguf_q8_0)
+
+__all__ = ["Device", "DeviceRequest", "DType", "Executable", "GpuBuffer", "Linear", "Matmul", "PinnedArray", "Quantization",
+           "Quantizer", "Tensor", "RatchetError", "ShapeError", "InvariantError", "EPILOGUE_NONE",
+           "EPILOGUE_GELU_TANH", "bf16_bits_to_f32", "f32_to_bf16_bits", "transcode_gguf_q8_0"]

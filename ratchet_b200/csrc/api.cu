@@ -1,0 +1,531 @@
+// C ABI of the library: device, storage, plan ("compile") and launch ("dispatch").
+// Stands where ratchet-core's device / storage / compiled-op layers stand
+// (crates/ratchet-core/src/gpu/device.rs, storage/gpu_buffer.rs, op.rs:304-362, compiled_op.rs,
+// executable.rs:25-54 of the reference).
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "kernels.hpp"
+#include "ratchet_b200.h"
+#include "spec.hpp"
+
+namespace rt {
+Status dtype_segments(rt_dtype dt, uint64_t numel, rt_segment *segs, int *n);
+Status quantize_q8_0(const float *x, uint64_t numel, rt_dtype dt, uint8_t *out);
+Status dequantize_q8_0(const uint8_t *src, uint64_t numel, rt_dtype dt, float *out);
+Status transcode_gguf_q8_0(const uint8_t *blocks, uint64_t n_blocks, rt_dtype dt, uint8_t *out);
+Status quantize_q4_k(const float *x, uint64_t numel, uint8_t *out);
+Status dequantize_q4_k(const uint8_t *src, uint64_t numel, float *out);
+} // namespace rt
+
+using namespace rt;
+
+// Device memory is recycled through size-class free lists, the role of the reference's buffer
+// pool (crates/ratchet-core/src/gpu/pools/buffer_pool.rs:97-119): a freed buffer is kept and
+// handed to the next request of the same class, so steady-state steps call neither cudaMalloc nor
+// cudaFree (which would serialise the device).
+struct rt_device {
+    int ordinal = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    std::mutex pool_mu;
+    std::unordered_map<uint64_t, std::vector<void *>> pool; // size class -> free blocks
+    uint64_t pooled_bytes = 0;
+};
+
+static inline uint64_t size_class(uint64_t n) {
+    if (n <= 4096) return (n + 255) / 256 * 256;
+    uint64_t c = 4096;
+    while (c < n) c <<= 1;
+    // quarter steps between powers of two bound the slack at 25 %
+    uint64_t q = c / 8;
+    uint64_t r = c / 2 + (n - c / 2 + q - 1) / q * q;
+    return r < c ? r : c;
+}
+
+struct rt_buffer {
+    rt_device *dev = nullptr;
+    void *ptr = nullptr;
+    uint64_t size = 0;  // bytes the caller may use
+    uint64_t klass = 0; // bytes allocated
+};
+
+enum PlanKernel { PK_GEMM_SIMT, PK_GEMV_SIMT, PK_Q8_GEMV_MMA };
+
+struct rt_plan {
+    rt_device *dev = nullptr;
+    Spec spec;
+    PlanKernel kernel = PK_GEMM_SIMT;
+    std::string name;
+    int launches = 1;
+    int split = 1;
+    int nv = 1;
+    MatmulParams params{}; // everything but the pointers
+    uint64_t lhs_scale_offset = 0;
+};
+
+struct rt_executable {
+    rt_device *dev = nullptr;
+    std::vector<rt_dispatch> nodes;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int launches = 0;
+};
+
+#define CUDA_TRY(expr)                                                                              \
+    do {                                                                                            \
+        cudaError_t e__ = (expr);                                                                   \
+        if (e__ != cudaSuccess)                                                                     \
+            return fail(RT_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e__));          \
+    } while (0)
+
+extern "C" {
+
+const char *rt_last_error(void) { return last_error().c_str(); }
+
+const char *rt_status_name(rt_status s) {
+    switch (s) {
+    case RT_OK: return "RT_OK";
+    case RT_ERR_SHAPE: return "RT_ERR_SHAPE";
+    case RT_ERR_DTYPE: return "RT_ERR_DTYPE";
+    case RT_ERR_INVARIANT: return "RT_ERR_INVARIANT";
+    case RT_ERR_ARG: return "RT_ERR_ARG";
+    case RT_ERR_CUDA: return "RT_ERR_CUDA";
+    case RT_ERR_UNSUPPORTED: return "RT_ERR_UNSUPPORTED";
+    case RT_ERR_NOMEM: return "RT_ERR_NOMEM";
+    case RT_ERR_COMM: return "RT_ERR_COMM";
+    case RT_ERR_COMM_TIMEOUT: return "RT_ERR_COMM_TIMEOUT";
+    }
+    return "RT_ERR_?";
+}
+
+const char *rt_version(void) { return "ratchet_b200 0.1.0 sm_100a"; }
+
+/* ------------------------------------------------------------------ dtypes and layouts */
+
+size_t rt_dtype_size(rt_dtype dt) { return dtype_valid(dt) ? dtype_size(dt) : 0; }
+int32_t rt_dtype_is_quantized(rt_dtype dt) { return dtype_valid(dt) && is_quantized(dt) ? 1 : 0; }
+
+rt_status rt_dtype_activation(rt_dtype dt, rt_dtype *out) {
+    if (!out || !dtype_valid(dt)) return fail(RT_ERR_ARG, "rt_dtype_activation: bad argument");
+    *out = activation_dt(dt);
+    return RT_OK;
+}
+
+rt_status rt_dtype_segments(rt_dtype dt, uint64_t numel, rt_segment *segs, int32_t *n_segs) {
+    if (!segs || !n_segs || !dtype_valid(dt)) return fail(RT_ERR_ARG, "rt_dtype_segments: bad argument");
+    rt_segment tmp[2];
+    int n = 0;
+    Status st = dtype_segments(dt, numel, tmp, &n);
+    if (!st.ok()) return fail(st);
+    if (*n_segs < n) return fail(RT_ERR_ARG, "rt_dtype_segments: segment array too small");
+    for (int i = 0; i < n; i++) segs[i] = tmp[i];
+    *n_segs = n;
+    return RT_OK;
+}
+
+rt_status rt_dtype_nbytes(rt_dtype dt, uint64_t numel, uint64_t *nbytes) {
+    if (!nbytes || !dtype_valid(dt)) return fail(RT_ERR_ARG, "rt_dtype_nbytes: bad argument");
+    rt_segment tmp[2];
+    int n = 0;
+    Status st = dtype_segments(dt, numel, tmp, &n);
+    if (!st.ok()) return fail(st);
+    uint64_t total = 0;
+    for (int i = 0; i < n; i++) total += tmp[i].size;
+    *nbytes = total;
+    return RT_OK;
+}
+
+rt_status rt_quantize_q8_0(const float *src, uint64_t numel, rt_dtype dt, void *out) {
+    if (!src || !out || (dt != RT_Q8_0H && dt != RT_Q8_0F)) return fail(RT_ERR_ARG, "rt_quantize_q8_0: bad argument");
+    Status st = quantize_q8_0(src, numel, dt, (uint8_t *)out);
+    return st.ok() ? RT_OK : fail(st);
+}
+
+rt_status rt_dequantize_q8_0(const void *src, uint64_t numel, rt_dtype dt, float *out) {
+    if (!src || !out || (dt != RT_Q8_0H && dt != RT_Q8_0F)) return fail(RT_ERR_ARG, "rt_dequantize_q8_0: bad argument");
+    Status st = dequantize_q8_0((const uint8_t *)src, numel, dt, out);
+    return st.ok() ? RT_OK : fail(st);
+}
+
+rt_status rt_transcode_gguf_q8_0(const void *blocks, uint64_t n_blocks, rt_dtype dt, void *out) {
+    if (!blocks || !out || (dt != RT_Q8_0H && dt != RT_Q8_0F))
+        return fail(RT_ERR_ARG, "rt_transcode_gguf_q8_0: bad argument");
+    Status st = transcode_gguf_q8_0((const uint8_t *)blocks, n_blocks, dt, (uint8_t *)out);
+    return st.ok() ? RT_OK : fail(st);
+}
+
+rt_status rt_quantize_q4_k(const float *src, uint64_t numel, void *out) {
+    if (!src || !out) return fail(RT_ERR_ARG, "rt_quantize_q4_k: bad argument");
+    Status st = quantize_q4_k(src, numel, (uint8_t *)out);
+    return st.ok() ? RT_OK : fail(st);
+}
+
+rt_status rt_dequantize_q4_k(const void *src, uint64_t numel, float *out) {
+    if (!src || !out) return fail(RT_ERR_ARG, "rt_dequantize_q4_k: bad argument");
+    Status st = dequantize_q4_k((const uint8_t *)src, numel, out);
+    return st.ok() ? RT_OK : fail(st);
+}
+
+/* ------------------------------------------------------------------ Matmul rules */
+
+rt_status rt_matmul_spec(const rt_matmul_desc *desc, rt_gemm_spec *spec) {
+    if (!desc || !spec) return fail(RT_ERR_ARG, "rt_matmul_spec: null argument");
+    Spec s;
+    Status st = resolve_spec(*desc, &s);
+    if (!st.ok()) return fail(st);
+    fill_public_spec(s, spec);
+    return RT_OK;
+}
+
+rt_status rt_matmul_out_shape(const rt_matmul_desc *desc, rt_shape *out) {
+    if (!desc || !out) return fail(RT_ERR_ARG, "rt_matmul_out_shape: null argument");
+    if (desc->lhs_shape.rank < 0 || desc->lhs_shape.rank > RT_MAX_RANK || desc->rhs_shape.rank < 0 ||
+        desc->rhs_shape.rank > RT_MAX_RANK)
+        return fail(RT_ERR_ARG, "rank out of range");
+    Dims c;
+    Status st = compute_c_shape(to_dims(desc->lhs_shape), to_dims(desc->rhs_shape), desc->trans_lhs != 0,
+                                desc->trans_rhs != 0, desc->trans_out != 0, &c);
+    if (!st.ok()) return fail(st);
+    if (!from_dims(c, out)) return fail(RT_ERR_SHAPE, "output rank exceeds RT_MAX_RANK");
+    return RT_OK;
+}
+
+/* ------------------------------------------------------------------ device and storage */
+
+rt_status rt_device_create(int32_t ordinal, rt_device **dev) {
+    if (!dev) return fail(RT_ERR_ARG, "rt_device_create: null argument");
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        return fail(RT_ERR_CUDA, std::string("no CUDA device: this library has no CPU path (") +
+                                     (e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0") + ")");
+    if (ordinal < 0 || ordinal >= count) return fail(RT_ERR_ARG, "rt_device_create: ordinal out of range");
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, ordinal));
+    if (prop.major != 10)
+        return fail(RT_ERR_UNSUPPORTED, std::string("device ") + prop.name + " is sm_" + std::to_string(prop.major) +
+                                            std::to_string(prop.minor) + "; the kernels are built for sm_100a only");
+    CUDA_TRY(cudaSetDevice(ordinal));
+    rt_device *d = new (std::nothrow) rt_device();
+    if (!d) return fail(RT_ERR_NOMEM, "out of host memory");
+    d->ordinal = ordinal;
+    d->sm_count = prop.multiProcessorCount;
+    d->cc_major = prop.major;
+    d->cc_minor = prop.minor;
+    e = cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        delete d;
+        return fail(RT_ERR_CUDA, std::string("cudaStreamCreate: ") + cudaGetErrorString(e));
+    }
+    *dev = d;
+    return RT_OK;
+}
+
+rt_status rt_device_destroy(rt_device *dev) {
+    if (!dev) return RT_OK;
+    cudaSetDevice(dev->ordinal);
+    if (dev->stream) cudaStreamSynchronize(dev->stream);
+    for (auto &kv : dev->pool)
+        for (void *p : kv.second) cudaFree(p);
+    if (dev->stream) cudaStreamDestroy(dev->stream);
+    delete dev;
+    return RT_OK;
+}
+
+rt_status rt_device_sync(rt_device *dev) {
+    if (!dev) return fail(RT_ERR_ARG, "rt_device_sync: null device");
+    CUDA_TRY(cudaSetDevice(dev->ordinal));
+    CUDA_TRY(cudaStreamSynchronize(dev->stream));
+    return RT_OK;
+}
+
+void *rt_device_stream(rt_device *dev) { return dev ? (void *)dev->stream : nullptr; }
+int32_t rt_device_sm_count(rt_device *dev) { return dev ? dev->sm_count : 0; }
+
+rt_status rt_buffer_alloc(rt_device *dev, uint64_t nbytes, rt_buffer **buf) {
+    if (!dev || !buf) return fail(RT_ERR_ARG, "rt_buffer_alloc: null argument");
+    uint64_t size = nbytes < 16 ? 16 : (nbytes + 3) / 4 * 4; // buffer_pool.rs:82-95
+    uint64_t klass = size_class(size);
+    void *p = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(dev->pool_mu);
+        auto it = dev->pool.find(klass);
+        if (it != dev->pool.end() && !it->second.empty()) {
+            p = it->second.back();
+            it->second.pop_back();
+            dev->pooled_bytes -= klass;
+        }
+    }
+    if (!p) {
+        CUDA_TRY(cudaSetDevice(dev->ordinal));
+        cudaError_t e = cudaMalloc(&p, klass);
+        if (e == cudaErrorMemoryAllocation) {
+            // give the pooled blocks back and retry once
+            cudaGetLastError();
+            std::lock_guard<std::mutex> lk(dev->pool_mu);
+            for (auto &kv : dev->pool) {
+                for (void *q : kv.second) cudaFree(q);
+                kv.second.clear();
+            }
+            dev->pooled_bytes = 0;
+            e = cudaMalloc(&p, klass);
+        }
+        if (e != cudaSuccess)
+            return fail(e == cudaErrorMemoryAllocation ? RT_ERR_NOMEM : RT_ERR_CUDA, std::string("cudaMalloc: ") + cudaGetErrorString(e));
+    }
+    rt_buffer *b = new (std::nothrow) rt_buffer();
+    if (!b) {
+        cudaFree(p);
+        return fail(RT_ERR_NOMEM, "out of host memory");
+    }
+    b->dev = dev;
+    b->ptr = p;
+    b->size = size;
+    b->klass = klass;
+    *buf = b;
+    return RT_OK;
+}
+
+// A freed block may be handed out again at once: work already queued on the device's stream that
+// still uses it runs before anything a later owner queues on that stream.
+rt_status rt_buffer_free(rt_buffer *buf) {
+    if (!buf) return RT_OK;
+    rt_device *dev = buf->dev;
+    {
+        std::lock_guard<std::mutex> lk(dev->pool_mu);
+        dev->pool[buf->klass].push_back(buf->ptr);
+        dev->pooled_bytes += buf->klass;
+    }
+    delete buf;
+    return RT_OK;
+}
+
+void *rt_buffer_ptr(rt_buffer *buf) { return buf ? buf->ptr : nullptr; }
+uint64_t rt_buffer_size(rt_buffer *buf) { return buf ? buf->size : 0; }
+
+rt_status rt_upload(rt_device *dev, rt_buffer *dst, uint64_t dst_off, const void *host, uint64_t n, int32_t sync) {
+    if (!dev || !dst || (!host && n)) return fail(RT_ERR_ARG, "rt_upload: null argument");
+    if (dst_off > dst->size || n > dst->size - dst_off) return fail(RT_ERR_ARG, "rt_upload: range exceeds the buffer");
+    CUDA_TRY(cudaSetDevice(dev->ordinal));
+    if (n) CUDA_TRY(cudaMemcpyAsync((char *)dst->ptr + dst_off, host, n, cudaMemcpyHostToDevice, dev->stream));
+    if (sync) CUDA_TRY(cudaStreamSynchronize(dev->stream));
+    return RT_OK;
+}
+
+rt_status rt_download(rt_device *dev, const rt_buffer *src, uint64_t src_off, void *host, uint64_t n, int32_t sync) {
+    if (!dev || !src || (!host && n)) return fail(RT_ERR_ARG, "rt_download: null argument");
+    if (src_off > src->size || n > src->size - src_off) return fail(RT_ERR_ARG, "rt_download: range exceeds the buffer");
+    CUDA_TRY(cudaSetDevice(dev->ordinal));
+    if (n) CUDA_TRY(cudaMemcpyAsync(host, (const char *)src->ptr + src_off, n, cudaMemcpyDeviceToHost, dev->stream));
+    if (sync) CUDA_TRY(cudaStreamSynchronize(dev->stream));
+    return RT_OK;
+}
+
+rt_status rt_host_alloc(uint64_t nbytes, void **ptr) {
+    if (!ptr) return fail(RT_ERR_ARG, "rt_host_alloc: null argument");
+    CUDA_TRY(cudaMallocHost(ptr, nbytes ? nbytes : 1));
+    return RT_OK;
+}
+
+rt_status rt_host_free(void *ptr) {
+    if (!ptr) return RT_OK;
+    CUDA_TRY(cudaFreeHost(ptr));
+    return RT_OK;
+}
+
+/* ------------------------------------------------------------------ compile + dispatch */
+
+rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **plan) {
+    if (!dev || !desc || !plan) return fail(RT_ERR_ARG, "rt_matmul_plan: null argument");
+    rt_plan *pl = new (std::nothrow) rt_plan();
+    if (!pl) return fail(RT_ERR_NOMEM, "out of host memory");
+    Status st = resolve_spec(*desc, &pl->spec);
+    if (!st.ok()) {
+        delete pl;
+        return fail(st);
+    }
+    const Spec &s = pl->spec;
+    pl->dev = dev;
+    MatmulParams &p = pl->params;
+    p.M = (int)s.M; p.N = (int)s.N; p.K = (int)s.K;
+    p.stacks = (int)s.stacks; p.lhs_stack = (int)s.lhs_stack; p.rhs_stack = (int)s.rhs_stack;
+    p.trans_lhs = s.trans_lhs; p.trans_rhs = s.trans_rhs; p.trans_out = s.trans_out;
+    p.bias_mode = BIAS_NONE;
+    if (s.has_bias) {
+        if (s.trans_out) p.bias_mode = BIAS_PER_M;
+        else if (s.N == 1 && !s.trans_lhs && s.bias_len == s.M && s.M != 1) p.bias_mode = BIAS_PER_M; // gemv.rs:476-490
+        else p.bias_mode = BIAS_PER_N;
+    }
+    p.bias_dt = s.has_bias ? desc->bias_dt : RT_F32;
+    p.epilogue = s.epilogue;
+    p.lhs_batch_elems = s.M * s.K;
+    p.lhs_batch_scale_bytes = 0;
+    pl->lhs_scale_offset = 0;
+    if (desc->lhs_dt == RT_Q8_0H || desc->lhs_dt == RT_Q8_0F) {
+        rt_segment seg[2];
+        int n = 0;
+        st = dtype_segments(desc->lhs_dt, (uint64_t)(s.lhs_stack * s.M * s.K), seg, &n);
+        if (!st.ok()) {
+            delete pl;
+            return fail(st);
+        }
+        pl->lhs_scale_offset = seg[1].offset;
+        p.lhs_batch_scale_bytes = s.M * s.K / 32 * (desc->lhs_dt == RT_Q8_0H ? 2 : 4);
+    }
+
+    // Routing (ops/matmul.rs:540-592 picks GEMV when rhs is a vector; here "skinny" nodes, where
+    // the weight bytes dominate, also take the streaming kernel).
+    const bool q8 = desc->lhs_dt == RT_Q8_0H || desc->lhs_dt == RT_Q8_0F;
+    const bool empty = s.M == 0 || s.N == 0 || s.stacks == 0;
+    if (q8 && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.N >= 1 && s.N <= 8 && (s.N == 1 || s.trans_rhs) && s.K > 0 && !empty) {
+        pl->kernel = PK_Q8_GEMV_MMA;
+        pl->nv = (int)s.N;
+        pl->split = q8_gemv_mma_pick_split(p.M, p.K, dev->sm_count);
+        pl->name = std::string("q8_gemv_mma_") + (desc->lhs_dt == RT_Q8_0H ? "h" : "f") + "_nv" + std::to_string(pl->nv) +
+                   "_split" + std::to_string(pl->split);
+    } else if (s.N == 1 && !s.trans_lhs) {
+        pl->kernel = PK_GEMV_SIMT;
+        pl->name = std::string("gemv_simt_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt);
+    } else {
+        pl->kernel = PK_GEMM_SIMT;
+        pl->name = std::string("gemm_simt_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt);
+    }
+    pl->launches = empty ? 0 : 1;
+    *plan = pl;
+    return RT_OK;
+}
+
+rt_status rt_plan_destroy(rt_plan *plan) {
+    delete plan;
+    return RT_OK;
+}
+
+rt_status rt_plan_spec(const rt_plan *plan, rt_gemm_spec *spec) {
+    if (!plan || !spec) return fail(RT_ERR_ARG, "rt_plan_spec: null argument");
+    fill_public_spec(plan->spec, spec);
+    return RT_OK;
+}
+
+const char *rt_plan_kernel(const rt_plan *plan) { return plan ? plan->name.c_str() : ""; }
+int32_t rt_plan_launches(const rt_plan *plan) { return plan ? plan->launches : 0; }
+
+rt_status rt_matmul_launch(rt_plan *plan, const void *lhs, const void *rhs, const void *bias, void *out, void *stream) {
+    if (!plan) return fail(RT_ERR_ARG, "rt_matmul_launch: null plan");
+    const Spec &s = plan->spec;
+    if (plan->launches == 0) return RT_OK; // empty output
+    if (!lhs || !rhs || !out || (s.has_bias && !bias)) return fail(RT_ERR_ARG, "rt_matmul_launch: null operand");
+    if (out == lhs || out == rhs || (s.has_bias && out == bias))
+        return fail(RT_ERR_INVARIANT, "Matmul is never in place: out aliases an operand");
+    CUDA_TRY(cudaSetDevice(plan->dev->ordinal));
+    cudaStream_t st = stream ? (cudaStream_t)stream : plan->dev->stream;
+    MatmulParams p = plan->params;
+    p.lhs = lhs;
+    p.lhs_scales = plan->lhs_scale_offset ? (const void *)((const char *)lhs + plan->lhs_scale_offset) : nullptr;
+    p.rhs = rhs;
+    p.bias = s.has_bias ? bias : nullptr;
+    p.out = out;
+    cudaError_t e = cudaSuccess;
+    switch (plan->kernel) {
+    case PK_Q8_GEMV_MMA:
+        e = launch_q8_gemv_mma(p, s.desc.lhs_dt == RT_Q8_0F, plan->nv, plan->split, st);
+        break;
+    case PK_GEMV_SIMT:
+        e = launch_matmul_simt(p, s.desc.lhs_dt, s.desc.rhs_dt, true, st);
+        break;
+    case PK_GEMM_SIMT:
+        e = launch_matmul_simt(p, s.desc.lhs_dt, s.desc.rhs_dt, false, st);
+        break;
+    }
+    if (e != cudaSuccess) return fail(RT_ERR_CUDA, std::string("kernel launch (") + plan->name + "): " + cudaGetErrorString(e));
+    return RT_OK;
+}
+
+static rt_status dispatch_nodes(rt_executable *exe, cudaStream_t st) {
+    for (auto &n : exe->nodes) {
+        rt_status s = rt_matmul_launch(n.plan, n.lhs, n.rhs, n.bias, n.out, (void *)st);
+        if (s != RT_OK) return s;
+    }
+    return RT_OK;
+}
+
+rt_status rt_executable_create(rt_device *dev, const rt_dispatch *nodes, int32_t n_nodes, int32_t use_graph, rt_executable **exe) {
+    if (!dev || !exe || (n_nodes > 0 && !nodes) || n_nodes < 0) return fail(RT_ERR_ARG, "rt_executable_create: bad argument");
+    rt_executable *x = new (std::nothrow) rt_executable();
+    if (!x) return fail(RT_ERR_NOMEM, "out of host memory");
+    x->dev = dev;
+    for (int i = 0; i < n_nodes; i++) {
+        if (!nodes[i].plan || nodes[i].plan->dev != dev) {
+            delete x;
+            return fail(RT_ERR_ARG, "rt_executable_create: node without a plan of this device");
+        }
+        x->nodes.push_back(nodes[i]);
+        x->launches += nodes[i].plan->launches;
+    }
+    if (use_graph && x->launches > 0) {
+        cudaError_t e = cudaSetDevice(dev->ordinal);
+        cudaStream_t cap = nullptr;
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaStreamBeginCapture(cap, cudaStreamCaptureModeRelaxed);
+        rt_status rs = RT_OK;
+        if (e == cudaSuccess) {
+            rs = dispatch_nodes(x, cap);
+            cudaError_t e2 = cudaStreamEndCapture(cap, &x->graph);
+            if (rs == RT_OK) e = e2;
+        }
+        if (rs == RT_OK && e == cudaSuccess) e = cudaGraphInstantiate(&x->exec, x->graph, 0);
+        if (cap) cudaStreamDestroy(cap);
+        if (rs != RT_OK || e != cudaSuccess) {
+            std::string msg = rs != RT_OK ? last_error() : std::string("graph capture: ") + cudaGetErrorString(e);
+            if (x->graph) cudaGraphDestroy(x->graph);
+            delete x;
+            return fail(rs != RT_OK ? rs : RT_ERR_CUDA, msg);
+        }
+    }
+    *exe = x;
+    return RT_OK;
+}
+
+rt_status rt_executable_dispatch(rt_executable *exe, void *stream) {
+    if (!exe) return fail(RT_ERR_ARG, "rt_executable_dispatch: null executable");
+    cudaStream_t st = stream ? (cudaStream_t)stream : exe->dev->stream;
+    if (exe->exec) {
+        CUDA_TRY(cudaSetDevice(exe->dev->ordinal));
+        CUDA_TRY(cudaGraphLaunch(exe->exec, st));
+        return RT_OK;
+    }
+    return dispatch_nodes(exe, st);
+}
+
+rt_status rt_executable_destroy(rt_executable *exe) {
+    if (!exe) return RT_OK;
+    if (exe->exec) cudaGraphExecDestroy(exe->exec);
+    if (exe->graph) cudaGraphDestroy(exe->graph);
+    delete exe;
+    return RT_OK;
+}
+
+int32_t rt_executable_launches(const rt_executable *exe) { return exe ? exe->launches : 0; }
+
+rt_status rt_dequantize_device(rt_device *dev, rt_dtype dt, uint64_t numel, const void *src, void *dst, void *stream) {
+    if (!dev || !src || !dst) return fail(RT_ERR_ARG, "rt_dequantize_device: null argument");
+    if (!dtype_valid(dt) || !is_quantized(dt)) return fail(RT_ERR_DTYPE, "rt_dequantize_device: not a block format");
+    rt_segment seg[2];
+    int n = 0;
+    Status st = dtype_segments(dt, numel, seg, &n);
+    if (!st.ok()) return fail(st);
+    CUDA_TRY(cudaSetDevice(dev->ordinal));
+    const void *scales = n == 2 ? (const void *)((const char *)src + seg[1].offset) : nullptr;
+    cudaStream_t s = stream ? (cudaStream_t)stream : dev->stream;
+    CUDA_TRY(launch_dequant(dt, (long long)numel, src, scales, dst, dt == RT_Q8_0H ? RT_F16 : RT_F32, dev->sm_count, s));
+    return RT_OK;
+}
+
+} // extern "C"

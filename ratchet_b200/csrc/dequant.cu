@@ -1,0 +1,68 @@
+// Dequantise a block-format tensor on the device: the parity hook for "bit-exact dequantised
+// weights" and the weight pre-pass of the large-M tensor-core GEMM.
+// Arithmetic per element: see decode.cuh (quant.rs:114-120, gemm.rs:400-406 of the reference).
+#include "decode.cuh"
+#include "kernels.hpp"
+
+namespace rt {
+
+namespace {
+
+template <int KIND, typename OutT>
+__global__ void __launch_bounds__(256) dequant_kernel(const void *src, const void *scales, OutT *dst, long long numel) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += stride)
+        dst[i] = from_f32<OutT>(lhs_element<KIND>(src, scales, i));
+}
+
+// Q8_0H -> f16, 16 codes per thread: the pre-pass form (same values as the element-wise kernel).
+__global__ void __launch_bounds__(256) dequant_q8h_f16_vec_kernel(const uint4 *codes, const __half *scales, uint4 *dst,
+                                                                 long long n16) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
+        const uint4 w = __ldg(codes + i);
+        const __half2 d = __half2half2(__ldg(scales + (i >> 1)));
+        __half2 h[8];
+        codes4_to_half2(w.x, h[0], h[1]);
+        codes4_to_half2(w.y, h[2], h[3]);
+        codes4_to_half2(w.z, h[4], h[5]);
+        codes4_to_half2(w.w, h[6], h[7]);
+#pragma unroll
+        for (int j = 0; j < 8; j++) h[j] = __hmul2(h[j], d); // f16(q) * d rounded to f16
+        dst[2 * i] = make_uint4(h2_as_u32(h[0]), h2_as_u32(h[1]), h2_as_u32(h[2]), h2_as_u32(h[3]));
+        dst[2 * i + 1] = make_uint4(h2_as_u32(h[4]), h2_as_u32(h[5]), h2_as_u32(h[6]), h2_as_u32(h[7]));
+    }
+}
+
+} // namespace
+
+cudaError_t launch_dequant(rt_dtype dt, long long numel, const void *src, const void *scales, void *dst, rt_dtype out_dt,
+                           int sm_count, cudaStream_t stream) {
+    if (numel == 0) return cudaSuccess;
+    const int threads = 256;
+    long long want = (numel + threads - 1) / threads;
+    const int blocks = (int)(want < (long long)sm_count * 16 ? want : (long long)sm_count * 16);
+    if (dt == RT_Q8_0H && out_dt == RT_F16) {
+        if (numel % 16 == 0 && (reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) % 16 == 0) {
+            long long n16 = numel / 16;
+            long long w2 = (n16 + threads - 1) / threads;
+            const int b2 = (int)(w2 < (long long)sm_count * 16 ? w2 : (long long)sm_count * 16);
+            dequant_q8h_f16_vec_kernel<<<b2, threads, 0, stream>>>((const uint4 *)src, (const __half *)scales, (uint4 *)dst, n16);
+        } else {
+            dequant_kernel<LK_Q8H, __half><<<blocks, threads, 0, stream>>>(src, scales, (__half *)dst, numel);
+        }
+    } else if (dt == RT_Q8_0H && out_dt == RT_F32) {
+        dequant_kernel<LK_Q8H, float><<<blocks, threads, 0, stream>>>(src, scales, (float *)dst, numel);
+    } else if (dt == RT_Q8_0F && out_dt == RT_F32) {
+        dequant_kernel<LK_Q8F, float><<<blocks, threads, 0, stream>>>(src, scales, (float *)dst, numel);
+    } else if (dt == RT_Q4_K && out_dt == RT_F32) {
+        dequant_kernel<LK_Q4K, float><<<blocks, threads, 0, stream>>>(src, scales, (float *)dst, numel);
+    } else if (dt == RT_Q4_K && out_dt == RT_F16) {
+        dequant_kernel<LK_Q4K, __half><<<blocks, threads, 0, stream>>>(src, scales, (__half *)dst, numel);
+    } else {
+        return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+} // namespace rt

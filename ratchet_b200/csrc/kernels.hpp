@@ -1,0 +1,20 @@
+// Launchers of the device kernels (one translation unit each).
+#pragma once
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+
+namespace rt {
+
+// General CUDA-core kernels: any legal node.
+cudaError_t launch_matmul_simt(const MatmulParams &p, rt_dtype lhs_dt, rt_dtype act_dt, bool gemv, cudaStream_t stream);
+
+// Q8_0 x f16 GEMV / skinny GEMM on warp MMAs.  nv = columns of op(rhs), 1..8 (rhs stored [nv][K]).
+int q8_gemv_mma_pick_split(int M, int K, int sm_count);
+cudaError_t launch_q8_gemv_mma(const MatmulParams &p, bool f32_scales, int nv, int split, cudaStream_t stream);
+
+// Block-format tensor -> f32 / f16 values.
+cudaError_t launch_dequant(rt_dtype dt, long long numel, const void *src, const void *scales, void *dst, rt_dtype out_dt,
+                           int sm_count, cudaStream_t stream);
+
+} // namespace rt

@@ -1,0 +1,182 @@
+// General-purpose Matmul kernels on the CUDA cores: every dtype pair, transpose combination,
+// batch broadcast, ragged extent and bias / GELU option of the node.  They cover what the
+// specialised kernels do not (f32 operands, transposed lhs, non-transposed rhs, odd extents) with
+// f32 products and f32 accumulation.
+//
+// Roles in the reference: the scalar GEMM of crates/ratchet-core/src/ops/gemm.rs:342-492 and the
+// workgroup GEMV of crates/ratchet-core/src/ops/gemv.rs:181-331.
+#include "decode.cuh"
+#include "kernels.hpp"
+
+namespace rt {
+
+namespace {
+
+constexpr int BM = 64, BN = 64, BK = 16;
+
+template <typename ActT>
+__device__ __forceinline__ float rhs_element(const void *rhs, long long idx) {
+    return to_f32(((const ActT *)rhs)[idx]);
+}
+
+template <int KIND, typename ActT>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(MatmulParams p) {
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Bs[BK][BN + 4];
+    const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
+    const int batch = blockIdx.z;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const long long abase = (long long)(batch % p.lhs_stack) * p.M * p.K;
+    const long long bbase = (long long)(batch % p.rhs_stack) * p.K * p.N;
+
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+
+    for (int k0 = 0; k0 < p.K; k0 += BK) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int ml, kl;
+            if (p.trans_lhs) { ml = t & 63; kl = (t >> 6) + 4 * i; }
+            else             { kl = t & 15; ml = (t >> 4) + 16 * i; }
+            const int m = m0 + ml, k = k0 + kl;
+            float v = 0.f;
+            if (m < p.M && k < p.K)
+                v = lhs_element<KIND>(p.lhs, p.lhs_scales, abase + (p.trans_lhs ? (long long)k * p.M + m : (long long)m * p.K + k));
+            As[kl][ml] = v;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int nl, kl;
+            if (p.trans_rhs) { kl = t & 15; nl = (t >> 4) + 16 * i; }
+            else             { nl = t & 63; kl = (t >> 6) + 4 * i; }
+            const int n = n0 + nl, k = k0 + kl;
+            float v = 0.f;
+            if (n < p.N && k < p.K)
+                v = rhs_element<ActT>(p.rhs, bbase + (p.trans_rhs ? (long long)n * p.K + k : (long long)k * p.N + n));
+            Bs[kl][nl] = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; kk++) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[i] = As[kk][ty + 16 * i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) b[j] = Bs[kk][tx + 16 * j];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+
+    const bool has_bias = p.bias_mode != BIAS_NONE;
+    ActT *out = (ActT *)p.out + (long long)batch * p.M * p.N;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int m = m0 + ty + 16 * i;
+        if (m >= p.M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx + 16 * j;
+            if (n >= p.N) continue;
+            float bias = 0.f;
+            if (has_bias) bias = load_bias(p.bias, p.bias_dt, p.bias_mode == BIAS_PER_M ? m : n);
+            const ActT v = epilogue_value<ActT>(acc[i][j], has_bias, bias, p.epilogue);
+            out[p.trans_out ? (long long)n * p.M + m : (long long)m * p.N + n] = v;
+        }
+    }
+}
+
+// y[r] = sum_k lhs[r][k] * x[k]: one warp per row, lanes stride over K.
+template <int KIND, typename ActT>
+__global__ void __launch_bounds__(256) gemv_simt_kernel(MatmulParams p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + warp;
+    const int batch = blockIdx.z;
+    if (row >= p.M) return;
+    const long long abase = (long long)(batch % p.lhs_stack) * p.M * p.K + (long long)row * p.K;
+    const ActT *x = (const ActT *)p.rhs + (long long)(batch % p.rhs_stack) * p.K;
+    float acc = 0.f;
+    constexpr bool dense16 = (KIND == LK_F16 || KIND == LK_BF16) && sizeof(ActT) == 2;
+    constexpr bool dense32 = KIND == LK_F32 && sizeof(ActT) == 4;
+    const bool aligned = ((abase * (long long)sizeof(ActT)) % 16 == 0) && (p.K % 8 == 0) &&
+                         ((reinterpret_cast<uintptr_t>(p.lhs) | reinterpret_cast<uintptr_t>(x)) % 16 == 0);
+    if ((dense16 || dense32) && aligned) {
+        if (dense16) {
+            const ActT *w = (const ActT *)p.lhs + abase;
+            for (int k = lane * 8; k < p.K; k += 256) {
+                const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(w + k));
+                const uint4 xv = __ldg(reinterpret_cast<const uint4 *>(x + k));
+                const ActT *wp = reinterpret_cast<const ActT *>(&wv);
+                const ActT *xp = reinterpret_cast<const ActT *>(&xv);
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc = fmaf(to_f32(wp[i]), to_f32(xp[i]), acc);
+            }
+        } else {
+            const float *w = (const float *)p.lhs + abase;
+            const float *xf = (const float *)x;
+            for (int k = lane * 4; k < p.K; k += 128) {
+                const float4 wv = __ldg(reinterpret_cast<const float4 *>(w + k));
+                const float4 xv = __ldg(reinterpret_cast<const float4 *>(xf + k));
+                acc = fmaf(wv.x, xv.x, acc);
+                acc = fmaf(wv.y, xv.y, acc);
+                acc = fmaf(wv.z, xv.z, acc);
+                acc = fmaf(wv.w, xv.w, acc);
+            }
+        }
+    } else {
+        for (int k = lane; k < p.K; k += 32)
+            acc = fmaf(lhs_element<KIND>(p.lhs, p.lhs_scales, abase + k), to_f32(x[k]), acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+        const bool has_bias = p.bias_mode != BIAS_NONE;
+        float bias = 0.f;
+        if (has_bias) bias = load_bias(p.bias, p.bias_dt, p.bias_mode == BIAS_PER_M ? row : 0);
+        ((ActT *)p.out)[(long long)batch * p.M + row] = epilogue_value<ActT>(acc, has_bias, bias, p.epilogue);
+    }
+}
+
+template <int KIND, typename ActT>
+cudaError_t launch_kind_act(const MatmulParams &p, bool gemv, cudaStream_t stream) {
+    if (gemv) {
+        dim3 grid((p.M + 7) / 8, 1, p.stacks);
+        gemv_simt_kernel<KIND, ActT><<<grid, 256, 0, stream>>>(p);
+    } else {
+        dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, p.stacks);
+        gemm_simt_kernel<KIND, ActT><<<grid, 256, 0, stream>>>(p);
+    }
+    return cudaGetLastError();
+}
+
+template <int KIND>
+cudaError_t launch_kind(const MatmulParams &p, rt_dtype act, bool gemv, cudaStream_t stream) {
+    switch (act) {
+    case RT_F32: return launch_kind_act<KIND, float>(p, gemv, stream);
+    case RT_F16: return launch_kind_act<KIND, __half>(p, gemv, stream);
+    case RT_BF16: return launch_kind_act<KIND, __nv_bfloat16>(p, gemv, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+} // namespace
+
+cudaError_t launch_matmul_simt(const MatmulParams &p, rt_dtype lhs_dt, rt_dtype act_dt, bool gemv, cudaStream_t stream) {
+    switch (lhs_dt) {
+    case RT_F32: return launch_kind<LK_F32>(p, act_dt, gemv, stream);
+    case RT_F16: return launch_kind<LK_F16>(p, act_dt, gemv, stream);
+    case RT_BF16: return launch_kind<LK_BF16>(p, act_dt, gemv, stream);
+    case RT_Q8_0H: return launch_kind<LK_Q8H>(p, act_dt, gemv, stream);
+    case RT_Q8_0F: return launch_kind<LK_Q8F>(p, act_dt, gemv, stream);
+    case RT_Q4_K: return launch_kind<LK_Q4K>(p, act_dt, gemv, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+} // namespace rt

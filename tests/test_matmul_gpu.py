@@ -1,0 +1,217 @@
+"""Parity of the CUDA path against the oracle, through the host mirror and the C ABI.  GPU only."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+import ratchet_b200 as rb
+from ratchet_b200 import DType, Device, Linear, Quantization, Quantizer, Tensor
+from util import TOL, TRANS_KINDS, Problem, check_problem, make_lhs, round_to, run_problem
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+F32, F16, BF16, Q8H, Q8F, Q4K = DType.F32, DType.F16, DType.BF16, DType.Q8_0H, DType.Q8_0F, DType.Q4_K
+
+
+# ----------------------------------------------------------------------------- dequantised weights: bit-exact
+
+@pytest.mark.parametrize("dt", [Q8H, Q8F, Q4K])
+def test_device_dequant_is_bit_exact(gpu, dt):
+    rng = np.random.default_rng(21)
+    shape = (96, 768)
+    t, vals = make_lhs(dt, shape, rng, 0.02)
+    got = t.to(gpu).dequantize_on_device()
+    if dt == Q8H:
+        assert got.dtype == np.float16
+        assert np.array_equal(got.view(np.uint16), vals.astype(np.float16).view(np.uint16))
+    else:
+        assert np.array_equal(got.view(np.uint32), vals.view(np.uint32))
+
+
+def test_device_dequant_matches_gguf_fixtures(gpu):
+    g = np.load(os.path.join(GOLDEN, "q8_gguf.npz"))
+    n = g["dequant"].size
+    t = rb.transcode_gguf_q8_0(g["blocks"], [n // 32, 32], Q8F, gpu)
+    assert np.array_equal(t.dequantize_on_device().reshape(-1).view(np.uint32), g["dequant"].reshape(-1).view(np.uint32))
+    g4 = np.load(os.path.join(GOLDEN, "q4k_gguf.npz"))
+    n4 = g4["dequant"].size
+    t4 = Tensor.from_quantized(g4["blocks"].reshape(-1), Q4K, [n4 // 256, 256], gpu)
+    assert np.array_equal(t4.dequantize_on_device().reshape(-1).view(np.uint32), g4["dequant"].reshape(-1).view(np.uint32))
+
+
+# ----------------------------------------------------------------------------- dense f32: the reference's own test space
+
+@pytest.mark.parametrize("i", range(int(np.load(os.path.join(GOLDEN, "sgemm.npz"))["n_cases"][0])))
+def test_sgemm_fixture(gpu, i):
+    z = np.load(os.path.join(GOLDEN, "sgemm.npz"))
+    key = f"c{i:03d}"
+    a, b, c = z[key + "_a"], z[key + "_b"], z[key + "_c"]
+    tl, tr, to, hb = (bool(v) for v in z[key + "_meta"])
+    bias = Tensor.from_data(z[key + "_bias"], gpu) if hb else None
+    out = Tensor.from_data(a, gpu).gemm(Tensor.from_data(b, gpu), bias, tl, tr, to).resolve().to(Device.CPU)
+    assert out.shape == list(c.shape)
+    # the reference's bar: ground.all_close(&ours, 1e-4, 1e-4) (matmul.rs:827)
+    assert np.allclose(out.to_numpy(), c, rtol=1e-4, atol=1e-4)
+
+
+def test_sgemm_property_space(gpu):
+    """SGEMMProblem (matmul.rs:743-756): B 1..3, M/K/N 1..256, bias, six transpose kinds; f32 and f16."""
+    rng = np.random.default_rng(22)
+    kinds = list(TRANS_KINDS.values())
+    for case in range(48):
+        B, M, K, N = int(rng.integers(1, 4)), *(int(v) for v in rng.integers(1, 257, size=3))
+        tl, tr, to = kinds[case % 6]
+        dt = F32 if case % 2 == 0 else F16
+        lhs = (B, K, M) if tl else (B, M, K)
+        rhs = (B, N, K) if tr else (B, K, N)
+        check_problem(Problem(dt, dt, lhs, rhs, (tl, tr, to), bias=bool(rng.integers(0, 2)), seed=100 + case), gpu)
+
+
+def test_reference_regression_shapes(gpu):
+    # debug_gemm (matmul.rs:854-890): transposed lhs, broadcast batch, extents not multiples of 32
+    check_problem(Problem(F32, F32, (2, 222, 252), (1, 222, 238), (True, False, False), bias=True, seed=31), gpu)
+    # debug_gemv (matmul.rs:892-926): 51865 rows, trans_out
+    for dt in (F32, F16):
+        _, kernel = check_problem(Problem(dt, dt, (1, 51865, 384), (1, 1, 384), (False, True, True), seed=32), gpu)
+        assert "gemv" in kernel
+    # test_qgemm (matmul.rs:831-852): Q8_0F [6,1500,64] x [6,64,1500], all stacks equal
+    check_problem(Problem(Q8F, F32, (6, 1500, 64), (6, 64, 1500), (False, False, False), seed=33), gpu)
+    # quantised GEMV at the Whisper logits shape
+    check_problem(Problem(Q8H, F16, (51865, 384), (1, 1, 384), (False, True, True), seed=34, w_std=0.02), gpu)
+
+
+def test_rank_and_broadcast_forms(gpu):
+    check_problem(Problem(F32, F32, (7, 5), (5,), (False, False, False), seed=41), gpu)           # implicit n
+    check_problem(Problem(F32, F32, (5,), (5, 9), (False, False, False), seed=42), gpu)           # implicit m
+    check_problem(Problem(F32, F32, (3, 2, 17, 5), (3, 2, 5, 9), (False, False, False), seed=43), gpu)
+    check_problem(Problem(F16, F16, (17, 40), (3, 2, 40, 9), (False, False, False), bias=True, seed=44), gpu)
+    check_problem(Problem(F32, F32, (4, 33, 20), (1, 20, 65), (False, False, True), seed=45), gpu)
+    check_problem(Problem(BF16, BF16, (2, 64, 96), (2, 96, 48), (False, False, False), bias=True, seed=46), gpu)
+
+
+def test_empty_and_degenerate(gpu):
+    a = Tensor.from_data(np.zeros((0, 4), dtype=np.float32), gpu)
+    b = Tensor.from_data(np.ones((4, 3), dtype=np.float32), gpu)
+    out = a.matmul(b).resolve().to(Device.CPU)
+    assert out.shape == [0, 3]
+    # K = 0: an empty sum, only the bias survives
+    a = Tensor.from_data(np.zeros((5, 0), dtype=np.float32), gpu)
+    b = Tensor.from_data(np.zeros((0, 3), dtype=np.float32), gpu)
+    bias = Tensor.from_data(np.array([1.0, 2.0, 3.0], dtype=np.float32), gpu)
+    out = a.gemm(b, bias, False, False, False).resolve().to(Device.CPU).to_numpy()
+    assert np.array_equal(out, np.tile(np.array([1.0, 2.0, 3.0], dtype=np.float32), (5, 1)))
+    check_problem(Problem(F32, F32, (1, 1), (1, 1), seed=47), gpu)
+
+
+def test_launch_rejects_aliasing_and_null(gpu):
+    lib = rb._lib.load()
+    a = Tensor.from_data(np.ones((8, 8), dtype=np.float32), gpu)
+    out = a.matmul(a)
+    plan = gpu.plan_for(out.op.desc)
+    assert lib.rt_matmul_launch(plan, a.ptr, a.ptr, None, a.ptr, None) == rb._lib.RT_ERR_INVARIANT
+    assert lib.rt_matmul_launch(plan, None, a.ptr, None, a.ptr, None) == rb._lib.RT_ERR_ARG
+
+
+# ----------------------------------------------------------------------------- Q8_0 GEMV (decode)
+
+@pytest.mark.parametrize("shape,seed", [((10240, 2560), 102), ((2560, 10240), 112)])
+def test_q8_gemv_phi2_shapes(gpu, shape, seed):
+    """BASELINE config 2: x f16 [1,1,K], W Q8_0H [N,K] from N(0,0.02), out f16 [1,1,N]."""
+    N, K = shape
+    for bias in (False, True):
+        p = Problem(Q8H, F16, shape, (1, 1, K), (False, True, True), bias=bias, seed=seed, w_std=0.02)
+        got, truth_r, truth, faithful, kernel = run_problem(p, gpu)
+        assert kernel.startswith("q8_gemv_mma_h_nv1"), kernel
+        err = oracle.rel_l2(got, truth_r)
+        err_ref = oracle.rel_l2(faithful, truth_r)
+        assert err <= 1e-3, (kernel, err)
+        assert err <= err_ref + 1e-4  # exact products: at least as close to the truth as the reference's arithmetic
+    # f32 scales with f16 activations (extension) and the reference's (Q8_0F, F32) pair
+    _, kernel = check_problem(Problem(Q8F, F16, shape, (1, 1, K), (False, True, True), bias=True, seed=seed, w_std=0.02), gpu)
+    assert kernel.startswith("q8_gemv_mma_f")
+    check_problem(Problem(Q8F, F32, shape, (1, 1, K), (False, True, True), bias=True, seed=seed, w_std=0.02), gpu)
+
+
+def test_q8_gemv_shapes_and_forms(gpu):
+    for N, K in [(16, 32), (15, 64), (17, 96), (33, 2560), (1000, 352), (4096, 4096), (7, 8192)]:
+        check_problem(Problem(Q8H, F16, (N, K), (1, K), (False, True, True), bias=True, seed=N + K, w_std=0.05), gpu)
+    # non-transposed vector [K,1] and no trans_out: out [N,1]
+    check_problem(Problem(Q8H, F16, (64, 256), (256, 1), (False, False, False), seed=51, w_std=0.05), gpu)
+    # batched vectors against one weight (the reference's GEMV does not broadcast W; GEMMSpec does)
+    check_problem(Problem(Q8H, F16, (96, 128), (3, 1, 128), (False, True, True), bias=True, seed=52, w_std=0.05), gpu)
+    # batched weights
+    check_problem(Problem(Q8H, F16, (3, 96, 128), (3, 1, 128), (False, True, True), seed=53, w_std=0.05), gpu)
+    # fused GELU epilogue
+    check_problem(Problem(Q8H, F16, (512, 1024), (1, 1024), (False, True, True), bias=True, epilogue=1, seed=54, w_std=0.05), gpu)
+
+
+@pytest.mark.parametrize("nv", [2, 3, 5, 8])
+def test_q8_skinny_gemm_streams_weights_once(gpu, nv):
+    for to in (True, False):
+        _, kernel = check_problem(Problem(Q8H, F16, (1000, 2560), (1, nv, 2560), (False, True, to), bias=True,
+                                          seed=60 + nv, w_std=0.02), gpu)
+        assert f"nv{nv}" in kernel
+
+
+# ----------------------------------------------------------------------------- Q8_0 GEMM (prefill)
+
+def test_q8_gemm_whisper_mlp_chain(gpu):
+    """BASELINE config 3: A f16 [1,1500,384] -> Q8_0 [1536,384] + b -> GELU -> Q8_0 [384,1536] + b."""
+    rng = np.random.default_rng(103)
+    w1_t, w1 = make_lhs(Q8H, (1536, 384), np.random.default_rng(1103), 0.02)
+    w2_t, w2 = make_lhs(Q8H, (384, 1536), np.random.default_rng(1104), 0.02)
+    b1 = round_to(F16, np.random.default_rng(2103).standard_normal(1536) * 0.02)
+    b2 = round_to(F16, np.random.default_rng(2104).standard_normal(384) * 0.02)
+    x = round_to(F16, rng.standard_normal((1, 1500, 384)))
+    fc1 = Linear(w1_t.to(gpu), Tensor.from_data(b1, gpu, F16), epilogue=rb.EPILOGUE_GELU_TANH)
+    fc2 = Linear(w2_t.to(gpu), Tensor.from_data(b2, gpu, F16))
+    y = fc2.schedule(fc1.schedule(Tensor.from_data(x, gpu, F16))).resolve().to(Device.CPU)
+    assert y.shape == [1, 1500, 384] and y.dt == F16
+    # oracle: hidden rounded to f16 between the two GEMMs, as the reference's graph does
+    h = oracle.matmul_truth(w1, x, b1, 1, 1, 1, 1536, 1500, 384, False, True, True, 1)
+    h16 = oracle.f64_to_f16(h).astype(np.float32)
+    t = oracle.matmul_truth(w2, h16, b2, 1, 1, 1, 384, 1500, 1536, False, True, True, 0)
+    assert oracle.rel_l2(y.to_f32().reshape(-1), oracle.f64_to_f16(t).astype(np.float32)) <= 1e-3
+    # and against the shader-faithful chain
+    hf = oracle.matmul_faithful(w1, x, b1, 1, 1, 1, 1536, 1500, 384, False, True, True, 1, "f16")
+    tf = oracle.matmul_faithful(w2, hf, b2, 1, 1, 1, 384, 1500, 1536, False, True, True, 0, "f16")
+    assert oracle.rel_l2(y.to_f32().reshape(-1), tf) <= 2e-3
+
+
+def test_q8_gemm_forms(gpu):
+    for (N, K, M) in [(64, 32, 9), (100, 96, 33), (1536, 384, 200), (257, 512, 129)]:
+        check_problem(Problem(Q8H, F16, (N, K), (2, M, K), (False, True, True), bias=True, seed=N + M, w_std=0.03), gpu)
+        check_problem(Problem(Q8H, F16, (N, K), (K, M), (False, False, False), seed=N + M + 1, w_std=0.03), gpu)
+    check_problem(Problem(Q8F, F32, (128, 256), (3, 50, 256), (False, True, True), bias=True, seed=71, w_std=0.03), gpu)
+    check_problem(Problem(Q8H, BF16, (320, 256), (2, 70, 256), (False, True, True), bias=True, epilogue=1, seed=72,
+                          w_std=0.03, bias_dt=F16), gpu)
+
+
+def test_dense_f32_phi2_fc1(gpu):
+    """BASELINE config 1: A f32 [1,128,2560], W f32 [10240,2560] N(0,0.02) rhs-transposed, b f32."""
+    err, _ = check_problem(Problem(F32, F32, (10240, 2560), (1, 128, 2560), (False, True, True), bias=True, seed=101,
+                                   w_std=0.02), gpu)
+    assert err <= 1e-5
+
+
+# ----------------------------------------------------------------------------- Q4_K
+
+@pytest.mark.parametrize("M", [1, 16, 512])
+def test_q4k_phi3_shapes(gpu, M):
+    """BASELINE config 4: W Q4_K [8192,3072] from N(0,0.02), x f16 [M,3072], out f16 [M,8192]."""
+    check_problem(Problem(Q4K, F16, (8192, 3072), (1, M, 3072), (False, True, True), seed=104, w_std=0.02), gpu)
+
+
+def test_q4k_forms(gpu):
+    check_problem(Problem(Q4K, F16, (40, 256), (1, 256), (False, True, True), bias=True, seed=81, w_std=0.02), gpu)
+    check_problem(Problem(Q4K, F16, (2, 33, 512), (2, 512, 7), (False, False, False), seed=82, w_std=0.02), gpu)
+    check_problem(Problem(Q4K, BF16, (64, 768), (5, 768), (False, True, True), bias=True, seed=83, w_std=0.02), gpu)
+
+
+# ----------------------------------------------------------------------------- bf16 prefill at reduced rows
+
+def test_q8_bf16_prefill_rows_of_config5(gpu):
+    """BASELINE config 5 on a slice of the rows: A bf16 [1,256,2560], W Q8_0H [10240,2560], f16 bias, GELU."""
+    check_problem(Problem(Q8H, BF16, (10240, 2560), (1, 256, 2560), (False, True, True), bias=True, epilogue=1,
+                          seed=105, w_std=0.02, bias_dt=F16), gpu)
