@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cuda/std/type_traits>
+
 #include "ratchet_b200.h"
 
 namespace rt {
@@ -60,10 +62,19 @@ __device__ __forceinline__ float load_bias(const void *bias, int bias_dt, int id
 
 // The reference's epilogue: val = dt(acc) + bias evaluated in dt (gemm.rs:485, gemv.rs:480);
 // the optional GELU is the cast -> f32 GELU -> cast chain of whisper/mlp.rs:18-22.
+// bf16 outputs are this library's extension (the reference has no bf16 Matmul): bias and GELU are
+// applied to the f32 accumulator and the result is rounded once.  A bf16 rounding is 2^-9
+// relative, so the reference's round-then-add chain would by itself cost more than the path's
+// 1e-3 rel-L2 budget.
 template <typename OutT>
 __device__ __forceinline__ OutT epilogue_value(float acc, bool has_bias, float bias, int epilogue) {
+    if (sizeof(OutT) == 2 && !cuda::std::is_same<OutT, __half>::value) {
+        float v = has_bias ? acc + bias : acc;
+        if (epilogue == RT_EPILOGUE_GELU_TANH) v = gelu_tanh_f32(v);
+        return from_f32<OutT>(v);
+    }
     OutT v = from_f32<OutT>(acc);
-    if (has_bias) v = from_f32<OutT>(to_f32(v) + bias); // one rounding of an exact-enough f32 sum == dt add
+    if (has_bias) v = from_f32<OutT>(to_f32(v) + bias); // one rounding of the f32 sum == the add in dt
     if (epilogue == RT_EPILOGUE_GELU_TANH) v = from_f32<OutT>(gelu_tanh_f32(to_f32(v)));
     return v;
 }

@@ -1,0 +1,419 @@
+// Tensor-core GEMM for sm_100a: D[R][S] = P[R][K] . Q[S][K]^T with both operands K-major and
+// 16-bit (f16 / bf16), f32 accumulation in tensor memory, fused bias / GELU epilogue.
+//
+// Takes the role of the reference's tiled GEMM (crates/ratchet-core/src/ops/gemm.rs:342-492) for
+// the nn::Linear form W.gemm(X, b, false, true, true) (crates/ratchet-nn/src/linear.rs:23), where
+// both W [N,K] and X [M,K] are K-major.  With trans_out the activations are P and the weight is Q
+// (output [M][N]); without it the roles swap (output [N][M]).  Quantised weights reach this
+// kernel as 16-bit values: the dequantise pre-pass (dequant.cu) writes them to a scratch buffer
+// owned by the plan with the reference's rounding (f16(q) * d rounded to f16, gemm.rs:400-406).
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: 128B-swizzled tiles of P (128 x 64) and Q (BN x 64) into a
+//               multi-stage shared-memory ring, completion on mbarriers
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (128 x BN x 16 per
+//               instruction), tcgen05.commit releases ring stages and publishes accumulators
+//   warps 2-5   epilogue: tcgen05.ld of one of two accumulator buffers (so the next tile's MMAs
+//               overlap), the reference's epilogue chain, vectorised global stores
+// Every wait is bounded by wall time; on expiry the kernel records the wait site in a device
+// flag, all roles leave their loops, tensor memory is freed and the kernel returns.  The host
+// reads the flag at the next rt_device_sync.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.hpp"
+
+namespace rt {
+
+__device__ int g_umma_error = 0;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64; // 64 x 16-bit = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+struct UmmaParams {
+    int R, S, K;
+    int stacks, p_stack, q_stack;
+    void *out;
+    long long out_batch_stride;
+    const void *bias;
+    int bias_dt, bias_mode; // BIAS_PER_N: index along S; BIAS_PER_M: index along R
+    int epilogue;
+    int tiles_r, tiles_s;
+    uint32_t idesc;
+};
+
+template <int BN> struct Cfg {
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN; // two accumulator buffers
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + BN * 4 /*bias*/;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false when the wait expired or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 32; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            atomicCAS(&g_umma_error, 0, site);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes, 8-row
+// groups 1024 bytes apart (the layout a 128B-swizzled TMA box produces).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;            // leading byte offset: unused for swizzled K-major
+    d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;            // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;            // 128-byte swizzle
+    return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+template <typename OutT> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    __half2 h = __halves2half2(__float2half_rn(a), __float2half_rn(b));
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    __nv_bfloat162 h = __halves2bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(b));
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const UmmaParams prm) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *tiles = smem;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + C::STAGES * C::STAGE_BYTES);
+    // bars[0..S): full, [S..2S): empty, [2S..2S+2): tmem_full, [2S+2..2S+4): tmem_empty
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * C::STAGES + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *bias_s = reinterpret_cast<float *>(smem + C::STAGES * C::STAGE_BYTES + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + C::STAGES);
+    const uint32_t bar_tfull = smem_u32(bars + 2 * C::STAGES), bar_tempty = smem_u32(bars + 2 * C::STAGES + 2);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tempty + 8 * a, 4); // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_k = (prm.K + BK - 1) / BK;
+    const int tiles_per_batch = prm.tiles_r * prm.tiles_s;
+    const int total_tiles = tiles_per_batch * prm.stacks;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+                const int r0 = (rem % prm.tiles_r) * BM, s0 = (rem / prm.tiles_r) * BN;
+                const int bp = b % prm.p_stack, bq = b % prm.q_stack;
+                for (int kb = 0; kb < num_k; kb++) {
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, 1)) { ok = false; break; }
+                    const uint32_t a_dst = smem_u32(tiles + stage * C::STAGE_BYTES);
+                    mbar_expect_tx(bar_full + 8 * stage, C::STAGE_BYTES);
+                    tma_load_3d(a_dst, &map_p, kb * BK, r0, bp, bar_full + 8 * stage);
+                    tma_load_3d(a_dst + C::A_BYTES, &map_q, kb * BK, s0, bq, bar_full + 8 * stage);
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, 2)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_k; kb++) {
+                    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + stage * C::STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + C::A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        umma_f16(d_tmem, umma_desc_sw128(a_addr + k * UMMA_K * 2), umma_desc_sw128(b_addr + k * UMMA_K * 2),
+                                 prm.idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(bar_empty + 8 * stage); // stage reusable once these MMAs have read it
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(bar_tfull + 8 * acc); // accumulator complete
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..5)
+        const int q = warp & 3; // the tensor-memory lane quarter this warp may read
+        const int ep_tid = threadIdx.x - 64;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        OutT *out_base = reinterpret_cast<OutT *>(prm.out);
+        const bool vec_ok = (prm.S % 8 == 0) && (reinterpret_cast<uintptr_t>(prm.out) % 16 == 0);
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+            const int r0 = (rem % prm.tiles_r) * BM, s0 = (rem / prm.tiles_r) * BN;
+            // bias values of this tile's columns, shared by the four epilogue warps
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (prm.bias_mode == BIAS_PER_N) {
+                for (int j = ep_tid; j < BN; j += 128)
+                    bias_s[j] = (s0 + j < prm.S) ? load_bias(prm.bias, prm.bias_dt, s0 + j) : 0.f;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, 4)) break;
+            tc_fence_after();
+            const int row = r0 + q * 32 + lane;
+            const bool has_bias = prm.bias_mode != BIAS_NONE;
+            float row_bias = 0.f;
+            if (prm.bias_mode == BIAS_PER_M && row < prm.R) row_bias = load_bias(prm.bias, prm.bias_dt, row);
+            OutT *out_row = out_base + (long long)b * prm.out_batch_stride + (long long)row * prm.S;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + acc * BN + c * 32 + ((uint32_t)(q * 32) << 16), v);
+                const int col0 = s0 + c * 32;
+                if (row < prm.R && col0 < prm.S) {
+                    if (vec_ok && col0 + 32 <= prm.S) {
+#pragma unroll
+                        for (int g = 0; g < 4; g++) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                const int i0 = g * 8 + j * 2;
+                                const float b0 = prm.bias_mode == BIAS_PER_N ? bias_s[c * 32 + i0] : row_bias;
+                                const float b1 = prm.bias_mode == BIAS_PER_N ? bias_s[c * 32 + i0 + 1] : row_bias;
+                                const OutT o0 = epilogue_value<OutT>(__uint_as_float(v[i0]), has_bias, b0, prm.epilogue);
+                                const OutT o1 = epilogue_value<OutT>(__uint_as_float(v[i0 + 1]), has_bias, b1, prm.epilogue);
+                                w[j] = pack2<OutT>(to_f32(o0), to_f32(o1));
+                            }
+                            *reinterpret_cast<uint4 *>(out_row + col0 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            if (col0 + i < prm.S) {
+                                const float bv = prm.bias_mode == BIAS_PER_N ? bias_s[c * 32 + i] : row_bias;
+                                out_row[col0 + i] = epilogue_value<OutT>(__uint_as_float(v[i]), has_bias, bv, prm.epilogue);
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // give copies that may still be in flight time to land before the CTA's memory is released
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// [stack][rows][K] 16-bit row-major -> boxes of box_rows x 64 elements, 128-byte swizzle, zero fill
+bool make_map(CUtensorMap *map, const void *base, rt_dtype dt, long long K, long long rows, long long stack, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)stack};
+    cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)K * 2 * (cuuint64_t)rows};
+    cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, dt == RT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int BN, typename OutT>
+cudaError_t launch_bn(const CUtensorMap &mp, const CUtensorMap &mq, UmmaParams prm, int sm_count, cudaStream_t stream) {
+    using C = Cfg<BN>;
+    static bool configured = false;
+    auto kernel = gemm_umma_kernel<BN, OutT>;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    prm.tiles_r = (prm.R + BM - 1) / BM;
+    prm.tiles_s = (prm.S + BN - 1) / BN;
+    // instruction descriptor: f32 accumulate, K-major A and B, N >> 3 at bit 17, M >> 4 at bit 24
+    prm.idesc |= (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    const long long total = (long long)prm.tiles_r * prm.tiles_s * prm.stacks;
+    const int grid = (int)(total < sm_count ? total : sm_count);
+    kernel<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(mp, mq, prm);
+    return cudaGetLastError();
+}
+
+} // namespace
+
+bool umma_gemm_supported(long long K) { return K >= 8 && K % 8 == 0 && encode_fn() != nullptr; }
+
+int umma_pick_bn(long long R, long long S, long long stacks, int sm_count) {
+    const long long t256 = ((R + BM - 1) / BM) * ((S + 255) / 256) * stacks;
+    return t256 >= sm_count ? 256 : 128;
+}
+
+// P: [p_stack][R][K] of p_dt, Q: [q_stack][S][K] of q_dt (f16 or bf16 each); out [stacks][R][S] of out_dt.
+cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dtype q_dt, void *out, rt_dtype out_dt,
+                             int R, int S, int K, int stacks, int p_stack, int q_stack, const void *bias, int bias_dt,
+                             int bias_mode, int epilogue, int bn, int sm_count, cudaStream_t stream) {
+    CUtensorMap mp, mq;
+    if (!make_map(&mp, P, p_dt, K, R, p_stack, BM) || !make_map(&mq, Q, q_dt, K, S, q_stack, bn))
+        return cudaErrorInvalidValue;
+    UmmaParams prm{};
+    prm.R = R; prm.S = S; prm.K = K;
+    prm.stacks = stacks; prm.p_stack = p_stack; prm.q_stack = q_stack;
+    prm.out = out;
+    prm.out_batch_stride = (long long)R * S;
+    prm.bias = bias; prm.bias_dt = bias_dt; prm.bias_mode = bias_mode;
+    prm.epilogue = epilogue;
+    prm.idesc = ((p_dt == RT_BF16 ? 1u : 0u) << 7) | ((q_dt == RT_BF16 ? 1u : 0u) << 10);
+    if (out_dt == RT_F16)
+        return bn == 256 ? launch_bn<256, __half>(mp, mq, prm, sm_count, stream) : launch_bn<128, __half>(mp, mq, prm, sm_count, stream);
+    if (out_dt == RT_BF16)
+        return bn == 256 ? launch_bn<256, __nv_bfloat16>(mp, mq, prm, sm_count, stream)
+                         : launch_bn<128, __nv_bfloat16>(mp, mq, prm, sm_count, stream);
+    return cudaErrorInvalidValue;
+}
+
+// Reads and clears the wait-expiry flag (0 = no kernel gave up a wait).
+cudaError_t umma_take_error(int *site, cudaStream_t stream) {
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbolAsync(site, g_umma_error, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return e;
+    e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return e;
+    if (*site != 0) e = cudaMemcpyToSymbolAsync(g_umma_error, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream);
+    return e;
+}
+
+} // namespace rt
