@@ -73,13 +73,14 @@ struct rt_plan {
     // tensor-core GEMM: operand roles, tile width, and the scratch that holds dequantised weights
     bool lhs_is_q = false; // the lhs is the kernel's Q operand (trans_out), else its P operand
     int R = 0, S = 0, u_stacks = 1, p_stack = 1, q_stack = 1, bn = 128;
-    void *scratch = nullptr;
+    void *scratch = nullptr;     // dequantised weights (f16)
     uint64_t scratch_bytes = 0;
+    void *act_scratch = nullptr; // bf16 activations cast to f16 (quantised weights only)
+    uint64_t act_scratch_bytes = 0;
     ~rt_plan() {
-        if (scratch) {
-            cudaSetDevice(dev->ordinal);
-            cudaFree(scratch);
-        }
+        if (scratch || act_scratch) cudaSetDevice(dev->ordinal);
+        if (scratch) cudaFree(scratch);
+        if (act_scratch) cudaFree(act_scratch);
     }
 };
 
@@ -451,6 +452,19 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
                             std::string("plan scratch: ") + cudaGetErrorString(e));
             }
             pl->launches = 2;
+            // tcgen05.mma kind::f16 takes one 16-bit format for both operands: the dequantised weights
+            // are f16 (bf16 would drop 3 of their 11 significant bits), so bf16 activations are cast
+            if (desc->rhs_dt == RT_BF16) {
+                pl->act_scratch_bytes = (uint64_t)(s.rhs_stack * s.N * s.K) * 2;
+                e = cudaMalloc(&pl->act_scratch, pl->act_scratch_bytes);
+                if (e != cudaSuccess) {
+                    pl->act_scratch = nullptr;
+                    delete pl;
+                    return fail(e == cudaErrorMemoryAllocation ? RT_ERR_NOMEM : RT_ERR_CUDA,
+                                std::string("plan scratch: ") + cudaGetErrorString(e));
+                }
+                pl->launches = 3;
+            }
         }
         pl->name = std::string("gemm_umma_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt) + "_bn" +
                    std::to_string(pl->bn) + (pl->scratch ? "_dequant_prepass" : "");
@@ -516,8 +530,16 @@ rt_status rt_matmul_launch(rt_plan *plan, const void *lhs, const void *rhs, cons
             w = plan->scratch;
             w_dt = RT_F16;
         }
-        const void *P = plan->lhs_is_q ? rhs : w, *Q = plan->lhs_is_q ? w : rhs;
-        const rt_dtype p_dt = plan->lhs_is_q ? s.desc.rhs_dt : w_dt, q_dt = plan->lhs_is_q ? w_dt : s.desc.rhs_dt;
+        const void *x = rhs;
+        rt_dtype x_dt = s.desc.rhs_dt;
+        if (plan->act_scratch) {
+            e = launch_cast_bf16_f16(rhs, plan->act_scratch, (long long)(s.rhs_stack * s.N * s.K), plan->dev->sm_count, st);
+            if (e != cudaSuccess) break;
+            x = plan->act_scratch;
+            x_dt = RT_F16;
+        }
+        const void *P = plan->lhs_is_q ? x : w, *Q = plan->lhs_is_q ? w : x;
+        const rt_dtype p_dt = plan->lhs_is_q ? x_dt : w_dt, q_dt = plan->lhs_is_q ? w_dt : x_dt;
         e = launch_gemm_umma(P, p_dt, Q, q_dt, out, s.out_dt, plan->R, plan->S, (int)s.K, plan->u_stacks, plan->p_stack,
                              plan->q_stack, p.bias, p.bias_dt, s.has_bias ? BIAS_PER_N : BIAS_NONE, p.epilogue, plan->bn,
                              plan->dev->sm_count, st);

@@ -34,7 +34,44 @@ __global__ void __launch_bounds__(256) dequant_q8h_f16_vec_kernel(const uint4 *c
     }
 }
 
+// bf16 -> f16, eight values per thread.  Exact for 2^-14 <= |x| <= 65504 (bf16 has 8 significant
+// bits, f16 has 11); larger magnitudes saturate to +-65504, smaller ones round into the f16
+// subnormals (absolute error below 2^-25).
+__global__ void __launch_bounds__(256) cast_bf16_f16_kernel(const uint4 *src, uint4 *dst, long long n8) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+        uint4 v = __ldg(src + i);
+        uint32_t *w = reinterpret_cast<uint32_t *>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float lo = fminf(fmaxf(__uint_as_float(w[j] << 16), -65504.f), 65504.f);
+            const float hi = fminf(fmaxf(__uint_as_float(w[j] & 0xFFFF0000u), -65504.f), 65504.f);
+            const __half2 h = __floats2half2_rn(lo, hi);
+            w[j] = h2_as_u32(h);
+        }
+        dst[i] = v;
+    }
+}
+
+__global__ void __launch_bounds__(256) cast_bf16_f16_tail_kernel(const __nv_bfloat16 *src, __half *dst, long long begin, long long n) {
+    const long long i = begin + (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = __float2half_rn(fminf(fmaxf(__bfloat162float(src[i]), -65504.f), 65504.f));
+}
+
 } // namespace
+
+cudaError_t launch_cast_bf16_f16(const void *src, void *dst, long long numel, int sm_count, cudaStream_t stream) {
+    if (numel == 0) return cudaSuccess;
+    const long long n8 = numel / 8;
+    if (n8 > 0) {
+        const long long want = (n8 + 255) / 256;
+        const int blocks = (int)(want < (long long)sm_count * 16 ? want : (long long)sm_count * 16);
+        cast_bf16_f16_kernel<<<blocks, 256, 0, stream>>>((const uint4 *)src, (uint4 *)dst, n8);
+    }
+    if (numel % 8)
+        cast_bf16_f16_tail_kernel<<<1, 256, 0, stream>>>((const __nv_bfloat16 *)src, (__half *)dst, n8 * 8, numel);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_dequant(rt_dtype dt, long long numel, const void *src, const void *scales, void *dst, rt_dtype out_dt,
                            int sm_count, cudaStream_t stream) {

@@ -387,6 +387,9 @@ int umma_pick_bn(long long R, long long S, long long stacks, int sm_count) {
 cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dtype q_dt, void *out, rt_dtype out_dt,
                              int R, int S, int K, int stacks, int p_stack, int q_stack, const void *bias, int bias_dt,
                              int bias_mode, int epilogue, int bn, int sm_count, cudaStream_t stream) {
+    // kind::f16 wants one format for both operands: an instruction descriptor that mixes f16 and
+    // bf16 is an illegal instruction on sm_100a
+    if (p_dt != q_dt || (p_dt != RT_F16 && p_dt != RT_BF16)) return cudaErrorInvalidValue;
     CUtensorMap mp, mq;
     if (!make_map(&mp, P, p_dt, K, R, p_stack, BM) || !make_map(&mq, Q, q_dt, K, S, q_stack, bn))
         return cudaErrorInvalidValue;

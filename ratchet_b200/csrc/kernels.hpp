@@ -26,4 +26,7 @@ cudaError_t umma_take_error(int *site, cudaStream_t stream);
 cudaError_t launch_dequant(rt_dtype dt, long long numel, const void *src, const void *scales, void *dst, rt_dtype out_dt,
                            int sm_count, cudaStream_t stream);
 
+// bf16 -> f16 (saturating) for the activations of a quantised-weight tensor-core GEMM.
+cudaError_t launch_cast_bf16_f16(const void *src, void *dst, long long numel, int sm_count, cudaStream_t stream);
+
 } // namespace rt
