@@ -163,6 +163,8 @@ rt_status rt_device_sync(rt_device *dev);
 /* The device's cudaStream_t, as a void*. */
 void *rt_device_stream(rt_device *dev);
 int32_t rt_device_sm_count(rt_device *dev);
+/* The CUDA ordinal the device was created with (gpu/device.rs:105 keeps `ordinal` too). */
+int32_t rt_device_ordinal(rt_device *dev);
 
 /* GPUBuffer::from_bytes / BufferPool allocation (storage/gpu_buffer.rs:46-61,
  * gpu/pools/buffer_pool.rs:82-95): sizes are rounded up to 4 B, minimum 16 B. */
@@ -219,6 +221,20 @@ rt_status rt_executable_dispatch(rt_executable *exe, void *stream);
 rt_status rt_executable_destroy(rt_executable *exe);
 /* Kernel launches one dispatch issues (graph or not). */
 int32_t rt_executable_launches(const rt_executable *exe);
+
+/* Linear-shaped Q8_0 GEMM for callers that must not allocate device memory: out[rows][n] =
+ * x[rows][k] . W[n][k]^T (+ bias[n]) (+ GELU), W as RT_Q8_0H, x / bias / out f16 -- the node
+ * W.gemm(x, b, false, true, true) of nn::Linear.  It has no counterpart in the reference.
+ * The dequantised weights go to an array of RT_STATIC_SCRATCH_BYTES built into the library
+ * (held by every GPU that loads it until exit) instead of a per-plan cudaMalloc, so weights with
+ * n*k*2 > RT_STATIC_SCRATCH_BYTES are refused with RT_ERR_UNSUPPORTED.  The first call on a
+ * device looks the array's address up; make that call before any stream capture.  All calls
+ * share the one array and it keeps the last call's contents: calls that may overlap on the GPU
+ * (different streams, or graphs replayed concurrently) race on it and must be serialised by the
+ * caller.  Nothing has to be cleared between calls.  `stream` NULL = the device's stream. */
+#define RT_STATIC_SCRATCH_BYTES (8u << 20)
+rt_status rt_linear_q8_0_static_scratch(rt_device *dev, const void *w, const void *x, const void *bias, void *out,
+                                        int64_t rows, int64_t n, int64_t k, int32_t epilogue, void *stream);
 
 /* Debug / parity helper: dequantise a device tensor into f32 (RT_Q8_0F, RT_Q4_K) or f16
  * (RT_Q8_0H) exactly as the kernels decode it, so "bit-exact dequantised weights" can be

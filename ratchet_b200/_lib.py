@@ -118,6 +118,7 @@ def load() -> ctypes.CDLL:
         "rt_device_sync": (c_int32, [V]),
         "rt_device_stream": (V, [V]),
         "rt_device_sm_count": (c_int32, [V]),
+        "rt_device_ordinal": (c_int32, [V]),
         "rt_buffer_alloc": (c_int32, [V, c_uint64, POINTER(V)]),
         "rt_buffer_free": (c_int32, [V]),
         "rt_buffer_ptr": (V, [V]),
@@ -136,6 +137,7 @@ def load() -> ctypes.CDLL:
         "rt_executable_dispatch": (c_int32, [V, V]),
         "rt_executable_destroy": (c_int32, [V]),
         "rt_executable_launches": (c_int32, [V]),
+        "rt_linear_q8_0_static_scratch": (c_int32, [V, V, V, V, V, c_int64, c_int64, c_int64, c_int32, V]),
         "rt_dequantize_device": (c_int32, [V, c_int32, c_uint64, V, V, V]),
     }
     for name, (res, args) in sig.items():

@@ -24,6 +24,7 @@ SOURCES = [
     "gemv_q8_mma.cu",
     "dequant.cu",
     "gemm_umma.cu",
+    "static_scratch.cu",
 ]
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

@@ -267,6 +267,7 @@ rt_status rt_device_sync(rt_device *dev) {
 
 void *rt_device_stream(rt_device *dev) { return dev ? (void *)dev->stream : nullptr; }
 int32_t rt_device_sm_count(rt_device *dev) { return dev ? dev->sm_count : 0; }
+int32_t rt_device_ordinal(rt_device *dev) { return dev ? dev->ordinal : -1; }
 
 rt_status rt_buffer_alloc(rt_device *dev, uint64_t nbytes, rt_buffer **buf) {
     if (!dev || !buf) return fail(RT_ERR_ARG, "rt_buffer_alloc: null argument");
