@@ -54,6 +54,8 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=LAYERS, help="MLP blocks per step (default: Phi-2's 32)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="dispatch node by node instead of one CUDA graph")
+    ap.add_argument("--extras", default="", help="comma list of the other configurations to time on one GPU and "
+                    "report under \"extras\": c1,c3,c4,c5,c5long or all")
     return ap.parse_args()
 
 
@@ -133,6 +135,114 @@ class ClockSampler:
         load = sm_sorted[len(sm_sorted) // 2:] if sm_sorted else []
         return {"sm_mhz": float(np.median(load)) if load else None, "sm_max_mhz": max(smax) if smax else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------- the other configurations
+
+def tensor_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
+def time_node(gpu, stream, make_node, copies: int, iters: int, warmup: int = 3):
+    """Times one Matmul node: `copies` independent operand sets are rotated so that a memory-bound
+    node never finds its weights in L2.  Returns microseconds per launch."""
+    import torch
+    import ratchet_b200 as rb
+    lib = rb._lib.load()
+    nodes = [make_node(i) for i in range(copies)]
+    for n in nodes:
+        n.resolve()
+    args = [(gpu.plan_for(n.op.desc), n.op.lhs.ptr, n.op.rhs.ptr, n.op.bias.ptr if n.op.bias is not None else None, n.ptr)
+            for n in nodes]
+    for i in range(warmup * copies):
+        rb._lib.check(lib.rt_matmul_launch(*args[i % copies], None))
+    gpu.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(iters):
+        rb._lib.check(lib.rt_matmul_launch(*args[i % copies], None))
+    e1.record(stream)
+    gpu.sync()
+    torch.cuda.synchronize()
+    kernel = lib.rt_plan_kernel(args[0][0]).decode()
+    launches = int(lib.rt_plan_launches(args[0][0]))
+    return e0.elapsed_time(e1) * 1e3 / iters, kernel, launches
+
+
+def run_extras(which, gpu, stream):
+    """Configurations 1, 3, 4, 5 of BASELINE.json on one GPU: time, TFLOP/s or GB/s, roofline fraction."""
+    import ratchet_b200 as rb
+    from ratchet_b200 import DType, Tensor
+    hbm, hbm_kind = peaks()
+    tf_burst, tf_sust, tf_kind = tensor_peaks()
+    qz = rb.Quantizer(rb.Quantization.SInt8)
+    out = []
+
+    def weight(shape, dt, seed, std=0.02):
+        w = np.random.default_rng(seed).standard_normal(shape, dtype=np.float32) * np.float32(std)
+        t = Tensor.from_data(w)
+        if dt == DType.Q8_0H:
+            return qz.sint8_quantize(t, DType.Q8_0H)
+        if dt == DType.Q4_K:
+            return rb.Quantizer.q4k_quantize(t)
+        return Tensor.from_data(w, dt=dt)
+
+    def act(shape, dt, seed):
+        return Tensor.from_data(np.random.default_rng(seed).standard_normal(shape, dtype=np.float32), dt=dt)
+
+    def record(name, us, kernel, launches, flops, nbytes, bound, note=""):
+        tfs, gbs = flops / us / 1e6, nbytes / us / 1e3
+        peak = tf_burst if bound == "tensor" else hbm
+        ach = tfs if bound == "tensor" else gbs
+        out.append({"workload": name, "us_per_call": us, "kernel": kernel, "launches_per_call": launches,
+                    "tflops": tfs, "gbs": gbs, "roofline": {"bound": bound, "achieved": ach, "peak": peak,
+                    "unit": "TFLOP/s" if bound == "tensor" else "GB/s", "frac": ach / peak,
+                    "peak_kind": f"of {tf_kind if bound == 'tensor' else hbm_kind}"}, "note": note})
+
+    def linear_node(w_dev, x_dev, b_dev, epilogue=0):
+        return w_dev.gemm(x_dev, b_dev, False, True, True, epilogue=epilogue)
+
+    if "c1" in which:
+        w = weight((10240, 2560), DType.F32, 1101).to(gpu)
+        b = weight((10240,), DType.F32, 2101).to(gpu)
+        x = act((1, 128, 2560), DType.F32, 101).to(gpu)
+        us, k, l = time_node(gpu, stream, lambda i: linear_node(w, x, b), 1, 20)
+        record("c1_dense_f32_phi2_fc1_m128", us, k, l, 2 * 128 * 10240 * 2560, 111452160, "hbm", "weights L2-resident between calls")
+    if "c3" in which:
+        w1, w2 = weight((1536, 384), DType.Q8_0H, 1103).to(gpu), weight((384, 1536), DType.Q8_0H, 1104).to(gpu)
+        b1, b2 = weight((1536,), DType.F16, 2103).to(gpu), weight((384,), DType.F16, 2104).to(gpu)
+        x = act((1, 1500, 384), DType.F16, 103).to(gpu)
+        h = linear_node(w1, x, b1, rb.EPILOGUE_GELU_TANH)
+        us1, k1, l1 = time_node(gpu, stream, lambda i: linear_node(w1, x, b1, rb.EPILOGUE_GELU_TANH), 1, 200)
+        h.resolve()
+        us2, k2, l2 = time_node(gpu, stream, lambda i: linear_node(w2, h, b2), 1, 200)
+        record("c3_whisper_tiny_mlp_q8_0_m1500", us1 + us2, k1 + " + " + k2, l1 + l2, 2 * 1500 * 384 * 1536 * 2, 12777216,
+               "tensor", "fc1+GELU then fc2, back-to-back launches; latency-bound (one wave)")
+    if "c4" in which:
+        hw = weight((8192, 3072), DType.Q4_K, 1104)
+        copies = 20  # 20 x 14.2 MB of weights: larger than L2
+        ws = [hw.to(gpu) for _ in range(copies)]
+        for M in (1, 16, 512):
+            x = act((1, M, 3072), DType.F16, 104).to(gpu)
+            us, k, l = time_node(gpu, stream, lambda i: linear_node(ws[i], x, None), copies, 200 if M < 512 else 60)
+            nbytes = 14155776 + 2 * M * 3072 + 2 * M * 8192
+            record(f"c4_q4_k_phi3_m{M}", us, k, l, 2 * M * 8192 * 3072, nbytes, "tensor" if M == 512 else "hbm",
+                   "rotating 20 weight copies")
+    for name, rows in (("c5", 2048), ("c5long", 8192)):
+        if name not in which:
+            continue
+        w = weight((10240, 2560), DType.Q8_0H, 1105).to(gpu)
+        b = weight((10240,), DType.F16, 2105).to(gpu)
+        x = act((4, rows, 2560), DType.BF16, 105).to(gpu)
+        us, k, l = time_node(gpu, stream, lambda i: linear_node(w, x, b, rb.EPILOGUE_GELU_TANH), 1, 10)
+        record(f"{name}_q8_0_prefill_bf16_4x{rows}", us, k, l, 2 * 4 * rows * 10240 * 2560,
+               4 * rows * 2560 * 2 + 27852800 + 4 * rows * 10240 * 2, "tensor", "bias + fused GELU, 1 GPU")
+    return out
 
 
 def cpu_step(weights_raw, x16, layers):
@@ -325,6 +435,9 @@ def main():
             gbs, l_used, dt = time_cpu(raw, x_pin.array.reshape(-1).copy(), budget_s=15.0, max_layers=layers)
             line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
                                     "sample": f"{l_used} of {layers} layers ({2 * l_used} GEMVs) in {dt:.2f} s, C oracle with OpenMP"}
+        if args.extras and world == 1:
+            which = {"c1", "c3", "c4", "c5", "c5long"} if args.extras == "all" else set(args.extras.split(","))
+            line["extras"] = run_extras(which, gpu, stream)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -23,6 +23,7 @@ RT_OK, RT_ERR_SHAPE, RT_ERR_DTYPE, RT_ERR_INVARIANT, RT_ERR_ARG, RT_ERR_CUDA, RT
 RT_F32, RT_F16, RT_BF16, RT_I32, RT_U32, RT_Q8_0H, RT_Q8_0F, RT_Q4_K = range(8)
 
 RT_EPILOGUE_NONE, RT_EPILOGUE_GELU_TANH = 0, 1
+RT_LAUNCH_LHS_CONSTANT = 1
 
 
 class rt_shape(Structure):
@@ -62,7 +63,8 @@ class rt_gemm_spec(Structure):
 
 
 class rt_dispatch(Structure):
-    _fields_ = [("plan", c_void_p), ("lhs", c_void_p), ("rhs", c_void_p), ("bias", c_void_p), ("out", c_void_p)]
+    _fields_ = [("plan", c_void_p), ("lhs", c_void_p), ("rhs", c_void_p), ("bias", c_void_p), ("out", c_void_p),
+                ("flags", ctypes.c_uint32)]
 
 
 class RatchetError(RuntimeError):
@@ -133,6 +135,7 @@ def load() -> ctypes.CDLL:
         "rt_plan_kernel": (c_char_p, [V]),
         "rt_plan_launches": (c_int32, [V]),
         "rt_matmul_launch": (c_int32, [V, V, V, V, V, V]),
+        "rt_matmul_launch_ex": (c_int32, [V, V, V, V, V, V, ctypes.c_uint32]),
         "rt_executable_create": (c_int32, [V, POINTER(rt_dispatch), c_int32, c_int32, POINTER(V)]),
         "rt_executable_dispatch": (c_int32, [V, V]),
         "rt_executable_destroy": (c_int32, [V]),

@@ -262,6 +262,8 @@ rt_status rt_device_sync(rt_device *dev) {
     if (site != 0)
         return fail(RT_ERR_CUDA, "a tensor-core GEMM gave up a bounded wait (site " + std::to_string(site) +
                                      "): its output is incomplete");
+    CUDA_TRY(gemv_take_error(&site, dev->stream));
+    if (site != 0) return fail(RT_ERR_CUDA, "a GEMV gave up waiting for its weight copies: its output is incomplete");
     return RT_OK;
 }
 
@@ -424,10 +426,12 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
     // the weight bytes dominate, also take the streaming kernel).
     const bool q8 = desc->lhs_dt == RT_Q8_0H || desc->lhs_dt == RT_Q8_0F;
     const bool empty = s.M == 0 || s.N == 0 || s.stacks == 0;
-    if (q8 && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.N >= 1 && s.N <= 8 && (s.N == 1 || s.trans_rhs) && s.K > 0 && !empty) {
+    const int gemv_split = (q8 && s.K > 0 && !empty && !force_simt())
+                               ? q8_gemv_mma_pick_split(p.M, p.K, dev->sm_count, desc->lhs_dt == RT_Q8_0H ? 2 : 4) : 0;
+    if (gemv_split > 0 && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.N >= 1 && s.N <= 8 && (s.N == 1 || s.trans_rhs) && s.K > 0 && !empty) {
         pl->kernel = PK_Q8_GEMV_MMA;
         pl->nv = (int)s.N;
-        pl->split = q8_gemv_mma_pick_split(p.M, p.K, dev->sm_count);
+        pl->split = gemv_split;
         pl->name = std::string("q8_gemv_mma_") + (desc->lhs_dt == RT_Q8_0H ? "h" : "f") + "_nv" + std::to_string(pl->nv) +
                    "_split" + std::to_string(pl->split);
     } else if (umma_eligible(*desc, s)) {
@@ -496,6 +500,11 @@ const char *rt_plan_kernel(const rt_plan *plan) { return plan ? plan->name.c_str
 int32_t rt_plan_launches(const rt_plan *plan) { return plan ? plan->launches : 0; }
 
 rt_status rt_matmul_launch(rt_plan *plan, const void *lhs, const void *rhs, const void *bias, void *out, void *stream) {
+    return rt_matmul_launch_ex(plan, lhs, rhs, bias, out, stream, 0);
+}
+
+rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, const void *bias, void *out, void *stream,
+                              uint32_t flags) {
     if (!plan) return fail(RT_ERR_ARG, "rt_matmul_launch: null plan");
     const Spec &s = plan->spec;
     if (plan->launches == 0) return RT_OK; // empty output
@@ -513,7 +522,7 @@ rt_status rt_matmul_launch(rt_plan *plan, const void *lhs, const void *rhs, cons
     cudaError_t e = cudaSuccess;
     switch (plan->kernel) {
     case PK_Q8_GEMV_MMA:
-        e = launch_q8_gemv_mma(p, s.desc.lhs_dt == RT_Q8_0F, plan->nv, plan->split, st);
+        e = launch_q8_gemv_mma(p, s.desc.lhs_dt == RT_Q8_0F, plan->nv, plan->split, (flags & RT_LAUNCH_LHS_CONSTANT) != 0, st);
         break;
     case PK_GEMV_SIMT:
         e = launch_matmul_simt(p, s.desc.lhs_dt, s.desc.rhs_dt, true, st);
@@ -553,7 +562,7 @@ rt_status rt_matmul_launch(rt_plan *plan, const void *lhs, const void *rhs, cons
 
 static rt_status dispatch_nodes(rt_executable *exe, cudaStream_t st) {
     for (auto &n : exe->nodes) {
-        rt_status s = rt_matmul_launch(n.plan, n.lhs, n.rhs, n.bias, n.out, (void *)st);
+        rt_status s = rt_matmul_launch_ex(n.plan, n.lhs, n.rhs, n.bias, n.out, (void *)st, n.flags);
         if (s != RT_OK) return s;
     }
     return RT_OK;

@@ -4,18 +4,24 @@
 // for the (Q8_0H, F16) pair, and of its GEMM (ops/gemm.rs:342-492) when op(rhs) has at most 8
 // columns, where the problem is bound by streaming the weight bytes once.
 //
-// Design (HBM-bound: 1 byte per weight, ~1.06 with scales):
-//  * a CTA owns 16 consecutive rows of W and a slice of K; its 8 warps interleave over the
-//    32-wide Q8_0 blocks of that slice, so one warp instruction streams 16 rows x 32 codes;
-//  * each lane issues 8-byte loads (4 lanes cover one block of one row = one 32-B sector) and
-//    keeps UNROLL blocks in flight;
-//  * codes become exact f16 values with two byte-permutes and one packed subtract per four codes;
-//    the 16x32 code tile times the 32xNV activation tile goes through two m16n8k16 tensor-core
-//    MMAs with f32 accumulation (products and sums are exact up to f32 rounding);
-//  * the per-block scale d multiplies the block's partial sum: sum_k (q*d)*x = d * sum_k q*x;
-//  * warps are reduced through shared memory in a fixed order; when K is split over a thread-block
-//    cluster, rank 0 gathers the other CTAs' partials through distributed shared memory, also in
-//    a fixed order, so results are deterministic;
+// Design (HBM-bound: 1 byte per weight, ~1.06 with scales; the whole problem is one wave):
+//  * a CTA owns 16 consecutive rows of W and a slice of K.  At kernel entry one thread asks the
+//    TMA engine for the CTA's whole share of the codes (one bulk copy per row into padded
+//    shared-memory rows, completion counted on an mbarrier) and the other threads fetch the
+//    block scales.  Up to five CTAs fit one SM, so every byte of W is in flight within the
+//    first microsecond and no register is spent on latency hiding;
+//  * the weight requests are issued BEFORE the kernel waits on its stream predecessor
+//    (programmatic dependent launch) when the caller states that the weights are constants, so
+//    layer i+1 streams its weights while layer i is still finishing; the activations, which the
+//    predecessor produces, are only read after that wait;
+//  * 8 warps interleave over the 32-wide Q8_0 blocks.  Codes become exact f16 values with two
+//    byte-permutes and one packed subtract per four codes; a 16x32 code tile times the 32xNV
+//    activation tile goes through two m16n8k16 tensor-core MMAs with f32 accumulation (products
+//    and sums exact up to f32 rounding); the block scale multiplies the block's partial sum:
+//    sum_k (q*d)*x = d * sum_k q*x;
+//  * warps are reduced through shared memory in a fixed order; when K is split over a
+//    thread-block cluster, rank 0 gathers the other CTAs' partials through distributed shared
+//    memory, also in a fixed order: results are deterministic;
 //  * epilogue = the reference's: f16(acc) + bias in f16, optional fused GELU.
 #include <cooperative_groups.h>
 
@@ -26,11 +32,14 @@ namespace cg = cooperative_groups;
 
 namespace rt {
 
+__device__ int g_gemv_error = 0;
+
 namespace {
 
 constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
 constexpr int ROWS = 16;
-constexpr int UNROLL = 4;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 __device__ __forceinline__ void mma_m16n8k16_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -38,110 +47,170 @@ __device__ __forceinline__ void mma_m16n8k16_f16(float (&c)[4], const uint32_t (
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint2 ldg_stream_u2(const void *p) {
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
 }
 
 __device__ __forceinline__ float scale_to_f32(__half s) { return __half2float(s); }
 __device__ __forceinline__ float scale_to_f32(float s) { return s; }
 
+// Row stride of the staged codes: a multiple of 16 (bulk-copy alignment) that is 32 mod 128, so the
+// eight rows a half-warp reads start 32 bytes apart in bank space (conflict-free 8-byte reads).
+__host__ __device__ inline int code_row_stride(int ks) { return ks + ((32 - ks % 128) + 128) % 128; }
+__host__ __device__ inline int scale_row_stride(int nblk_slice) { return nblk_slice | 1; }
+
+// Shared memory: [codes 16 x cstride][scales 16 x sstride][mbarrier]; the first 4 KB double as the
+// cross-warp reduction buffer once the codes have been consumed (the mbarrier lies beyond it).
+__host__ __device__ inline size_t bar_offset(int blocks_per_cta, int scale_size) {
+    const size_t codes = (size_t)ROWS * code_row_stride(blocks_per_cta * 32);
+    const size_t scales = ((size_t)ROWS * scale_row_stride(blocks_per_cta) * scale_size + 15) & ~(size_t)15;
+    const size_t red = (size_t)WARPS * ROWS * 8 * sizeof(float);
+    return codes + scales < red ? red : codes + scales;
+}
+
 // ScaleT: __half (Q8_0H) or float (Q8_0F).  NV: number of activation vectors (1..8).
 // SPLIT: K is split over a cluster of gridDim.y CTAs.
 template <typename ScaleT, int NV, bool SPLIT>
-__global__ void __launch_bounds__(WARPS * 32) q8_gemv_mma_kernel(MatmulParams p, int blocks_per_cta) {
-    __shared__ float red[WARPS][ROWS][8];
-
+__global__ void __launch_bounds__(THREADS, 5) q8_gemv_bulk_kernel(MatmulParams p, int blocks_per_cta, int lhs_constant) {
+    extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int batch = blockIdx.z;
     const int nblk = p.K >> 5;
     const int split = SPLIT ? (int)blockIdx.y : 0;
     const int blk_begin = split * blocks_per_cta;
-    const int blk_end = min(nblk, blk_begin + blocks_per_cta);
+    const int blk_cnt = max(0, min(nblk, blk_begin + blocks_per_cta) - blk_begin);
+    const int ks = blocks_per_cta * 32;
+    const int cstride = code_row_stride(ks);
+    const int sstride = scale_row_stride(blocks_per_cta);
+    uint8_t *codes_s = smem;
+    ScaleT *scales_s = reinterpret_cast<ScaleT *>(smem + ROWS * cstride);
+    uint64_t *bar = reinterpret_cast<uint64_t *>(smem + bar_offset(blocks_per_cta, (int)sizeof(ScaleT)));
+    const uint32_t bar_addr = smem_u32(bar);
 
-    const int row0 = blockIdx.x * ROWS + g;
-    // rows past the end re-read the last row; their results are never stored
-    const int ra = min(row0, p.M - 1), rb = min(row0 + 8, p.M - 1);
+    const int row_base = blockIdx.x * ROWS;
+    const int rows_here = min(ROWS, p.M - row_base);
     const long long lb = batch % p.lhs_stack;
     const uint8_t *codes = (const uint8_t *)p.lhs + lb * p.lhs_batch_elems;
     const ScaleT *scales = (const ScaleT *)((const uint8_t *)p.lhs_scales + lb * p.lhs_batch_scale_bytes);
-    const uint8_t *qa = codes + (long long)ra * p.K + c * 8;
-    const uint8_t *qb = codes + (long long)rb * p.K + c * 8;
-    const ScaleT *sa = scales + (long long)ra * nblk;
-    const ScaleT *sb = scales + (long long)rb * nblk;
-    // activation vectors: op(rhs) is [K][NV]; both storage orders of a vector batch are handled
-    // by the element strides below (NV == 1: contiguous K)
+
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_addr) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // let the next kernel in the stream start its own prologue and weight requests
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!lhs_constant) asm volatile("griddepcontrol.wait;" ::: "memory");
+    __syncthreads();
+
+    // ---- weight requests: codes through the TMA engine, scales through the load/store unit
+    const uint32_t row_bytes = (uint32_t)blk_cnt * 32u;
+    if (threadIdx.x == 0 && row_bytes > 0) {
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_addr), "r"(row_bytes * (uint32_t)rows_here) : "memory");
+        for (int r = 0; r < rows_here; r++) {
+            const uint8_t *src = codes + (long long)(row_base + r) * p.K + (long long)blk_begin * 32;
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(codes_s + r * cstride)), "l"(src), "r"(row_bytes), "r"(bar_addr) : "memory");
+        }
+    }
+    for (int i = threadIdx.x; i < ROWS * blk_cnt; i += THREADS) {
+        const int r = i / blk_cnt, j = i - r * blk_cnt;
+        const int row = min(row_base + r, p.M - 1);
+        scales_s[r * sstride + j] = __ldg(scales + (long long)row * nblk + blk_begin + j);
+    }
+    if (lhs_constant) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // ---- activations: written by the stream predecessor, so only touched after the wait
     const int vec = NV == 1 ? 0 : min(g, NV - 1);
     const long long rbatch = batch % p.rhs_stack;
-    const __half *x = (const __half *)p.rhs + rbatch * (long long)p.K * NV + (long long)vec * p.K + c * 8;
+    const __half *x = (const __half *)p.rhs + rbatch * (long long)p.K * NV + (long long)vec * p.K + (long long)blk_begin * 32 + c * 8;
+    {
+        // warm L1 with this CTA's slice of x while the weights are still on their way
+        const char *xb = (const char *)((const __half *)p.rhs + rbatch * (long long)p.K * NV + (long long)blk_begin * 32);
+        for (int v = 0; v < NV; v++)
+            for (int off = threadIdx.x * 128; off < blk_cnt * 64; off += THREADS * 128)
+                asm volatile("prefetch.global.L1 [%0];" ::"l"(xb + (long long)v * p.K * 2 + off));
+    }
+    __syncthreads(); // scales staged
 
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-
-    for (int blk0 = blk_begin + warp; blk0 < blk_end; blk0 += WARPS * UNROLL) {
-        uint2 wa[UNROLL], wb[UNROLL];
-        uint4 xv[UNROLL];
-        float da[UNROLL], db[UNROLL];
-#pragma unroll
-        for (int u = 0; u < UNROLL; u++) {
-            const int blk = blk0 + u * WARPS;
-            if (blk < blk_end) {
-                wa[u] = ldg_stream_u2(qa + blk * 32);
-                wb[u] = ldg_stream_u2(qb + blk * 32);
-                da[u] = scale_to_f32(__ldg(sa + blk));
-                db[u] = scale_to_f32(__ldg(sb + blk));
-                xv[u] = __ldg(reinterpret_cast<const uint4 *>(x + blk * 32));
-            } else {
-                wa[u] = make_uint2(0x0u, 0x0u);
-                wb[u] = make_uint2(0x0u, 0x0u);
-                da[u] = db[u] = 0.f;
-                xv[u] = make_uint4(0u, 0u, 0u, 0u);
+    // ---- wait for the codes (bounded)
+    bool ok = true;
+    if (row_bytes > 0 && !mbar_try_wait(bar_addr, 0)) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (!mbar_try_wait(bar_addr, 0)) {
+            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                ok = false;
+                atomicCAS(&g_gemv_error, 0, 1);
+                break;
             }
-        }
-#pragma unroll
-        for (int u = 0; u < UNROLL; u++) {
-            __half2 a01, a23, a45, a67, b01, b23, b45, b67;
-            codes4_to_half2(wa[u].x, a01, a23);
-            codes4_to_half2(wa[u].y, a45, a67);
-            codes4_to_half2(wb[u].x, b01, b23);
-            codes4_to_half2(wb[u].y, b45, b67);
-            float t[4] = {0.f, 0.f, 0.f, 0.f};
-            // The k index inside a block is permuted identically for W and x: lane c owns
-            // elements c*8..c*8+7; the first MMA consumes 0..3 of them, the second 4..7.
-            uint32_t fa[4] = {h2_as_u32(a01), h2_as_u32(b01), h2_as_u32(a23), h2_as_u32(b23)};
-            mma_m16n8k16_f16(t, fa, xv[u].x, xv[u].y);
-            uint32_t fb[4] = {h2_as_u32(a45), h2_as_u32(b45), h2_as_u32(a67), h2_as_u32(b67)};
-            mma_m16n8k16_f16(t, fb, xv[u].z, xv[u].w);
-            acc[0] = fmaf(da[u], t[0], acc[0]);
-            acc[1] = fmaf(da[u], t[1], acc[1]);
-            acc[2] = fmaf(db[u], t[2], acc[2]);
-            acc[3] = fmaf(db[u], t[3], acc[3]);
         }
     }
 
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (ok) {
+        const uint8_t *qa = codes_s + g * cstride + c * 8;
+        const uint8_t *qb = codes_s + (g + 8) * cstride + c * 8;
+        const ScaleT *sa = scales_s + g * sstride, *sb = scales_s + (g + 8) * sstride;
+#pragma unroll 2
+        for (int blk = warp; blk < blk_cnt; blk += WARPS) {
+            const uint2 wa = *reinterpret_cast<const uint2 *>(qa + blk * 32);
+            const uint2 wb = *reinterpret_cast<const uint2 *>(qb + blk * 32);
+            const uint4 xv = *reinterpret_cast<const uint4 *>(x + blk * 32);
+            const float da = scale_to_f32(sa[blk]), db = scale_to_f32(sb[blk]);
+            __half2 a01, a23, a45, a67, b01, b23, b45, b67;
+            codes4_to_half2(wa.x, a01, a23);
+            codes4_to_half2(wa.y, a45, a67);
+            codes4_to_half2(wb.x, b01, b23);
+            codes4_to_half2(wb.y, b45, b67);
+            float t[4] = {0.f, 0.f, 0.f, 0.f};
+            // The k index inside a block is permuted identically for W and x: lane c owns
+            // elements c*8..c*8+7; the first MMA consumes 0..3 of them, the second 4..7.
+            const uint32_t fa[4] = {h2_as_u32(a01), h2_as_u32(b01), h2_as_u32(a23), h2_as_u32(b23)};
+            mma_m16n8k16_f16(t, fa, xv.x, xv.y);
+            const uint32_t fb[4] = {h2_as_u32(a45), h2_as_u32(b45), h2_as_u32(a67), h2_as_u32(b67)};
+            mma_m16n8k16_f16(t, fb, xv.z, xv.w);
+            acc[0] = fmaf(da, t[0], acc[0]);
+            acc[1] = fmaf(da, t[1], acc[1]);
+            acc[2] = fmaf(db, t[2], acc[2]);
+            acc[3] = fmaf(db, t[3], acc[3]);
+        }
+    }
+    __syncthreads(); // every warp is done with the staged codes: the region becomes the reduction buffer
+
     // C fragment: acc[0],acc[1] -> (row g, cols 2c,2c+1); acc[2],acc[3] -> (row g+8, same cols)
-    red[warp][g][2 * c] = acc[0];
-    red[warp][g][2 * c + 1] = acc[1];
-    red[warp][g + 8][2 * c] = acc[2];
-    red[warp][g + 8][2 * c + 1] = acc[3];
+    float *red = reinterpret_cast<float *>(smem); // [WARPS][ROWS][8]
+    red[(warp * ROWS + g) * 8 + 2 * c] = acc[0];
+    red[(warp * ROWS + g) * 8 + 2 * c + 1] = acc[1];
+    red[(warp * ROWS + g + 8) * 8 + 2 * c] = acc[2];
+    red[(warp * ROWS + g + 8) * 8 + 2 * c + 1] = acc[3];
     __syncthreads();
 
     const int r = threadIdx.x >> 3, v = threadIdx.x & 7; // first 128 threads: one (row, vector) each
     float sum = 0.f;
     if (threadIdx.x < ROWS * 8) {
 #pragma unroll
-        for (int w = 0; w < WARPS; w++) sum += red[w][r][v];
+        for (int w = 0; w < WARPS; w++) sum += red[(w * ROWS + r) * 8 + v];
     }
     if (SPLIT) {
         cg::cluster_group cluster = cg::this_cluster();
         __syncthreads();
-        if (threadIdx.x < ROWS * 8) red[0][r][v] = sum;
+        if (threadIdx.x < ROWS * 8) red[r * 8 + v] = sum;
         cluster.sync();
         if (cluster.block_rank() == 0 && threadIdx.x < ROWS * 8) {
             const unsigned n = cluster.num_blocks();
             for (unsigned k = 1; k < n; k++) {
-                const float *remote = cluster.map_shared_rank(&red[0][0][0], k);
+                const float *remote = cluster.map_shared_rank(red, k);
                 sum += remote[r * 8 + v];
             }
         }
@@ -149,7 +218,7 @@ __global__ void __launch_bounds__(WARPS * 32) q8_gemv_mma_kernel(MatmulParams p,
         if (cluster.block_rank() != 0) return;
     }
     if (threadIdx.x < ROWS * 8 && v < NV) {
-        const int row = blockIdx.x * ROWS + r;
+        const int row = row_base + r;
         if (row < p.M) {
             const bool has_bias = p.bias_mode != BIAS_NONE;
             float bias = 0.f;
@@ -163,59 +232,86 @@ __global__ void __launch_bounds__(WARPS * 32) q8_gemv_mma_kernel(MatmulParams p,
     }
 }
 
+size_t smem_bytes(int blocks_per_cta, int scale_size) { return bar_offset(blocks_per_cta, scale_size) + 16; }
+
 template <typename ScaleT, int NV>
-cudaError_t launch_nv(const MatmulParams &p, int split, cudaStream_t stream) {
+cudaError_t launch_nv(const MatmulParams &p, int split, bool lhs_constant, cudaStream_t stream) {
     const int nblk = p.K / 32;
     const int bpc = (nblk + split - 1) / split;
-    dim3 grid((p.M + ROWS - 1) / ROWS, split, p.stacks), block(WARPS * 32);
-    if (split == 1) {
-        q8_gemv_mma_kernel<ScaleT, NV, false><<<grid, block, 0, stream>>>(p, bpc);
-        return cudaGetLastError();
+    const size_t smem = smem_bytes(bpc, (int)sizeof(ScaleT));
+    auto kernel = split == 1 ? q8_gemv_bulk_kernel<ScaleT, NV, false> : q8_gemv_bulk_kernel<ScaleT, NV, true>;
+    static size_t configured[2] = {0, 0};
+    if (smem > 48 * 1024 && configured[split != 1] < smem) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured[split != 1] = smem;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = 0;
+    cfg.gridDim = dim3((p.M + ROWS - 1) / ROWS, split, p.stacks);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = split;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    n++;
+    if (split > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = split;
+        attr[n].val.clusterDim.z = 1;
+        n++;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, q8_gemv_mma_kernel<ScaleT, NV, true>, p, bpc);
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, p, bpc, lhs_constant ? 1 : 0);
 }
 
 template <typename ScaleT>
-cudaError_t launch_scale(const MatmulParams &p, int nv, int split, cudaStream_t stream) {
+cudaError_t launch_scale(const MatmulParams &p, int nv, int split, bool lhs_constant, cudaStream_t stream) {
     switch (nv) {
-    case 1: return launch_nv<ScaleT, 1>(p, split, stream);
-    case 2: return launch_nv<ScaleT, 2>(p, split, stream);
-    case 3: return launch_nv<ScaleT, 3>(p, split, stream);
-    case 4: return launch_nv<ScaleT, 4>(p, split, stream);
-    case 5: return launch_nv<ScaleT, 5>(p, split, stream);
-    case 6: return launch_nv<ScaleT, 6>(p, split, stream);
-    case 7: return launch_nv<ScaleT, 7>(p, split, stream);
-    case 8: return launch_nv<ScaleT, 8>(p, split, stream);
+    case 1: return launch_nv<ScaleT, 1>(p, split, lhs_constant, stream);
+    case 2: return launch_nv<ScaleT, 2>(p, split, lhs_constant, stream);
+    case 3: return launch_nv<ScaleT, 3>(p, split, lhs_constant, stream);
+    case 4: return launch_nv<ScaleT, 4>(p, split, lhs_constant, stream);
+    case 5: return launch_nv<ScaleT, 5>(p, split, lhs_constant, stream);
+    case 6: return launch_nv<ScaleT, 6>(p, split, lhs_constant, stream);
+    case 7: return launch_nv<ScaleT, 7>(p, split, lhs_constant, stream);
+    case 8: return launch_nv<ScaleT, 8>(p, split, lhs_constant, stream);
     }
     return cudaErrorInvalidValue;
 }
 
 } // namespace
 
-int q8_gemv_mma_pick_split(int M, int K, int sm_count) {
+// K split over a cluster: as few CTAs per row group as keep (a) the CTA's share of W within the
+// shared memory of one of five co-resident CTAs and (b) the grid long enough to fill every SM.
+// Returns 0 when even an eight-way split does not fit one SM's shared memory.
+int q8_gemv_mma_pick_split(int M, int K, int sm_count, int scale_size) {
     const int nblk = K / 32;
     const int groups = (M + ROWS - 1) / ROWS;
-    const int want = 4 * sm_count; // CTAs needed to keep every SM's load queue full
+    const size_t per_cta_target = 44 * 1024, per_cta_max = 200 * 1024;
     int split = 1;
-    // split K while the grid is short and every warp still gets at least two blocks
-    while (split < 8 && groups * split < want && nblk / (split * 2) >= 2 * WARPS) split *= 2;
+    while (split < 8 && smem_bytes((nblk + split - 1) / split, scale_size) > per_cta_target) split *= 2;
+    while (split < 8 && groups * split < 4 * sm_count && nblk / (split * 2) >= 2 * WARPS) split *= 2;
+    if (smem_bytes((nblk + split - 1) / split, scale_size) > per_cta_max) return 0;
     return split;
 }
 
-cudaError_t launch_q8_gemv_mma(const MatmulParams &p, bool f32_scales, int nv, int split, cudaStream_t stream) {
-    return f32_scales ? launch_scale<float>(p, nv, split, stream) : launch_scale<__half>(p, nv, split, stream);
+cudaError_t launch_q8_gemv_mma(const MatmulParams &p, bool f32_scales, int nv, int split, bool lhs_constant, cudaStream_t stream) {
+    return f32_scales ? launch_scale<float>(p, nv, split, lhs_constant, stream)
+                      : launch_scale<__half>(p, nv, split, lhs_constant, stream);
+}
+
+cudaError_t gemv_take_error(int *site, cudaStream_t stream) {
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbolAsync(site, g_gemv_error, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return e;
+    e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return e;
+    if (*site != 0) e = cudaMemcpyToSymbolAsync(g_gemv_error, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream);
+    return e;
 }
 
 } // namespace rt

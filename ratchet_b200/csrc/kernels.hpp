@@ -10,8 +10,12 @@ namespace rt {
 cudaError_t launch_matmul_simt(const MatmulParams &p, rt_dtype lhs_dt, rt_dtype act_dt, bool gemv, cudaStream_t stream);
 
 // Q8_0 x f16 GEMV / skinny GEMM on warp MMAs.  nv = columns of op(rhs), 1..8 (rhs stored [nv][K]).
-int q8_gemv_mma_pick_split(int M, int K, int sm_count);
-cudaError_t launch_q8_gemv_mma(const MatmulParams &p, bool f32_scales, int nv, int split, cudaStream_t stream);
+// pick_split returns the K split (cluster size), or 0 when the shape does not fit the kernel.
+// lhs_constant: the weight bytes are not written by any work in flight on the stream, so the
+// kernel may request them before it waits for its stream predecessor.
+int q8_gemv_mma_pick_split(int M, int K, int sm_count, int scale_size);
+cudaError_t launch_q8_gemv_mma(const MatmulParams &p, bool f32_scales, int nv, int split, bool lhs_constant, cudaStream_t stream);
+cudaError_t gemv_take_error(int *site, cudaStream_t stream);
 
 // Tensor-core GEMM (tcgen05): D[R][S] = P[R][K] . Q[S][K]^T, 16-bit K-major operands, bias along S.
 bool umma_gemm_supported(long long K);

@@ -199,6 +199,7 @@ class Executable:
             arr[i].lhs, arr[i].rhs = t.op.lhs.ptr, t.op.rhs.ptr
             arr[i].bias = t.op.bias.ptr if t.op.bias is not None else None
             arr[i].out = t.ptr
+            arr[i].flags = _lib.RT_LAUNCH_LHS_CONSTANT if t.op.lhs.op is None else 0
         self._h = c_void_p()
         check(_lib.load().rt_executable_create(device._h, arr, len(nodes), int(use_graph), byref(self._h)))
         self.launches = int(_lib.load().rt_executable_launches(self._h))
@@ -367,8 +368,10 @@ class Tensor:
                                        f"TensorError: operand on {s.device}, expected {device}")
             plan = device.plan_for(op.desc)
             out = GpuBuffer(device, t.nbytes())
-            check(lib.rt_matmul_launch(plan, op.lhs.ptr, op.rhs.ptr, op.bias.ptr if op.bias is not None else None,
-                                       out.ptr, None))
+            # a leaf lhs is a constant of the graph (uploaded weights): nothing in flight writes it
+            flags = _lib.RT_LAUNCH_LHS_CONSTANT if op.lhs.op is None else 0
+            check(lib.rt_matmul_launch_ex(plan, op.lhs.ptr, op.rhs.ptr, op.bias.ptr if op.bias is not None else None,
+                                          out.ptr, None, flags))
             t.storage = out
         if sync:
             device.sync()
