@@ -202,15 +202,19 @@ int32_t rt_plan_launches(const rt_plan *plan);
  * `out` must not alias them and holds rt_dtype_nbytes(spec.out_dt, numel(out_shape)). */
 rt_status rt_matmul_launch(rt_plan *plan, const void *lhs, const void *rhs, const void *bias, void *out, void *stream);
 
-/* Launch flags.  RT_LAUNCH_LHS_CONSTANT: the caller states that no work in flight on the stream
- * writes the lhs bytes (a weight uploaded earlier, the leaf tensors of the reference's graph,
- * tensor.rs:589-599).  A kernel may then request the weights before it waits for its stream
- * predecessor (programmatic dependent launch), which overlaps one layer's weight streaming with
- * the previous layer's tail.  Never set it for an lhs that an earlier node of the same stream
- * produces (attention scores, activations). */
+/* Launch options.
+ * RT_LAUNCH_LHS_CONSTANT: the caller states that no work in flight on the stream writes the lhs
+ * bytes (a weight uploaded earlier: the leaf tensors of the reference's graph, tensor.rs:589-599).
+ * A kernel may then request the weights before it waits for its stream predecessor (programmatic
+ * dependent launch), which overlaps one layer's weight streaming with the previous layer's tail.
+ * Never set it for an lhs that an earlier node of the same stream produces (attention scores). */
 #define RT_LAUNCH_LHS_CONSTANT 1u
+typedef struct rt_launch_opts {
+    uint32_t flags;
+} rt_launch_opts;
+/* rt_matmul_launch with options; opts may be NULL. */
 rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, const void *bias, void *out, void *stream,
-                              uint32_t flags);
+                              const rt_launch_opts *opts);
 
 /* One dispatch: the operands of one planned node. */
 typedef struct rt_dispatch {
@@ -219,7 +223,7 @@ typedef struct rt_dispatch {
     const void *rhs;
     const void *bias; /* NULL when the node has no bias */
     void *out;
-    uint32_t flags;   /* RT_LAUNCH_* */
+    rt_launch_opts opts;
 } rt_dispatch;
 
 /* Executable (executable.rs:13-54): an ordered list of compiled nodes with their buffers bound,

@@ -62,9 +62,13 @@ class rt_gemm_spec(Structure):
                 ("is_gemv", c_int32)]
 
 
+class rt_launch_opts(Structure):
+    _fields_ = [("flags", ctypes.c_uint32)]
+
+
 class rt_dispatch(Structure):
     _fields_ = [("plan", c_void_p), ("lhs", c_void_p), ("rhs", c_void_p), ("bias", c_void_p), ("out", c_void_p),
-                ("flags", ctypes.c_uint32)]
+                ("opts", rt_launch_opts)]
 
 
 class RatchetError(RuntimeError):
@@ -135,7 +139,7 @@ def load() -> ctypes.CDLL:
         "rt_plan_kernel": (c_char_p, [V]),
         "rt_plan_launches": (c_int32, [V]),
         "rt_matmul_launch": (c_int32, [V, V, V, V, V, V]),
-        "rt_matmul_launch_ex": (c_int32, [V, V, V, V, V, V, ctypes.c_uint32]),
+        "rt_matmul_launch_ex": (c_int32, [V, V, V, V, V, V, POINTER(rt_launch_opts)]),
         "rt_executable_create": (c_int32, [V, POINTER(rt_dispatch), c_int32, c_int32, POINTER(V)]),
         "rt_executable_dispatch": (c_int32, [V, V]),
         "rt_executable_destroy": (c_int32, [V]),

@@ -429,9 +429,9 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
     const int gemv_split = (q8 && s.K > 0 && !empty && !force_simt())
                                ? q8_gemv_mma_pick_split(p.M, p.K, dev->sm_count, desc->lhs_dt == RT_Q8_0H ? 2 : 4) : 0;
     if (gemv_split > 0 && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.N >= 1 && s.N <= 8 && (s.N == 1 || s.trans_rhs) && s.K > 0 && !empty) {
-        pl->kernel = PK_Q8_GEMV_MMA;
         pl->nv = (int)s.N;
         pl->split = gemv_split;
+        pl->kernel = PK_Q8_GEMV_MMA;
         pl->name = std::string("q8_gemv_mma_") + (desc->lhs_dt == RT_Q8_0H ? "h" : "f") + "_nv" + std::to_string(pl->nv) +
                    "_split" + std::to_string(pl->split);
     } else if (umma_eligible(*desc, s)) {
@@ -500,12 +500,13 @@ const char *rt_plan_kernel(const rt_plan *plan) { return plan ? plan->name.c_str
 int32_t rt_plan_launches(const rt_plan *plan) { return plan ? plan->launches : 0; }
 
 rt_status rt_matmul_launch(rt_plan *plan, const void *lhs, const void *rhs, const void *bias, void *out, void *stream) {
-    return rt_matmul_launch_ex(plan, lhs, rhs, bias, out, stream, 0);
+    return rt_matmul_launch_ex(plan, lhs, rhs, bias, out, stream, nullptr);
 }
 
 rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, const void *bias, void *out, void *stream,
-                              uint32_t flags) {
+                              const rt_launch_opts *opts) {
     if (!plan) return fail(RT_ERR_ARG, "rt_matmul_launch: null plan");
+    const uint32_t flags = opts ? opts->flags : 0;
     const Spec &s = plan->spec;
     if (plan->launches == 0) return RT_OK; // empty output
     if (!lhs || !rhs || !out || (s.has_bias && !bias)) return fail(RT_ERR_ARG, "rt_matmul_launch: null operand");
@@ -562,7 +563,7 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
 
 static rt_status dispatch_nodes(rt_executable *exe, cudaStream_t st) {
     for (auto &n : exe->nodes) {
-        rt_status s = rt_matmul_launch_ex(n.plan, n.lhs, n.rhs, n.bias, n.out, (void *)st, n.flags);
+        rt_status s = rt_matmul_launch_ex(n.plan, n.lhs, n.rhs, n.bias, n.out, (void *)st, &n.opts);
         if (s != RT_OK) return s;
     }
     return RT_OK;

@@ -15,7 +15,7 @@
 //               instruction), tcgen05.commit releases ring stages and publishes accumulators
 //   warps 2-5   epilogue: tcgen05.ld of one of two accumulator buffers (so the next tile's MMAs
 //               overlap), the reference's epilogue chain, vectorised global stores
-// Every wait is bounded by wall time; on expiry the kernel records the wait site in a device
+// Every wait is bounded (about two seconds of SM cycles); on expiry the kernel records the wait site in a device
 // flag, all roles leave their loops, tensor memory is freed and the kernel returns.  The host
 // reads the flag at the next rt_device_sync.
 #include <cuda.h>
@@ -33,7 +33,7 @@ constexpr int BM = 128;
 constexpr int BK = 64; // 64 x 16-bit = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+constexpr unsigned long long WAIT_LIMIT_CYCLES = 4000000000ull; // about 2 s at the SM clock
 
 struct UmmaParams {
     int R, S, K;
@@ -58,11 +58,9 @@ template <int BN> struct Cfg {
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
+// The SM's own cycle counter bounds the waits: it is a register read, where %globaltimer is a
+// long-latency access that would sit on the critical path of every stage hand-over.
+__device__ __forceinline__ unsigned long long wait_clock() { return (unsigned long long)clock64(); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -83,13 +81,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false when the wait expired or another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
+    const unsigned long long t0 = wait_clock();
     while (true) {
 #pragma unroll 1
         for (int i = 0; i < 32; i++)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        if (wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;
             atomicCAS(&g_umma_error, 0, site);
             return false;
@@ -313,8 +311,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     __syncthreads();
     if (*abort_flag) {
         // give copies that may still be in flight time to land before the CTA's memory is released
-        const unsigned long long t0 = globaltimer_ns();
-        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+        const unsigned long long t0 = wait_clock();
+        while (wait_clock() - t0 < 400000ull) __nanosleep(1000);
     }
     if (warp == 1) {
         tc_fence_after();

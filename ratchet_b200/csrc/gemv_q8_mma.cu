@@ -39,7 +39,7 @@ namespace {
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
 constexpr int ROWS = 16;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+constexpr unsigned long long WAIT_LIMIT_CYCLES = 4000000000ull; // about 2 s at the SM clock
 
 __device__ __forceinline__ void mma_m16n8k16_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -49,11 +49,9 @@ __device__ __forceinline__ void mma_m16n8k16_f16(float (&c)[4], const uint32_t (
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
+// The SM's own cycle counter bounds the waits: it is a register read, where %globaltimer is a
+// long-latency access that would sit on the critical path of every stage hand-over.
+__device__ __forceinline__ unsigned long long wait_clock() { return (unsigned long long)clock64(); }
 
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -147,9 +145,9 @@ __global__ void __launch_bounds__(THREADS, 5) q8_gemv_bulk_kernel(MatmulParams p
     // ---- wait for the codes (bounded)
     bool ok = true;
     if (row_bytes > 0 && !mbar_try_wait(bar_addr, 0)) {
-        const unsigned long long t0 = globaltimer_ns();
+        const unsigned long long t0 = wait_clock();
         while (!mbar_try_wait(bar_addr, 0)) {
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
                 ok = false;
                 atomicCAS(&g_gemv_error, 0, 1);
                 break;

@@ -199,7 +199,7 @@ class Executable:
             arr[i].lhs, arr[i].rhs = t.op.lhs.ptr, t.op.rhs.ptr
             arr[i].bias = t.op.bias.ptr if t.op.bias is not None else None
             arr[i].out = t.ptr
-            arr[i].flags = _lib.RT_LAUNCH_LHS_CONSTANT if t.op.lhs.op is None else 0
+            arr[i].opts.flags = _lib.RT_LAUNCH_LHS_CONSTANT if t.op.lhs.op is None else 0
         self._h = c_void_p()
         check(_lib.load().rt_executable_create(device._h, arr, len(nodes), int(use_graph), byref(self._h)))
         self.launches = int(_lib.load().rt_executable_launches(self._h))
@@ -356,22 +356,24 @@ class Tensor:
         """Tensor::resolve (tensor.rs:738-787): plan + dispatch every unresolved node, then wait."""
         device = self.device.try_gpu()
         lib = _lib.load()
-        for t in self.execution_order():
-            if t.resolved():
-                continue
+        todo = [t for t in self.execution_order() if not t.resolved()]
+        for t in todo:
             if t.op is None:
                 raise RatchetError(_lib.RT_ERR_ARG, "RT_ERR_ARG", "unresolved tensor without an op")
-            op = t.op
-            for s in op.srcs():
-                if not isinstance(s.storage, GpuBuffer) or s.device is not device:
+            for s in t.op.srcs():
+                if s.resolved() and (not isinstance(s.storage, GpuBuffer) or s.device is not device):
                     raise RatchetError(_lib.RT_ERR_ARG, "RT_ERR_ARG",
                                        f"TensorError: operand on {s.device}, expected {device}")
+        for i, t in enumerate(todo):
+            op = t.op
             plan = device.plan_for(op.desc)
             out = GpuBuffer(device, t.nbytes())
+            opts = _lib.rt_launch_opts()
             # a leaf lhs is a constant of the graph (uploaded weights): nothing in flight writes it
-            flags = _lib.RT_LAUNCH_LHS_CONSTANT if op.lhs.op is None else 0
+            if op.lhs.op is None:
+                opts.flags = _lib.RT_LAUNCH_LHS_CONSTANT
             check(lib.rt_matmul_launch_ex(plan, op.lhs.ptr, op.rhs.ptr, op.bias.ptr if op.bias is not None else None,
-                                          out.ptr, None, flags))
+                                          out.ptr, None, byref(opts)))
             t.storage = out
         if sync:
             device.sync()
