@@ -27,6 +27,7 @@ extern "C" {
 #endif
 
 #define RT_MAX_RANK 8
+#define RT_MAX_PEERS 8
 
 typedef enum rt_status {
     RT_OK = 0,
@@ -209,8 +210,19 @@ rt_status rt_matmul_launch(rt_plan *plan, const void *lhs, const void *rhs, cons
  * dependent launch), which overlaps one layer's weight streaming with the previous layer's tail.
  * Never set it for an lhs that an earlier node of the same stream produces (attention scores). */
 #define RT_LAUNCH_LHS_CONSTANT 1u
+/* n_out > 0 places the result somewhere else than `out`: element (r, s) of the node's [R][S]
+ * output goes to outs[d][r*out_ld + out_col + s] for every d < n_out.  This is the N-sharded
+ * prefill form (no reference counterpart: the reference is single-device, gpu/device.rs:15-16):
+ * each GPU computes the column slice of its weight shard and writes it into every GPU's
+ * full-width [rows][N] output through peer-mapped pointers (rt_ipc_open), so no separate
+ * all-gather runs.  Only the tensor-core GEMM takes it (RT_ERR_UNSUPPORTED otherwise), with
+ * trans_out set and one shared weight.  The caller synchronises all GPUs before reading. */
 typedef struct rt_launch_opts {
     uint32_t flags;
+    int32_t n_out;
+    void *outs[RT_MAX_PEERS];
+    int64_t out_ld;
+    int64_t out_col;
 } rt_launch_opts;
 /* rt_matmul_launch with options; opts may be NULL. */
 rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, const void *bias, void *out, void *stream,
@@ -250,6 +262,30 @@ int32_t rt_executable_launches(const rt_executable *exe);
 #define RT_STATIC_SCRATCH_BYTES (8u << 20)
 rt_status rt_linear_q8_0_static_scratch(rt_device *dev, const void *w, const void *x, const void *bias, void *out,
                                         int64_t rows, int64_t n, int64_t k, int32_t epilogue, void *stream);
+
+/* ------------------------------------------------------------------ N-sharded prefill (multi-GPU)
+ * No reference counterpart: the reference is single-device (gpu/device.rs:15-16).  One process per
+ * GPU; W is split along N (rows of the [N,K] weight, and the bias), the activations are replicated,
+ * every GPU computes out[:, n0:n1].  The slices meet either through rt_comm_all_gather (NCCL over
+ * NVLink) or by launching with scattered outputs (rt_launch_opts.n_out) into peer-mapped buffers. */
+typedef struct rt_comm rt_comm;
+#define RT_COMM_ID_BYTES 128
+#define RT_IPC_HANDLE_BYTES 64
+/* ncclGetUniqueId: rank 0 creates the id and sends it to the other ranks. */
+rt_status rt_comm_unique_id(void *id);
+/* Joins without blocking and polls until every rank has joined or timeout_ms passed
+ * (RT_ERR_COMM_TIMEOUT; 0 = 60 s). */
+rt_status rt_comm_init_rank(rt_device *dev, int32_t n_ranks, int32_t rank, const void *id, int32_t timeout_ms, rt_comm **comm);
+/* recv = n_ranks chunks of bytes_per_rank, chunk r = rank r's send buffer.  Asynchronous on `stream`. */
+rt_status rt_comm_all_gather(rt_comm *comm, const void *send, void *recv, uint64_t bytes_per_rank, void *stream);
+rt_status rt_comm_destroy(rt_comm *comm);
+/* CUDA IPC: export a buffer's 64-byte handle, map a peer's buffer into this process. */
+rt_status rt_ipc_export(rt_buffer *buf, void *handle);
+rt_status rt_ipc_open(rt_device *dev, const void *handle, void **ptr);
+rt_status rt_ipc_close(rt_device *dev, void *ptr);
+/* Host: rows [r0, r1) of a [rows][k] tensor repacked in the dtype's own segment layout, i.e. an
+ * ordinary tensor of shape [r1-r0][k] holding rt_dtype_nbytes(dt, (r1-r0)*k) bytes. */
+rt_status rt_shard_rows(rt_dtype dt, const void *src, uint64_t rows, uint64_t k, uint64_t r0, uint64_t r1, void *dst);
 
 /* Debug / parity helper: dequantise a device tensor into f32 (RT_Q8_0F, RT_Q4_K) or f16
  * (RT_Q8_0H) exactly as the kernels decode it, so "bit-exact dequantised weights" can be

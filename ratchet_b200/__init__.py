@@ -11,6 +11,8 @@ from ._lib import RT_EPILOGUE_NONE as EPILOGUE_NONE
 from .tensor import (Device, DeviceRequest, DType, Executable, GpuBuffer, Linear, Matmul, PinnedArray, Quantization, Quantizer,
                      Tensor, bf16_bits_to_f32, f32_to_bf16_bits, transcode_gguf_q8_0)
 
-__all__ = ["Device", "DeviceRequest", "DType", "Executable", "GpuBuffer", "Linear", "Matmul", "PinnedArray", "Quantization",
+from .sharded import Comm, ShardedLinear, shard_bounds, shard_rows
+
+__all__ = ["Comm", "ShardedLinear", "shard_bounds", "shard_rows", "Device", "DeviceRequest", "DType", "Executable", "GpuBuffer", "Linear", "Matmul", "PinnedArray", "Quantization",
            "Quantizer", "Tensor", "RatchetError", "ShapeError", "InvariantError", "EPILOGUE_NONE",
            "EPILOGUE_GELU_TANH", "bf16_bits_to_f32", "f32_to_bf16_bits", "transcode_gguf_q8_0"]

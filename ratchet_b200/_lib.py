@@ -63,7 +63,8 @@ class rt_gemm_spec(Structure):
 
 
 class rt_launch_opts(Structure):
-    _fields_ = [("flags", ctypes.c_uint32)]
+    _fields_ = [("flags", ctypes.c_uint32), ("n_out", c_int32), ("outs", c_void_p * 8), ("out_ld", c_int64),
+                ("out_col", c_int64)]
 
 
 class rt_dispatch(Structure):
@@ -145,6 +146,14 @@ def load() -> ctypes.CDLL:
         "rt_executable_destroy": (c_int32, [V]),
         "rt_executable_launches": (c_int32, [V]),
         "rt_linear_q8_0_static_scratch": (c_int32, [V, V, V, V, V, c_int64, c_int64, c_int64, c_int32, V]),
+        "rt_comm_unique_id": (c_int32, [V]),
+        "rt_comm_init_rank": (c_int32, [V, c_int32, c_int32, V, c_int32, POINTER(V)]),
+        "rt_comm_all_gather": (c_int32, [V, V, V, c_uint64, V]),
+        "rt_comm_destroy": (c_int32, [V]),
+        "rt_ipc_export": (c_int32, [V, V]),
+        "rt_ipc_open": (c_int32, [V, V, POINTER(V)]),
+        "rt_ipc_close": (c_int32, [V, V]),
+        "rt_shard_rows": (c_int32, [c_int32, V, c_uint64, c_uint64, c_uint64, c_uint64, V]),
         "rt_dequantize_device": (c_int32, [V, c_int32, c_uint64, V, V, V]),
     }
     for name, (res, args) in sig.items():

@@ -19,6 +19,7 @@ INCLUDE = os.path.join(ROOT, "include")
 SOURCES = [
     "spec.cpp",
     "quant_host.cpp",
+    "comm.cpp",
     "api.cu",
     "matmul_simt.cu",
     "gemv_q8_mma.cu",
@@ -65,7 +66,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     with ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as ex:
         objs = list(ex.map(lambda s: _compile(s, force, verbose, hdr), SOURCES))
     if force or not os.path.exists(LIB) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
-        cmd = [NVCC, *ARCH, "-shared", "-o", LIB, *objs, "-lcudart"]
+        cmd = [NVCC, *ARCH, "-shared", "-o", LIB, *objs, "-lcudart", "-ldl"]
         r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}")

@@ -507,9 +507,18 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
                               const rt_launch_opts *opts) {
     if (!plan) return fail(RT_ERR_ARG, "rt_matmul_launch: null plan");
     const uint32_t flags = opts ? opts->flags : 0;
+    const bool scatter = opts && opts->n_out > 0;
+    if (scatter) {
+        if (plan->kernel != PK_GEMM_UMMA) return fail(RT_ERR_UNSUPPORTED, "scattered outputs are only taken by the tensor-core GEMM");
+        if (opts->n_out > RT_MAX_PEERS || opts->out_col < 0 || opts->out_ld < opts->out_col + plan->S)
+            return fail(RT_ERR_ARG, "rt_matmul_launch_ex: bad scatter description");
+        for (int d = 0; d < opts->n_out; d++)
+            if (!opts->outs[d]) return fail(RT_ERR_ARG, "rt_matmul_launch_ex: null scatter destination");
+    }
     const Spec &s = plan->spec;
     if (plan->launches == 0) return RT_OK; // empty output
-    if (!lhs || !rhs || !out || (s.has_bias && !bias)) return fail(RT_ERR_ARG, "rt_matmul_launch: null operand");
+    if (!lhs || !rhs || (!out && !(opts && opts->n_out > 0)) || (s.has_bias && !bias))
+        return fail(RT_ERR_ARG, "rt_matmul_launch: null operand");
     if (out == lhs || out == rhs || (s.has_bias && out == bias))
         return fail(RT_ERR_INVARIANT, "Matmul is never in place: out aliases an operand");
     CUDA_TRY(cudaSetDevice(plan->dev->ordinal));
@@ -551,9 +560,18 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
         }
         const void *P = plan->lhs_is_q ? x : w, *Q = plan->lhs_is_q ? w : x;
         const rt_dtype p_dt = plan->lhs_is_q ? x_dt : w_dt, q_dt = plan->lhs_is_q ? w_dt : x_dt;
+        UmmaScatter sc{};
+        if (scatter) {
+            if (!plan->lhs_is_q || plan->u_stacks != 1)
+                return fail(RT_ERR_UNSUPPORTED, "scattered outputs need trans_out and one shared weight");
+            sc.n_out = opts->n_out;
+            for (int d = 0; d < opts->n_out; d++) sc.outs[d] = opts->outs[d];
+            sc.out_ld = opts->out_ld;
+            sc.out_col = opts->out_col;
+        }
         e = launch_gemm_umma(P, p_dt, Q, q_dt, out, s.out_dt, plan->R, plan->S, (int)s.K, plan->u_stacks, plan->p_stack,
                              plan->q_stack, p.bias, p.bias_dt, s.has_bias ? BIAS_PER_N : BIAS_NONE, p.epilogue, plan->bn,
-                             plan->dev->sm_count, st);
+                             plan->dev->sm_count, st, scatter ? &sc : nullptr);
         break;
     }
     }

@@ -40,6 +40,13 @@ struct UmmaParams {
     int stacks, p_stack, q_stack;
     void *out;
     long long out_batch_stride;
+    // Output placement: element (r, s) of batch b goes to outs[d][b*out_batch_stride + r*out_ld + out_col + s] for
+    // every destination d.  One destination with out_ld = S, out_col = 0 is the plain case; several
+    // destinations are the N-sharded form, where each GPU writes its column slice straight into
+    // every GPU's full-width output through peer-mapped pointers (plain stores over NVLink).
+    int n_out;
+    void *outs[RT_MAX_PEERS];
+    long long out_ld, out_col;
     const void *bias;
     int bias_dt, bias_mode; // BIAS_PER_N: index along S; BIAS_PER_M: index along R
     int epilogue;
@@ -247,8 +254,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
         const int ep_tid = threadIdx.x - 64;
         int acc = 0;
         uint32_t acc_phase = 0;
-        OutT *out_base = reinterpret_cast<OutT *>(prm.out);
-        const bool vec_ok = (prm.S % 8 == 0) && (reinterpret_cast<uintptr_t>(prm.out) % 16 == 0);
+        bool vec_ok = (prm.out_ld % 8 == 0) && (prm.out_col % 8 == 0) && (prm.out_batch_stride % 8 == 0);
+        for (int d = 0; d < prm.n_out; d++) vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(prm.outs[d]) % 16 == 0);
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
             const int r0 = (rem % prm.tiles_r) * BM, s0 = (rem / prm.tiles_r) * BN;
@@ -266,7 +273,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             const bool has_bias = prm.bias_mode != BIAS_NONE;
             float row_bias = 0.f;
             if (prm.bias_mode == BIAS_PER_M && row < prm.R) row_bias = load_bias(prm.bias, prm.bias_dt, row);
-            OutT *out_row = out_base + (long long)b * prm.out_batch_stride + (long long)row * prm.S;
+            const long long row_off = (long long)b * prm.out_batch_stride + (long long)row * prm.out_ld + prm.out_col;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; c++) {
                 uint32_t v[32];
@@ -286,14 +293,17 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                                 const OutT o1 = epilogue_value<OutT>(__uint_as_float(v[i0 + 1]), has_bias, b1, prm.epilogue);
                                 w[j] = pack2<OutT>(to_f32(o0), to_f32(o1));
                             }
-                            *reinterpret_cast<uint4 *>(out_row + col0 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                            const uint4 pk = make_uint4(w[0], w[1], w[2], w[3]);
+                            for (int d = 0; d < prm.n_out; d++)
+                                *reinterpret_cast<uint4 *>(reinterpret_cast<OutT *>(prm.outs[d]) + row_off + col0 + g * 8) = pk;
                         }
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; i++) {
                             if (col0 + i < prm.S) {
                                 const float bv = prm.bias_mode == BIAS_PER_N ? bias_s[c * 32 + i] : row_bias;
-                                out_row[col0 + i] = epilogue_value<OutT>(__uint_as_float(v[i]), has_bias, bv, prm.epilogue);
+                                const OutT o = epilogue_value<OutT>(__uint_as_float(v[i]), has_bias, bv, prm.epilogue);
+                                for (int d = 0; d < prm.n_out; d++) reinterpret_cast<OutT *>(prm.outs[d])[row_off + col0 + i] = o;
                             }
                         }
                     }
@@ -384,7 +394,7 @@ int umma_pick_bn(long long R, long long S, long long stacks, int sm_count) {
 // P: [p_stack][R][K] of p_dt, Q: [q_stack][S][K] of q_dt (f16 or bf16 each); out [stacks][R][S] of out_dt.
 cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dtype q_dt, void *out, rt_dtype out_dt,
                              int R, int S, int K, int stacks, int p_stack, int q_stack, const void *bias, int bias_dt,
-                             int bias_mode, int epilogue, int bn, int sm_count, cudaStream_t stream) {
+                             int bias_mode, int epilogue, int bn, int sm_count, cudaStream_t stream, const UmmaScatter *scatter) {
     // kind::f16 wants one format for both operands: an instruction descriptor that mixes f16 and
     // bf16 is an illegal instruction on sm_100a
     if (p_dt != q_dt || (p_dt != RT_F16 && p_dt != RT_BF16)) return cudaErrorInvalidValue;
@@ -395,7 +405,20 @@ cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dty
     prm.R = R; prm.S = S; prm.K = K;
     prm.stacks = stacks; prm.p_stack = p_stack; prm.q_stack = q_stack;
     prm.out = out;
-    prm.out_batch_stride = (long long)R * S;
+    if (scatter && scatter->n_out > 0) {
+        if (scatter->n_out > RT_MAX_PEERS) return cudaErrorInvalidValue;
+        prm.n_out = scatter->n_out;
+        for (int d = 0; d < scatter->n_out; d++) prm.outs[d] = scatter->outs[d];
+        prm.out_ld = scatter->out_ld;
+        prm.out_col = scatter->out_col;
+        prm.out_batch_stride = (long long)R * scatter->out_ld;
+    } else {
+        prm.n_out = 1;
+        prm.outs[0] = out;
+        prm.out_ld = S;
+        prm.out_col = 0;
+        prm.out_batch_stride = (long long)R * S;
+    }
     prm.bias = bias; prm.bias_dt = bias_dt; prm.bias_mode = bias_mode;
     prm.epilogue = epilogue;
     prm.idesc = ((p_dt == RT_BF16 ? 1u : 0u) << 7) | ((q_dt == RT_BF16 ? 1u : 0u) << 10);

@@ -18,11 +18,18 @@ cudaError_t launch_q8_gemv_mma(const MatmulParams &p, bool f32_scales, int nv, i
 cudaError_t gemv_take_error(int *site, cudaStream_t stream);
 
 // Tensor-core GEMM (tcgen05): D[R][S] = P[R][K] . Q[S][K]^T, 16-bit K-major operands, bias along S.
+// Several destinations for one result: see UmmaParams in gemm_umma.cu.
+struct UmmaScatter {
+    int n_out;
+    void *outs[RT_MAX_PEERS];
+    long long out_ld, out_col;
+};
 bool umma_gemm_supported(long long K);
 int umma_pick_bn(long long R, long long S, long long stacks, int sm_count);
 cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dtype q_dt, void *out, rt_dtype out_dt,
                              int R, int S, int K, int stacks, int p_stack, int q_stack, const void *bias, int bias_dt,
-                             int bias_mode, int epilogue, int bn, int sm_count, cudaStream_t stream);
+                             int bias_mode, int epilogue, int bn, int sm_count, cudaStream_t stream,
+                             const UmmaScatter *scatter = nullptr);
 // Reads and clears the device flag a kernel sets when one of its bounded waits expires.
 cudaError_t umma_take_error(int *site, cudaStream_t stream);
 
