@@ -54,6 +54,7 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=LAYERS, help="MLP blocks per step (default: Phi-2's 32)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="dispatch node by node instead of one CUDA graph")
+    ap.add_argument("--no-sharded", action="store_true", help="with --gpus > 1: skip the N-sharded prefill GEMM section")
     ap.add_argument("--extras", default="", help="comma list of the other configurations to time on one GPU and "
                     "report under \"extras\": c1,c3,c4,c5,c5long or all")
     return ap.parse_args()
@@ -246,6 +247,64 @@ def run_extras(which, gpu, stream):
     return out
 
 
+def run_sharded(rank, world, gpu, stream, dist, torch, rows_per_batch=2048, iters=10):
+    """BASELINE config 5 on `world` GPUs: A bf16 [4, rows, 2560] replicated, W Q8_0H [10240, 2560] split along N,
+    f16 bias, fused GELU.  Times the local slice alone, slice + NCCL all-gather, and the peer-store epilogue
+    (every rank ends with the full [4*rows, 10240]); device events, max over ranks."""
+    import ratchet_b200 as rb
+    from ratchet_b200 import DType, GpuBuffer, Tensor
+    N, K, rows = 10240, 2560, 4 * rows_per_batch
+    qz = rb.Quantizer(rb.Quantization.SInt8)
+    w = qz.sint8_quantize(Tensor.from_data(np.random.default_rng(1105).standard_normal((N, K), dtype=np.float32) * np.float32(0.02)), DType.Q8_0H)
+    b = Tensor.from_data(np.random.default_rng(2105).standard_normal(N, dtype=np.float32) * np.float32(0.02), dt=DType.F16)
+    x = Tensor.from_data(np.random.default_rng(105).standard_normal((rows, K), dtype=np.float32), gpu, DType.BF16)
+
+    def exchange(obj):
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
+
+    lin = rb.ShardedLinear(w, b, gpu, rank, world, epilogue=rb.EPILOGUE_GELU_TANH)
+    per = N // world
+    local = GpuBuffer(gpu, rows * per * 2)
+    gathered = GpuBuffer(gpu, rows * N * 2)
+    comm = rb.Comm(gpu, rank, world, exchange)
+    lin.bind_outputs(rows, DType.BF16, exchange)
+    node = lin._node(x)
+    plan = gpu.plan_for(node.op.desc)
+    lib = rb._lib.load()
+
+    def compute_only():
+        rb._lib.check(lib.rt_matmul_launch(plan, lin.w.ptr, x.ptr, lin.b.ptr, local.ptr, None))
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        gpu.sync(); dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            fn()
+        e1.record(stream)
+        gpu.sync(); dist.barrier(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device=f"cuda:{gpu.ordinal}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) * 1e3  # us
+
+    us_compute = timed(compute_only)
+    us_nccl = timed(lambda: lin.launch_nccl(x, comm, local, gathered))
+    us_peer = timed(lambda: lin.launch_peer(x))
+    dist.barrier()
+    lin.close_peers()
+    comm.close()
+    flops = 2.0 * rows * N * K
+    return {"workload": f"c5_q8_0_prefill_bf16_4x{rows_per_batch}_n_sharded", "n_gpus": world, "rows": rows,
+            "out_bytes_gathered_per_gpu": rows * N * 2,
+            "compute_only_us": us_compute, "gemm_plus_nccl_all_gather_us": us_nccl, "peer_store_epilogue_us": us_peer,
+            "tflops_compute_only": flops / us_compute / 1e6, "tflops_nccl": flops / us_nccl / 1e6, "tflops_peer": flops / us_peer / 1e6,
+            "kernel": lib.rt_plan_kernel(plan).decode()}
+
+
 def cpu_step(weights_raw, x16, layers):
     """One decode step on the CPU oracle (shader-faithful arithmetic, OpenMP)."""
     import oracle
@@ -399,6 +458,10 @@ def main():
     assert np.all(np.isfinite(y_dev.astype(np.float32))), "non-finite benchmark output"
     assert np.array_equal(y_dev.view(np.uint16), y_pin.array.reshape(-1).view(np.uint16)), "legs disagree"
 
+    sharded = None
+    if world > 1 and not args.no_sharded:
+        res = [run_sharded(rank, world, gpu, stream, dist, torch, rows_per_batch=r) for r in (2048, 8192)]
+        sharded = res
     if world > 1:
         t = torch.tensor([dev_ms, e2e_ms, e2e_wall_ms], device=f"cuda:{local_rank}", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -437,6 +500,8 @@ def main():
             gbs, l_used, dt = time_cpu(raw, x_pin.array.reshape(-1).copy(), budget_s=15.0, max_layers=layers)
             line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
                                     "sample": f"{l_used} of {layers} layers ({2 * l_used} GEMVs) in {dt:.2f} s, C oracle with OpenMP"}
+        if sharded is not None:
+            line["sharded"] = sharded
         if args.extras and world == 1:
             which = {"c1", "c3", "c4", "c5", "c5long"} if args.extras == "all" else set(args.extras.split(","))
             line["extras"] = run_extras(which, gpu, stream)

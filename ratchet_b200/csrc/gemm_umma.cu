@@ -8,13 +8,14 @@
 // kernel as 16-bit values: the dequantise pre-pass (dequant.cu) writes them to a scratch buffer
 // owned by the plan with the reference's rounding (f16(q) * d rounded to f16, gemm.rs:400-406).
 //
-// Structure (one persistent CTA per SM, 192 threads):
+// Structure (one persistent CTA per SM, 320 threads):
 //   warp 0      TMA producer: 128B-swizzled tiles of P (128 x 64) and Q (BN x 64) into a
 //               multi-stage shared-memory ring, completion on mbarriers
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (128 x BN x 16 per
 //               instruction), tcgen05.commit releases ring stages and publishes accumulators
-//   warps 2-5   epilogue: tcgen05.ld of one of two accumulator buffers (so the next tile's MMAs
-//               overlap), the reference's epilogue chain, vectorised global stores
+//   warps 2-9   epilogue: tcgen05.ld of one of two accumulator buffers (so the next tile's MMAs
+//               overlap), the reference's epilogue chain, stores staged through shared memory so
+//               that every store instruction writes whole 128-byte lines
 // Every wait is bounded (about two seconds of SM cycles); on expiry the kernel records the wait site in a device
 // flag, all roles leave their loops, tensor memory is freed and the kernel returns.  The host
 // reads the flag at the next rt_device_sync.
@@ -32,7 +33,9 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64; // 64 x 16-bit = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 8;             // two per tensor-memory lane quarter, alternating 64-column rounds
+constexpr int NUM_THREADS = 64 + EPI_WARPS * 32;
+constexpr int STG_ROW_BYTES = 128;       // 64 outputs of 2 bytes; 16-byte chunks XOR-swizzled by row: conflict-free both ways
 constexpr unsigned long long WAIT_LIMIT_CYCLES = 4000000000ull; // about 2 s at the SM clock
 
 struct UmmaParams {
@@ -60,7 +63,8 @@ template <int BN> struct Cfg {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = 2 * BN; // two accumulator buffers
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + BN * 4 /*bias*/;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + BN * 4 /*bias*/ +
+                                      EPI_WARPS * 32 * STG_ROW_BYTES /*store staging*/;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -170,6 +174,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * C::STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     float *bias_s = reinterpret_cast<float *>(smem + C::STAGES * C::STAGE_BYTES + 256);
+    uint8_t *stage_out = smem + C::STAGES * C::STAGE_BYTES + 256 + BN * 4;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + C::STAGES);
@@ -182,7 +187,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(bar_tfull + 8 * a, 1);
-            mbar_init(bar_tempty + 8 * a, 4); // one arrival per epilogue warp
+            mbar_init(bar_tempty + 8 * a, EPI_WARPS); // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -249,24 +254,25 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             }
         }
     } else {
-        // ---------------------------------------------------------------- epilogue (warps 2..5)
-        const int q = warp & 3; // the tensor-memory lane quarter this warp may read
+        // ---------------------------------------------------------------- epilogue (warps 2..9)
+        const int q = warp & 3;            // the tensor-memory lane quarter this warp may read
+        const int half = (warp - 2) >> 2;  // which of the alternating 64-column rounds it takes
         const int ep_tid = threadIdx.x - 64;
         int acc = 0;
         uint32_t acc_phase = 0;
-        bool vec_ok = (prm.out_ld % 8 == 0) && (prm.out_col % 8 == 0) && (prm.out_batch_stride % 8 == 0);
+        bool vec_ok = (prm.S % 8 == 0) && (prm.out_ld % 8 == 0) && (prm.out_col % 8 == 0) && (prm.out_batch_stride % 8 == 0);
         for (int d = 0; d < prm.n_out; d++) vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(prm.outs[d]) % 16 == 0);
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
             const int r0 = (rem % prm.tiles_r) * BM, s0 = (rem / prm.tiles_r) * BN;
             if (*abort_flag) break;
             // bias values of this tile's columns, shared by the four epilogue warps
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
             if (prm.bias_mode == BIAS_PER_N) {
-                for (int j = ep_tid; j < BN; j += 128)
+                for (int j = ep_tid; j < BN; j += EPI_WARPS * 32)
                     bias_s[j] = (s0 + j < prm.S) ? load_bias(prm.bias, prm.bias_dt, s0 + j) : 0.f;
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
             if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, 4)) break;
             tc_fence_after();
             const int row = r0 + q * 32 + lane;
@@ -274,13 +280,26 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             float row_bias = 0.f;
             if (prm.bias_mode == BIAS_PER_M && row < prm.R) row_bias = load_bias(prm.bias, prm.bias_dt, row);
             const long long row_off = (long long)b * prm.out_batch_stride + (long long)row * prm.out_ld + prm.out_col;
+            // 64 columns per round: two tensor-memory loads, the epilogue arithmetic, then through a
+            // per-warp staging buffer so that global stores run along rows: 8 lanes x 16 B = one full
+            // 128-byte line per row (this matters most when the destination is a peer GPU over NVLink)
+            uint8_t *stg = stage_out + (warp - 2) * (32 * STG_ROW_BYTES);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + acc * BN + c * 32 + ((uint32_t)(q * 32) << 16), v);
-                const int col0 = s0 + c * 32;
-                if (row < prm.R && col0 < prm.S) {
-                    if (vec_ok && col0 + 32 <= prm.S) {
+            for (int cc = half; cc < BN / 64; cc += 2) {
+                const int colbase = s0 + cc * 64;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int c = cc * 2 + h;
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + acc * BN + c * 32 + ((uint32_t)(q * 32) << 16), v);
+                    if (cc + 2 >= BN / 64 && h == 1) {
+                        // the accumulator has been read completely: hand it back to the MMA warp now
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+                    }
+                    const int col0 = s0 + c * 32;
+                    if (vec_ok) {
 #pragma unroll
                         for (int g = 0; g < 4; g++) {
                             uint32_t w[4];
@@ -293,11 +312,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                                 const OutT o1 = epilogue_value<OutT>(__uint_as_float(v[i0 + 1]), has_bias, b1, prm.epilogue);
                                 w[j] = pack2<OutT>(to_f32(o0), to_f32(o1));
                             }
-                            const uint4 pk = make_uint4(w[0], w[1], w[2], w[3]);
-                            for (int d = 0; d < prm.n_out; d++)
-                                *reinterpret_cast<uint4 *>(reinterpret_cast<OutT *>(prm.outs[d]) + row_off + col0 + g * 8) = pk;
+                            *reinterpret_cast<uint4 *>(stg + lane * STG_ROW_BYTES + (((h * 4 + g) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
-                    } else {
+                    } else if (row < prm.R && col0 < prm.S) {
 #pragma unroll
                         for (int i = 0; i < 32; i++) {
                             if (col0 + i < prm.S) {
@@ -308,10 +325,22 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                         }
                     }
                 }
+                if (vec_ok) {
+                    __syncwarp();
+                    const int colv = colbase + (lane & 7) * 8;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int rl = 4 * i + (lane >> 3);
+                        const int rg = r0 + q * 32 + rl;
+                        if (rg < prm.R && colv < prm.S) {
+                            const uint4 pk = *reinterpret_cast<const uint4 *>(stg + rl * STG_ROW_BYTES + (((lane & 7) ^ (rl & 7)) << 4));
+                            const long long off = (long long)b * prm.out_batch_stride + (long long)rg * prm.out_ld + prm.out_col + colv;
+                            for (int d = 0; d < prm.n_out; d++) *reinterpret_cast<uint4 *>(reinterpret_cast<OutT *>(prm.outs[d]) + off) = pk;
+                        }
+                    }
+                    __syncwarp();
+                }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
     }
