@@ -23,6 +23,7 @@ SOURCES = [
     "api.cu",
     "matmul_simt.cu",
     "gemv_q8_mma.cu",
+    "gemv_q8_umma.cu",
     "dequant.cu",
     "gemm_umma.cu",
     "static_scratch.cu",

@@ -58,7 +58,7 @@ struct rt_buffer {
     uint64_t klass = 0; // bytes allocated
 };
 
-enum PlanKernel { PK_GEMM_SIMT, PK_GEMV_SIMT, PK_Q8_GEMV_MMA, PK_GEMM_UMMA };
+enum PlanKernel { PK_GEMM_SIMT, PK_GEMV_SIMT, PK_Q8_GEMV_MMA, PK_Q8_GEMV_UMMA, PK_GEMM_UMMA };
 
 struct rt_plan {
     rt_device *dev = nullptr;
@@ -68,6 +68,7 @@ struct rt_plan {
     int launches = 1;
     int split = 1;
     int nv = 1;
+    GemvUmmaConfig gemv_umma{};
     MatmulParams params{}; // everything but the pointers
     uint64_t lhs_scale_offset = 0;
     // tensor-core GEMM: operand roles, tile width, and the scratch that holds dequantised weights
@@ -262,6 +263,9 @@ rt_status rt_device_sync(rt_device *dev) {
     if (site != 0)
         return fail(RT_ERR_CUDA, "a tensor-core GEMM gave up a bounded wait (site " + std::to_string(site) +
                                      "): its output is incomplete");
+    CUDA_TRY(gemv_umma_take_error(&site, dev->stream));
+    if (site != 0)
+        return fail(RT_ERR_CUDA, "a tensor-memory GEMV gave up a bounded wait (site " + std::to_string(site) + "): its output is incomplete");
     CUDA_TRY(gemv_take_error(&site, dev->stream));
     if (site != 0) return fail(RT_ERR_CUDA, "a GEMV gave up waiting for its weight copies: its output is incomplete");
     return RT_OK;
@@ -431,7 +435,16 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
     if (gemv_split > 0 && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.N >= 1 && s.N <= 8 && (s.N == 1 || s.trans_rhs) && s.K > 0 && !empty) {
         pl->nv = (int)s.N;
         pl->split = gemv_split;
-        pl->kernel = PK_Q8_GEMV_MMA;
+        // one vector against f16-scaled Q8_0 at a size that fills the machine: the tensor-memory GEMV
+        const char *env_gu = getenv("RT_GEMV_UMMA");
+        const bool umma_ok = !(env_gu && env_gu[0] == '0') && desc->lhs_dt == RT_Q8_0H && s.N == 1 && s.stacks == 1 &&
+                             s.lhs_stack == 1 && s.rhs_stack == 1 &&
+                             q8_gemv_umma_config(p.M, p.K, dev->sm_count, &pl->gemv_umma) && pl->gemv_umma.rb >= 8;
+        pl->kernel = umma_ok ? PK_Q8_GEMV_UMMA : PK_Q8_GEMV_MMA;
+        if (umma_ok)
+            pl->name = std::string("q8_gemv_umma_h_rb") + std::to_string(pl->gemv_umma.rb) + "_split" +
+                       std::to_string(pl->gemv_umma.split) + "_ring" + std::to_string(pl->gemv_umma.ring);
+        else
         pl->name = std::string("q8_gemv_mma_") + (desc->lhs_dt == RT_Q8_0H ? "h" : "f") + "_nv" + std::to_string(pl->nv) +
                    "_split" + std::to_string(pl->split);
     } else if (umma_eligible(*desc, s)) {
@@ -533,6 +546,11 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
     switch (plan->kernel) {
     case PK_Q8_GEMV_MMA:
         e = launch_q8_gemv_mma(p, s.desc.lhs_dt == RT_Q8_0F, plan->nv, plan->split, (flags & RT_LAUNCH_LHS_CONSTANT) != 0, st);
+        break;
+    case PK_Q8_GEMV_UMMA:
+        if ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) % 16 != 0)
+            return fail(RT_ERR_ARG, "rt_matmul_launch: lhs and rhs must be 16-byte aligned");
+        e = launch_q8_gemv_umma(p, plan->gemv_umma, (flags & RT_LAUNCH_LHS_CONSTANT) != 0, st);
         break;
     case PK_GEMV_SIMT:
         e = launch_matmul_simt(p, s.desc.lhs_dt, s.desc.rhs_dt, true, st);

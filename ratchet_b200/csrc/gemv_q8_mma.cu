@@ -122,10 +122,13 @@ __global__ void __launch_bounds__(THREADS, 5) q8_gemv_bulk_kernel(MatmulParams p
                          ::"r"(smem_u32(codes_s + r * cstride)), "l"(src), "r"(row_bytes), "r"(bar_addr) : "memory");
         }
     }
-    for (int i = threadIdx.x; i < ROWS * blk_cnt; i += THREADS) {
-        const int r = i / blk_cnt, j = i - r * blk_cnt;
+    {
+        // 16 threads per row, no division: thread t stages scales t%16, t%16+16, ... of row t/16
+        const int r = threadIdx.x >> 4;
         const int row = min(row_base + r, p.M - 1);
-        scales_s[r * sstride + j] = __ldg(scales + (long long)row * nblk + blk_begin + j);
+        const ScaleT *src = scales + (long long)row * nblk + blk_begin;
+        ScaleT *dst = scales_s + r * sstride;
+        for (int j = threadIdx.x & 15; j < blk_cnt; j += 16) dst[j] = __ldg(src + j);
     }
     if (lhs_constant) asm volatile("griddepcontrol.wait;" ::: "memory");
 

@@ -1,0 +1,462 @@
+// Q8_0 GEMV (one activation vector) on the 5th-generation tensor cores: y[r] = sum_k W[r][k] * x[k].
+//
+// Takes the role of the reference's subgroup GEMV (crates/ratchet-core/src/ops/gemv.rs:333-558) for
+// the (Q8_0H, F16) pair at decode shapes.  The problem is bound by reading every weight byte once
+// (1.06 bytes per weight); what has to be kept off the critical path is the instruction stream.
+// Converting int8 codes to f16 in registers costs more than one instruction per code, which at
+// 26 M codes per launch is more issue time than the 4.3 us HBM budget.  Here no code ever passes
+// through a register:
+//
+//  * the int8 codes go from HBM to shared memory by TMA (128-byte swizzle) and are consumed there
+//    by tcgen05.mma kind::i8 (M = 128 weight rows, N = 16, K = 32 = one Q8_0 block), one
+//    instruction per block, s32 accumulators in tensor memory;
+//  * the activation vector is turned once per CTA into block-floating-point int8 digits: per block
+//    of 32 a power-of-two scale xs and a 15-bit integer m = hi*256 + lo per element, stored as
+//    two int8 rows (hi, lo) of the MMA's B operand; |x - m*xs| <= 2^-15 of the block's largest
+//    element, far inside the path's 1e-3 bar (f16 inputs carry 11 bits);
+//  * per block the epilogue warps (lane = weight row) read the two s32 sums from tensor memory and
+//    add d[row][block] * xs[block] * (256*hi + lo) to the row's f32 accumulator: the only per-row
+//    work, about ten instructions per block per warp of 32 rows;
+//  * a CTA owns a contiguous range of at most 128 rows (N / #CTAs, so all SMs get equal bytes) and,
+//    for fat weights, a slice of K: the CTAs of a thread-block cluster split K and rank 0 adds the
+//    slices' row sums through distributed shared memory in rank order (deterministic);
+//  * the producer warp asks for its whole share to be prefetched into L2 at once and then keeps a
+//    small ring of stages full, and it does so before the kernel waits for its stream predecessor
+//    when the caller states that the weights are constants (programmatic dependent launch).  A CTA
+//    needs less than half of an SM's shared memory and half of its tensor memory, so the next
+//    layer's CTAs are resident and prefetching while this layer computes.
+// Every wait is bounded (about two seconds of SM cycles); on expiry the kernel sets a device flag,
+// leaves its loops, frees tensor memory and returns; the next rt_device_sync reports it.
+#include <cooperative_groups.h>
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.hpp"
+
+namespace cg = cooperative_groups;
+
+namespace rt {
+
+__device__ int g_gemv_umma_error = 0;
+
+namespace {
+
+constexpr int THREADS = 192;          // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: digits + epilogue
+constexpr int STAGE_K = 256;          // bytes of K per ring stage = 8 Q8_0 blocks = two 128-byte swizzle rows
+constexpr int TMEM_COLS = 256;        // half of an SM's tensor memory: two groups of 8 slots of 16 columns
+constexpr unsigned long long WAIT_LIMIT_CYCLES = 4000000000ull;
+
+struct UmmaGemvParams {
+    MatmulParams p;
+    int rb;            // weight rows per cluster (<= 128)
+    int rb8;           // rb rounded up to 8: rows of a staged sub-tile
+    int ks;            // bytes of K per CTA (multiple of 256)
+    int nstages_k;     // ks / 256
+    int ring;          // ring stages
+    int stage_bytes;
+    int split;         // cluster size along K
+    int lhs_constant;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long wait_clock() { return (unsigned long long)clock64(); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = wait_clock();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 32; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            atomicCAS(&g_gemv_umma_error, 0, site);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+
+// K-major operand tile, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+    // the predicate is false: the accumulator slot is overwritten, every block starts from zero
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}\n"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld2(uint32_t taddr, int &a, int &b) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory map (all offsets from a 1024-byte aligned base):
+//   [B digits: (ks/128) tiles of 16 rows x 128 B][ring: stages of {A0: rb8 x 128, A1: rb8 x 128, scales: rb8 x 16 (to 1024)}]
+//   [guard: (128 - rb8) x 128, read by MMAs past a sub-tile's last row][xs: ks/32 floats][red: 128 floats][barriers]
+__global__ void __launch_bounds__(THREADS, 2)
+q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s, const UmmaGemvParams up) {
+    extern __shared__ uint8_t smem_raw[];
+    const MatmulParams &p = up.p;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = up.split > 1 ? (int)(blockIdx.x % up.split) : 0;
+    const int cluster_id = (int)(blockIdx.x / up.split);
+    const int row_begin = cluster_id * up.rb;
+    if (row_begin >= p.M) return; // the whole cluster leaves together: nothing has been set up yet
+
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int n_ksteps = up.ks / 128;
+    uint8_t *b_tiles = smem;
+    uint8_t *ring = b_tiles + (size_t)n_ksteps * 2048;
+    uint8_t *guard_end = ring + (size_t)up.ring * up.stage_bytes + (size_t)(128 - up.rb8) * 128;
+    float *xs = reinterpret_cast<float *>(guard_end);
+    float *red = xs + up.ks / 32;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(red + 128);
+    // bars: [0..R) full, [R..2R) empty, [2R..2R+2) tmem_full, [2R+2..2R+4) tmem_empty, [2R+4] digits ready
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * up.ring + 5);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + up.ring);
+    const uint32_t bar_tfull = smem_u32(bars + 2 * up.ring), bar_tempty = smem_u32(bars + 2 * up.ring + 2);
+    const uint32_t bar_x = smem_u32(bars + 2 * up.ring + 4);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < up.ring; s++) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 5); // the MMAs' commit + the four epilogue warps (they read the stage's scales)
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tempty + 8 * a, 4);
+        }
+        mbar_init(bar_x, 4);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // the next kernel in the stream may start its prologue and its weight requests
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int k_begin = rank * up.ks; // first byte of K of this CTA
+    const int rows_here = min(up.rb, p.M - row_begin);
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (!up.lhs_constant) asm volatile("griddepcontrol.wait;" ::: "memory");
+        // whole share into L2 now (eight rows per request), so the depth of the HBM queue does not depend on the ring
+        for (int r = lane * 8; r < rows_here; r += 32 * 8) {
+            const int nr = min(8, rows_here - r);
+            for (int i = 0; i < nr; i++) {
+                const char *src = (const char *)p.lhs + (long long)(row_begin + r + i) * p.K + k_begin;
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(up.ks) : "memory");
+            }
+        }
+        if (lane == 0) {
+            int slot = 0;
+            uint32_t phase = 0;
+            const uint32_t tx = (uint32_t)up.rb * (2 * 128 + 16);
+            for (int s = 0; s < up.nstages_k; s++) {
+                if (!mbar_wait(bar_empty + 8 * slot, phase ^ 1, abort_flag, 1)) break;
+                const uint32_t st = smem_u32(ring + (size_t)slot * up.stage_bytes);
+                const uint32_t full = bar_full + 8 * slot;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(tx) : "memory");
+                const int kb = k_begin + s * STAGE_K;
+                tma_load_2d(st, &map_w, kb, row_begin, full);
+                tma_load_2d(st + up.rb8 * 128, &map_w, kb + 128, row_begin, full);
+                tma_load_2d(st + 2 * up.rb8 * 128, &map_s, kb / 32, row_begin, full);
+                if (++slot == up.ring) { slot = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            // instruction descriptor: s32 accumulate, signed 8-bit A and B, K-major, N = 16, M = 128
+            const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+            bool ok = mbar_wait(bar_x, 0, abort_flag, 2);
+            int slot = 0, tg = 0;
+            uint32_t phase = 0, tphase = 0;
+            for (int s = 0; s < up.nstages_k && ok; s++) {
+                if (!mbar_wait(bar_tempty + 8 * tg, tphase ^ 1, abort_flag, 3)) break;
+                if (!mbar_wait(bar_full + 8 * slot, phase, abort_flag, 4)) break;
+                tc_fence_after();
+                const uint32_t a0 = smem_u32(ring + (size_t)slot * up.stage_bytes);
+#pragma unroll
+                for (int kk = 0; kk < 2; kk++) {
+                    const uint32_t a_addr = a0 + kk * up.rb8 * 128;
+                    const uint32_t b_addr = smem_u32(b_tiles + (size_t)(s * 2 + kk) * 2048);
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        umma_i8(tmem_base + tg * 128 + (kk * 4 + j) * 16, umma_desc_sw128(a_addr + j * 32), umma_desc_sw128(b_addr + j * 32), idesc);
+                }
+                umma_commit(bar_empty + 8 * slot);
+                umma_commit(bar_tfull + 8 * tg);
+                if (++slot == up.ring) { slot = 0; phase ^= 1; }
+                if (++tg == 2) { tg = 0; tphase ^= 1; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ digits, then epilogue (warps 2..5)
+        const int q = warp & 3;          // tensor-memory lane quarter of this warp
+        const int et = threadIdx.x - 64; // 0..127
+        // zero the B tiles: rows 2..15 of every tile stay zero, rows 0 and 1 receive the digits
+        for (int i = et; i < n_ksteps * 2048 / 16; i += 128) reinterpret_cast<uint4 *>(b_tiles)[i] = make_uint4(0u, 0u, 0u, 0u);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // the activations are the stream predecessor's output
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        {
+            const __half *x = (const __half *)p.rhs + k_begin;
+            const int sub = et & 3; // 4 threads per block of 32 elements, 8 elements each
+            for (int blk = et >> 2; blk < up.ks / 32; blk += 32) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(x + blk * 32 + sub * 8);
+                const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float2 f = __half22float2(h2[i]);
+                    v[2 * i] = f.x;
+                    v[2 * i + 1] = f.y;
+                }
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                // amax < 2^(E-126) for its exponent field E: scale it below 2^14
+                const int E = (int)((__float_as_uint(amax) >> 23) & 0xFFu);
+                const float scale = amax > 0.f ? __uint_as_float((uint32_t)(140 - E + 127) << 23) : 0.f;
+                const float inv = amax > 0.f ? __uint_as_float((uint32_t)(E - 13) << 23) : 0.f;
+                uint32_t hi_w[2] = {0u, 0u}, lo_w[2] = {0u, 0u};
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    int m = __float2int_rn(v[i] * scale);
+                    m = max(-16383, min(16383, m));
+                    const int hi = (m + 128) >> 8;
+                    const int lo = m - (hi << 8);
+                    hi_w[i >> 2] |= (uint32_t)(hi & 0xFF) << (8 * (i & 3));
+                    lo_w[i >> 2] |= (uint32_t)(lo & 0xFF) << (8 * (i & 3));
+                }
+                // tile of k-step blk/4; byte position of these 8 elements in the 128-byte row; 16-byte chunks XOR the row index
+                uint8_t *tile = b_tiles + (size_t)(blk >> 2) * 2048;
+                const int kpos = (blk & 3) * 32 + sub * 8;
+                const int chunk = kpos >> 4, within = kpos & 15;
+                *reinterpret_cast<uint2 *>(tile + 0 * 128 + ((chunk ^ 0) << 4) + within) = make_uint2(hi_w[0], hi_w[1]);
+                *reinterpret_cast<uint2 *>(tile + 1 * 128 + ((chunk ^ 1) << 4) + within) = make_uint2(lo_w[0], lo_w[1]);
+                if (sub == 0) xs[blk] = inv;
+            }
+        }
+        // the MMAs read the tiles through the async proxy
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory"); // xs visible to all epilogue warps
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_x);
+
+        const int row_local = q * 32 + lane;
+        float acc = 0.f;
+        int slot = 0, tg = 0;
+        uint32_t phase = 0, tphase = 0;
+        for (int s = 0; s < up.nstages_k; s++) {
+            if (!mbar_wait(bar_full + 8 * slot, phase, abort_flag, 5)) break;
+            const uint4 sc = *reinterpret_cast<const uint4 *>(ring + (size_t)slot * up.stage_bytes + 2 * up.rb8 * 128 + min(row_local, up.rb8 - 1) * 16);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
+            if (!mbar_wait(bar_tfull + 8 * tg, tphase, abort_flag, 6)) break;
+            tc_fence_after();
+            int hi[8], lo[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) tmem_ld2(tmem_base + tg * 128 + j * 16 + ((uint32_t)(q * 32) << 16), hi[j], lo[j]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * tg);
+            const __half2 *d2 = reinterpret_cast<const __half2 *>(&sc);
+            const float4 xa = *reinterpret_cast<const float4 *>(xs + s * 8), xb = *reinterpret_cast<const float4 *>(xs + s * 8 + 4);
+            const float xsv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float d = (j & 1) ? __high2float(d2[j >> 1]) : __low2float(d2[j >> 1]);
+                const float t = fmaf(256.f, (float)hi[j], (float)lo[j]);
+                acc = fmaf(d * xsv[j], t, acc);
+            }
+            if (++slot == up.ring) { slot = 0; phase ^= 1; }
+            if (++tg == 2) { tg = 0; tphase ^= 1; }
+        }
+        red[row_local] = acc;
+    }
+
+    // ---------------------------------------------------------------------- K slices meet, epilogue, teardown
+    tc_fence_before();
+    __syncthreads();
+    if (up.split > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        if (rank == 0 && threadIdx.x < 128) {
+            float sum = red[threadIdx.x];
+            for (int r = 1; r < up.split; r++) sum += cluster.map_shared_rank(red, r)[threadIdx.x];
+            red[threadIdx.x] = sum; // only this thread reads or writes its entry of rank 0's buffer from here on
+        }
+        cluster.sync(); // the other ranks' shared memory stays alive until rank 0 has read it
+    }
+    if (rank == 0 && threadIdx.x < rows_here && !*abort_flag) {
+        const int row = row_begin + threadIdx.x;
+        const bool has_bias = p.bias_mode != BIAS_NONE;
+        float bias = 0.f;
+        if (has_bias) bias = load_bias(p.bias, p.bias_dt, p.bias_mode == BIAS_PER_M ? row : 0);
+        ((__half *)p.out)[row] = epilogue_value<__half>(red[threadIdx.x], has_bias, bias, p.epilogue);
+    }
+    if (*abort_flag) {
+        const unsigned long long t0 = wait_clock();
+        while (wait_clock() - t0 < 400000ull) __nanosleep(1000);
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+size_t smem_for(int ks, int rb8, int ring, int stage_bytes) {
+    return 1024 + (size_t)(ks / 128) * 2048 + (size_t)ring * stage_bytes + (size_t)(128 - rb8) * 128 + (size_t)(ks / 32) * 4 + 128 * 4 +
+           (size_t)(2 * ring + 5) * 8 + 64;
+}
+
+} // namespace
+
+// Work split for a [M][K] Q8_0H weight: K slices per cluster, rows per cluster, ring depth.  False when
+// the shape is not one this kernel takes (the plan then uses the warp-MMA GEMV).
+bool q8_gemv_umma_config(int M, int K, int sm_count, GemvUmmaConfig *cfg) {
+    if (M < 1 || K < 256 || K % 256 != 0 || !encode_fn()) return false;
+    int split = 1;
+    while (split < 8 && (K / split > 3072 || (K / split) % 256 != 0)) split *= 2;
+    if (K % (split * 256) != 0 || K / split > 3072) return false;
+    int clusters = sm_count / split;
+    if (clusters < 1) return false;
+    int rb = (M + clusters - 1) / clusters;
+    if (rb > 128) return false;
+    const int rb8 = (rb + 7) & ~7;
+    const int ks = K / split;
+    const int stage_bytes = 2 * rb8 * 128 + ((rb8 * 16 + 1023) & ~1023);
+    const size_t budget = 110 * 1024; // two CTAs (this layer's and the next one's) share an SM
+    int ring = 8;
+    while (ring > 2 && smem_for(ks, rb8, ring, stage_bytes) > budget) ring--;
+    if (smem_for(ks, rb8, ring, stage_bytes) > 200 * 1024) return false;
+    if (ring > ks / STAGE_K) ring = ks / STAGE_K < 2 ? 2 : ks / STAGE_K;
+    cfg->split = split; cfg->clusters = clusters; cfg->rb = rb; cfg->rb8 = rb8; cfg->ks = ks; cfg->ring = ring;
+    cfg->stage_bytes = stage_bytes;
+    cfg->smem_bytes = smem_for(ks, rb8, ring, stage_bytes);
+    return true;
+}
+
+cudaError_t launch_q8_gemv_umma(const MatmulParams &p, const GemvUmmaConfig &cfg, bool lhs_constant, cudaStream_t stream) {
+    CUtensorMap map_w, map_s;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)p.M};
+        cuuint64_t strides[1] = {(cuuint64_t)p.K};
+        cuuint32_t box[2] = {128, (cuuint32_t)cfg.rb};
+        cuuint32_t estr[2] = {1, 1};
+        if (encode_fn()(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(p.lhs), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)(p.K / 32), (cuuint64_t)p.M};
+        cuuint64_t strides[1] = {(cuuint64_t)(p.K / 32) * 2};
+        cuuint32_t box[2] = {8, (cuuint32_t)cfg.rb};
+        cuuint32_t estr[2] = {1, 1};
+        if (encode_fn()(&map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(p.lhs_scales), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    UmmaGemvParams up{};
+    up.p = p;
+    up.rb = cfg.rb; up.rb8 = cfg.rb8; up.ks = cfg.ks; up.nstages_k = cfg.ks / STAGE_K; up.ring = cfg.ring;
+    up.stage_bytes = cfg.stage_bytes; up.split = cfg.split; up.lhs_constant = lhs_constant ? 1 : 0;
+    static size_t configured = 0;
+    if (cfg.smem_bytes > configured) {
+        cudaError_t e = cudaFuncSetAttribute(q8_gemv_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.smem_bytes);
+        if (e != cudaSuccess) return e;
+        configured = cfg.smem_bytes;
+    }
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(cfg.clusters * cfg.split);
+    lc.blockDim = dim3(THREADS);
+    lc.dynamicSmemBytes = cfg.smem_bytes;
+    lc.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    n++;
+    if (cfg.split > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cfg.split;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        n++;
+    }
+    lc.attrs = attr;
+    lc.numAttrs = n;
+    return cudaLaunchKernelEx(&lc, q8_gemv_umma_kernel, map_w, map_s, up);
+}
+
+cudaError_t gemv_umma_take_error(int *site, cudaStream_t stream) {
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbolAsync(site, g_gemv_umma_error, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return e;
+    e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return e;
+    if (*site != 0) e = cudaMemcpyToSymbolAsync(g_gemv_umma_error, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream);
+    return e;
+}
+
+} // namespace rt

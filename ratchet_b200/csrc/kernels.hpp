@@ -17,6 +17,15 @@ int q8_gemv_mma_pick_split(int M, int K, int sm_count, int scale_size);
 cudaError_t launch_q8_gemv_mma(const MatmulParams &p, bool f32_scales, int nv, int split, bool lhs_constant, cudaStream_t stream);
 cudaError_t gemv_take_error(int *site, cudaStream_t stream);
 
+// Q8_0H x f16 GEMV on tcgen05 kind::i8 (one activation vector, stacks == 1, K % 256 == 0).
+struct GemvUmmaConfig {
+    int split, clusters, rb, rb8, ks, ring, stage_bytes;
+    size_t smem_bytes;
+};
+bool q8_gemv_umma_config(int M, int K, int sm_count, GemvUmmaConfig *cfg);
+cudaError_t launch_q8_gemv_umma(const MatmulParams &p, const GemvUmmaConfig &cfg, bool lhs_constant, cudaStream_t stream);
+cudaError_t gemv_umma_take_error(int *site, cudaStream_t stream);
+
 // Tensor-core GEMM (tcgen05): D[R][S] = P[R][K] . Q[S][K]^T, 16-bit K-major operands, bias along S.
 // Several destinations for one result: see UmmaParams in gemm_umma.cu.
 struct UmmaScatter {

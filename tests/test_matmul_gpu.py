@@ -122,7 +122,7 @@ def test_q8_gemv_phi2_shapes(gpu, shape, seed):
     for bias in (False, True):
         p = Problem(Q8H, F16, shape, (1, 1, K), (False, True, True), bias=bias, seed=seed, w_std=0.02)
         got, truth_r, truth, faithful, kernel = run_problem(p, gpu)
-        assert kernel.startswith("q8_gemv_mma_h_nv1"), kernel
+        assert kernel.startswith("q8_gemv_umma_h"), kernel
         err = oracle.rel_l2(got, truth_r)
         err_ref = oracle.rel_l2(faithful, truth_r)
         assert err <= 1e-3, (kernel, err)
