@@ -43,7 +43,9 @@ namespace {
 
 constexpr int THREADS = 192;          // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: digits + epilogue
 constexpr int STAGE_K = 256;          // bytes of K per ring stage = 8 Q8_0 blocks = two 128-byte swizzle rows
-constexpr int TMEM_COLS = 256;        // half of an SM's tensor memory: two groups of 8 slots of 16 columns
+constexpr int TMEM_COLS = 256;        // half of an SM's tensor memory
+constexpr int TG_COLS = 32;           // tensor-memory columns per stage (see the MMA issuer)
+constexpr int TGROUPS = TMEM_COLS / TG_COLS;
 constexpr unsigned long long WAIT_LIMIT_CYCLES = 4000000000ull;
 
 struct UmmaGemvParams {
@@ -53,7 +55,8 @@ struct UmmaGemvParams {
     int ks;            // bytes of K per CTA (multiple of 256)
     int nstages_k;     // ks / 256
     int ring;          // ring stages
-    int stage_bytes;
+    int stage_bytes;   // 2 * rb8 * 128
+    int b_bytes;       // digit tiles (and read-past guard), multiple of 1024
     int split;         // cluster size along K
     int lhs_constant;
 };
@@ -94,12 +97,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
 
-// K-major operand tile, 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+// K-major operand tile, 128-byte swizzle, 8-row groups `group_stride` bytes apart.  The digit tiles
+// hold 8 rows and use a stride of 0: rows 8..15 of the N = 16 operand repeat rows 0..7, which only
+// duplicates accumulator columns that the next block overwrites (see the MMA issuer).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t group_stride) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
     d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)(group_stride >> 4) << 32;
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
     return d;
@@ -114,15 +119,20 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld2(uint32_t taddr, int &a, int &b) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "r"(taddr) : "memory");
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // Shared-memory map (all offsets from a 1024-byte aligned base):
-//   [B digits: (ks/128) tiles of 16 rows x 128 B][ring: stages of {A0: rb8 x 128, A1: rb8 x 128, scales: rb8 x 16 (to 1024)}]
-//   [guard: (128 - rb8) x 128, read by MMAs past a sub-tile's last row][xs: ks/32 floats][red: 128 floats][barriers]
+//   [ring: stages of {A0: rb8 x 128, A1: rb8 x 128}][B digits: (ks/128) tiles of 8 rows x 128 B, at least
+//   (128 - rb8) x 128 bytes because the MMAs read 128 rows from every sub-tile][scales: ring x rb8 x 16]
+//   [xs: ks/32 floats][red: split x 128 floats][barriers]
 __global__ void __launch_bounds__(THREADS, 2)
 q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s, const UmmaGemvParams up) {
     extern __shared__ uint8_t smem_raw[];
@@ -135,29 +145,30 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int n_ksteps = up.ks / 128;
-    uint8_t *b_tiles = smem;
-    uint8_t *ring = b_tiles + (size_t)n_ksteps * 2048;
-    uint8_t *guard_end = ring + (size_t)up.ring * up.stage_bytes + (size_t)(128 - up.rb8) * 128;
-    float *xs = reinterpret_cast<float *>(guard_end);
+    uint8_t *ring = smem;                                            // [ring][2 sub-tiles][rb8 x 128]
+    uint8_t *b_tiles = ring + (size_t)up.ring * up.stage_bytes;      // [ks/128][8 rows x 128]; also absorbs MMA reads past a sub-tile's last row
+    uint8_t *scales_s = b_tiles + up.b_bytes;                        // [ring][rb8 x 16]
+    float *xs = reinterpret_cast<float *>(scales_s + (size_t)up.ring * up.rb8 * 16);
     float *red = xs + up.ks / 32;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(red + 128);
-    // bars: [0..R) full, [R..2R) empty, [2R..2R+2) tmem_full, [2R+2..2R+4) tmem_empty, [2R+4] digits ready
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * up.ring + 5);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(red + 128 * up.split);
+    // bars: [0..R) full, [R..2R) empty, then TGROUPS tmem_full, TGROUPS tmem_empty, digits ready, K-slice sums arrived
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * up.ring + 2 * TGROUPS + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + up.ring);
-    const uint32_t bar_tfull = smem_u32(bars + 2 * up.ring), bar_tempty = smem_u32(bars + 2 * up.ring + 2);
-    const uint32_t bar_x = smem_u32(bars + 2 * up.ring + 4);
+    const uint32_t bar_tfull = smem_u32(bars + 2 * up.ring), bar_tempty = smem_u32(bars + 2 * up.ring + TGROUPS);
+    const uint32_t bar_x = smem_u32(bars + 2 * up.ring + 2 * TGROUPS), bar_red = smem_u32(bars + 2 * up.ring + 2 * TGROUPS + 1);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < up.ring; s++) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 5); // the MMAs' commit + the four epilogue warps (they read the stage's scales)
         }
-        for (int a = 0; a < 2; a++) {
+        for (int a = 0; a < TGROUPS; a++) {
             mbar_init(bar_tfull + 8 * a, 1);
             mbar_init(bar_tempty + 8 * a, 4);
         }
         mbar_init(bar_x, 4);
+        mbar_init(bar_red, (up.split > 1 ? up.split - 1 : 1) * 128); // one arrival per row of every other K slice
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -170,6 +181,8 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // every CTA of the cluster has initialised its barriers before any other may arrive on them
+    if (up.split > 1) cg::this_cluster().sync();
     const uint32_t tmem_base = *tmem_slot;
     const int k_begin = rank * up.ks; // first byte of K of this CTA
     const int rows_here = min(up.rb, p.M - row_begin);
@@ -197,7 +210,7 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const int kb = k_begin + s * STAGE_K;
                 tma_load_2d(st, &map_w, kb, row_begin, full);
                 tma_load_2d(st + up.rb8 * 128, &map_w, kb + 128, row_begin, full);
-                tma_load_2d(st + 2 * up.rb8 * 128, &map_s, kb / 32, row_begin, full);
+                tma_load_2d(smem_u32(scales_s + (size_t)slot * up.rb8 * 16), &map_s, kb / 32, row_begin, full);
                 if (++slot == up.ring) { slot = 0; phase ^= 1; }
             }
         }
@@ -206,6 +219,7 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (lane == 0) {
             // instruction descriptor: s32 accumulate, signed 8-bit A and B, K-major, N = 16, M = 128
             const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+            const uint64_t a_desc_ring = umma_desc_sw128(smem_u32(ring), 1024), b_desc_base = umma_desc_sw128(smem_u32(b_tiles), 0);
             bool ok = mbar_wait(bar_x, 0, abort_flag, 2);
             int slot = 0, tg = 0;
             uint32_t phase = 0, tphase = 0;
@@ -213,35 +227,52 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (!mbar_wait(bar_tempty + 8 * tg, tphase ^ 1, abort_flag, 3)) break;
                 if (!mbar_wait(bar_full + 8 * slot, phase, abort_flag, 4)) break;
                 tc_fence_after();
-                const uint32_t a0 = smem_u32(ring + (size_t)slot * up.stage_bytes);
+                // descriptors differ only in their 16-byte address field: one add per operand per MMA keeps the
+                // issuing thread, which is the pace-maker of this kernel, short
+                const uint64_t a_desc = a_desc_ring + (uint64_t)((uint32_t)(slot * up.stage_bytes) >> 4);
+                const uint64_t b_desc = b_desc_base + (uint64_t)(s * 2 * (1024 >> 4));
+                const uint32_t d0 = tmem_base + tg * TG_COLS;
 #pragma unroll
                 for (int kk = 0; kk < 2; kk++) {
-                    const uint32_t a_addr = a0 + kk * up.rb8 * 128;
-                    const uint32_t b_addr = smem_u32(b_tiles + (size_t)(s * 2 + kk) * 2048);
+                    const uint64_t ak = a_desc + (uint64_t)((uint32_t)(kk * up.rb8 * 128) >> 4), bk = b_desc + (uint64_t)(kk * (1024 >> 4));
+                    // Block jj of the stage writes columns [2jj, 2jj+16) of the stage's group: its two sums (the hi
+                    // and lo digit rows of B) followed by columns it does not need.  MMAs of one thread execute in
+                    // issue order and block jj+1 starts two columns later, so the last writer of column c < 16 is
+                    // block c/2: after the eighth block the group's first sixteen columns hold hi0, lo0, hi1,
+                    // lo1, ... and one load fetches the whole stage.
 #pragma unroll
-                    for (int j = 0; j < 4; j++)
-                        umma_i8(tmem_base + tg * 128 + (kk * 4 + j) * 16, umma_desc_sw128(a_addr + j * 32), umma_desc_sw128(b_addr + j * 32), idesc);
+                    for (int j = 0; j < 4; j++) umma_i8(d0 + (kk * 4 + j) * 2, ak + 2 * j, bk + 2 * j, idesc);
                 }
                 umma_commit(bar_empty + 8 * slot);
                 umma_commit(bar_tfull + 8 * tg);
                 if (++slot == up.ring) { slot = 0; phase ^= 1; }
-                if (++tg == 2) { tg = 0; tphase ^= 1; }
+                if (++tg == TGROUPS) { tg = 0; tphase ^= 1; }
             }
         }
     } else {
         // ------------------------------------------------------------------ digits, then epilogue (warps 2..5)
         const int q = warp & 3;          // tensor-memory lane quarter of this warp
         const int et = threadIdx.x - 64; // 0..127
-        // zero the B tiles: rows 2..15 of every tile stay zero, rows 0 and 1 receive the digits
-        for (int i = et; i < n_ksteps * 2048 / 16; i += 128) reinterpret_cast<uint4 *>(b_tiles)[i] = make_uint4(0u, 0u, 0u, 0u);
+        // zero the B tiles: rows 2..7 of every tile stay zero, rows 0 and 1 receive the digits
+        for (int i = et; i < n_ksteps * 1024 / 16; i += 128) reinterpret_cast<uint4 *>(b_tiles)[i] = make_uint4(0u, 0u, 0u, 0u);
         asm volatile("bar.sync 1, 128;" ::: "memory");
         // the activations are the stream predecessor's output
         asm volatile("griddepcontrol.wait;" ::: "memory");
         {
             const __half *x = (const __half *)p.rhs + k_begin;
             const int sub = et & 3; // 4 threads per block of 32 elements, 8 elements each
-            for (int blk = et >> 2; blk < up.ks / 32; blk += 32) {
-                const uint4 raw = *reinterpret_cast<const uint4 *>(x + blk * 32 + sub * 8);
+            constexpr int MAX_IT = 3072 / 32 / 32; // blocks per thread quad at the largest K slice
+            uint4 pre[MAX_IT];
+#pragma unroll
+            for (int it = 0; it < MAX_IT; it++) { // all loads first: one L2 round trip, not one per iteration
+                const int blk = (et >> 2) + it * 32;
+                pre[it] = blk < up.ks / 32 ? *reinterpret_cast<const uint4 *>(x + blk * 32 + sub * 8) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int it = 0; it < MAX_IT; it++) {
+                const int blk = (et >> 2) + it * 32;
+                if (blk >= up.ks / 32) break;
+                const uint4 raw = pre[it];
                 const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
                 float v[8];
 #pragma unroll
@@ -270,7 +301,7 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     lo_w[i >> 2] |= (uint32_t)(lo & 0xFF) << (8 * (i & 3));
                 }
                 // tile of k-step blk/4; byte position of these 8 elements in the 128-byte row; 16-byte chunks XOR the row index
-                uint8_t *tile = b_tiles + (size_t)(blk >> 2) * 2048;
+                uint8_t *tile = b_tiles + (size_t)(blk >> 2) * 1024;
                 const int kpos = (blk & 3) * 32 + sub * 8;
                 const int chunk = kpos >> 4, within = kpos & 15;
                 *reinterpret_cast<uint2 *>(tile + 0 * 128 + ((chunk ^ 0) << 4) + within) = make_uint2(hi_w[0], hi_w[1]);
@@ -290,15 +321,13 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         uint32_t phase = 0, tphase = 0;
         for (int s = 0; s < up.nstages_k; s++) {
             if (!mbar_wait(bar_full + 8 * slot, phase, abort_flag, 5)) break;
-            const uint4 sc = *reinterpret_cast<const uint4 *>(ring + (size_t)slot * up.stage_bytes + 2 * up.rb8 * 128 + min(row_local, up.rb8 - 1) * 16);
+            const uint4 sc = *reinterpret_cast<const uint4 *>(scales_s + (size_t)slot * up.rb8 * 16 + min(row_local, up.rb8 - 1) * 16);
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
             if (!mbar_wait(bar_tfull + 8 * tg, tphase, abort_flag, 6)) break;
             tc_fence_after();
-            int hi[8], lo[8];
-#pragma unroll
-            for (int j = 0; j < 8; j++) tmem_ld2(tmem_base + tg * 128 + j * 16 + ((uint32_t)(q * 32) << 16), hi[j], lo[j]);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            int dv[16];
+            tmem_ld16(tmem_base + tg * TG_COLS + ((uint32_t)(q * 32) << 16), dv);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * tg);
@@ -308,11 +337,11 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 const float d = (j & 1) ? __high2float(d2[j >> 1]) : __low2float(d2[j >> 1]);
-                const float t = fmaf(256.f, (float)hi[j], (float)lo[j]);
+                const float t = fmaf(256.f, (float)dv[2 * j], (float)dv[2 * j + 1]);
                 acc = fmaf(d * xsv[j], t, acc);
             }
             if (++slot == up.ring) { slot = 0; phase ^= 1; }
-            if (++tg == 2) { tg = 0; tphase ^= 1; }
+            if (++tg == TGROUPS) { tg = 0; tphase ^= 1; }
         }
         red[row_local] = acc;
     }
@@ -321,14 +350,33 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     tc_fence_before();
     __syncthreads();
     if (up.split > 1) {
+        // Ranks 1.. push their row sums into rank 0's shared memory and arrive on its barrier (release);
+        // rank 0 waits for them and adds in rank order.  Nobody waits for rank 0, so only it stays behind.
         cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync();
-        if (rank == 0 && threadIdx.x < 128) {
+        if (rank != 0) {
+            if (threadIdx.x < 128) {
+                float *dst = cluster.map_shared_rank(red, 0) + rank * 128 + threadIdx.x;
+                *dst = red[threadIdx.x];
+                uint32_t remote_bar;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(bar_red), "r"(0));
+                asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+            }
+        } else if (threadIdx.x < 128) {
+            uint32_t done = 0;
+            const unsigned long long t0 = wait_clock();
+            while (!done) {
+                asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                             : "=r"(done) : "r"(bar_red) : "memory");
+                if (!done && wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
+                    *abort_flag = 1;
+                    atomicCAS(&g_gemv_umma_error, 0, 7);
+                    break;
+                }
+            }
             float sum = red[threadIdx.x];
-            for (int r = 1; r < up.split; r++) sum += cluster.map_shared_rank(red, r)[threadIdx.x];
-            red[threadIdx.x] = sum; // only this thread reads or writes its entry of rank 0's buffer from here on
+            for (int r = 1; r < up.split; r++) sum += red[r * 128 + threadIdx.x];
+            red[threadIdx.x] = sum; // only this thread touches its entry from here on
         }
-        cluster.sync(); // the other ranks' shared memory stays alive until rank 0 has read it
     }
     if (rank == 0 && threadIdx.x < rows_here && !*abort_flag) {
         const int row = row_begin + threadIdx.x;
@@ -363,9 +411,16 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-size_t smem_for(int ks, int rb8, int ring, int stage_bytes) {
-    return 1024 + (size_t)(ks / 128) * 2048 + (size_t)ring * stage_bytes + (size_t)(128 - rb8) * 128 + (size_t)(ks / 32) * 4 + 128 * 4 +
-           (size_t)(2 * ring + 5) * 8 + 64;
+int b_region_bytes(int ks, int rb8) {
+    int b = (ks / 128) * 1024;
+    const int guard = (128 - rb8) * 128;
+    if (b < guard) b = guard;
+    return (b + 1023) & ~1023;
+}
+
+size_t smem_for(int ks, int rb8, int ring, int stage_bytes, int split) {
+    return 1024 + (size_t)ring * stage_bytes + b_region_bytes(ks, rb8) + (size_t)ring * rb8 * 16 + (size_t)(ks / 32) * 4 +
+           (size_t)split * 128 * 4 + (size_t)(2 * ring + 2 * TGROUPS + 2) * 8 + 64;
 }
 
 } // namespace
@@ -383,15 +438,16 @@ bool q8_gemv_umma_config(int M, int K, int sm_count, GemvUmmaConfig *cfg) {
     if (rb > 128) return false;
     const int rb8 = (rb + 7) & ~7;
     const int ks = K / split;
-    const int stage_bytes = 2 * rb8 * 128 + ((rb8 * 16 + 1023) & ~1023);
-    const size_t budget = 110 * 1024; // two CTAs (this layer's and the next one's) share an SM
+    const int stage_bytes = 2 * rb8 * 128;
+    const size_t budget = 112 * 1024; // two CTAs (this layer's and the next one's) share an SM
     int ring = 8;
-    while (ring > 2 && smem_for(ks, rb8, ring, stage_bytes) > budget) ring--;
-    if (smem_for(ks, rb8, ring, stage_bytes) > 200 * 1024) return false;
+    while (ring > 2 && smem_for(ks, rb8, ring, stage_bytes, split) > budget) ring--;
+    if (smem_for(ks, rb8, ring, stage_bytes, split) > 200 * 1024) return false;
     if (ring > ks / STAGE_K) ring = ks / STAGE_K < 2 ? 2 : ks / STAGE_K;
     cfg->split = split; cfg->clusters = clusters; cfg->rb = rb; cfg->rb8 = rb8; cfg->ks = ks; cfg->ring = ring;
     cfg->stage_bytes = stage_bytes;
-    cfg->smem_bytes = smem_for(ks, rb8, ring, stage_bytes);
+    cfg->b_bytes = b_region_bytes(ks, rb8);
+    cfg->smem_bytes = smem_for(ks, rb8, ring, stage_bytes, split);
     return true;
 }
 
@@ -420,7 +476,7 @@ cudaError_t launch_q8_gemv_umma(const MatmulParams &p, const GemvUmmaConfig &cfg
     UmmaGemvParams up{};
     up.p = p;
     up.rb = cfg.rb; up.rb8 = cfg.rb8; up.ks = cfg.ks; up.nstages_k = cfg.ks / STAGE_K; up.ring = cfg.ring;
-    up.stage_bytes = cfg.stage_bytes; up.split = cfg.split; up.lhs_constant = lhs_constant ? 1 : 0;
+    up.stage_bytes = cfg.stage_bytes; up.b_bytes = cfg.b_bytes; up.split = cfg.split; up.lhs_constant = lhs_constant ? 1 : 0;
     static size_t configured = 0;
     if (cfg.smem_bytes > configured) {
         cudaError_t e = cudaFuncSetAttribute(q8_gemv_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.smem_bytes);

@@ -19,7 +19,7 @@ cudaError_t gemv_take_error(int *site, cudaStream_t stream);
 
 // Q8_0H x f16 GEMV on tcgen05 kind::i8 (one activation vector, stacks == 1, K % 256 == 0).
 struct GemvUmmaConfig {
-    int split, clusters, rb, rb8, ks, ring, stage_bytes;
+    int split, clusters, rb, rb8, ks, ring, stage_bytes, b_bytes;
     size_t smem_bytes;
 };
 bool q8_gemv_umma_config(int M, int K, int sm_count, GemvUmmaConfig *cfg);
