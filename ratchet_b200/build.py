@@ -24,6 +24,7 @@ SOURCES = [
     "matmul_simt.cu",
     "gemv_q8_mma.cu",
     "gemv_q8_umma.cu",
+    "gemv_q4k_mma.cu",
     "dequant.cu",
     "gemm_umma.cu",
     "static_scratch.cu",

@@ -58,7 +58,7 @@ struct rt_buffer {
     uint64_t klass = 0; // bytes allocated
 };
 
-enum PlanKernel { PK_GEMM_SIMT, PK_GEMV_SIMT, PK_Q8_GEMV_MMA, PK_Q8_GEMV_UMMA, PK_GEMM_UMMA };
+enum PlanKernel { PK_GEMM_SIMT, PK_GEMV_SIMT, PK_Q8_GEMV_MMA, PK_Q8_GEMV_UMMA, PK_Q4K_GEMV, PK_GEMM_UMMA };
 
 struct rt_plan {
     rt_device *dev = nullptr;
@@ -266,6 +266,8 @@ rt_status rt_device_sync(rt_device *dev) {
     CUDA_TRY(gemv_umma_take_error(&site, dev->stream));
     if (site != 0)
         return fail(RT_ERR_CUDA, "a tensor-memory GEMV gave up a bounded wait (site " + std::to_string(site) + "): its output is incomplete");
+    CUDA_TRY(gemv_q4k_take_error(&site, dev->stream));
+    if (site != 0) return fail(RT_ERR_CUDA, "a Q4_K GEMV gave up waiting for its weight copies: its output is incomplete");
     CUDA_TRY(gemv_take_error(&site, dev->stream));
     if (site != 0) return fail(RT_ERR_CUDA, "a GEMV gave up waiting for its weight copies: its output is incomplete");
     return RT_OK;
@@ -447,6 +449,13 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
         else
         pl->name = std::string("q8_gemv_mma_") + (desc->lhs_dt == RT_Q8_0H ? "h" : "f") + "_nv" + std::to_string(pl->nv) +
                    "_split" + std::to_string(pl->split);
+    } else if (desc->lhs_dt == RT_Q4_K && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.N >= 1 && s.N <= 16 &&
+               (s.N == 1 || s.trans_rhs) && !empty && !force_simt() &&
+               q4k_gemv_pick_split(p.M, p.K, (int)s.N, dev->sm_count) > 0) {
+        pl->kernel = PK_Q4K_GEMV;
+        pl->nv = (int)s.N;
+        pl->split = q4k_gemv_pick_split(p.M, p.K, (int)s.N, dev->sm_count);
+        pl->name = std::string("q4k_gemv_mma_nv") + std::to_string(pl->nv) + "_split" + std::to_string(pl->split);
     } else if (umma_eligible(*desc, s)) {
         pl->kernel = PK_GEMM_UMMA;
         pl->lhs_is_q = s.trans_out;
@@ -546,6 +555,11 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
     switch (plan->kernel) {
     case PK_Q8_GEMV_MMA:
         e = launch_q8_gemv_mma(p, s.desc.lhs_dt == RT_Q8_0F, plan->nv, plan->split, (flags & RT_LAUNCH_LHS_CONSTANT) != 0, st);
+        break;
+    case PK_Q4K_GEMV:
+        if ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) % 16 != 0)
+            return fail(RT_ERR_ARG, "rt_matmul_launch: lhs and rhs must be 16-byte aligned");
+        e = launch_q4k_gemv(p, plan->nv, plan->split, (flags & RT_LAUNCH_LHS_CONSTANT) != 0, st);
         break;
     case PK_Q8_GEMV_UMMA:
         if ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) % 16 != 0)

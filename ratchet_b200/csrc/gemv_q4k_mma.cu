@@ -1,0 +1,328 @@
+// Q4_K GEMV / skinny GEMM for f16 activations: y[v][r] = sum_k W[r][k] * x[v][k], 1..16 vectors.
+//
+// The reference declares the Q4_K block (crates/ratchet-loader/src/k_quants.rs:95-103) but has no
+// kernel for it; this kernel gives the format the same decode path Q8_0 has.  W is raw GGUF
+// super-blocks: 144 bytes per 256 values = {f16 d, f16 dmin, 12 bytes of 6-bit (scale, min) pairs,
+// 128 bytes of nibbles}; value = (d*sc_j)*q - dmin*m_j for sub-block j of 32.
+//
+// Design (HBM-bound: 0.5625 bytes per weight):
+//  * a CTA owns 16 consecutive rows and a slice of K.  At entry one thread asks the TMA engine for
+//    the CTA's whole share (one bulk copy per row into padded shared-memory rows) before the kernel
+//    waits for its stream predecessor when the weights are constants; the activations are staged
+//    after that wait, permuted to the order in which nibbles leave a 32-bit word, together with
+//    their per-sub-block sums;
+//  * all threads decode the super-block headers once into a table of (s1, s3) per (row, sub-block)
+//    with s1 = d*sc and s3 = 1024*s1 + dmin*m;
+//  * 8 warps interleave over pairs of sub-blocks (one 8-byte load per row holds both: low and high
+//    nibbles).  A nibble q becomes the f16 value 1024+q with one shift and one AND/OR; a 16x32 tile
+//    meets the activations in two m16n8k16 tensor-core MMAs (f32 accumulate), and
+//    sum_k (s1*q - dmin*m) x = s1 * sum_k (1024+q) x - s3 * sum_k x;
+//  * warps are reduced through shared memory in a fixed order and K slices through distributed
+//    shared memory in rank order: deterministic results;
+//  * epilogue = the reference's: f16(acc) + bias in f16, optional fused GELU.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+#include "decode.cuh"
+#include "kernels.hpp"
+
+namespace cg = cooperative_groups;
+
+namespace rt {
+
+__device__ int g_gemv_q4k_error = 0;
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
+constexpr int ROWS = 16;
+constexpr int SB_BYTES = 144;
+constexpr unsigned long long WAIT_LIMIT_CYCLES = 4000000000ull;
+
+__device__ __forceinline__ void mma_m16n8k16_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// row stride of the staged super-blocks: a multiple of 16 that is 32 mod 128 (conflict-free 8-byte reads by 8 rows)
+__host__ __device__ inline int row_stride(int nsb) { const int b = nsb * SB_BYTES; return b + ((32 - b % 128) + 128) % 128; }
+
+struct Q4kLayout {
+    int codes, table, x, xsum, red, bar, total; // byte offsets
+};
+__host__ __device__ inline Q4kLayout layout(int nsb, int nv) {
+    Q4kLayout l;
+    l.codes = 0;
+    l.table = ROWS * row_stride(nsb);                       // float2 [ROWS][nsb*8 + 1]
+    l.x = l.table + ROWS * (nsb * 8 + 1) * 8;                // half [nv][nsb*256], permuted
+    const int cols = nv <= 8 ? 8 : 16;
+    l.xsum = l.x + ((nv * nsb * 256 * 2 + 15) & ~15);        // float [nsb*8][cols]
+    l.red = l.xsum + nsb * 8 * cols * 4;                     // float [WARPS][ROWS][cols]
+    l.bar = l.red + WARPS * ROWS * cols * 4;
+    l.total = l.bar + 16;
+    return l;
+}
+
+// NVG: groups of 8 activation vectors (1 or 2).  SPLIT: K is split over a cluster of gridDim.y CTAs.
+template <int NVG, bool SPLIT>
+__global__ void __launch_bounds__(THREADS) q4k_gemv_kernel(MatmulParams p, int nv, int sb_per_cta, int lhs_constant) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, c = lane & 3;
+    const int batch = blockIdx.z;
+    const int nsb_total = p.K >> 8;
+    const int split = SPLIT ? (int)blockIdx.y : 0;
+    const int sb_begin = split * sb_per_cta;
+    const int nsb = max(0, min(nsb_total, sb_begin + sb_per_cta) - sb_begin);
+    const Q4kLayout L = layout(sb_per_cta, nv);
+    const int rstride = row_stride(sb_per_cta);
+    uint8_t *codes_s = smem + L.codes;
+    float2 *table = reinterpret_cast<float2 *>(smem + L.table);
+    const int tstride = sb_per_cta * 8 + 1;
+    __half *x_s = reinterpret_cast<__half *>(smem + L.x);
+    float *xsum = reinterpret_cast<float *>(smem + L.xsum);
+    float *red = reinterpret_cast<float *>(smem + L.red);
+    const uint32_t bar_addr = smem_u32(smem + L.bar);
+    constexpr int COLS = NVG * 8;
+
+    const int row_base = blockIdx.x * ROWS;
+    const int rows_here = min(ROWS, p.M - row_base);
+    const uint8_t *w = (const uint8_t *)p.lhs + (long long)(batch % p.lhs_stack) * p.M * nsb_total * SB_BYTES;
+
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_addr) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!lhs_constant) asm volatile("griddepcontrol.wait;" ::: "memory");
+    __syncthreads();
+
+    const uint32_t row_bytes = (uint32_t)nsb * SB_BYTES;
+    if (threadIdx.x == 0 && row_bytes > 0) {
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_addr), "r"(row_bytes * (uint32_t)rows_here) : "memory");
+        for (int r = 0; r < rows_here; r++) {
+            const uint8_t *src = w + ((long long)(row_base + r) * nsb_total + sb_begin) * SB_BYTES;
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(codes_s + r * rstride)), "l"(src), "r"(row_bytes), "r"(bar_addr) : "memory");
+        }
+    }
+    if (lhs_constant) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // ---- activations of this K slice: permuted copy and per-sub-block sums
+    // Within every 8 consecutive elements the order becomes 0,2,1,3,4,6,5,7: the order in which the
+    // nibbles of two 32-bit words leave the AND / shift sequence below as f16 pairs.
+    const int kslice = nsb * 256;
+    const long long rbatch = batch % p.rhs_stack;
+    for (int i = threadIdx.x; i < nv * (kslice / 8); i += THREADS) {
+        const int v = i / (kslice / 8), o = i - v * (kslice / 8);
+        const __half *src = (const __half *)p.rhs + (rbatch * nv + v) * (long long)p.K + (long long)sb_begin * 256 + o * 8;
+        const uint4 raw = *reinterpret_cast<const uint4 *>(src);
+        const __half *h = reinterpret_cast<const __half *>(&raw);
+        __half out[8] = {h[0], h[2], h[1], h[3], h[4], h[6], h[5], h[7]};
+        *reinterpret_cast<uint4 *>(x_s + (long long)v * sb_per_cta * 256 + o * 8) = *reinterpret_cast<const uint4 *>(out);
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) s += __half2float(h[j]);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        if ((o & 3) == 0) xsum[(o >> 2) * COLS + v] = s; // four consecutive 8-element groups = one sub-block
+    }
+    // vectors past nv (the MMA has 8 or 16 columns) read vector nv-1 and a zero sum is not needed: their outputs are dropped
+
+    // ---- wait for the super-blocks (bounded)
+    bool ok = true;
+    if (row_bytes > 0 && !mbar_try_wait(bar_addr, 0)) {
+        const unsigned long long t0 = (unsigned long long)clock64();
+        while (!mbar_try_wait(bar_addr, 0)) {
+            if ((unsigned long long)clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                ok = false;
+                atomicCAS(&g_gemv_q4k_error, 0, 1);
+                break;
+            }
+        }
+    }
+
+    // ---- header table: (s1, s3) per (row, sub-block)
+    if (ok) {
+        const int r = threadIdx.x >> 4;
+        for (int i = threadIdx.x & 15; i < nsb * 8; i += 16) {
+            const int sb = i >> 3, j = i & 7;
+            float2 e = make_float2(0.f, 0.f);
+            if (r < rows_here) {
+                const uint8_t *blk = codes_s + r * rstride + sb * SB_BYTES;
+                const float d = __half2float(*reinterpret_cast<const __half *>(blk));
+                const float dmin = __half2float(*reinterpret_cast<const __half *>(blk + 2));
+                int sc, m;
+                q4k_scale_min(j, blk + 4, sc, m);
+                const float s1 = d * (float)sc;
+                e = make_float2(s1, fmaf(1024.f, s1, dmin * (float)m));
+            }
+            table[r * tstride + i] = e;
+        }
+    }
+    __syncthreads();
+
+    float acc[NVG][4];
+#pragma unroll
+    for (int n = 0; n < NVG; n++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[n][i] = 0.f;
+
+    if (ok) {
+        const uint8_t *qa = codes_s + g * rstride + 16 + c * 8;
+        const uint8_t *qb = codes_s + (g + 8) * rstride + 16 + c * 8;
+        const float2 *ta = table + g * tstride, *tb = table + (g + 8) * tstride;
+        // B fragment column n = g <-> activation vector (clamped); one pointer per group of 8 vectors
+        const __half *xl[NVG];
+#pragma unroll
+        for (int n = 0; n < NVG; n++) xl[n] = x_s + (long long)min(n * 8 + g, nv - 1) * sb_per_cta * 256 + c * 8;
+        const uint32_t magic = 0x64006400u, mask = 0x000F000Fu;
+#pragma unroll 1
+        for (int pr = warp; pr < nsb * 4; pr += WARPS) { // a pair = sub-blocks 2*pr (low nibbles) and 2*pr+1 (high nibbles)
+            const int sb = pr >> 2, jp = pr & 3;
+            const int off = sb * SB_BYTES + jp * 32;
+            const uint2 wa = *reinterpret_cast<const uint2 *>(qa + off);
+            const uint2 wb = *reinterpret_cast<const uint2 *>(qb + off);
+#pragma unroll
+            for (int hl = 0; hl < 2; hl++) { // 0: low nibbles, 1: high nibbles
+                const int sub = pr * 2 + hl;  // sub-block index inside the slice
+                const int sh = hl * 4;
+                uint32_t fa[4], fb[4];
+                fa[0] = ((wa.x >> sh) & mask) | magic;        // row g   : elements 0,2
+                fa[2] = ((wa.x >> (sh + 8)) & mask) | magic;  // row g   : elements 1,3
+                fa[1] = ((wb.x >> sh) & mask) | magic;        // row g+8 : elements 0,2
+                fa[3] = ((wb.x >> (sh + 8)) & mask) | magic;
+                fb[0] = ((wa.y >> sh) & mask) | magic;        // elements 4,6
+                fb[2] = ((wa.y >> (sh + 8)) & mask) | magic;  // elements 5,7
+                fb[1] = ((wb.y >> sh) & mask) | magic;
+                fb[3] = ((wb.y >> (sh + 8)) & mask) | magic;
+                const float2 ea = ta[sub], eb = tb[sub];
+#pragma unroll
+                for (int n = 0; n < NVG; n++) {
+                    const uint4 xv = *reinterpret_cast<const uint4 *>(xl[n] + sub * 32);
+                    float t[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_m16n8k16_f16(t, fa, xv.x, xv.y);
+                    mma_m16n8k16_f16(t, fb, xv.z, xv.w);
+                    const float2 xs2 = *reinterpret_cast<const float2 *>(xsum + sub * COLS + n * 8 + 2 * c);
+                    acc[n][0] += ea.x * t[0] - ea.y * xs2.x;
+                    acc[n][1] += ea.x * t[1] - ea.y * xs2.y;
+                    acc[n][2] += eb.x * t[2] - eb.y * xs2.x;
+                    acc[n][3] += eb.x * t[3] - eb.y * xs2.y;
+                }
+            }
+        }
+    }
+
+    // C fragment: acc[n][0..1] -> (row g, cols n*8 + 2c, +1); acc[n][2..3] -> (row g+8, same cols)
+#pragma unroll
+    for (int n = 0; n < NVG; n++) {
+        red[(warp * ROWS + g) * COLS + n * 8 + 2 * c] = acc[n][0];
+        red[(warp * ROWS + g) * COLS + n * 8 + 2 * c + 1] = acc[n][1];
+        red[(warp * ROWS + g + 8) * COLS + n * 8 + 2 * c] = acc[n][2];
+        red[(warp * ROWS + g + 8) * COLS + n * 8 + 2 * c + 1] = acc[n][3];
+    }
+    __syncthreads();
+    const int r = threadIdx.x >> 4, v = threadIdx.x & 15; // one (row, vector) per thread
+    float sum = 0.f;
+    if (v < COLS) {
+#pragma unroll
+        for (int w8 = 0; w8 < WARPS; w8++) sum += red[(w8 * ROWS + r) * COLS + v];
+    }
+    if (SPLIT) {
+        cg::cluster_group cluster = cg::this_cluster();
+        __syncthreads();
+        if (v < COLS) red[r * COLS + v] = sum;
+        cluster.sync();
+        if (cluster.block_rank() == 0 && v < COLS) {
+            const unsigned n = cluster.num_blocks();
+            for (unsigned k = 1; k < n; k++) sum += cluster.map_shared_rank(red, k)[r * COLS + v];
+        }
+        cluster.sync(); // keep every CTA's shared memory alive until rank 0 has read it
+        if (cluster.block_rank() != 0) return;
+    }
+    if (v < nv && ok) {
+        const int row = row_base + r;
+        if (row < p.M) {
+            const bool has_bias = p.bias_mode != BIAS_NONE;
+            float bias = 0.f;
+            if (has_bias) bias = load_bias(p.bias, p.bias_dt, p.bias_mode == BIAS_PER_M ? row : v);
+            const __half o = epilogue_value<__half>(sum, has_bias, bias, p.epilogue);
+            const long long ob = (long long)batch * p.M * nv;
+            ((__half *)p.out)[p.trans_out ? ob + (long long)v * p.M + row : ob + (long long)row * nv + v] = o;
+        }
+    }
+}
+
+template <int NVG>
+cudaError_t launch_g(const MatmulParams &p, int nv, int split, bool lhs_constant, cudaStream_t stream) {
+    const int nsb_total = p.K / 256;
+    const int spc = (nsb_total + split - 1) / split;
+    const size_t smem = (size_t)layout(spc, nv).total;
+    auto kernel = split == 1 ? q4k_gemv_kernel<NVG, false> : q4k_gemv_kernel<NVG, true>;
+    static size_t configured[2] = {0, 0};
+    if (smem > 48 * 1024 && configured[split != 1] < smem) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured[split != 1] = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((p.M + ROWS - 1) / ROWS, split, p.stacks);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    n++;
+    if (split > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = split;
+        attr[n].val.clusterDim.z = 1;
+        n++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, p, nv, spc, lhs_constant ? 1 : 0);
+}
+
+} // namespace
+
+// K split over a cluster (1, 2, 4 or 8), or 0 when the shape does not fit the kernel.
+int q4k_gemv_pick_split(int M, int K, int nv, int sm_count) {
+    if (K < 256 || K % 256 != 0 || nv < 1 || nv > 16 || M < 1) return 0;
+    const int nsb = K / 256;
+    const int groups = (M + ROWS - 1) / ROWS;
+    const size_t target = 56 * 1024, limit = 200 * 1024; // four CTAs per SM
+    int split = 1;
+    while (split < 8 && (size_t)layout((nsb + split - 1) / split, nv).total > target) split *= 2;
+    while (split < 8 && groups * split < 3 * sm_count && nsb / (split * 2) >= 2) split *= 2;
+    if ((size_t)layout((nsb + split - 1) / split, nv).total > limit) return 0;
+    return split;
+}
+
+cudaError_t launch_q4k_gemv(const MatmulParams &p, int nv, int split, bool lhs_constant, cudaStream_t stream) {
+    return nv <= 8 ? launch_g<1>(p, nv, split, lhs_constant, stream) : launch_g<2>(p, nv, split, lhs_constant, stream);
+}
+
+cudaError_t gemv_q4k_take_error(int *site, cudaStream_t stream) {
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbolAsync(site, g_gemv_q4k_error, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return e;
+    e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return e;
+    if (*site != 0) e = cudaMemcpyToSymbolAsync(g_gemv_q4k_error, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream);
+    return e;
+}
+
+} // namespace rt

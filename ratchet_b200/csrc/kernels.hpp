@@ -26,6 +26,11 @@ bool q8_gemv_umma_config(int M, int K, int sm_count, GemvUmmaConfig *cfg);
 cudaError_t launch_q8_gemv_umma(const MatmulParams &p, const GemvUmmaConfig &cfg, bool lhs_constant, cudaStream_t stream);
 cudaError_t gemv_umma_take_error(int *site, cudaStream_t stream);
 
+// Q4_K x f16 GEMV / skinny GEMM on warp MMAs.  nv = columns of op(rhs), 1..16 (rhs stored [nv][K]).
+int q4k_gemv_pick_split(int M, int K, int nv, int sm_count);
+cudaError_t launch_q4k_gemv(const MatmulParams &p, int nv, int split, bool lhs_constant, cudaStream_t stream);
+cudaError_t gemv_q4k_take_error(int *site, cudaStream_t stream);
+
 // Tensor-core GEMM (tcgen05): D[R][S] = P[R][K] . Q[S][K]^T, 16-bit K-major operands, bias along S.
 // Several destinations for one result: see UmmaParams in gemm_umma.cu.
 struct UmmaScatter {

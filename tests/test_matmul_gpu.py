@@ -203,6 +203,20 @@ def test_q4k_phi3_shapes(gpu, M):
     check_problem(Problem(Q4K, F16, (8192, 3072), (1, M, 3072), (False, True, True), seed=104, w_std=0.02), gpu)
 
 
+def test_q4k_gemv_shapes_and_vectors(gpu):
+    """The streaming Q4_K kernel: ragged rows, K slices over a cluster, 1..16 activation vectors, both output orders."""
+    for N, K in [(16, 256), (37, 512), (1000, 1024), (3072, 8192), (5, 4096)]:
+        _, kernel = check_problem(Problem(Q4K, F16, (N, K), (1, K), (False, True, True), bias=True, seed=N + K, w_std=0.02), gpu)
+        assert kernel.startswith("q4k_gemv_mma"), kernel
+    for nv in (2, 7, 8, 9, 16):
+        for to in (True, False):
+            _, kernel = check_problem(Problem(Q4K, F16, (520, 1536), (1, nv, 1536), (False, True, to), bias=True, epilogue=1,
+                                              seed=90 + nv, w_std=0.02), gpu)
+            assert f"nv{nv}" in kernel, kernel
+    check_problem(Problem(Q4K, F16, (3, 64, 512), (3, 1, 512), (False, True, True), seed=91, w_std=0.02), gpu)  # batched weights
+    check_problem(Problem(Q4K, F16, (64, 512), (4, 1, 512), (False, True, True), seed=92, w_std=0.02), gpu)     # broadcast weight
+
+
 def test_q4k_forms(gpu):
     check_problem(Problem(Q4K, F16, (40, 256), (1, 256), (False, True, True), bias=True, seed=81, w_std=0.02), gpu)
     check_problem(Problem(Q4K, F16, (2, 33, 512), (2, 512, 7), (False, False, False), seed=82, w_std=0.02), gpu)
