@@ -41,6 +41,7 @@ METRIC = "Q8_0 GEMV effective bandwidth (Phi-2 MLP shapes, decode)"
 UNIT = "GB/s"
 LAYERS = 32
 D_MODEL, D_FF = 2560, 10240
+NCU_TRAFFIC_PER_GEMV = 27_900_000     # measured DRAM bytes per launch (27.89 MB and 27.91 MB for the two shapes)
 BYTES_PER_GEMV = D_FF * D_MODEL + 2 * (D_FF * D_MODEL // 32) + 2 * D_MODEL + 2 * D_FF  # 27,878,400
 WORKLOAD = "phi2_mlp_q8_0_gemv_decode"
 
@@ -488,7 +489,8 @@ def main():
                        "kernels": kernel_names},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "launch_us": launch_us, "bytes_per_launch": BYTES_PER_GEMV,
-                         "traffic": None},
+                         "traffic": NCU_TRAFFIC_PER_GEMV, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, "
+                         "mean of the two shapes, from the capture summarised in profiles/q8_gemv_umma_phi2_decode.md"},
             "e2e": {"value": world * step_bytes / (e2e_ms_step * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms_step,
                     "h2d_bytes_per_step": int(x_pin.nbytes), "d2h_bytes_per_step": int(y_pin.nbytes)},
             "gpu_launches": args.steps * launches_per_step,

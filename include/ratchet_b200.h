@@ -61,7 +61,8 @@ typedef enum rt_epilogue {
     /* bias add, then the tanh GELU of crates/ratchet-core/src/ops/unary.rs:97-119 evaluated
      * in f32 on the value rounded to the output dtype, then rounded again: the chain
      * fc1 -> full() -> gelu() -> cast() of crates/ratchet-models/src/whisper/mlp.rs:18-22
-     * fused into the producing kernel. */
+     * fused into the producing kernel.  bf16 outputs (which the reference does not have) are
+     * the exception: bias and GELU act on the f32 accumulator and the result is rounded once. */
     RT_EPILOGUE_GELU_TANH = 1
 } rt_epilogue;
 
