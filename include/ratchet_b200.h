@@ -243,12 +243,18 @@ typedef struct rt_dispatch {
  * dispatched in one call in list order on one stream (the reference records them into one
  * compute pass and submits once).  With `use_graph` != 0 the list is captured once into a CUDA
  * graph at creation (on a private stream; capturing executes nothing) and each dispatch is one
- * graph launch.  Plans and buffers must outlive the executable. */
+ * graph launch.  A list of two or more single-vector Q8_0H GEMVs whose weights are all flagged
+ * RT_LAUNCH_LHS_CONSTANT becomes ONE persistent kernel instead (grid barriers between the nodes,
+ * weights of later nodes streamed while earlier ones compute; same bits as node-by-node dispatch);
+ * only one dispatch of such an executable may be in flight at a time.  Plans and buffers must
+ * outlive the executable. */
 rt_status rt_executable_create(rt_device *dev, const rt_dispatch *nodes, int32_t n_nodes, int32_t use_graph, rt_executable **exe);
 rt_status rt_executable_dispatch(rt_executable *exe, void *stream);
 rt_status rt_executable_destroy(rt_executable *exe);
 /* Kernel launches one dispatch issues (graph or not). */
 int32_t rt_executable_launches(const rt_executable *exe);
+/* How the list is dispatched: "nodes", "graph", or the persistent kernel's name. */
+const char *rt_executable_kernel(const rt_executable *exe);
 
 /* Linear-shaped Q8_0 GEMM for callers that must not allocate device memory: out[rows][n] =
  * x[rows][k] . W[n][k]^T (+ bias[n]) (+ GELU), W as RT_Q8_0H, x / bias / out f16 -- the node

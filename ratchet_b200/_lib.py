@@ -145,6 +145,7 @@ def load() -> ctypes.CDLL:
         "rt_executable_dispatch": (c_int32, [V, V]),
         "rt_executable_destroy": (c_int32, [V]),
         "rt_executable_launches": (c_int32, [V]),
+        "rt_executable_kernel": (c_char_p, [V]),
         "rt_linear_q8_0_static_scratch": (c_int32, [V, V, V, V, V, c_int64, c_int64, c_int64, c_int32, V]),
         "rt_comm_unique_id": (c_int32, [V]),
         "rt_comm_init_rank": (c_int32, [V, c_int32, c_int32, V, c_int32, POINTER(V)]),

@@ -23,7 +23,7 @@ SOURCES = [
     "api.cu",
     "matmul_simt.cu",
     "gemv_q8_mma.cu",
-    "gemv_q8_umma.cu",
+    "gemv_q8_umma.cu", "gemv_q8_chain.cu",
     "gemv_q4k_mma.cu",
     "dequant.cu",
     "gemm_umma.cu",

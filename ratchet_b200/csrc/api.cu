@@ -90,6 +90,9 @@ struct rt_executable {
     std::vector<rt_dispatch> nodes;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
+    GemvChain *chain = nullptr; // the whole node list as one persistent kernel (gemv_q8_chain.cu)
+    bool chain_refused = false; // its launch was refused once: dispatch node by node from then on
+    std::string how = "nodes";
     int launches = 0;
 };
 
@@ -266,6 +269,9 @@ rt_status rt_device_sync(rt_device *dev) {
     CUDA_TRY(gemv_umma_take_error(&site, dev->stream));
     if (site != 0)
         return fail(RT_ERR_CUDA, "a tensor-memory GEMV gave up a bounded wait (site " + std::to_string(site) + "): its output is incomplete");
+    CUDA_TRY(gemv_chain_take_error(&site, dev->stream));
+    if (site != 0)
+        return fail(RT_ERR_CUDA, "a GEMV chain gave up a bounded wait (site " + std::to_string(site) + "): its outputs are incomplete");
     CUDA_TRY(gemv_q4k_take_error(&site, dev->stream));
     if (site != 0) return fail(RT_ERR_CUDA, "a Q4_K GEMV gave up waiting for its weight copies: its output is incomplete");
     CUDA_TRY(gemv_take_error(&site, dev->stream));
@@ -369,6 +375,12 @@ rt_status rt_host_free(void *ptr) {
 }
 
 /* ------------------------------------------------------------------ compile + dispatch */
+
+// RT_GEMV_CHAIN=0 keeps executables on one launch per node (a debugging and A/B timing switch).
+static bool chain_enabled() {
+    const char *v = getenv("RT_GEMV_CHAIN");
+    return !(v && v[0] == '0');
+}
 
 // RT_FORCE_KERNEL=simt keeps every node on the CUDA-core kernels (a debugging switch in the
 // spirit of the reference's RATCHET_* variables, gpu/device.rs:92-99).
@@ -521,6 +533,16 @@ rt_status rt_plan_spec(const rt_plan *plan, rt_gemm_spec *spec) {
 const char *rt_plan_kernel(const rt_plan *plan) { return plan ? plan->name.c_str() : ""; }
 int32_t rt_plan_launches(const rt_plan *plan) { return plan ? plan->launches : 0; }
 
+static MatmulParams bound_params(const rt_plan *plan, const void *lhs, const void *rhs, const void *bias, void *out) {
+    MatmulParams p = plan->params;
+    p.lhs = lhs;
+    p.lhs_scales = plan->lhs_scale_offset ? (const void *)((const char *)lhs + plan->lhs_scale_offset) : nullptr;
+    p.rhs = rhs;
+    p.bias = plan->spec.has_bias ? bias : nullptr;
+    p.out = out;
+    return p;
+}
+
 rt_status rt_matmul_launch(rt_plan *plan, const void *lhs, const void *rhs, const void *bias, void *out, void *stream) {
     return rt_matmul_launch_ex(plan, lhs, rhs, bias, out, stream, nullptr);
 }
@@ -545,12 +567,7 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
         return fail(RT_ERR_INVARIANT, "Matmul is never in place: out aliases an operand");
     CUDA_TRY(cudaSetDevice(plan->dev->ordinal));
     cudaStream_t st = stream ? (cudaStream_t)stream : plan->dev->stream;
-    MatmulParams p = plan->params;
-    p.lhs = lhs;
-    p.lhs_scales = plan->lhs_scale_offset ? (const void *)((const char *)lhs + plan->lhs_scale_offset) : nullptr;
-    p.rhs = rhs;
-    p.bias = s.has_bias ? bias : nullptr;
-    p.out = out;
+    MatmulParams p = bound_params(plan, lhs, rhs, bias, out);
     cudaError_t e = cudaSuccess;
     switch (plan->kernel) {
     case PK_Q8_GEMV_MMA:
@@ -632,7 +649,35 @@ rt_status rt_executable_create(rt_device *dev, const rt_dispatch *nodes, int32_t
         x->nodes.push_back(nodes[i]);
         x->launches += nodes[i].plan->launches;
     }
+    // A list of tensor-memory Q8_0 GEMVs over constant weights runs as one persistent kernel.
+    if (use_graph && n_nodes >= 2 && chain_enabled()) {
+        bool all = true;
+        std::vector<MatmulParams> ps;
+        for (const rt_dispatch &n : x->nodes) {
+            if (n.plan->kernel != PK_Q8_GEMV_UMMA || !(n.opts.flags & RT_LAUNCH_LHS_CONSTANT) || n.opts.n_out > 0 || !n.lhs || !n.rhs ||
+                !n.out || (n.plan->spec.has_bias && !n.bias)) {
+                all = false;
+                break;
+            }
+            ps.push_back(bound_params(n.plan, n.lhs, n.rhs, n.bias, n.out));
+        }
+        if (all) {
+            std::string why;
+            cudaError_t e = gemv_chain_create(ps, dev->ordinal, dev->sm_count, &x->chain, &why);
+            if (e != cudaSuccess) {
+                delete x;
+                return fail(RT_ERR_CUDA, std::string("gemv_chain_create: ") + cudaGetErrorString(e));
+            }
+            if (x->chain) {
+                x->how = gemv_chain_name(x->chain);
+                x->launches = 1;
+                *exe = x;
+                return RT_OK;
+            }
+        }
+    }
     if (use_graph && x->launches > 0) {
+        x->how = "graph";
         cudaError_t e = cudaSetDevice(dev->ordinal);
         cudaStream_t cap = nullptr;
         if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking);
@@ -659,6 +704,17 @@ rt_status rt_executable_create(rt_device *dev, const rt_dispatch *nodes, int32_t
 rt_status rt_executable_dispatch(rt_executable *exe, void *stream) {
     if (!exe) return fail(RT_ERR_ARG, "rt_executable_dispatch: null executable");
     cudaStream_t st = stream ? (cudaStream_t)stream : exe->dev->stream;
+    if (exe->chain && !exe->chain_refused) {
+        CUDA_TRY(cudaSetDevice(exe->dev->ordinal));
+        cudaError_t e = gemv_chain_launch(exe->chain, st);
+        if (e == cudaSuccess) return RT_OK;
+        // a refused launch (e.g. the cooperative grid does not fit beside other work) is not sticky
+        cudaGetLastError();
+        exe->chain_refused = true;
+        exe->how = std::string("nodes (chain launch refused: ") + cudaGetErrorString(e) + ")";
+        exe->launches = 0;
+        for (auto &n : exe->nodes) exe->launches += n.plan->launches;
+    }
     if (exe->exec) {
         CUDA_TRY(cudaSetDevice(exe->dev->ordinal));
         CUDA_TRY(cudaGraphLaunch(exe->exec, st));
@@ -671,11 +727,13 @@ rt_status rt_executable_destroy(rt_executable *exe) {
     if (!exe) return RT_OK;
     if (exe->exec) cudaGraphExecDestroy(exe->exec);
     if (exe->graph) cudaGraphDestroy(exe->graph);
+    if (exe->chain) gemv_chain_destroy(exe->chain);
     delete exe;
     return RT_OK;
 }
 
 int32_t rt_executable_launches(const rt_executable *exe) { return exe ? exe->launches : 0; }
+const char *rt_executable_kernel(const rt_executable *exe) { return exe ? exe->how.c_str() : ""; }
 
 rt_status rt_dequantize_device(rt_device *dev, rt_dtype dt, uint64_t numel, const void *src, void *dst, void *stream) {
     if (!dev || !src || !dst) return fail(RT_ERR_ARG, "rt_dequantize_device: null argument");

@@ -20,11 +20,12 @@
 //  * a CTA owns a contiguous range of at most 128 rows (N / #CTAs, so all SMs get equal bytes) and,
 //    for fat weights, a slice of K: the CTAs of a thread-block cluster split K and rank 0 adds the
 //    slices' row sums through distributed shared memory in rank order (deterministic);
-//  * the producer warp asks for its whole share to be prefetched into L2 at once and then keeps a
-//    small ring of stages full, and it does so before the kernel waits for its stream predecessor
-//    when the caller states that the weights are constants (programmatic dependent launch).  A CTA
-//    needs less than half of an SM's shared memory and half of its tensor memory, so the next
-//    layer's CTAs are resident and prefetching while this layer computes.
+//  * the producer warp keeps a small ring of stages full, and it starts before the kernel waits for
+//    its stream predecessor when the caller states that the weights are constants (programmatic
+//    dependent launch).  A CTA needs less than half of an SM's shared memory and half of its tensor
+//    memory, so the next layer's CTAs are resident with their first stages loaded while this layer
+//    computes.  (Asking for the whole share with cp.async.bulk.prefetch.L2 as well measured 3 %
+//    slower: the requests compete with the running layer's refills.)
 // Every wait is bounded (about two seconds of SM cycles); on expiry the kernel sets a device flag,
 // leaves its loops, frees tensor memory and returns; the next rt_device_sync reports it.
 #include <cooperative_groups.h>
@@ -32,6 +33,7 @@
 
 #include "common.cuh"
 #include "kernels.hpp"
+#include "umma_gemv.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -46,7 +48,6 @@ constexpr int STAGE_K = 256;          // bytes of K per ring stage = 8 Q8_0 bloc
 constexpr int TMEM_COLS = 256;        // half of an SM's tensor memory
 constexpr int TG_COLS = 32;           // tensor-memory columns per stage (see the MMA issuer)
 constexpr int TGROUPS = TMEM_COLS / TG_COLS;
-constexpr unsigned long long WAIT_LIMIT_CYCLES = 4000000000ull;
 
 struct UmmaGemvParams {
     MatmulParams p;
@@ -61,73 +62,11 @@ struct UmmaGemvParams {
     int lhs_constant;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long wait_clock() { return (unsigned long long)clock64(); }
+using namespace umma_gemv;
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = wait_clock();
-    while (true) {
-#pragma unroll 1
-        for (int i = 0; i < 32; i++)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
-            *abort_flag = 1;
-            atomicCAS(&g_gemv_umma_error, 0, site);
-            return false;
-        }
-    }
+    return mbar_wait_flag(bar, parity, abort_flag, site, &g_gemv_umma_error);
 }
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-
-// K-major operand tile, 128-byte swizzle, 8-row groups `group_stride` bytes apart.  The digit tiles
-// hold 8 rows and use a stride of 0: rows 8..15 of the N = 16 operand repeat rows 0..7, which only
-// duplicates accumulator columns that the next block overwrites (see the MMA issuer).
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t group_stride) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(group_stride >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-
-__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
-    // the predicate is false: the accumulator slot is overwritten, every block starts from zero
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}\n"
-                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-                 : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // Shared-memory map (all offsets from a 1024-byte aligned base):
 //   [ring: stages of {A0: rb8 x 128, A1: rb8 x 128}][B digits: (ks/128) tiles of 8 rows x 128 B, at least
@@ -190,14 +129,6 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
         if (!up.lhs_constant) asm volatile("griddepcontrol.wait;" ::: "memory");
-        // whole share into L2 now (eight rows per request), so the depth of the HBM queue does not depend on the ring
-        for (int r = lane * 8; r < rows_here; r += 32 * 8) {
-            const int nr = min(8, rows_here - r);
-            for (int i = 0; i < nr; i++) {
-                const char *src = (const char *)p.lhs + (long long)(row_begin + r + i) * p.K + k_begin;
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(up.ks) : "memory");
-            }
-        }
         if (lane == 0) {
             int slot = 0;
             uint32_t phase = 0;
@@ -272,41 +203,7 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int it = 0; it < MAX_IT; it++) {
                 const int blk = (et >> 2) + it * 32;
                 if (blk >= up.ks / 32) break;
-                const uint4 raw = pre[it];
-                const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float2 f = __half22float2(h2[i]);
-                    v[2 * i] = f.x;
-                    v[2 * i + 1] = f.y;
-                }
-                float amax = 0.f;
-#pragma unroll
-                for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-                // amax < 2^(E-126) for its exponent field E: scale it below 2^14
-                const int E = (int)((__float_as_uint(amax) >> 23) & 0xFFu);
-                const float scale = amax > 0.f ? __uint_as_float((uint32_t)(140 - E + 127) << 23) : 0.f;
-                const float inv = amax > 0.f ? __uint_as_float((uint32_t)(E - 13) << 23) : 0.f;
-                uint32_t hi_w[2] = {0u, 0u}, lo_w[2] = {0u, 0u};
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    int m = __float2int_rn(v[i] * scale);
-                    m = max(-16383, min(16383, m));
-                    const int hi = (m + 128) >> 8;
-                    const int lo = m - (hi << 8);
-                    hi_w[i >> 2] |= (uint32_t)(hi & 0xFF) << (8 * (i & 3));
-                    lo_w[i >> 2] |= (uint32_t)(lo & 0xFF) << (8 * (i & 3));
-                }
-                // tile of k-step blk/4; byte position of these 8 elements in the 128-byte row; 16-byte chunks XOR the row index
-                uint8_t *tile = b_tiles + (size_t)(blk >> 2) * 1024;
-                const int kpos = (blk & 3) * 32 + sub * 8;
-                const int chunk = kpos >> 4, within = kpos & 15;
-                *reinterpret_cast<uint2 *>(tile + 0 * 128 + ((chunk ^ 0) << 4) + within) = make_uint2(hi_w[0], hi_w[1]);
-                *reinterpret_cast<uint2 *>(tile + 1 * 128 + ((chunk ^ 1) << 4) + within) = make_uint2(lo_w[0], lo_w[1]);
-                if (sub == 0) xs[blk] = inv;
+                digits_of_quarter_block(pre[it], blk, sub, b_tiles, xs);
             }
         }
         // the MMAs read the tiles through the async proxy
@@ -337,8 +234,7 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 const float d = (j & 1) ? __high2float(d2[j >> 1]) : __low2float(d2[j >> 1]);
-                const float t = fmaf(256.f, (float)dv[2 * j], (float)dv[2 * j + 1]);
-                acc = fmaf(d * xsv[j], t, acc);
+                acc = add_block(acc, d, xsv[j], dv[2 * j], dv[2 * j + 1]);
             }
             if (++slot == up.ring) { slot = 0; phase ^= 1; }
             if (++tg == TGROUPS) { tg = 0; tphase ^= 1; }
@@ -395,22 +291,6 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
-            qres != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
-
 int b_region_bytes(int ks, int rb8) {
     int b = (ks / 128) * 1024;
     const int guard = (128 - rb8) * 128;
@@ -428,7 +308,7 @@ size_t smem_for(int ks, int rb8, int ring, int stage_bytes, int split) {
 // Work split for a [M][K] Q8_0H weight: K slices per cluster, rows per cluster, ring depth.  False when
 // the shape is not one this kernel takes (the plan then uses the warp-MMA GEMV).
 bool q8_gemv_umma_config(int M, int K, int sm_count, GemvUmmaConfig *cfg) {
-    if (M < 1 || K < 256 || K % 256 != 0 || !encode_fn()) return false;
+    if (M < 1 || K < 256 || K % 256 != 0 || !encode_tiled_fn()) return false;
     int split = 1;
     while (split < 8 && (K / split > 3072 || (K / split) % 256 != 0)) split *= 2;
     if (K % (split * 256) != 0 || K / split > 3072) return false;
@@ -458,7 +338,7 @@ cudaError_t launch_q8_gemv_umma(const MatmulParams &p, const GemvUmmaConfig &cfg
         cuuint64_t strides[1] = {(cuuint64_t)p.K};
         cuuint32_t box[2] = {128, (cuuint32_t)cfg.rb};
         cuuint32_t estr[2] = {1, 1};
-        if (encode_fn()(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(p.lhs), dims, strides, box, estr,
+        if (encode_tiled_fn()(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(p.lhs), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
@@ -468,7 +348,7 @@ cudaError_t launch_q8_gemv_umma(const MatmulParams &p, const GemvUmmaConfig &cfg
         cuuint64_t strides[1] = {(cuuint64_t)(p.K / 32) * 2};
         cuuint32_t box[2] = {8, (cuuint32_t)cfg.rb};
         cuuint32_t estr[2] = {1, 1};
-        if (encode_fn()(&map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(p.lhs_scales), dims, strides, box, estr,
+        if (encode_tiled_fn()(&map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(p.lhs_scales), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;

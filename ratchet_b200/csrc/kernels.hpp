@@ -1,5 +1,7 @@
 // Launchers of the device kernels (one translation unit each).
 #pragma once
+#include <string>
+#include <vector>
 #include <cuda_runtime.h>
 
 #include "common.cuh"
@@ -25,6 +27,16 @@ struct GemvUmmaConfig {
 bool q8_gemv_umma_config(int M, int K, int sm_count, GemvUmmaConfig *cfg);
 cudaError_t launch_q8_gemv_umma(const MatmulParams &p, const GemvUmmaConfig &cfg, bool lhs_constant, cudaStream_t stream);
 cudaError_t gemv_umma_take_error(int *site, cudaStream_t stream);
+
+// A list of such GEMVs (constant weights, node l+1 may read what node l wrote) as one persistent
+// cooperative kernel with grid barriers between the nodes.  gemv_chain_create returns cudaSuccess
+// with *out == nullptr and a reason when the list is not one the kernel takes.
+struct GemvChain;
+cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device, int sm_count, GemvChain **out, std::string *why);
+cudaError_t gemv_chain_launch(GemvChain *chain, cudaStream_t stream);
+void gemv_chain_destroy(GemvChain *chain);
+const char *gemv_chain_name(const GemvChain *chain);
+cudaError_t gemv_chain_take_error(int *site, cudaStream_t stream);
 
 // Q4_K x f16 GEMV / skinny GEMM on warp MMAs.  nv = columns of op(rhs), 1..16 (rhs stored [nv][K]).
 int q4k_gemv_pick_split(int M, int K, int nv, int sm_count);

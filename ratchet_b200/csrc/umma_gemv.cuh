@@ -1,0 +1,157 @@
+// Device helpers shared by the tcgen05 Q8_0 GEMV kernels (single launch and persistent chain): mbarrier,
+// TMA, tcgen05 wrappers, and the conversion of a slice of the f16 activation vector into the
+// block-floating-point int8 digit tiles the MMAs read as their B operand.  Both kernels must
+// produce the same bits for the same node, so the arithmetic lives here once.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rt {
+namespace umma_gemv {
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+constexpr unsigned long long WAIT_LIMIT_CYCLES = 4000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long wait_clock() { return (unsigned long long)clock64(); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after WAIT_LIMIT_CYCLES, or as soon as the CTA's abort flag is up; the first
+// site that gives up is recorded in *error_word (a __device__ int the host reads at its next sync).
+__device__ __forceinline__ bool mbar_wait_flag(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site, int *error_word) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = wait_clock();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 32; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            atomicCAS(error_word, 0, site);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+
+// K-major operand tile, 128-byte swizzle, 8-row groups `group_stride` bytes apart.  The digit tiles
+// hold 8 rows and use a stride of 0: rows 8..15 of the N = 16 operand repeat rows 0..7, which only
+// duplicates accumulator columns that the next block overwrites (see the MMA issuer).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t group_stride) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(group_stride >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+    // the predicate is false: the accumulator slot is overwritten, every block starts from zero
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}\n"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Two-column accumulator slot of one Q8_0 block (its hi and lo digit sums).
+__device__ __forceinline__ void tmem_ld2_nowait(uint32_t taddr, int &v0, int &v1) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(v0), "=r"(v1) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Eight consecutive activations (one quarter of a Q8_0 block; the four threads of a quad hold one
+// block) -> their hi / lo int8 digits in the block's B tile, and the block's power-of-two scale.
+//   m = round(x / xs), |m| <= 16383, m = 256 * hi + lo with lo in [-128, 127];  x ~ m * xs.
+// `raw` holds the eight f16 values, `blk` is the block index inside the CTA's K slice, `sub` the
+// quarter (0..3).  Tiles: 8 rows x 128 bytes per 128 bytes of K (row 0 = hi, row 1 = lo, rows 2..7
+// zero), 128-byte swizzle: 16-byte chunks XOR the row index.
+__device__ __forceinline__ void digits_of_quarter_block(const uint4 raw, int blk, int sub, uint8_t *b_tiles, float *xs) {
+    const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __half22float2(h2[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    // amax < 2^(E-126) for its exponent field E: scale it below 2^14
+    const int E = (int)((__float_as_uint(amax) >> 23) & 0xFFu);
+    const float scale = amax > 0.f ? __uint_as_float((uint32_t)(140 - E + 127) << 23) : 0.f;
+    const float inv = amax > 0.f ? __uint_as_float((uint32_t)(E - 13) << 23) : 0.f;
+    uint32_t hi_w[2] = {0u, 0u}, lo_w[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        int m = __float2int_rn(v[i] * scale);
+        m = max(-16383, min(16383, m));
+        const int hi = (m + 128) >> 8;
+        const int lo = m - (hi << 8);
+        hi_w[i >> 2] |= (uint32_t)(hi & 0xFF) << (8 * (i & 3));
+        lo_w[i >> 2] |= (uint32_t)(lo & 0xFF) << (8 * (i & 3));
+    }
+    uint8_t *tile = b_tiles + (size_t)(blk >> 2) * 1024;
+    const int kpos = (blk & 3) * 32 + sub * 8;
+    const int chunk = kpos >> 4, within = kpos & 15;
+    *reinterpret_cast<uint2 *>(tile + 0 * 128 + ((chunk ^ 0) << 4) + within) = make_uint2(hi_w[0], hi_w[1]);
+    *reinterpret_cast<uint2 *>(tile + 1 * 128 + ((chunk ^ 1) << 4) + within) = make_uint2(lo_w[0], lo_w[1]);
+    if (sub == 0) xs[blk] = inv;
+}
+
+// One block's contribution to a row: d = weight scale, xsv = activation scale, (hi, lo) = the MMA's two sums.
+__device__ __forceinline__ float add_block(float acc, float d, float xsv, int hi, int lo) {
+    const float t = fmaf(256.f, (float)hi, (float)lo);
+    return fmaf(d * xsv, t, acc);
+}
+
+} // namespace umma_gemv
+} // namespace rt

@@ -203,6 +203,7 @@ class Executable:
         self._h = c_void_p()
         check(_lib.load().rt_executable_create(device._h, arr, len(nodes), int(use_graph), byref(self._h)))
         self.launches = int(_lib.load().rt_executable_launches(self._h))
+        self.kernel = _lib.load().rt_executable_kernel(self._h).decode()
 
     def dispatch(self) -> None:
         check(_lib.load().rt_executable_dispatch(self._h, None))
@@ -399,6 +400,17 @@ class Tensor:
             check(lib.rt_download(self.device._h, self.storage._h, 0, raw.ctypes.data_as(c_void_p), n, 1))
             return Tensor(self.shape, self.dt, Device.CPU, raw[:n])
         raise RatchetError(_lib.RT_ERR_UNSUPPORTED, "RT_ERR_UNSUPPORTED", "GPU to GPU moves are not part of this path")
+
+    def write(self, data: np.ndarray) -> "Tensor":
+        """Overwrites a resolved GPU tensor's bytes from host memory (queue.write_buffer on the tensor's
+        own storage): how a caller feeds new input to an Executable whose buffers are bound."""
+        if not self.device.is_gpu() or not isinstance(self.storage, GpuBuffer):
+            raise RatchetError(_lib.RT_ERR_ARG, "RT_ERR_ARG", "write takes a resolved GPU tensor")
+        raw = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        if raw.size != self.nbytes():
+            raise RatchetError(_lib.RT_ERR_ARG, "RT_ERR_ARG", f"write: {raw.size} bytes for a tensor of {self.nbytes()}")
+        check(_lib.load().rt_upload(self.device._h, self.storage._h, 0, raw.ctypes.data_as(c_void_p), raw.size, 0))
+        return self
 
     # ------------------------------------------------------------------ host views
     def to_numpy(self) -> np.ndarray:

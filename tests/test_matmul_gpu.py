@@ -133,6 +133,82 @@ def test_q8_gemv_phi2_shapes(gpu, shape, seed):
     check_problem(Problem(Q8F, F32, shape, (1, 1, K), (False, True, True), bias=True, seed=seed, w_std=0.02), gpu)
 
 
+def _decode_chain(gpu, shapes, seed, with_bias):
+    rng = np.random.default_rng(seed)
+    x0 = rng.standard_normal(shapes[0][1]).astype(np.float16)
+    h = Tensor.from_data(x0, gpu)
+    x_dev, nodes, host = h, [], []
+    for i, shape in enumerate(shapes):
+        w_t, w_vals = make_lhs(Q8H, shape, np.random.default_rng(seed + 10 + i), 0.02 if shape[1] < 8192 else 0.01)
+        b_vals = b_t = None
+        if with_bias[i]:
+            b_vals = round_to(F16, (np.random.default_rng(seed + 50 + i).standard_normal(shape[0]) * 0.02).astype(np.float32))
+            b_t = Tensor.from_data(b_vals, gpu, F16)
+        epi = rb.EPILOGUE_GELU_TANH if i % 2 == 0 else 0
+        h = w_t.to(gpu).gemm(h, b_t, False, True, True, epilogue=epi)
+        nodes.append(h)
+        host.append((w_vals, b_vals, epi))
+    return x_dev, nodes, host
+
+
+@pytest.mark.parametrize("shapes", [
+    [(2560, 2560), (2560, 2560), (2560, 2560)],                        # no K split: clusters of one
+    [(10240, 2560), (2560, 10240), (8192, 2560), (2560, 8192)],        # fc1 / fc2: K split four ways on every second node
+], ids=["square_x3", "phi2_mlp_x2"])
+def test_q8_gemv_chain_is_one_kernel_and_matches_node_by_node(gpu, monkeypatch, shapes):
+    """A decode step's GEMVs as ONE persistent kernel (grid barriers between the nodes): every node's
+    output has the bits of node-by-node dispatch, and meets the bar against the fp64 oracle."""
+    x_dev, nodes, host = _decode_chain(gpu, shapes, 4100, [True, False, False, True][:len(shapes)])
+    nodes[-1].resolve()
+    exe = rb.Executable(gpu, nodes, use_graph=True)
+    assert exe.kernel.startswith("q8_gemv_chain"), exe.kernel
+    assert exe.launches == 1
+    monkeypatch.setenv("RT_GEMV_CHAIN", "0")
+    exe_nodes = rb.Executable(gpu, nodes, use_graph=True)
+    assert exe_nodes.kernel == "graph" and exe_nodes.launches == len(shapes)
+    for trial in range(3):  # new input every time: the outputs must really be recomputed
+        x = np.random.default_rng(4200 + trial).standard_normal(shapes[0][1]).astype(np.float16)
+        x_dev.write(x)
+        exe_nodes.dispatch()
+        gpu.sync()
+        want = [n.to(Device.CPU).to_numpy().reshape(-1).copy() for n in nodes]
+        for n in nodes:
+            n.write(np.zeros(n.numel(), dtype=np.float16))
+        exe.dispatch()
+        exe.dispatch()  # back to back: the barrier counter is reset between dispatches
+        gpu.sync()
+        got = [n.to(Device.CPU).to_numpy().reshape(-1).copy() for n in nodes]
+        h = x.astype(np.float32)
+        for i, (w_vals, b_vals, epi) in enumerate(host):
+            assert np.array_equal(got[i].view(np.uint16), want[i].view(np.uint16)), f"node {i} differs from node-by-node dispatch"
+            M, K = shapes[i]
+            truth = oracle.matmul_truth(w_vals, h, b_vals, 1, 1, 1, M, 1, K, False, True, True, epi)
+            assert oracle.rel_l2(got[i].astype(np.float32), oracle.f64_to_f16(truth).astype(np.float32)) <= TOL[F16]
+            h = got[i].astype(np.float32)  # the next node's input is what this one wrote
+
+
+@pytest.mark.parametrize("shapes,kind", [
+    ([(4096, 10240), (2560, 4096)], "chain"),   # K = 10240 splits four ways, K = 4096 two ways: both in one kernel
+    ([(2560, 2560), (512, 2560)], "graph"),     # 512 rows are too few for the tensor-memory GEMV: one launch per node
+], ids=["mixed_k_splits", "not_eligible"])
+def test_q8_gemv_lists_chain_or_graph(gpu, shapes, kind):
+    x_dev, nodes, host = _decode_chain(gpu, shapes, 4300, [False, True])
+    nodes[-1].resolve()
+    exe = rb.Executable(gpu, nodes, use_graph=True)
+    assert exe.kernel.startswith("q8_gemv_chain") if kind == "chain" else exe.kernel == "graph", exe.kernel
+    for n in nodes:
+        n.write(np.zeros(n.numel(), dtype=np.float16))
+    exe.dispatch()
+    gpu.sync()
+    h = x_dev.to(Device.CPU).to_numpy().reshape(-1).astype(np.float32)
+    for i, (w_vals, b_vals, epi) in enumerate(host):
+        M, K = shapes[i]
+        got = nodes[i].to(Device.CPU).to_numpy().reshape(-1)
+        truth = oracle.matmul_truth(w_vals, h, b_vals, 1, 1, 1, M, 1, K, False, True, True, epi)
+        assert oracle.rel_l2(got.astype(np.float32), oracle.f64_to_f16(truth).astype(np.float32)) <= TOL[F16]
+        h = got.astype(np.float32)
+
+
 def test_q8_gemv_shapes_and_forms(gpu):
     for N, K in [(16, 32), (15, 64), (17, 96), (33, 2560), (1000, 352), (4096, 4096), (7, 8192)]:
         check_problem(Problem(Q8H, F16, (N, K), (1, K), (False, True, True), bias=True, seed=N + K, w_std=0.05), gpu)
