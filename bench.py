@@ -475,7 +475,11 @@ def main():
     y_dev = y.to(Device.CPU).to_numpy().reshape(-1)
     assert np.all(np.isfinite(y_dev.astype(np.float32))), "non-finite benchmark output"
     assert np.array_equal(y_dev.view(np.uint16), y_e2e.view(np.uint16)), "legs disagree"
-    assert np.array_equal(y_dev.view(np.uint16), y_pin.array.reshape(-1).view(np.uint16)), "node-by-node result differs"
+    y_lazy = y_pin.array.reshape(-1).astype(np.float64)  # one launch per node: other kernels, another summation order
+    rel = float(np.linalg.norm(y_dev.astype(np.float64) - y_lazy) / max(np.linalg.norm(y_lazy), 1e-30))
+    # 64 chained GEMVs, each rounding its output to f16: last-digit differences are fed forward and grow
+    # with the depth (2e-4 after three nodes, 2e-3 after 64); per-node parity is what the tests check
+    assert rel <= 2e-2, f"executable and node-by-node results differ: rel-L2 {rel:.3e}"
 
     sharded = None
     if world > 1 and not args.no_sharded:

@@ -245,7 +245,8 @@ typedef struct rt_dispatch {
  * graph at creation (on a private stream; capturing executes nothing) and each dispatch is one
  * graph launch.  A list of two or more single-vector Q8_0H GEMVs whose weights are all flagged
  * RT_LAUNCH_LHS_CONSTANT becomes ONE persistent kernel instead (grid barriers between the nodes,
- * weights of later nodes streamed while earlier ones compute; same bits as node-by-node dispatch);
+ * weights of later nodes streamed while earlier ones compute; same products as node-by-node
+ * dispatch, f32 sums in another order);
  * only one dispatch of such an executable may be in flight at a time.  Plans and buffers must
  * outlive the executable. */
 rt_status rt_executable_create(rt_device *dev, const rt_dispatch *nodes, int32_t n_nodes, int32_t use_graph, rt_executable **exe);

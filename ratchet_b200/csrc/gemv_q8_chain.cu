@@ -18,8 +18,8 @@
 //    of the activations, s32 sums in tensor memory, per-block rescale by four epilogue warps.  K slices of
 //    fat weights meet in global memory: each slice's CTA stores its row sums and counts itself in, and the
 //    one that arrives last adds the slices in rank order and writes the rows (thread-block clusters would
-//    do this in shared memory, but clusters of four leave 16 of the 148 SMs without a CTA).  Results are
-//    bit-identical to launching the nodes one by one;
+//    do this in shared memory, but clusters of four leave 16 of the 148 SMs without a CTA).  The products
+//    are those of launching the nodes one by one; the f32 sums are taken in another order;
 //  * with the SM to itself a CTA owns all 512 tensor-memory columns: every block of a stage gets its own
 //    16-column accumulator (no overlapping writes), so two warps can issue MMAs for alternate stages.
 // Every wait is bounded; a wait that runs out records its site, raises the CTA's abort flag and the CTA
@@ -44,33 +44,55 @@ namespace {
 
 using namespace umma_gemv;
 
-constexpr int N_ISSUE = 2;                               // MMA-issuing warps (stage g belongs to issuer g % N_ISSUE)
-constexpr int THREADS = 64 + 128 + 32 * (N_ISSUE - 1);   // warp 0 producer, warp 1 issuer 0, warps 2-5 epilogue, warps 6.. issuers 1..
-constexpr int STAGE_K = 256;                             // bytes of K per ring stage = 8 Q8_0 blocks
+constexpr int N_ISSUE = 2;                               // MMA-issuing warps (stage g belongs to issuer g % n_issue)
+constexpr int THREADS = 64 + 256 + 32 * (N_ISSUE - 1);   // warp 0 producer, warp 1 issuer 0, warps 2-9 epilogue, warps 10.. issuers 1..
+constexpr int CHUNK_K = 128;                             // bytes of K per sub-tile row (one swizzle row) = 4 Q8_0 blocks
+constexpr int MAX_S = 8;                                 // sub-tiles (chunks) per ring stage
+constexpr int MAX_TILES = 4;                             // 128-row MMA tiles per stage
 constexpr int TMEM_COLS = 512;
-constexpr int TG_COLS = 128;                             // 8 blocks x 16 columns
+constexpr int TG_COLS = 256;                             // MAX_TILES x 4 blocks x 16 columns
 constexpr int TGROUPS = TMEM_COLS / TG_COLS;
 constexpr int MAX_KS = 3072;                             // bytes of K per CTA and node
+constexpr int GUARD_BYTES = 16384;                       // an MMA tile may read up to 128 rows past its stage
 constexpr size_t SMEM_LIMIT = 227 * 1024;
 
-struct alignas(64) ChainNodeDev {
-    CUtensorMap map_w; // codes  [M][K] u8, box 128 x rb, 128-byte swizzle
-    CUtensorMap map_s; // scales [M][K/32] f16, box 8 x rb
+// How a node's weights sit in a ring stage, and how the MMAs tile them.
+//
+// A stage holds S consecutive chunks of K (128 bytes each) for the CTA's rb rows: S sub-tiles of rb8
+// rows x 128 bytes, one after the other, i.e. a stream of S * rb8 rows of 128 bytes.  An MMA takes 128
+// consecutive rows of that stream as its A operand, whatever sub-tiles they belong to: tile t covers
+// stream rows [128 t, 128 t + 128), which are rows of chunks c0[t] .. c1[t].  Its B operand holds, for
+// every one of those chunks d = c - c0[t], the chunk's hi digits in row 2d and its lo digits in row
+// 2d + 1, so accumulator columns (2d, 2d + 1) of the lanes that hold chunk c's rows are that chunk's
+// sums; the other columns of those lanes pair weights with another chunk's activations and are never
+// read.  With rb = 70 a 128-row MMA is full instead of 55 % full: 48 MMAs per node instead of 80.
+struct alignas(16) ChainNodeInfo { // 128 bytes: what the warps other than the producer need of a node
     const void *rhs;
     void *out;
     const void *bias;
     int M, K;
-    int rb, rb8, ks, nstages, split;
+    int rb, rb8, ks, split;
+    int S, nstages, tiles;       // chunks per stage, stages per node, MMA tiles per stage
+    int b_tile_bytes;            // 1024 (8 digit rows: at most 4 chunks per tile) or 2048 (16 rows)
+    int c0[MAX_TILES], c1[MAX_TILES];
     int bias_mode, bias_dt, epilogue;
+    int inv_S_q16;               // ceil(65536 / S): chunk / S without a division
+    int pad[4];
+};
+static_assert(sizeof(ChainNodeInfo) == 128, "ChainNodeInfo is copied as 32 words");
+
+struct alignas(64) ChainNodeDev : ChainNodeInfo {
+    CUtensorMap map_w; // codes  [M][K] u8, box 128 x rb, 128-byte swizzle
+    CUtensorMap map_s; // scales [M][K/32] f16, box (ks/32) x rb
 };
 
 struct ChainParams {
     const ChainNodeDev *nodes;
     int n_nodes;
     int ring;            // stages in the ring
-    int slot_bytes;      // codes of one stage: 2 sub-tiles of rb8_max x 128
-    int scale_slot_bytes;
-    int b_bytes;         // digit tiles (and the guard for MMA reads past a sub-tile's last row)
+    int slot_bytes;      // codes of one stage (the largest S * rb8 * 128 of the chain)
+    int b_bytes;         // digit tiles, and the guard behind the ring
+    int scale_buf_bytes; // one node's scales: rb8 rows of ks/32 f16 (two buffers)
     int n_issue;         // MMA-issuing warps in use (<= N_ISSUE)
     unsigned long long *counter; // grid barrier: arrivals so far
     unsigned int *unit_count;    // [n_nodes][gridDim.x]: K slices of a unit that have stored their row sums
@@ -87,29 +109,37 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *ring = smem;                                         // [ring][2 sub-tiles][rb8 x 128]
-    uint8_t *b_tiles = ring + (size_t)cp.ring * cp.slot_bytes;    // [MAX_KS/128][8 rows x 128]
-    uint8_t *scales_s = b_tiles + cp.b_bytes;                     // [ring][rb8 x 16]
-    float *xs = reinterpret_cast<float *>(scales_s + (size_t)cp.ring * cp.scale_slot_bytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(xs + MAX_KS / 32);
-    // bars: [0..R) full, [R..2R) empty, TGROUPS tmem_full, TGROUPS tmem_empty, digits ready
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * cp.ring + 2 * TGROUPS + 2);
+    uint8_t *ring = smem;                                         // [ring][S sub-tiles][rb8 x 128]
+    uint8_t *b_tiles = ring + (size_t)cp.ring * cp.slot_bytes;    // [nstages][tiles][8 or 16 rows x 128]
+    uint8_t *scales_s = b_tiles + cp.b_bytes;                     // [2][rb8][ks/32] f16
+    float *xs = reinterpret_cast<float *>(scales_s + 2 * (size_t)cp.scale_buf_bytes);
+    float *part = xs + MAX_KS / 32;                               // [2 block pairs][MAX_TILES x 128 stream rows]: row sums
+    ChainNodeInfo *info = reinterpret_cast<ChainNodeInfo *>(part + 2 * MAX_TILES * 128); // [2]: this node's and the next one's
+    uint64_t *bars = reinterpret_cast<uint64_t *>(info + 2);
+    // bars: [0..R) full, [R..2R) empty, TGROUPS tmem_full, TGROUPS tmem_empty, digits ready, 2 scales full, 2 scales empty
+    const int n_bars = 2 * cp.ring + 2 * TGROUPS + 1 + 4;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + n_bars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     volatile unsigned int *arrived_before = reinterpret_cast<volatile unsigned int *>(tmem_slot + 2);
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + cp.ring);
     const uint32_t bar_tfull = smem_u32(bars + 2 * cp.ring), bar_tempty = smem_u32(bars + 2 * cp.ring + TGROUPS);
     const uint32_t bar_x = smem_u32(bars + 2 * cp.ring + 2 * TGROUPS);
+    const uint32_t bar_sfull = bar_x + 8, bar_sempty = bar_x + 24;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < cp.ring; s++) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 5); // the MMAs' commit + the four epilogue warps (they read the stage's scales)
+            mbar_init(bar_empty + 8 * s, 1); // the MMAs' commit
         }
         for (int a = 0; a < TGROUPS; a++) {
             mbar_init(bar_tfull + 8 * a, 1);
-            mbar_init(bar_tempty + 8 * a, 4);
+            mbar_init(bar_tempty + 8 * a, 8);
         }
-        mbar_init(bar_x, 4);
+        mbar_init(bar_x, 8);
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_sfull + 8 * a, 1);
+            mbar_init(bar_sempty + 8 * a, 8);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -117,6 +147,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    if (warp == 2) reinterpret_cast<int *>(info)[lane] = reinterpret_cast<const int *>(static_cast<const ChainNodeInfo *>(cp.nodes))[lane];
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -125,8 +156,8 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
     if (warp == 0) {
         // ------------------------------------------------------------------ producer: all nodes, one ring
         if (lane == 0) {
-            int slot = 0;
-            uint32_t phase = 0;
+            int slot = 0, sbuf = 0;
+            uint32_t phase = 0, sphase = 0;
             bool ok = true;
             for (int l = 0; l < cp.n_nodes && ok; l++) {
                 const ChainNodeDev &nd = cp.nodes[l];
@@ -134,59 +165,67 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 const int row_begin = unit * nd.rb;
                 if (row_begin >= nd.M) continue;
                 const int k_begin = rank * nd.ks;
-                const uint32_t tx = (uint32_t)nd.rb * (2 * 128 + 16);
-                const int nstages = nd.nstages, rb8 = nd.rb8;
+                const int nstages = nd.nstages, rb8 = nd.rb8, S = nd.S;
                 const CUtensorMap *map_w = &nd.map_w, *map_s = &nd.map_s;
                 // the maps live in global memory (written by the host before the launch): the tensor-map proxy
                 // has to acquire them before this CTA's first copy through them
                 asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(map_w) : "memory");
                 asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(map_s) : "memory");
+                // the node's scales: one copy, into the buffer the node before the previous one has left
+                if (!mbar_wait(bar_sempty + 8 * sbuf, sphase ^ 1, abort_flag, 9)) break;
+                {
+                    const uint32_t full = bar_sfull + 8 * sbuf;
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"((uint32_t)(nd.rb * (nd.ks / 16))) : "memory");
+                    tma_load_2d(smem_u32(scales_s + (size_t)sbuf * cp.scale_buf_bytes), map_s, k_begin / 32, row_begin, full);
+                    if (++sbuf == 2) { sbuf = 0; sphase ^= 1; }
+                }
+                const uint32_t tx = (uint32_t)nd.rb * 128u * (uint32_t)S;
                 for (int s = 0; s < nstages; s++) {
                     if (!mbar_wait(bar_empty + 8 * slot, phase ^ 1, abort_flag, 1)) { ok = false; break; }
                     const uint32_t st = smem_u32(ring + (size_t)slot * cp.slot_bytes);
                     const uint32_t full = bar_full + 8 * slot;
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(tx) : "memory");
-                    const int kb = k_begin + s * STAGE_K;
-                    tma_load_2d(st, map_w, kb, row_begin, full);
-                    tma_load_2d(st + rb8 * 128, map_w, kb + 128, row_begin, full);
-                    tma_load_2d(smem_u32(scales_s + (size_t)slot * cp.scale_slot_bytes), map_s, kb / 32, row_begin, full);
+                    const int kb = k_begin + s * S * CHUNK_K;
+                    for (int c = 0; c < S; c++) tma_load_2d(st + c * rb8 * 128, map_w, kb + c * CHUNK_K, row_begin, full);
                     if (++slot == cp.ring) { slot = 0; phase ^= 1; }
                 }
             }
         }
-    } else if (warp == 1 || warp >= 6) {
+    } else if (warp == 1 || warp >= 10) {
         // ------------------------------------------------------------------ MMA issuers
-        const int issuer = warp == 1 ? 0 : warp - 5;
+        const int issuer = warp == 1 ? 0 : warp - 9;
         if (lane == 0) {
             // instruction descriptor: s32 accumulate, signed 8-bit A and B, K-major, N = 16, M = 128
             const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
-            const uint64_t a_desc_ring = umma_desc_sw128(smem_u32(ring), 1024), b_desc_base = umma_desc_sw128(smem_u32(b_tiles), 0);
+            const uint64_t a_desc_ring = umma_desc_sw128(smem_u32(ring), 1024);
             int slot = 0, tg = 0, turn = 0;
             uint32_t phase = 0, tphase = 0, xphase = 0;
             bool ok = true;
             for (int l = 0; l < cp.n_nodes && ok; l++) {
-                const ChainNodeDev &nd = cp.nodes[l];
+                // the epilogue warps put node l's description into shared memory while node l-1 ran
+                const ChainNodeInfo &nd = info[l & 1];
                 const int unit = (int)blockIdx.x / nd.split;
-                if (unit * nd.rb >= nd.M) continue;
-                // this node's digits are in place (one phase of bar_x per node that has rows here)
+                const bool has_rows = unit * nd.rb < nd.M;
+                const int nstages = nd.nstages, tiles = nd.tiles, btb = nd.b_tile_bytes;
+                // one phase of bar_x per node: the node's digits are in place (and the next node's description)
                 if (!mbar_wait(bar_x, xphase, abort_flag, 2)) break;
                 xphase ^= 1;
-                const int rb8 = nd.rb8, nstages = nd.nstages;
+                if (!has_rows) continue;
+                // 16-row digit tiles are two 8-row groups 1024 bytes apart; 8-row tiles repeat their group (stride 0)
+                const uint64_t b_desc_base = umma_desc_sw128(smem_u32(b_tiles), btb == 2048 ? 1024 : 0);
                 for (int s = 0; s < nstages; s++) {
                     if (turn == issuer) {
                         if (!mbar_wait(bar_tempty + 8 * tg, tphase ^ 1, abort_flag, 3)) { ok = false; break; }
                         if (!mbar_wait(bar_full + 8 * slot, phase, abort_flag, 4)) { ok = false; break; }
                         tc_fence_after();
                         const uint64_t a_desc = a_desc_ring + (uint64_t)((uint32_t)(slot * cp.slot_bytes) >> 4);
-                        const uint64_t b_desc = b_desc_base + (uint64_t)(s * 2 * (1024 >> 4));
                         const uint32_t d0 = tmem_base + tg * TG_COLS;
+                        for (int t = 0; t < tiles; t++) {
+                            const uint64_t at = a_desc + (uint64_t)(t * (128 * 128 >> 4));
+                            const uint64_t bt = b_desc_base + (uint64_t)((uint32_t)((s * tiles + t) * btb) >> 4);
+                            // block j of the chunks: 32 bytes further along K in both operands; its own 16 columns
 #pragma unroll
-                        for (int kk = 0; kk < 2; kk++) {
-                            const uint64_t ak = a_desc + (uint64_t)((uint32_t)(kk * rb8 * 128) >> 4), bk = b_desc + (uint64_t)(kk * (1024 >> 4));
-                            // block jj of the stage owns columns [16 jj, 16 jj + 16): its two sums (the hi and lo digit
-                            // rows of B) and fourteen columns nobody reads
-#pragma unroll
-                            for (int j = 0; j < 4; j++) umma_i8(d0 + (kk * 4 + j) * 16, ak + 2 * j, bk + 2 * j, idesc);
+                            for (int j = 0; j < 4; j++) umma_i8(d0 + (t * 4 + j) * 16, at + 2 * j, bt + 2 * j, idesc);
                         }
                         umma_commit(bar_empty + 8 * slot);
                         umma_commit(bar_tfull + 8 * tg);
@@ -198,21 +237,25 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
             }
         }
     } else {
-        // ------------------------------------------------------------------ digits, epilogue, grid barrier (warps 2..5)
-        const int q = warp & 3;          // tensor-memory lane quarter of this warp
-        const int et = threadIdx.x - 64; // 0..127
-        const int row_local = q * 32 + lane;
-        // rows 2..7 of every digit tile stay zero for the whole kernel, rows 0 and 1 receive each node's digits
-        for (int i = et; i < cp.b_bytes / 16; i += 128) reinterpret_cast<uint4 *>(b_tiles)[i] = make_uint4(0u, 0u, 0u, 0u);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        int slot = 0, tg = 0;
-        uint32_t phase = 0, tphase = 0;
+        // ------------------------------------------------------------------ digits, epilogue, grid barrier (warps 2..9)
+        // Two warps per tensor-memory lane quarter: the first takes blocks 0 and 1 of every chunk, the second
+        // blocks 2 and 3.
+        const int q = warp & 3;               // tensor-memory lane quarter of this warp
+        const int half = (warp - 2) >> 2;     // which two blocks of every chunk
+        const int et = threadIdx.x - 64;      // 0..255
+        const int row_local = q * 32 + lane;  // this thread's tensor-memory lane
+        int tg = 0, sbuf = 0;
+        uint32_t tphase = 0, sphase = 0;
         bool ok = true;
         for (int l = 0; l < cp.n_nodes && ok; l++) {
-            const ChainNodeDev &nd = cp.nodes[l];
+            const ChainNodeInfo &nd = info[l & 1];
             const int split = nd.split, unit = (int)blockIdx.x / split, rank = (int)blockIdx.x % split;
             const int row_begin = unit * nd.rb;
             const bool has_rows = row_begin < nd.M;
+            // the next node's description, fetched while this node waits and computes (nobody reads the other
+            // copy any more: node l-1 is over for every warp of this CTA once its sums were taken)
+            int next_word = 0;
+            if (warp == 2 && l + 1 < cp.n_nodes) next_word = reinterpret_cast<const int *>(static_cast<const ChainNodeInfo *>(cp.nodes + l + 1))[lane];
             if (l > 0) {
                 // node l-1 is complete on every CTA: (l) * gridDim.x arrivals
                 if (et == 0) {
@@ -230,94 +273,176 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                         }
                     }
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
                 if (*abort_flag) break;
             }
+            if (warp == 2 && l + 1 < cp.n_nodes) reinterpret_cast<int *>(info + ((l + 1) & 1))[lane] = next_word;
+            if (!has_rows) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_x);
+            }
             if (has_rows) {
-                const int ks = nd.ks, nstages = nd.nstages, scale_row = min(row_local, nd.rb8 - 1) * 16;
-                const int k_begin = rank * ks;
+                const int ks = nd.ks, nstages = nd.nstages, rb8 = nd.rb8, S = nd.S, tiles = nd.tiles, btb = nd.b_tile_bytes;
+                const int k_begin = rank * ks, inv_S = nd.inv_S_q16;
                 const int rows_here = min(nd.rb, nd.M - row_begin);
+                int c0[MAX_TILES], c1[MAX_TILES];
+#pragma unroll
+                for (int t = 0; t < MAX_TILES; t++) { c0[t] = nd.c0[t]; c1[t] = nd.c1[t]; }
                 {
                     // another SM wrote these activations during this launch: read them from L2
                     const __half *x = (const __half *)nd.rhs + k_begin;
                     const int sub = et & 3; // 4 threads per block of 32 elements, 8 elements each
-                    constexpr int MAX_IT = MAX_KS / 32 / 32;
+                    constexpr int MAX_IT = (MAX_KS / 32 + 63) / 64;
                     uint4 pre[MAX_IT];
 #pragma unroll
                     for (int it = 0; it < MAX_IT; it++) { // all loads first: one L2 round trip, not one per iteration
-                        const int blk = (et >> 2) + it * 32;
+                        const int blk = (et >> 2) + it * 64;
                         pre[it] = blk < ks / 32 ? __ldcg(reinterpret_cast<const uint4 *>(x + blk * 32 + sub * 8)) : make_uint4(0u, 0u, 0u, 0u);
                     }
 #pragma unroll
                     for (int it = 0; it < MAX_IT; it++) {
-                        const int blk = (et >> 2) + it * 32;
+                        const int blk = (et >> 2) + it * 64;
                         if (blk >= ks / 32) break;
-                        digits_of_quarter_block(pre[it], blk, sub, b_tiles, xs);
+                        uint2 hi8, lo8;
+                        float inv;
+                        quantize_quarter_block(pre[it], hi8, lo8, inv);
+                        if (sub == 0) xs[blk] = inv;
+                        // the chunk's digits go into every MMA tile that holds some of the chunk's rows
+                        const int chunk = blk >> 2, stage = (chunk * inv_S) >> 16, cl = chunk - stage * S;
+                        const int kpos = (blk & 3) * 32 + sub * 8;
+#pragma unroll
+                        for (int t = 0; t < MAX_TILES; t++) {
+                            if (t < tiles && cl >= c0[t] && cl <= c1[t]) {
+                                const int row = 2 * (cl - c0[t]);
+                                uint8_t *tile = b_tiles + (size_t)(stage * tiles + t) * btb + (row >> 3) * 1024;
+                                store_digits8(tile, row & 7, kpos, hi8);
+                                store_digits8(tile, (row & 7) + 1, kpos, lo8);
+                            }
+                        }
                     }
                 }
                 // the MMAs read the tiles through the async proxy
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                asm volatile("bar.sync 1, 128;" ::: "memory"); // xs visible to all epilogue warps
+                asm volatile("bar.sync 1, 256;" ::: "memory"); // xs visible to all epilogue warps
                 if (lane == 0) mbar_arrive(bar_x);
 
-                float acc = 0.f;
+                // where this thread's lane sits in the stage's row stream, tile by tile
+                int my_cl[MAX_TILES], my_row[MAX_TILES], my_k[MAX_TILES], col0[MAX_TILES];
+                bool mine[MAX_TILES], warp_has[MAX_TILES];
+                float acc[MAX_TILES];
+                const bool narrow = rb8 >= 32; // a warp's 32 lanes then belong to at most two chunks: two column pairs do
+#pragma unroll
+                for (int t = 0; t < MAX_TILES; t++) {
+                    const int pos = 128 * t + row_local, pos_w = 128 * t + q * 32;
+                    my_cl[t] = pos / rb8;
+                    my_row[t] = pos - my_cl[t] * rb8;
+                    warp_has[t] = t < tiles && pos_w < S * rb8;
+                    mine[t] = t < tiles && pos < S * rb8 && my_row[t] < rows_here;
+                    const int d_first = min(pos_w / rb8 - c0[t], narrow ? 6 : 4); // first of the column pairs this warp loads
+                    col0[t] = 2 * d_first;
+                    my_k[t] = my_cl[t] - c0[t] - d_first;
+                    acc[t] = 0.f;
+                }
+                const uint8_t *scales_n = scales_s + (size_t)sbuf * cp.scale_buf_bytes;
+                const int srow = ks / 16; // bytes per row of the node's scales
+                if (!mbar_wait(bar_sfull + 8 * sbuf, sphase, abort_flag, 10)) break;
                 for (int s = 0; s < nstages; s++) {
-                    if (!mbar_wait(bar_full + 8 * slot, phase, abort_flag, 5)) { ok = false; break; }
-                    const uint4 sc = *reinterpret_cast<const uint4 *>(scales_s + (size_t)slot * cp.scale_slot_bytes + scale_row);
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
                     if (!mbar_wait(bar_tfull + 8 * tg, tphase, abort_flag, 6)) { ok = false; break; }
                     tc_fence_after();
-                    int hi[8], lo[8];
-                    const uint32_t t0 = tmem_base + tg * TG_COLS + ((uint32_t)(q * 32) << 16);
+                    const uint32_t t0 = tmem_base + tg * TG_COLS + ((uint32_t)(q * 32) << 16) + half * 32;
+                    // all of the stage's loads first (one wait), then the arithmetic
+                    int v[MAX_TILES][2][8];
+                    if (narrow) {
 #pragma unroll
-                    for (int j = 0; j < 8; j++) tmem_ld2_nowait(t0 + j * 16, hi[j], lo[j]);
+                        for (int t = 0; t < MAX_TILES; t++) {
+                            if (!warp_has[t]) continue;
+#pragma unroll
+                            for (int j = 0; j < 2; j++) tmem_ld4_nowait(t0 + (t * 4 + j) * 16 + col0[t], v[t][j]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int t = 0; t < MAX_TILES; t++) {
+                            if (!warp_has[t]) continue;
+#pragma unroll
+                            for (int j = 0; j < 2; j++) tmem_ld8_nowait(t0 + (t * 4 + j) * 16 + col0[t], v[t][j]);
+                        }
+                    }
                     tmem_ld_wait();
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_tempty + 8 * tg);
-                    const __half2 *d2 = reinterpret_cast<const __half2 *>(&sc);
-                    const float4 xa = *reinterpret_cast<const float4 *>(xs + s * 8), xb = *reinterpret_cast<const float4 *>(xs + s * 8 + 4);
-                    const float xsv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+                    if (lane == 0) mbar_arrive(bar_tempty + 8 * tg); // the sums are in registers: the MMAs may reuse the columns
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const float d = (j & 1) ? __high2float(d2[j >> 1]) : __low2float(d2[j >> 1]);
-                        acc = add_block(acc, d, xsv[j], hi[j], lo[j]);
+                    for (int t = 0; t < MAX_TILES; t++) {
+                        if (!mine[t]) continue;
+                        const int blk0 = (s * S + my_cl[t]) * 4 + half * 2;
+                        const __half2 d2 = *reinterpret_cast<const __half2 *>(scales_n + (size_t)my_row[t] * srow + blk0 * 2);
+                        const float2 xv = *reinterpret_cast<const float2 *>(xs + blk0);
+                        const int k = my_k[t];
+#pragma unroll
+                        for (int j = 0; j < 2; j++) {
+                            int hi, lo;
+                            if (narrow) {
+                                hi = k == 0 ? v[t][j][0] : v[t][j][2];
+                                lo = k == 0 ? v[t][j][1] : v[t][j][3];
+                            } else {
+                                hi = k == 0 ? v[t][j][0] : k == 1 ? v[t][j][2] : k == 2 ? v[t][j][4] : v[t][j][6];
+                                lo = k == 0 ? v[t][j][1] : k == 1 ? v[t][j][3] : k == 2 ? v[t][j][5] : v[t][j][7];
+                            }
+                            const float d = j ? __high2float(d2) : __low2float(d2);
+                            acc[t] = add_block(acc[t], d, j ? xv.y : xv.x, hi, lo);
+                        }
                     }
-                    if (++slot == cp.ring) { slot = 0; phase ^= 1; }
                     if (++tg == TGROUPS) { tg = 0; tphase ^= 1; }
                 }
                 if (!ok) break;
+                // the scales buffer is free for the node after the next one
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_sempty + 8 * sbuf);
+                if (++sbuf == 2) { sbuf = 0; sphase ^= 1; }
+                // a row's chunks and block pairs were summed by different threads: add them in a fixed order
+#pragma unroll
+                for (int t = 0; t < MAX_TILES; t++)
+                    if (mine[t]) part[half * (MAX_TILES * 128) + 128 * t + row_local] = acc[t];
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                const bool my_rows = et < rows_here; // from here on thread et of the first four warps owns row et
+                float sum = 0.f;
+                if (my_rows) {
+                    for (int c = 0; c < S; c++) sum += part[c * rb8 + et] + part[MAX_TILES * 128 + c * rb8 + et];
+                }
                 bool writes_rows = true;
                 if (split > 1) {
                     // K slices meet: store this slice's row sums, count it in; the slice that arrives last adds all
-                    // of them in rank order (the order of the single-launch kernel) and writes the rows.
-                    if (row_local < rows_here) cp.partial[(size_t)rank * cp.partial_ld + row_begin + row_local] = acc;
-                    __threadfence();
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (et == 0) *arrived_before = atomicAdd(cp.unit_count + (size_t)l * gridDim.x + unit, 1u);
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    // of them in rank order and writes the rows.
+                    if (my_rows) cp.partial[(size_t)rank * cp.partial_ld + row_begin + et] = sum;
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    if (et == 0) {
+                        __threadfence(); // the CTA's sums (ordered before by the barrier) are out before the count
+                        *arrived_before = atomicAdd(cp.unit_count + (size_t)l * gridDim.x + unit, 1u);
+                        __threadfence(); // and the other slices' sums are read after it
+                    }
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
                     writes_rows = *arrived_before == (unsigned int)(split - 1);
-                    if (writes_rows && row_local < rows_here) {
-                        __threadfence();
-                        const float *pr = cp.partial + row_begin + row_local;
-                        acc = __ldcg(pr);
-                        for (int r = 1; r < split; r++) acc += __ldcg(pr + (size_t)r * cp.partial_ld);
+                    if (writes_rows && my_rows) {
+                        const float *pr = cp.partial + row_begin + et;
+                        sum = __ldcg(pr);
+                        for (int r = 1; r < split; r++) sum += __ldcg(pr + (size_t)r * cp.partial_ld);
                     }
                 }
-                if (writes_rows && row_local < rows_here) { // this thread holds the sum of tensor-memory lane row_local
-                    const int row = row_begin + row_local;
+                if (writes_rows && my_rows) {
+                    const int row = row_begin + et;
                     const bool has_bias = nd.bias_mode != BIAS_NONE;
                     float bias = 0.f;
                     if (has_bias) bias = load_bias(nd.bias, nd.bias_dt, nd.bias_mode == BIAS_PER_M ? row : 0);
-                    ((__half *)nd.out)[row] = epilogue_value<__half>(acc, has_bias, bias, nd.epilogue);
+                    ((__half *)nd.out)[row] = epilogue_value<__half>(sum, has_bias, bias, nd.epilogue);
                 }
             }
             if (l + 1 < cp.n_nodes) {
                 // publish: this CTA's part of node l is in memory (and its reads of node l's inputs are over)
-                __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (et == 0) atomicAdd(cp.counter, 1ull);
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (et == 0) {
+                    __threadfence();
+                    atomicAdd(cp.counter, 1ull);
+                }
             }
         }
     }
@@ -337,14 +462,45 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
 
 int split_for(int K) {
     int split = 1;
-    while (split < 8 && (K / split > MAX_KS || (K / split) % STAGE_K != 0)) split *= 2;
-    if (K % (split * STAGE_K) != 0 || K / split > MAX_KS) return 0;
+    while (split < 8 && (K / split > MAX_KS || (K / split) % 256 != 0)) split *= 2;
+    if (K % (split * 256) != 0 || K / split > MAX_KS) return 0;
     return split;
 }
 
-size_t smem_for(int ring, int slot_bytes, int scale_slot_bytes, int b_bytes) {
-    return 1024 + (size_t)ring * (slot_bytes + scale_slot_bytes) + b_bytes + (size_t)(MAX_KS / 32) * 4 +
-           (size_t)(2 * ring + 2 * TGROUPS + 2) * 8 + 64;
+// Chunks per stage: the divisor of the node's chunk count that needs the fewest MMAs (ties: the smaller
+// stage), under the limits of the stage (64 KB), of tensor memory (MAX_TILES tiles) and of the digit tiles
+// (at most 8 chunks per MMA tile).
+bool pick_stage(ChainNodeDev &nd) {
+    const int nchunks = nd.ks / CHUNK_K;
+    int best_cost = 1 << 30;
+    nd.S = 0;
+    for (int S = 1; S <= MAX_S && S <= nchunks; S++) {
+        if (nchunks % S != 0) continue;
+        const int rows = S * nd.rb8, tiles = (rows + 127) / 128;
+        if (tiles > MAX_TILES || rows * 128 > 64 * 1024) continue;
+        const int cost = (nchunks / S) * tiles;
+        if (cost < best_cost) { best_cost = cost; nd.S = S; }
+    }
+    if (nd.S == 0) return false;
+    nd.nstages = nchunks / nd.S;
+    nd.inv_S_q16 = (65536 + nd.S - 1) / nd.S;
+    nd.tiles = (nd.S * nd.rb8 + 127) / 128;
+    int span = 1;
+    for (int t = 0; t < MAX_TILES; t++) {
+        nd.c0[t] = nd.c1[t] = 0;
+        if (t >= nd.tiles) continue;
+        nd.c0[t] = (128 * t) / nd.rb8;
+        nd.c1[t] = std::min(nd.S - 1, (128 * t + 127) / nd.rb8);
+        span = std::max(span, nd.c1[t] - nd.c0[t] + 1);
+    }
+    if (span > 8) return false;
+    nd.b_tile_bytes = span > 4 ? 2048 : 1024;
+    return true;
+}
+
+size_t smem_for(int ring, int slot_bytes, int b_bytes, int scale_buf_bytes) {
+    return 1024 + (size_t)ring * slot_bytes + b_bytes + 2 * (size_t)scale_buf_bytes + (size_t)(MAX_KS / 32) * 4 + (size_t)2 * MAX_TILES * 128 * 4 +
+           2 * sizeof(ChainNodeInfo) + (size_t)(2 * ring + 2 * TGROUPS + 5) * 8 + 64;
 }
 
 } // namespace
@@ -382,7 +538,7 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
     std::vector<int> splits;
     int max_split = 1, partial_ld = 0;
     for (const MatmulParams &p : nodes) {
-        const int s = p.K >= STAGE_K ? split_for(p.K) : 0;
+        const int s = p.K >= 256 ? split_for(p.K) : 0;
         if (s == 0) { *why = "K is not a multiple of 256 per slice"; return cudaSuccess; }
         splits.push_back(s);
         if (s > max_split) max_split = s;
@@ -404,19 +560,23 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
     if (grid < 1) { *why = "no resident CTA"; return cudaSuccess; }
 
     std::vector<ChainNodeDev> host(nodes.size());
-    int rb8_max = 8;
+    int slot_bytes = 0, b_bytes = GUARD_BYTES, scale_buf_bytes = 0, mmas = 0;
     for (size_t i = 0; i < nodes.size(); i++) {
         const MatmulParams &p = nodes[i];
         ChainNodeDev &nd = host[i];
         std::memset(&nd, 0, sizeof(nd));
         const int units = grid / splits[i];
         const int rb = (p.M + units - 1) / units;
-        if (rb > 128 || rb < 8) { *why = "rows per CTA outside 8..128"; return cudaSuccess; }
+        if (rb > 128 || rb < 9) { *why = "rows per CTA outside 9..128"; return cudaSuccess; }
         nd.M = p.M; nd.K = p.K; nd.rb = rb; nd.rb8 = (rb + 7) & ~7; nd.split = splits[i];
-        nd.ks = p.K / splits[i]; nd.nstages = nd.ks / STAGE_K;
+        nd.ks = p.K / splits[i];
+        if (!pick_stage(nd)) { *why = "no stage shape for this node"; return cudaSuccess; }
         nd.rhs = p.rhs; nd.out = p.out; nd.bias = p.bias;
         nd.bias_mode = p.bias_mode; nd.bias_dt = p.bias_dt; nd.epilogue = p.epilogue;
-        if (nd.rb8 > rb8_max) rb8_max = nd.rb8;
+        slot_bytes = std::max(slot_bytes, nd.S * nd.rb8 * 128);
+        b_bytes = std::max(b_bytes, nd.nstages * nd.tiles * nd.b_tile_bytes);
+        scale_buf_bytes = std::max(scale_buf_bytes, nd.rb8 * (nd.ks / 16));
+        mmas = std::max(mmas, nd.nstages * nd.tiles * 4);
         if ((reinterpret_cast<uintptr_t>(p.lhs) | reinterpret_cast<uintptr_t>(p.rhs) | reinterpret_cast<uintptr_t>(p.lhs_scales)) % 16 != 0) {
             *why = "operands not 16-byte aligned";
             return cudaSuccess;
@@ -433,7 +593,7 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
         {
             cuuint64_t dims[2] = {(cuuint64_t)(p.K / 32), (cuuint64_t)p.M};
             cuuint64_t strides[1] = {(cuuint64_t)(p.K / 32) * 2};
-            cuuint32_t box[2] = {8, (cuuint32_t)rb};
+            cuuint32_t box[2] = {(cuuint32_t)(nd.ks / 32), (cuuint32_t)rb};
             cuuint32_t estr[2] = {1, 1};
             if (encode(&nd.map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(p.lhs_scales), dims, strides, box, estr,
                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -449,18 +609,18 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
         const char *v = getenv("RT_CHAIN_ISSUERS");
         cp.n_issue = v ? std::max(1, std::min(N_ISSUE, atoi(v))) : N_ISSUE;
     }
-    cp.slot_bytes = 2 * rb8_max * 128;
-    cp.scale_slot_bytes = rb8_max * 16;
-    cp.b_bytes = (MAX_KS / 128) * 1024; // 24 KB >= the 128 - rb8 rows an MMA may read past the ring's last sub-tile
+    cp.slot_bytes = (slot_bytes + 1023) & ~1023;
+    cp.b_bytes = (b_bytes + 1023) & ~1023;
+    cp.scale_buf_bytes = (scale_buf_bytes + 127) & ~127;
     int ring = 16;
-    while (ring > 2 && smem_for(ring, cp.slot_bytes, cp.scale_slot_bytes, cp.b_bytes) > SMEM_LIMIT) ring--;
-    if (smem_for(ring, cp.slot_bytes, cp.scale_slot_bytes, cp.b_bytes) > SMEM_LIMIT) {
+    while (ring > 2 && smem_for(ring, cp.slot_bytes, cp.b_bytes, cp.scale_buf_bytes) > SMEM_LIMIT) ring--;
+    if (smem_for(ring, cp.slot_bytes, cp.b_bytes, cp.scale_buf_bytes) > SMEM_LIMIT) {
         delete c;
         *why = "ring does not fit";
         return cudaSuccess;
     }
     cp.ring = ring;
-    c->smem = smem_for(ring, cp.slot_bytes, cp.scale_slot_bytes, cp.b_bytes);
+    c->smem = smem_for(ring, cp.slot_bytes, cp.b_bytes, cp.scale_buf_bytes);
     c->counters_bytes = 8 + sizeof(unsigned int) * nodes.size() * (size_t)grid;
     partial_ld = (partial_ld + 31) & ~31;
     e = cudaMalloc(&c->d_nodes, host.size() * sizeof(ChainNodeDev));
@@ -477,7 +637,7 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
     cp.partial = c->d_partial;
     cp.partial_ld = partial_ld;
     c->name = "q8_gemv_chain_h_nodes" + std::to_string(cp.n_nodes) + "_grid" + std::to_string(grid) + "_maxsplit" + std::to_string(max_split) +
-              "_ring" + std::to_string(ring);
+              "_ring" + std::to_string(ring) + "x" + std::to_string(cp.slot_bytes / 1024) + "k_mma" + std::to_string(mmas);
     *out = c;
     return cudaSuccess;
 }

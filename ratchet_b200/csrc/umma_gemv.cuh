@@ -99,19 +99,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// Two-column accumulator slot of one Q8_0 block (its hi and lo digit sums).
-__device__ __forceinline__ void tmem_ld2_nowait(uint32_t taddr, int &v0, int &v1) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(v0), "=r"(v1) : "r"(taddr) : "memory");
+// Four accumulator columns (two hi / lo pairs) of one MMA, no wait; the upper four values are left alone.
+__device__ __forceinline__ void tmem_ld4_nowait(uint32_t taddr, int (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(taddr) : "memory");
+}
+// Eight accumulator columns (four hi / lo pairs) of one MMA, no wait.
+__device__ __forceinline__ void tmem_ld8_nowait(uint32_t taddr, int (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Eight consecutive activations (one quarter of a Q8_0 block; the four threads of a quad hold one
-// block) -> their hi / lo int8 digits in the block's B tile, and the block's power-of-two scale.
+// block) -> their hi / lo int8 digits (eight bytes each) and the block's power-of-two scale.
 //   m = round(x / xs), |m| <= 16383, m = 256 * hi + lo with lo in [-128, 127];  x ~ m * xs.
-// `raw` holds the eight f16 values, `blk` is the block index inside the CTA's K slice, `sub` the
-// quarter (0..3).  Tiles: 8 rows x 128 bytes per 128 bytes of K (row 0 = hi, row 1 = lo, rows 2..7
-// zero), 128-byte swizzle: 16-byte chunks XOR the row index.
-__device__ __forceinline__ void digits_of_quarter_block(const uint4 raw, int blk, int sub, uint8_t *b_tiles, float *xs) {
+__device__ __forceinline__ void quantize_quarter_block(const uint4 raw, uint2 &hi8, uint2 &lo8, float &xs_of_block) {
     const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
     float v[8];
 #pragma unroll
@@ -128,7 +132,7 @@ __device__ __forceinline__ void digits_of_quarter_block(const uint4 raw, int blk
     // amax < 2^(E-126) for its exponent field E: scale it below 2^14
     const int E = (int)((__float_as_uint(amax) >> 23) & 0xFFu);
     const float scale = amax > 0.f ? __uint_as_float((uint32_t)(140 - E + 127) << 23) : 0.f;
-    const float inv = amax > 0.f ? __uint_as_float((uint32_t)(E - 13) << 23) : 0.f;
+    xs_of_block = amax > 0.f ? __uint_as_float((uint32_t)(E - 13) << 23) : 0.f;
     uint32_t hi_w[2] = {0u, 0u}, lo_w[2] = {0u, 0u};
 #pragma unroll
     for (int i = 0; i < 8; i++) {
@@ -139,17 +143,35 @@ __device__ __forceinline__ void digits_of_quarter_block(const uint4 raw, int blk
         hi_w[i >> 2] |= (uint32_t)(hi & 0xFF) << (8 * (i & 3));
         lo_w[i >> 2] |= (uint32_t)(lo & 0xFF) << (8 * (i & 3));
     }
+    hi8 = make_uint2(hi_w[0], hi_w[1]);
+    lo8 = make_uint2(lo_w[0], lo_w[1]);
+}
+
+// Stores eight digit bytes at byte `kpos` (a multiple of 8 below 128) of row `row` (0..7) of a K-major
+// 8-row x 128-byte operand tile with the 128-byte swizzle: 16-byte chunks XOR the row index.
+__device__ __forceinline__ void store_digits8(uint8_t *tile, int row, int kpos, uint2 v) {
+    const int chunk = kpos >> 4, within = kpos & 15;
+    *reinterpret_cast<uint2 *>(tile + row * 128 + ((chunk ^ row) << 4) + within) = v;
+}
+
+// The single-launch kernel's layout: one 8-row tile per 128 bytes of K, row 0 = hi, row 1 = lo, rows
+// 2..7 zero.  `blk` is the block index inside the CTA's K slice, `sub` the quarter (0..3).
+__device__ __forceinline__ void digits_of_quarter_block(const uint4 raw, int blk, int sub, uint8_t *b_tiles, float *xs) {
+    uint2 hi8, lo8;
+    float inv;
+    quantize_quarter_block(raw, hi8, lo8, inv);
     uint8_t *tile = b_tiles + (size_t)(blk >> 2) * 1024;
     const int kpos = (blk & 3) * 32 + sub * 8;
-    const int chunk = kpos >> 4, within = kpos & 15;
-    *reinterpret_cast<uint2 *>(tile + 0 * 128 + ((chunk ^ 0) << 4) + within) = make_uint2(hi_w[0], hi_w[1]);
-    *reinterpret_cast<uint2 *>(tile + 1 * 128 + ((chunk ^ 1) << 4) + within) = make_uint2(lo_w[0], lo_w[1]);
+    store_digits8(tile, 0, kpos, hi8);
+    store_digits8(tile, 1, kpos, lo8);
     if (sub == 0) xs[blk] = inv;
 }
 
 // One block's contribution to a row: d = weight scale, xsv = activation scale, (hi, lo) = the MMA's two sums.
 __device__ __forceinline__ float add_block(float acc, float d, float xsv, int hi, int lo) {
-    const float t = fmaf(256.f, (float)hi, (float)lo);
+    // 256 * hi + lo fits an int (|hi|, |lo| < 2^20): one exact integer add, one rounding to f32 - the same
+    // value as fmaf(256, hi, lo)
+    const float t = (float)(hi * 256 + lo);
     return fmaf(d * xsv, t, acc);
 }
 
