@@ -11,17 +11,21 @@
 //    that fills nearly all of shared memory (the share of a Phi-2 sized node fits whole), bounded only by
 //    free slots: weights are constants, so it runs ahead into the next nodes while the current one
 //    computes and while the CTAs meet, and HBM never waits for the dependency;
-//  * nodes are separated by a grid barrier (one atomic counter; arrival after the node's outputs are
-//    fenced, an acquire poll before the next node's activations are read), not by a launch;
+//  * nodes are separated neither by a launch nor by a barrier: every output row is also written as one
+//    32-bit word {f16 value, 16-bit tag of this dispatch} into an exchange buffer of its node, and the
+//    next node's CTAs poll exactly the words they convert until the tags are this dispatch's.  A word
+//    is its own flag, so no fence and no counter is on the path (a fence costs about 1.5 us while the
+//    SM's weight stream is in flight);
 //  * the arithmetic is that of the single-launch kernel (gemv_q8_umma.cu, shared code in umma_gemv.cuh):
 //    int8 codes straight from shared memory into tcgen05.mma kind::i8 against block-floating int8 digits
-//    of the activations, s32 sums in tensor memory, per-block rescale by four epilogue warps.  K slices of
-//    fat weights meet in global memory: each slice's CTA stores its row sums and counts itself in, and the
-//    one that arrives last adds the slices in rank order and writes the rows (thread-block clusters would
-//    do this in shared memory, but clusters of four leave 16 of the 148 SMs without a CTA).  The products
-//    are those of launching the nodes one by one; the f32 sums are taken in another order;
+//    of the activations, s32 sums in tensor memory, per-block rescale by eight epilogue warps.  K slices of
+//    fat weights meet in global memory the same way: slices 1.. store {f32 sum, 32-bit tag} words, slice 0
+//    polls them, adds in rank order and writes the rows (thread-block clusters would do this in shared
+//    memory, but clusters of four leave 16 of the 148 SMs without a CTA).  The products are those of
+//    launching the nodes one by one; the f32 sums are taken in another order;
 //  * with the SM to itself a CTA owns all 512 tensor-memory columns: every block of a stage gets its own
-//    16-column accumulator (no overlapping writes), so two warps can issue MMAs for alternate stages.
+//    16-column accumulator (no overlapping writes), so several warps can issue a stage's MMAs side by side
+//    (one thread issues a tcgen05.mma about every 140 cycles, the tensor pipe takes them faster).
 // Every wait is bounded; a wait that runs out records its site, raises the CTA's abort flag and the CTA
 // leaves its loops, frees tensor memory and returns; the other CTAs run into their own limits.
 #include <cuda.h>
@@ -44,7 +48,7 @@ namespace {
 
 using namespace umma_gemv;
 
-constexpr int N_ISSUE = 2;                               // MMA-issuing warps (stage g belongs to issuer g % n_issue)
+constexpr int N_ISSUE = 4;                               // MMA-issuing warps: MMA m of a stage belongs to issuer m % n_issue
 constexpr int THREADS = 64 + 256 + 32 * (N_ISSUE - 1);   // warp 0 producer, warp 1 issuer 0, warps 2-9 epilogue, warps 10.. issuers 1..
 constexpr int CHUNK_K = 128;                             // bytes of K per sub-tile row (one swizzle row) = 4 Q8_0 blocks
 constexpr int MAX_S = 8;                                 // sub-tiles (chunks) per ring stage
@@ -77,7 +81,9 @@ struct alignas(16) ChainNodeInfo { // 128 bytes: what the warps other than the p
     int c0[MAX_TILES], c1[MAX_TILES];
     int bias_mode, bias_dt, epilogue;
     int inv_S_q16;               // ceil(65536 / S): chunk / S without a division
-    int pad[4];
+    int x_off;                   // this node's output words in the exchange buffer (32-bit words)
+    int p_off;                   // this node's K-slice sums in the slice buffer (64-bit words), rank-major, ld = M
+    int pad[2];
 };
 static_assert(sizeof(ChainNodeInfo) == 128, "ChainNodeInfo is copied as 32 words");
 
@@ -94,10 +100,9 @@ struct ChainParams {
     int b_bytes;         // digit tiles, and the guard behind the ring
     int scale_buf_bytes; // one node's scales: rb8 rows of ks/32 f16 (two buffers)
     int n_issue;         // MMA-issuing warps in use (<= N_ISSUE)
-    unsigned long long *counter; // grid barrier: arrivals so far
-    unsigned int *unit_count;    // [n_nodes][gridDim.x]: K slices of a unit that have stored their row sums
-    float *partial;              // [max split][partial_ld]: row sums of the K slices of the node in flight
-    int partial_ld;
+    unsigned int *xbuf;          // every node's output rows as {f16 value, 16-bit tag} words
+    unsigned long long *pbuf;    // K-sliced nodes: the slices' row sums as {f32 sum, 32-bit tag} words
+    unsigned int tag;            // this dispatch's tag: 1..65535, never the previous dispatch's
 };
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site) {
@@ -120,7 +125,6 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
     const int n_bars = 2 * cp.ring + 2 * TGROUPS + 1 + 4;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + n_bars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    volatile unsigned int *arrived_before = reinterpret_cast<volatile unsigned int *>(tmem_slot + 2);
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + cp.ring);
     const uint32_t bar_tfull = smem_u32(bars + 2 * cp.ring), bar_tempty = smem_u32(bars + 2 * cp.ring + TGROUPS);
     const uint32_t bar_x = smem_u32(bars + 2 * cp.ring + 2 * TGROUPS);
@@ -129,10 +133,10 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
     if (threadIdx.x == 0) {
         for (int s = 0; s < cp.ring; s++) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 1); // the MMAs' commit
+            mbar_init(bar_empty + 8 * s, cp.n_issue); // every issuer's commit
         }
         for (int a = 0; a < TGROUPS; a++) {
-            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tfull + 8 * a, cp.n_issue);
             mbar_init(bar_tempty + 8 * a, 8);
         }
         mbar_init(bar_x, 8);
@@ -194,11 +198,11 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
     } else if (warp == 1 || warp >= 10) {
         // ------------------------------------------------------------------ MMA issuers
         const int issuer = warp == 1 ? 0 : warp - 9;
-        if (lane == 0) {
+        if (lane == 0 && issuer < cp.n_issue) {
             // instruction descriptor: s32 accumulate, signed 8-bit A and B, K-major, N = 16, M = 128
             const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
             const uint64_t a_desc_ring = umma_desc_sw128(smem_u32(ring), 1024);
-            int slot = 0, tg = 0, turn = 0;
+            int slot = 0, tg = 0;
             uint32_t phase = 0, tphase = 0, xphase = 0;
             bool ok = true;
             for (int l = 0; l < cp.n_nodes && ok; l++) {
@@ -214,23 +218,21 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 // 16-row digit tiles are two 8-row groups 1024 bytes apart; 8-row tiles repeat their group (stride 0)
                 const uint64_t b_desc_base = umma_desc_sw128(smem_u32(b_tiles), btb == 2048 ? 1024 : 0);
                 for (int s = 0; s < nstages; s++) {
-                    if (turn == issuer) {
-                        if (!mbar_wait(bar_tempty + 8 * tg, tphase ^ 1, abort_flag, 3)) { ok = false; break; }
-                        if (!mbar_wait(bar_full + 8 * slot, phase, abort_flag, 4)) { ok = false; break; }
-                        tc_fence_after();
-                        const uint64_t a_desc = a_desc_ring + (uint64_t)((uint32_t)(slot * cp.slot_bytes) >> 4);
-                        const uint32_t d0 = tmem_base + tg * TG_COLS;
-                        for (int t = 0; t < tiles; t++) {
-                            const uint64_t at = a_desc + (uint64_t)(t * (128 * 128 >> 4));
-                            const uint64_t bt = b_desc_base + (uint64_t)((uint32_t)((s * tiles + t) * btb) >> 4);
-                            // block j of the chunks: 32 bytes further along K in both operands; its own 16 columns
-#pragma unroll
-                            for (int j = 0; j < 4; j++) umma_i8(d0 + (t * 4 + j) * 16, at + 2 * j, bt + 2 * j, idesc);
-                        }
-                        umma_commit(bar_empty + 8 * slot);
-                        umma_commit(bar_tfull + 8 * tg);
+                    if (!mbar_wait(bar_tempty + 8 * tg, tphase ^ 1, abort_flag, 3)) { ok = false; break; }
+                    if (!mbar_wait(bar_full + 8 * slot, phase, abort_flag, 4)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t a_desc = a_desc_ring + (uint64_t)((uint32_t)(slot * cp.slot_bytes) >> 4);
+                    const uint32_t d0 = tmem_base + tg * TG_COLS;
+                    // MMA m = 4 t + j: tile t (128 stream rows), block j of the chunks (32 bytes further along K in
+                    // both operands), its own 16 columns
+                    for (int m = issuer; m < 4 * tiles; m += cp.n_issue) {
+                        const int t = m >> 2, j = m & 3;
+                        const uint64_t at = a_desc + (uint64_t)(t * (128 * 128 >> 4)) + 2 * j;
+                        const uint64_t bt = b_desc_base + (uint64_t)((uint32_t)((s * tiles + t) * btb) >> 4) + 2 * j;
+                        umma_i8(d0 + m * 16, at, bt, idesc);
                     }
-                    if (++turn == cp.n_issue) turn = 0;
+                    umma_commit(bar_empty + 8 * slot);
+                    umma_commit(bar_tfull + 8 * tg);
                     if (++slot == cp.ring) { slot = 0; phase ^= 1; }
                     if (++tg == TGROUPS) { tg = 0; tphase ^= 1; }
                 }
@@ -244,7 +246,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
         const int half = (warp - 2) >> 2;     // which two blocks of every chunk
         const int et = threadIdx.x - 64;      // 0..255
         const int row_local = q * 32 + lane;  // this thread's tensor-memory lane
-        int tg = 0, sbuf = 0;
+        int tg = 0, sbuf = 0, prev_x_off = 0;
         uint32_t tphase = 0, sphase = 0;
         bool ok = true;
         for (int l = 0; l < cp.n_nodes && ok; l++) {
@@ -256,26 +258,6 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
             // copy any more: node l-1 is over for every warp of this CTA once its sums were taken)
             int next_word = 0;
             if (warp == 2 && l + 1 < cp.n_nodes) next_word = reinterpret_cast<const int *>(static_cast<const ChainNodeInfo *>(cp.nodes + l + 1))[lane];
-            if (l > 0) {
-                // node l-1 is complete on every CTA: (l) * gridDim.x arrivals
-                if (et == 0) {
-                    const unsigned long long target = (unsigned long long)l * gridDim.x;
-                    const unsigned long long t0 = wait_clock();
-                    while (true) {
-                        unsigned long long v;
-                        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(cp.counter) : "memory");
-                        if (v >= target) break;
-                        if (*abort_flag) break;
-                        if (wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
-                            *abort_flag = 1;
-                            atomicCAS(&g_gemv_chain_error, 0, 8);
-                            break;
-                        }
-                    }
-                }
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                if (*abort_flag) break;
-            }
             if (warp == 2 && l + 1 < cp.n_nodes) reinterpret_cast<int *>(info + ((l + 1) & 1))[lane] = next_word;
             if (!has_rows) {
                 __syncwarp();
@@ -289,15 +271,46 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
 #pragma unroll
                 for (int t = 0; t < MAX_TILES; t++) { c0[t] = nd.c0[t]; c1[t] = nd.c1[t]; }
                 {
-                    // another SM wrote these activations during this launch: read them from L2
-                    const __half *x = (const __half *)nd.rhs + k_begin;
                     const int sub = et & 3; // 4 threads per block of 32 elements, 8 elements each
                     constexpr int MAX_IT = (MAX_KS / 32 + 63) / 64;
                     uint4 pre[MAX_IT];
+                    if (l == 0) {
+                        // the first node's activations were there before the launch
+                        const __half *x = (const __half *)nd.rhs + k_begin;
 #pragma unroll
-                    for (int it = 0; it < MAX_IT; it++) { // all loads first: one L2 round trip, not one per iteration
-                        const int blk = (et >> 2) + it * 64;
-                        pre[it] = blk < ks / 32 ? __ldcg(reinterpret_cast<const uint4 *>(x + blk * 32 + sub * 8)) : make_uint4(0u, 0u, 0u, 0u);
+                        for (int it = 0; it < MAX_IT; it++) {
+                            const int blk = (et >> 2) + it * 64;
+                            pre[it] = blk < ks / 32 ? __ldcg(reinterpret_cast<const uint4 *>(x + blk * 32 + sub * 8)) : make_uint4(0u, 0u, 0u, 0u);
+                        }
+                    } else {
+                        // The previous node's rows arrive as {f16, tag} words from the CTAs that compute them: poll the
+                        // eight words of each of this thread's quarter blocks until all carry this dispatch's tag.
+                        const unsigned int *xw = cp.xbuf + prev_x_off + k_begin;
+                        const unsigned long long t0 = wait_clock();
+#pragma unroll
+                        for (int it = 0; it < MAX_IT; it++) {
+                            const int blk = (et >> 2) + it * 64;
+                            pre[it] = make_uint4(0u, 0u, 0u, 0u);
+                            if (blk >= ks / 32) continue;
+                            const unsigned int *src = xw + blk * 32 + sub * 8;
+                            while (true) {
+                                uint4 a, b;
+                                asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(src) : "memory");
+                                asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(src + 4) : "memory");
+                                const unsigned int want = cp.tag << 16;
+                                const unsigned int miss = ((a.x ^ want) | (a.y ^ want) | (a.z ^ want) | (a.w ^ want) | (b.x ^ want) | (b.y ^ want) | (b.z ^ want) | (b.w ^ want)) >> 16;
+                                if (miss == 0) {
+                                    pre[it] = make_uint4((a.x & 0xFFFFu) | (a.y << 16), (a.z & 0xFFFFu) | (a.w << 16), (b.x & 0xFFFFu) | (b.y << 16), (b.z & 0xFFFFu) | (b.w << 16));
+                                    break;
+                                }
+                                if (*abort_flag) break;
+                                if (wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
+                                    *abort_flag = 1;
+                                    atomicCAS(&g_gemv_chain_error, 0, 8);
+                                    break;
+                                }
+                            }
+                        }
                     }
 #pragma unroll
                     for (int it = 0; it < MAX_IT; it++) {
@@ -324,6 +337,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 // the MMAs read the tiles through the async proxy
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("bar.sync 1, 256;" ::: "memory"); // xs visible to all epilogue warps
+                if (*abort_flag) break;
                 if (lane == 0) mbar_arrive(bar_x);
 
                 // where this thread's lane sits in the stage's row stream, tile by tile
@@ -411,21 +425,32 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 }
                 bool writes_rows = true;
                 if (split > 1) {
-                    // K slices meet: store this slice's row sums, count it in; the slice that arrives last adds all
-                    // of them in rank order and writes the rows.
-                    if (my_rows) cp.partial[(size_t)rank * cp.partial_ld + row_begin + et] = sum;
-                    asm volatile("bar.sync 1, 256;" ::: "memory");
-                    if (et == 0) {
-                        __threadfence(); // the CTA's sums (ordered before by the barrier) are out before the count
-                        *arrived_before = atomicAdd(cp.unit_count + (size_t)l * gridDim.x + unit, 1u);
-                        __threadfence(); // and the other slices' sums are read after it
-                    }
-                    asm volatile("bar.sync 1, 256;" ::: "memory");
-                    writes_rows = *arrived_before == (unsigned int)(split - 1);
-                    if (writes_rows && my_rows) {
-                        const float *pr = cp.partial + row_begin + et;
-                        sum = __ldcg(pr);
-                        for (int r = 1; r < split; r++) sum += __ldcg(pr + (size_t)r * cp.partial_ld);
+                    // K slices meet: slices 1.. store {sum, tag} words, slice 0 polls them and adds in rank order
+                    unsigned long long *pw = cp.pbuf + nd.p_off + row_begin + et;
+                    if (rank != 0) {
+                        writes_rows = false;
+                        if (my_rows) {
+                            const unsigned long long word = ((unsigned long long)cp.tag << 32) | __float_as_uint(sum);
+                            asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(pw + (size_t)rank * nd.M), "l"(word) : "memory");
+                        }
+                    } else if (my_rows) {
+                        const unsigned long long t0 = wait_clock();
+                        for (int r = 1; r < split; r++) {
+                            while (true) {
+                                unsigned long long word;
+                                asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(word) : "l"(pw + (size_t)r * nd.M) : "memory");
+                                if ((unsigned int)(word >> 32) == cp.tag) {
+                                    sum += __uint_as_float((unsigned int)word);
+                                    break;
+                                }
+                                if (*abort_flag) break;
+                                if (wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
+                                    *abort_flag = 1;
+                                    atomicCAS(&g_gemv_chain_error, 0, 7);
+                                    break;
+                                }
+                            }
+                        }
                     }
                 }
                 if (writes_rows && my_rows) {
@@ -433,17 +458,17 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                     const bool has_bias = nd.bias_mode != BIAS_NONE;
                     float bias = 0.f;
                     if (has_bias) bias = load_bias(nd.bias, nd.bias_dt, nd.bias_mode == BIAS_PER_M ? row : 0);
-                    ((__half *)nd.out)[row] = epilogue_value<__half>(sum, has_bias, bias, nd.epilogue);
+                    const __half y = epilogue_value<__half>(sum, has_bias, bias, nd.epilogue);
+                    // for the next node: value and tag in one word, so the word is its own "ready" flag
+                    const unsigned int word = (cp.tag << 16) | (unsigned int)__half_as_ushort(y);
+                    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(cp.xbuf + nd.x_off + row), "r"(word) : "memory");
+                    ((__half *)nd.out)[row] = y; // for the caller, after the kernel
                 }
             }
-            if (l + 1 < cp.n_nodes) {
-                // publish: this CTA's part of node l is in memory (and its reads of node l's inputs are over)
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                if (et == 0) {
-                    __threadfence();
-                    atomicAdd(cp.counter, 1ull);
-                }
-            }
+            prev_x_off = nd.x_off;
+            // every warp is done with node l's description, digits scales and sums before the next node's are written
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (*abort_flag) break;
         }
     }
 
@@ -509,9 +534,9 @@ struct GemvChain {
     int device = 0;
     ChainParams cp{};
     ChainNodeDev *d_nodes = nullptr;
-    unsigned char *d_counters = nullptr; // grid barrier counter (8 bytes), then the per-unit slice counts
-    size_t counters_bytes = 0;
-    float *d_partial = nullptr;
+    unsigned int *d_xbuf = nullptr;        // {f16, tag} words of every node's output rows
+    unsigned long long *d_pbuf = nullptr;  // {f32, tag} words of the K slices' row sums
+    unsigned int tag = 0;                  // the last dispatch's tag
     int grid = 0;
     size_t smem = 0;
     std::string name;
@@ -523,8 +548,8 @@ void gemv_chain_destroy(GemvChain *c) {
     if (!c) return;
     cudaSetDevice(c->device);
     if (c->d_nodes) cudaFree(c->d_nodes);
-    if (c->d_counters) cudaFree(c->d_counters);
-    if (c->d_partial) cudaFree(c->d_partial);
+    if (c->d_xbuf) cudaFree(c->d_xbuf);
+    if (c->d_pbuf) cudaFree(c->d_pbuf);
     delete c;
 }
 
@@ -536,13 +561,15 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
     if (!encode) { *why = "no cuTensorMapEncodeTiled"; return cudaSuccess; }
     if (nodes.size() < 2) { *why = "fewer than two nodes"; return cudaSuccess; }
     std::vector<int> splits;
-    int max_split = 1, partial_ld = 0;
-    for (const MatmulParams &p : nodes) {
+    int max_split = 1;
+    for (size_t i = 0; i < nodes.size(); i++) {
+        const MatmulParams &p = nodes[i];
         const int s = p.K >= 256 ? split_for(p.K) : 0;
         if (s == 0) { *why = "K is not a multiple of 256 per slice"; return cudaSuccess; }
         splits.push_back(s);
         if (s > max_split) max_split = s;
-        if (s > 1 && p.M > partial_ld) partial_ld = p.M;
+        // the nodes hand their rows on through tagged words: node i must read exactly what node i-1 wrote
+        if (i > 0 && (p.rhs != nodes[i - 1].out || p.K != nodes[i - 1].M)) { *why = "not a chain: a node does not read its predecessor's output"; return cudaSuccess; }
     }
 
     cudaError_t e = cudaSetDevice(device);
@@ -561,6 +588,7 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
 
     std::vector<ChainNodeDev> host(nodes.size());
     int slot_bytes = 0, b_bytes = GUARD_BYTES, scale_buf_bytes = 0, mmas = 0;
+    size_t x_words = 0, p_words = 0;
     for (size_t i = 0; i < nodes.size(); i++) {
         const MatmulParams &p = nodes[i];
         ChainNodeDev &nd = host[i];
@@ -577,6 +605,10 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
         b_bytes = std::max(b_bytes, nd.nstages * nd.tiles * nd.b_tile_bytes);
         scale_buf_bytes = std::max(scale_buf_bytes, nd.rb8 * (nd.ks / 16));
         mmas = std::max(mmas, nd.nstages * nd.tiles * 4);
+        nd.x_off = (int)x_words;
+        x_words += (size_t)((p.M + 31) & ~31);
+        nd.p_off = (int)p_words;
+        if (nd.split > 1) p_words += (size_t)nd.split * p.M;
         if ((reinterpret_cast<uintptr_t>(p.lhs) | reinterpret_cast<uintptr_t>(p.rhs) | reinterpret_cast<uintptr_t>(p.lhs_scales)) % 16 != 0) {
             *why = "operands not 16-byte aligned";
             return cudaSuccess;
@@ -621,31 +653,29 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
     }
     cp.ring = ring;
     c->smem = smem_for(ring, cp.slot_bytes, cp.b_bytes, cp.scale_buf_bytes);
-    c->counters_bytes = 8 + sizeof(unsigned int) * nodes.size() * (size_t)grid;
-    partial_ld = (partial_ld + 31) & ~31;
     e = cudaMalloc(&c->d_nodes, host.size() * sizeof(ChainNodeDev));
-    if (e == cudaSuccess) e = cudaMalloc(&c->d_counters, c->counters_bytes);
-    if (e == cudaSuccess && partial_ld > 0) e = cudaMalloc(&c->d_partial, sizeof(float) * (size_t)max_split * partial_ld);
+    if (e == cudaSuccess) e = cudaMalloc(&c->d_xbuf, sizeof(unsigned int) * x_words);
+    if (e == cudaSuccess) e = cudaMemset(c->d_xbuf, 0, sizeof(unsigned int) * x_words); // tag 0: no dispatch
+    if (e == cudaSuccess && p_words > 0) e = cudaMalloc(&c->d_pbuf, sizeof(unsigned long long) * p_words);
+    if (e == cudaSuccess && p_words > 0) e = cudaMemset(c->d_pbuf, 0, sizeof(unsigned long long) * p_words);
     if (e == cudaSuccess) e = cudaMemcpy(c->d_nodes, host.data(), host.size() * sizeof(ChainNodeDev), cudaMemcpyHostToDevice);
     if (e != cudaSuccess) {
         gemv_chain_destroy(c);
         return e;
     }
     cp.nodes = c->d_nodes;
-    cp.counter = reinterpret_cast<unsigned long long *>(c->d_counters);
-    cp.unit_count = reinterpret_cast<unsigned int *>(c->d_counters + 8);
-    cp.partial = c->d_partial;
-    cp.partial_ld = partial_ld;
+    cp.xbuf = c->d_xbuf;
+    cp.pbuf = c->d_pbuf;
     c->name = "q8_gemv_chain_h_nodes" + std::to_string(cp.n_nodes) + "_grid" + std::to_string(grid) + "_maxsplit" + std::to_string(max_split) +
               "_ring" + std::to_string(ring) + "x" + std::to_string(cp.slot_bytes / 1024) + "k_mma" + std::to_string(mmas);
     *out = c;
     return cudaSuccess;
 }
 
-// One dispatch of the whole chain: the counters start from zero, then one cooperative launch.
+// One dispatch of the whole chain: a new tag, one cooperative launch.
 cudaError_t gemv_chain_launch(GemvChain *c, cudaStream_t stream) {
-    cudaError_t e = cudaMemsetAsync(c->d_counters, 0, c->counters_bytes, stream);
-    if (e != cudaSuccess) return e;
+    c->tag = c->tag >= 65535u ? 1u : c->tag + 1u;
+    c->cp.tag = c->tag;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(c->grid);
     lc.blockDim = dim3(THREADS);
