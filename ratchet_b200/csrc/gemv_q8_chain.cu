@@ -103,6 +103,7 @@ struct ChainParams {
     unsigned int *xbuf;          // every node's output rows as {f16 value, 16-bit tag} words
     unsigned long long *pbuf;    // K-sliced nodes: the slices' row sums as {f32 sum, 32-bit tag} words
     unsigned int tag;            // this dispatch's tag: 1..65535, never the previous dispatch's
+    int pace;            // least number of cycles between two chunk copies of the producer (0: none)
 };
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site) {
@@ -162,6 +163,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
         if (lane == 0) {
             int slot = 0, sbuf = 0;
             uint32_t phase = 0, sphase = 0;
+            long long last_copy = clock64();
             bool ok = true;
             for (int l = 0; l < cp.n_nodes && ok; l++) {
                 const ChainNodeDev &nd = cp.nodes[l];
@@ -190,7 +192,15 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                     const uint32_t full = bar_full + 8 * slot;
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(tx) : "memory");
                     const int kb = k_begin + s * S * CHUNK_K;
-                    for (int c = 0; c < S; c++) tma_load_2d(st + c * rb8 * 128, map_w, kb + c * CHUNK_K, row_begin, full);
+                    for (int c = 0; c < S; c++) {
+                        // Copies are spread over the node's time instead of bursting when the MMAs free the slots:
+                        // MMA operand reads (about 100 bytes per cycle) and copy writes share the shared-memory port.
+                        if (cp.pace > 0) {
+                            while (clock64() - last_copy < cp.pace) {}
+                            last_copy = clock64();
+                        }
+                        tma_load_2d(st + c * rb8 * 128, map_w, kb + c * CHUNK_K, row_begin, full);
+                    }
                     if (++slot == cp.ring) { slot = 0; phase ^= 1; }
                 }
             }
@@ -468,6 +478,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
             prev_x_off = nd.x_off;
             // every warp is done with node l's description, digits scales and sums before the next node's are written
             asm volatile("bar.sync 1, 256;" ::: "memory");
+
             if (*abort_flag) break;
         }
     }
@@ -640,6 +651,9 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
     {
         const char *v = getenv("RT_CHAIN_ISSUERS");
         cp.n_issue = v ? std::max(1, std::min(N_ISSUE, atoi(v))) : N_ISSUE;
+        const char *pv = getenv("RT_CHAIN_PACE");
+        cp.pace = pv ? std::max(0, atoi(pv)) : 300;
+
     }
     cp.slot_bytes = (slot_bytes + 1023) & ~1023;
     cp.b_bytes = (b_bytes + 1023) & ~1023;
