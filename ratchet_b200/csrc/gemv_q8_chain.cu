@@ -48,13 +48,13 @@ namespace {
 
 using namespace umma_gemv;
 
-constexpr int N_ISSUE = 4;                               // MMA-issuing warps: MMA m of a stage belongs to issuer m % n_issue
+constexpr int N_ISSUE = 4;                               // MMA-issuing warps at most: stage g belongs to issuer g % n_issue
 constexpr int THREADS = 64 + 256 + 32 * (N_ISSUE - 1);   // warp 0 producer, warp 1 issuer 0, warps 2-9 epilogue, warps 10.. issuers 1..
 constexpr int CHUNK_K = 128;                             // bytes of K per sub-tile row (one swizzle row) = 4 Q8_0 blocks
 constexpr int MAX_S = 8;                                 // sub-tiles (chunks) per ring stage
-constexpr int MAX_TILES = 4;                             // 128-row MMA tiles per stage
+constexpr int MAX_TILES = 3;                             // 128-row MMA tiles per stage
 constexpr int TMEM_COLS = 512;
-constexpr int TG_COLS = 256;                             // MAX_TILES x 4 blocks x 16 columns
+constexpr int TG_COLS = 128;                             // columns of one stage's accumulators (see col_stride)
 constexpr int TGROUPS = TMEM_COLS / TG_COLS;
 constexpr int MAX_KS = 3072;                             // bytes of K per CTA and node
 constexpr int GUARD_BYTES = 16384;                       // an MMA tile may read up to 128 rows past its stage
@@ -78,12 +78,13 @@ struct alignas(16) ChainNodeInfo { // 128 bytes: what the warps other than the p
     int rb, rb8, ks, split;
     int S, nstages, tiles;       // chunks per stage, stages per node, MMA tiles per stage
     int b_tile_bytes;            // 1024 (8 digit rows: at most 4 chunks per tile) or 2048 (16 rows)
-    int c0[MAX_TILES], c1[MAX_TILES];
+    int c0[4], c1[4];
     int bias_mode, bias_dt, epilogue;
     int inv_S_q16;               // ceil(65536 / S): chunk / S without a division
+    int col_stride;              // tensor-memory columns between two MMAs' accumulators: 8 or 16
     int x_off;                   // this node's output words in the exchange buffer (32-bit words)
     int p_off;                   // this node's K-slice sums in the slice buffer (64-bit words), rank-major, ld = M
-    int pad[2];
+    int pad[1];
 };
 static_assert(sizeof(ChainNodeInfo) == 128, "ChainNodeInfo is copied as 32 words");
 
@@ -122,22 +123,23 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
     float *part = xs + MAX_KS / 32;                               // [2 block pairs][MAX_TILES x 128 stream rows]: row sums
     ChainNodeInfo *info = reinterpret_cast<ChainNodeInfo *>(part + 2 * MAX_TILES * 128); // [2]: this node's and the next one's
     uint64_t *bars = reinterpret_cast<uint64_t *>(info + 2);
-    // bars: [0..R) full, [R..2R) empty, TGROUPS tmem_full, TGROUPS tmem_empty, digits ready, 2 scales full, 2 scales empty
+    // bars: [0..R) full, [R..2R) done (the stage's MMAs are complete: its sums are in tensor memory AND its slot is
+    // free - one tcgen05.commit per stage, a commit costs the tensor pipe about as much as an MMA), TGROUPS
+    // unused, TGROUPS tmem_empty, digits ready, 2 scales full, 2 scales empty
     const int n_bars = 2 * cp.ring + 2 * TGROUPS + 1 + 4;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + n_bars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + cp.ring);
-    const uint32_t bar_tfull = smem_u32(bars + 2 * cp.ring), bar_tempty = smem_u32(bars + 2 * cp.ring + TGROUPS);
+    const uint32_t bar_full = smem_u32(bars), bar_done = smem_u32(bars + cp.ring);
+    const uint32_t bar_tempty = smem_u32(bars + 2 * cp.ring + TGROUPS);
     const uint32_t bar_x = smem_u32(bars + 2 * cp.ring + 2 * TGROUPS);
     const uint32_t bar_sfull = bar_x + 8, bar_sempty = bar_x + 24;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < cp.ring; s++) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, cp.n_issue); // every issuer's commit
+            mbar_init(bar_done + 8 * s, 1); // the commit of the stage's issuer
         }
         for (int a = 0; a < TGROUPS; a++) {
-            mbar_init(bar_tfull + 8 * a, cp.n_issue);
             mbar_init(bar_tempty + 8 * a, 8);
         }
         mbar_init(bar_x, 8);
@@ -187,7 +189,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 }
                 const uint32_t tx = (uint32_t)nd.rb * 128u * (uint32_t)S;
                 for (int s = 0; s < nstages; s++) {
-                    if (!mbar_wait(bar_empty + 8 * slot, phase ^ 1, abort_flag, 1)) { ok = false; break; }
+                    if (!mbar_wait(bar_done + 8 * slot, phase ^ 1, abort_flag, 1)) { ok = false; break; }
                     const uint32_t st = smem_u32(ring + (size_t)slot * cp.slot_bytes);
                     const uint32_t full = bar_full + 8 * slot;
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(tx) : "memory");
@@ -212,7 +214,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
             // instruction descriptor: s32 accumulate, signed 8-bit A and B, K-major, N = 16, M = 128
             const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
             const uint64_t a_desc_ring = umma_desc_sw128(smem_u32(ring), 1024);
-            int slot = 0, tg = 0;
+            int slot = 0, tg = 0, turn = 0;
             uint32_t phase = 0, tphase = 0, xphase = 0;
             bool ok = true;
             for (int l = 0; l < cp.n_nodes && ok; l++) {
@@ -220,7 +222,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 const ChainNodeInfo &nd = info[l & 1];
                 const int unit = (int)blockIdx.x / nd.split;
                 const bool has_rows = unit * nd.rb < nd.M;
-                const int nstages = nd.nstages, tiles = nd.tiles, btb = nd.b_tile_bytes;
+                const int nstages = nd.nstages, tiles = nd.tiles, btb = nd.b_tile_bytes, cstride = nd.col_stride;
                 // one phase of bar_x per node: the node's digits are in place (and the next node's description)
                 if (!mbar_wait(bar_x, xphase, abort_flag, 2)) break;
                 xphase ^= 1;
@@ -228,21 +230,27 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 // 16-row digit tiles are two 8-row groups 1024 bytes apart; 8-row tiles repeat their group (stride 0)
                 const uint64_t b_desc_base = umma_desc_sw128(smem_u32(b_tiles), btb == 2048 ? 1024 : 0);
                 for (int s = 0; s < nstages; s++) {
-                    if (!mbar_wait(bar_tempty + 8 * tg, tphase ^ 1, abort_flag, 3)) { ok = false; break; }
-                    if (!mbar_wait(bar_full + 8 * slot, phase, abort_flag, 4)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint64_t a_desc = a_desc_ring + (uint64_t)((uint32_t)(slot * cp.slot_bytes) >> 4);
-                    const uint32_t d0 = tmem_base + tg * TG_COLS;
-                    // MMA m = 4 t + j: tile t (128 stream rows), block j of the chunks (32 bytes further along K in
-                    // both operands), its own 16 columns
-                    for (int m = issuer; m < 4 * tiles; m += cp.n_issue) {
-                        const int t = m >> 2, j = m & 3;
-                        const uint64_t at = a_desc + (uint64_t)(t * (128 * 128 >> 4)) + 2 * j;
-                        const uint64_t bt = b_desc_base + (uint64_t)((uint32_t)((s * tiles + t) * btb) >> 4) + 2 * j;
-                        umma_i8(d0 + m * 16, at, bt, idesc);
+                    if (turn == issuer) { // a stage is one issuer's: its single commit covers all of the stage's MMAs
+                        if (!mbar_wait(bar_tempty + 8 * tg, tphase ^ 1, abort_flag, 3)) { ok = false; break; }
+                        if (!mbar_wait(bar_full + 8 * slot, phase, abort_flag, 4)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint64_t a_desc = a_desc_ring + (uint64_t)((uint32_t)(slot * cp.slot_bytes) >> 4);
+                        const uint32_t d0 = tmem_base + tg * TG_COLS;
+                        for (int t = 0; t < tiles; t++) {
+                            // tile t: 128 stream rows; block j of the chunks: 32 bytes further along K in both operands,
+                            // its own 16 columns
+                            const uint64_t at = a_desc + (uint64_t)(t * (128 * 128 >> 4));
+                            const uint64_t bt = b_desc_base + (uint64_t)((uint32_t)((s * tiles + t) * btb) >> 4);
+#pragma unroll
+                            // An MMA writes 16 columns, of which at most the first 2 * (chunks of the tile) are ever read.
+                            // With a stride of 8 the next MMA of this thread overwrites the unread upper half (the tensor
+                            // pipe runs one thread's MMAs in issue order), which fits four stages into tensor memory, so
+                            // that no stage of a node waits for the epilogue of another.
+                            for (int j = 0; j < 4; j++) umma_i8(d0 + (t * 4 + j) * cstride, at + 2 * j, bt + 2 * j, idesc);
+                        }
+                        umma_commit(bar_done + 8 * slot);
                     }
-                    umma_commit(bar_empty + 8 * slot);
-                    umma_commit(bar_tfull + 8 * tg);
+                    if (++turn == cp.n_issue) turn = 0;
                     if (++slot == cp.ring) { slot = 0; phase ^= 1; }
                     if (++tg == TGROUPS) { tg = 0; tphase ^= 1; }
                 }
@@ -256,8 +264,8 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
         const int half = (warp - 2) >> 2;     // which two blocks of every chunk
         const int et = threadIdx.x - 64;      // 0..255
         const int row_local = q * 32 + lane;  // this thread's tensor-memory lane
-        int tg = 0, sbuf = 0, prev_x_off = 0;
-        uint32_t tphase = 0, sphase = 0;
+        int tg = 0, sbuf = 0, prev_x_off = 0, slot = 0;
+        uint32_t sphase = 0, phase = 0;
         bool ok = true;
         for (int l = 0; l < cp.n_nodes && ok; l++) {
             const ChainNodeInfo &nd = info[l & 1];
@@ -274,7 +282,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 if (lane == 0) mbar_arrive(bar_x);
             }
             if (has_rows) {
-                const int ks = nd.ks, nstages = nd.nstages, rb8 = nd.rb8, S = nd.S, tiles = nd.tiles, btb = nd.b_tile_bytes;
+                const int ks = nd.ks, nstages = nd.nstages, rb8 = nd.rb8, S = nd.S, tiles = nd.tiles, btb = nd.b_tile_bytes, cstride = nd.col_stride;
                 const int k_begin = rank * ks, inv_S = nd.inv_S_q16;
                 const int rows_here = min(nd.rb, nd.M - row_begin);
                 int c0[MAX_TILES], c1[MAX_TILES];
@@ -354,6 +362,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 int my_cl[MAX_TILES], my_row[MAX_TILES], my_k[MAX_TILES], col0[MAX_TILES];
                 bool mine[MAX_TILES], warp_has[MAX_TILES];
                 float acc[MAX_TILES];
+                int sc_off[MAX_TILES], xs_off[MAX_TILES];
                 const bool narrow = rb8 >= 32; // a warp's 32 lanes then belong to at most two chunks: two column pairs do
 #pragma unroll
                 for (int t = 0; t < MAX_TILES; t++) {
@@ -362,45 +371,55 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                     my_row[t] = pos - my_cl[t] * rb8;
                     warp_has[t] = t < tiles && pos_w < S * rb8;
                     mine[t] = t < tiles && pos < S * rb8 && my_row[t] < rows_here;
-                    const int d_first = min(pos_w / rb8 - c0[t], narrow ? 6 : 4); // first of the column pairs this warp loads
+                    // first of the column pairs this warp loads: two pairs (narrow) or four, inside the MMA's cstride columns
+                    const int d_first = min(pos_w / rb8 - c0[t], cstride / 2 - (narrow ? 2 : 4));
                     col0[t] = 2 * d_first;
                     my_k[t] = my_cl[t] - c0[t] - d_first;
                     acc[t] = 0.f;
+                    // where this lane's scales and activation scales are (lanes outside the stage read some valid
+                    // place: their sums are dropped)
+                    const int cl_in = min(my_cl[t], S - 1), row_in = min(my_row[t], rb8 - 1);
+                    sc_off[t] = row_in * (ks / 16) + (cl_in * 4 + half * 2) * 2;
+                    xs_off[t] = cl_in * 4 + half * 2;
                 }
                 const uint8_t *scales_n = scales_s + (size_t)sbuf * cp.scale_buf_bytes;
                 const int srow = ks / 16; // bytes per row of the node's scales
                 if (!mbar_wait(bar_sfull + 8 * sbuf, sphase, abort_flag, 10)) break;
                 for (int s = 0; s < nstages; s++) {
-                    if (!mbar_wait(bar_tfull + 8 * tg, tphase, abort_flag, 6)) { ok = false; break; }
+                    if (!mbar_wait(bar_done + 8 * slot, phase, abort_flag, 6)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t t0 = tmem_base + tg * TG_COLS + ((uint32_t)(q * 32) << 16) + half * 32;
+                    const uint32_t t0 = tmem_base + tg * TG_COLS + ((uint32_t)(q * 32) << 16) + half * 2 * cstride;
                     // all of the stage's loads first (one wait), then the arithmetic
-                    int v[MAX_TILES][2][8];
+                    int v[MAX_TILES][2][8] = {};
                     if (narrow) {
 #pragma unroll
                         for (int t = 0; t < MAX_TILES; t++) {
                             if (!warp_has[t]) continue;
 #pragma unroll
-                            for (int j = 0; j < 2; j++) tmem_ld4_nowait(t0 + (t * 4 + j) * 16 + col0[t], v[t][j]);
+                            for (int j = 0; j < 2; j++) tmem_ld4_nowait(t0 + (t * 4 + j) * cstride + col0[t], v[t][j]);
                         }
                     } else {
 #pragma unroll
                         for (int t = 0; t < MAX_TILES; t++) {
                             if (!warp_has[t]) continue;
 #pragma unroll
-                            for (int j = 0; j < 2; j++) tmem_ld8_nowait(t0 + (t * 4 + j) * 16 + col0[t], v[t][j]);
+                            for (int j = 0; j < 2; j++) tmem_ld8_nowait(t0 + (t * 4 + j) * cstride + col0[t], v[t][j]);
                         }
                     }
                     tmem_ld_wait();
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_tempty + 8 * tg); // the sums are in registers: the MMAs may reuse the columns
+                    // no branches from here to the end of the stage: three independent chains the scheduler can interleave
+                    __half2 d2[MAX_TILES];
+                    float2 xv[MAX_TILES];
 #pragma unroll
                     for (int t = 0; t < MAX_TILES; t++) {
-                        if (!mine[t]) continue;
-                        const int blk0 = (s * S + my_cl[t]) * 4 + half * 2;
-                        const __half2 d2 = *reinterpret_cast<const __half2 *>(scales_n + (size_t)my_row[t] * srow + blk0 * 2);
-                        const float2 xv = *reinterpret_cast<const float2 *>(xs + blk0);
+                        d2[t] = *reinterpret_cast<const __half2 *>(scales_n + sc_off[t] + s * S * 8);
+                        xv[t] = *reinterpret_cast<const float2 *>(xs + xs_off[t] + s * S * 4);
+                    }
+#pragma unroll
+                    for (int t = 0; t < MAX_TILES; t++) {
                         const int k = my_k[t];
 #pragma unroll
                         for (int j = 0; j < 2; j++) {
@@ -412,11 +431,12 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                                 hi = k == 0 ? v[t][j][0] : k == 1 ? v[t][j][2] : k == 2 ? v[t][j][4] : v[t][j][6];
                                 lo = k == 0 ? v[t][j][1] : k == 1 ? v[t][j][3] : k == 2 ? v[t][j][5] : v[t][j][7];
                             }
-                            const float d = j ? __high2float(d2) : __low2float(d2);
-                            acc[t] = add_block(acc[t], d, j ? xv.y : xv.x, hi, lo);
+                            const float d = j ? __high2float(d2[t]) : __low2float(d2[t]);
+                            acc[t] = add_block(acc[t], d, j ? xv[t].y : xv[t].x, hi, lo);
                         }
                     }
-                    if (++tg == TGROUPS) { tg = 0; tphase ^= 1; }
+                    if (++tg == TGROUPS) tg = 0;
+                    if (++slot == cp.ring) { slot = 0; phase ^= 1; }
                 }
                 if (!ok) break;
                 // the scales buffer is free for the node after the next one
@@ -514,6 +534,12 @@ bool pick_stage(ChainNodeDev &nd) {
         if (nchunks % S != 0) continue;
         const int rows = S * nd.rb8, tiles = (rows + 127) / 128;
         if (tiles > MAX_TILES || rows * 128 > 64 * 1024) continue;
+        // a stage's accumulators have TG_COLS columns: 8 per MMA (and 8 more behind the last) when no tile holds
+        // rows of more than four chunks, else 16 per MMA
+        int span = 1;
+        for (int t = 0; t < tiles; t++) span = std::max(span, std::min(S - 1, (128 * t + 127) / nd.rb8) - (128 * t) / nd.rb8 + 1);
+        if (span > 8) continue;
+        if ((span <= 4 ? tiles * 4 * 8 + 8 : tiles * 4 * 16) > TG_COLS) continue;
         const int cost = (nchunks / S) * tiles;
         if (cost < best_cost) { best_cost = cost; nd.S = S; }
     }
@@ -531,6 +557,7 @@ bool pick_stage(ChainNodeDev &nd) {
     }
     if (span > 8) return false;
     nd.b_tile_bytes = span > 4 ? 2048 : 1024;
+    nd.col_stride = span > 4 ? 16 : 8;
     return true;
 }
 
@@ -650,7 +677,7 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
     cp.n_nodes = (int)nodes.size();
     {
         const char *v = getenv("RT_CHAIN_ISSUERS");
-        cp.n_issue = v ? std::max(1, std::min(N_ISSUE, atoi(v))) : N_ISSUE;
+        cp.n_issue = v ? std::max(1, std::min(N_ISSUE, atoi(v))) : 2;
         const char *pv = getenv("RT_CHAIN_PACE");
         cp.pace = pv ? std::max(0, atoi(pv)) : 300;
 
