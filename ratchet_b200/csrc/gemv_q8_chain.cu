@@ -465,19 +465,39 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                         }
                     } else if (my_rows) {
                         const unsigned long long t0 = wait_clock();
-                        for (int r = 1; r < split; r++) {
+                        unsigned long long w1 = 0, w2 = 0, w3 = 0;
+                        if (split == 4) {
+                            // the common case, all three slices asked for at once: one L2 round trip per try, not three
                             while (true) {
-                                unsigned long long word;
-                                asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(word) : "l"(pw + (size_t)r * nd.M) : "memory");
-                                if ((unsigned int)(word >> 32) == cp.tag) {
-                                    sum += __uint_as_float((unsigned int)word);
-                                    break;
-                                }
+                                asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w1) : "l"(pw + (size_t)1 * nd.M) : "memory");
+                                asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w2) : "l"(pw + (size_t)2 * nd.M) : "memory");
+                                asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w3) : "l"(pw + (size_t)3 * nd.M) : "memory");
+                                if ((unsigned int)(w1 >> 32) == cp.tag && (unsigned int)(w2 >> 32) == cp.tag && (unsigned int)(w3 >> 32) == cp.tag) break;
                                 if (*abort_flag) break;
                                 if (wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
                                     *abort_flag = 1;
                                     atomicCAS(&g_gemv_chain_error, 0, 7);
                                     break;
+                                }
+                            }
+                            sum += __uint_as_float((unsigned int)w1); // rank order
+                            sum += __uint_as_float((unsigned int)w2);
+                            sum += __uint_as_float((unsigned int)w3);
+                        } else {
+                            for (int r = 1; r < split; r++) {
+                                while (true) {
+                                    unsigned long long word;
+                                    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(word) : "l"(pw + (size_t)r * nd.M) : "memory");
+                                    if ((unsigned int)(word >> 32) == cp.tag) {
+                                        sum += __uint_as_float((unsigned int)word);
+                                        break;
+                                    }
+                                    if (*abort_flag) break;
+                                    if (wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
+                                        *abort_flag = 1;
+                                        atomicCAS(&g_gemv_chain_error, 0, 7);
+                                        break;
+                                    }
                                 }
                             }
                         }
