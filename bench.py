@@ -41,7 +41,7 @@ METRIC = "Q8_0 GEMV effective bandwidth (Phi-2 MLP shapes, decode)"
 UNIT = "GB/s"
 LAYERS = 32
 D_MODEL, D_FF = 2560, 10240
-NCU_TRAFFIC_PER_GEMV = 27_900_000     # measured DRAM bytes per launch (27.89 MB and 27.91 MB for the two shapes)
+NCU_TRAFFIC_PER_GEMV = 27_900_000     # measured DRAM bytes per GEMV (27.88 MB per node of the chain kernel; 27.89 / 27.91 MB single launches)
 BYTES_PER_GEMV = D_FF * D_MODEL + 2 * (D_FF * D_MODEL // 32) + 2 * D_MODEL + 2 * D_FF  # 27,878,400
 WORKLOAD = "phi2_mlp_q8_0_gemv_decode"
 
@@ -55,6 +55,7 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=LAYERS, help="MLP blocks per step (default: Phi-2's 32)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="dispatch node by node instead of one CUDA graph")
+    ap.add_argument("--no-lazy", action="store_true", help="skip the node-by-node lazy-graph leg reported beside e2e")
     ap.add_argument("--no-sharded", action="store_true", help="with --gpus > 1: skip the N-sharded prefill GEMM section")
     ap.add_argument("--extras", default="", help="comma list of the other configurations to time on one GPU and "
                     "report under \"extras\": c1,c3,c4,c5,c5long or all")
@@ -460,12 +461,12 @@ def main():
     e2e_ms = ev2.elapsed_time(ev3)                 # device timeline, host gaps included
     e2e_wall_ms = (time.perf_counter() - t0) * 1e3  # the host's view of the same region
     y_e2e = y_pin.array.reshape(-1).copy()
-    lazy_steps = max(3, min(args.steps, 30))
-    for _ in range(3):
+    lazy_steps = 1 if args.no_lazy else max(3, min(args.steps, 30))
+    for _ in range(0 if args.no_lazy else 3):
         lazy_step()
     barrier()
     t0 = time.perf_counter()
-    for _ in range(lazy_steps):
+    for _ in range(lazy_steps):   # at least once: its result is compared with the executable's below
         lazy_step()
     barrier()
     lazy_ms_step = (time.perf_counter() - t0) * 1e3 / lazy_steps
@@ -512,7 +513,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "launch_us": launch_us, "bytes_per_launch": BYTES_PER_GEMV,
                          "traffic": NCU_TRAFFIC_PER_GEMV, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, "
-                         "mean of the two shapes, from the capture summarised in profiles/q8_gemv_umma_phi2_decode.md"},
+                         "mean of the two shapes, from the captures summarised in profiles/q8_gemv_chain_phi2_decode.md and profiles/q8_gemv_umma_phi2_decode.md"},
             "e2e": {"value": world * step_bytes / (e2e_ms_step * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms_step,
                     "h2d_bytes_per_step": int(x_pin.nbytes), "d2h_bytes_per_step": int(y_pin.nbytes),
                     "api": "Tensor.write(x) + Executable.dispatch() + Tensor.to(CPU)",
