@@ -511,8 +511,11 @@ def main():
                        "parallelism": "replicas only (independent decode streams)" if world > 1 else "single GPU",
                        "kernels": kernel_names},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": f"of {peak_kind}", "launch_us": launch_us, "bytes_per_launch": BYTES_PER_GEMV,
-                         "traffic": NCU_TRAFFIC_PER_GEMV, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, "
+                         "peak_kind": f"of {peak_kind}", "kernel": exe.kernel.split("_h_")[0] if exe.kernel.startswith("q8_gemv_chain") else kernel_names[0],
+                         "gemv_per_launch": gemvs // max(launches_per_step, 1), "launch_us": launch_us * (gemvs // max(launches_per_step, 1)),
+                         "us_per_gemv": launch_us, "bytes_per_gemv": BYTES_PER_GEMV,
+                         "bytes_per_launch": BYTES_PER_GEMV * (gemvs // max(launches_per_step, 1)),
+                         "traffic": NCU_TRAFFIC_PER_GEMV * (gemvs // max(launches_per_step, 1)), "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, "
                          "mean of the two shapes, from the captures summarised in profiles/q8_gemv_chain_phi2_decode.md and profiles/q8_gemv_umma_phi2_decode.md"},
             "e2e": {"value": world * step_bytes / (e2e_ms_step * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms_step,
                     "h2d_bytes_per_step": int(x_pin.nbytes), "d2h_bytes_per_step": int(y_pin.nbytes),

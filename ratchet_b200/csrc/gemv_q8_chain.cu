@@ -23,9 +23,14 @@
 //    polls them, adds in rank order and writes the rows (thread-block clusters would do this in shared
 //    memory, but clusters of four leave 16 of the 148 SMs without a CTA).  The products are those of
 //    launching the nodes one by one; the f32 sums are taken in another order;
-//  * with the SM to itself a CTA owns all 512 tensor-memory columns: every block of a stage gets its own
-//    16-column accumulator (no overlapping writes), so several warps can issue a stage's MMAs side by side
-//    (one thread issues a tcgen05.mma about every 140 cycles, the tensor pipe takes them faster).
+//  * with the SM to itself a CTA owns all 512 tensor-memory columns: four regions of 128, one per stage in
+//    flight, so no stage of a node waits for the epilogue of another; stages alternate between the issuing
+//    warps, and one tcgen05.commit per stage signals both "sums ready" and "slot free";
+//  * a node's MMAs take 128 consecutive rows of the stage's row stream, whichever 128-byte chunks of K they
+//    belong to (see ChainNodeDev): every MMA is full, 48 per Phi-2 node instead of 80;
+//  * the producer spaces its copies (cp.pace): bursts of copy writes and the MMAs' operand reads would meet
+//    at the shared-memory port.
+// The dispatch is only legal as a cooperative launch: CTAs wait for one another, so all must be resident.
 // Every wait is bounded; a wait that runs out records its site, raises the CTA's abort flag and the CTA
 // leaves its loops, frees tensor memory and returns; the other CTAs run into their own limits.
 #include <cuda.h>
