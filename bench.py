@@ -338,6 +338,7 @@ def run_reference(args, rank):
     if rank != 0:
         return
     import oracle
+    oracle.use_all_cores()
     raw = [(t1.to_numpy(), t2.to_numpy()) for t1, t2 in make_weights(args.layers, 102)]
     x16 = np.random.default_rng(102).standard_normal(D_MODEL).astype(np.float16)
     t0 = time.perf_counter()
@@ -528,6 +529,7 @@ def main():
         }
         if world == 1 and not args.no_cpu_baseline:
             import oracle
+            oracle.use_all_cores()
             raw = [(a.to_numpy(), b.to_numpy()) for a, b in host_w]
             gbs, l_used, dt = time_cpu(raw, x_pin.array.reshape(-1).copy(), budget_s=15.0, max_layers=layers)
             line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",

@@ -59,6 +59,14 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def use_all_cores() -> int:
+    """Threads = the cores this process may run on, whatever OMP_NUM_THREADS says (torchrun exports 1)."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_num_threads(ctypes.c_int(n))
+    return num_threads()
+
+
 # ----------------------------------------------------------------------------- conversions
 
 def f64_to_f16(x: np.ndarray) -> np.ndarray:

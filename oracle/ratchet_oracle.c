@@ -491,6 +491,15 @@ void orc_q8h_gemv_packed(const uint8_t *wbuf, int64_t N, int64_t K, const uint16
     free(xf);
 }
 
+/* The launcher of a multi-process run may export OMP_NUM_THREADS=1; the timed baseline sets its own count. */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
