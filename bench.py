@@ -179,7 +179,7 @@ def time_node(gpu, stream, make_node, copies: int, iters: int, warmup: int = 3):
 
 
 def run_extras(which, gpu, stream):
-    """Configurations 1, 3, 4, 5 of BASELINE.json on one GPU: time, TFLOP/s or GB/s, roofline fraction."""
+    """The other workload configurations (1, 3, 4, 5) on one GPU: time, TFLOP/s or GB/s, roofline fraction."""
     import ratchet_b200 as rb
     from ratchet_b200 import DType, Tensor
     hbm, hbm_kind = peaks()
