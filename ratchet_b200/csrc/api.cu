@@ -74,6 +74,7 @@ struct rt_plan {
     // tensor-core GEMM: operand roles, tile width, and the scratch that holds dequantised weights
     bool lhs_is_q = false; // the lhs is the kernel's Q operand (trans_out), else its P operand
     int R = 0, S = 0, u_stacks = 1, p_stack = 1, q_stack = 1, bn = 128;
+    bool tf32x3 = false;   // dense f32 on the tensor cores: three TF32 MMAs per product
     void *scratch = nullptr;     // dequantised weights (f16)
     uint64_t scratch_bytes = 0;
     void *act_scratch = nullptr; // bf16 activations cast to f16 (quantised weights only)
@@ -266,6 +267,9 @@ rt_status rt_device_sync(rt_device *dev) {
     if (site != 0)
         return fail(RT_ERR_CUDA, "a tensor-core GEMM gave up a bounded wait (site " + std::to_string(site) +
                                      "): its output is incomplete");
+    CUDA_TRY(umma_tf32_take_error(&site, dev->stream));
+    if (site != 0)
+        return fail(RT_ERR_CUDA, "an f32 tensor-core GEMM gave up a bounded wait (site " + std::to_string(site) + "): its output is incomplete");
     CUDA_TRY(gemv_umma_take_error(&site, dev->stream));
     if (site != 0)
         return fail(RT_ERR_CUDA, "a tensor-memory GEMV gave up a bounded wait (site " + std::to_string(site) + "): its output is incomplete");
@@ -393,10 +397,14 @@ static bool force_simt() {
 static bool umma_eligible(const rt_matmul_desc &d, const Spec &s) {
     if (force_simt()) return false;
     if (s.trans_lhs || !s.trans_rhs) return false;
-    if (d.rhs_dt != RT_F16 && d.rhs_dt != RT_BF16) return false;
-    const bool dense = d.lhs_dt == d.rhs_dt;
-    if (!dense && d.lhs_dt != RT_Q8_0H && d.lhs_dt != RT_Q4_K) return false;
-    if (!umma_gemm_supported(s.K)) return false;
+    if (d.rhs_dt == RT_F32) {
+        if (d.lhs_dt != RT_F32 || !umma_tf32_supported(s.K)) return false;
+    } else {
+        if (d.rhs_dt != RT_F16 && d.rhs_dt != RT_BF16) return false;
+        const bool dense = d.lhs_dt == d.rhs_dt;
+        if (!dense && d.lhs_dt != RT_Q8_0H && d.lhs_dt != RT_Q4_K) return false;
+        if (!umma_gemm_supported(s.K)) return false;
+    }
     if (s.M < 1 || s.N < 16 || s.stacks < 1) return false;
     if ((double)s.M * (double)s.N * (double)s.K * (double)s.stacks < (double)(1 << 21)) return false;
     return true;
@@ -478,7 +486,8 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
         const int lhs_st = (int)s.lhs_stack, rhs_st = flatten ? 1 : (int)s.rhs_stack;
         pl->p_stack = s.trans_out ? rhs_st : lhs_st;
         pl->q_stack = s.trans_out ? lhs_st : rhs_st;
-        pl->bn = umma_pick_bn(pl->R, pl->S, pl->u_stacks, dev->sm_count);
+        pl->tf32x3 = desc->rhs_dt == RT_F32;
+        pl->bn = pl->tf32x3 ? 128 : umma_pick_bn(pl->R, pl->S, pl->u_stacks, dev->sm_count);
         pl->launches = 1;
         if (is_quantized(desc->lhs_dt)) {
             pl->scratch_bytes = (uint64_t)(s.lhs_stack * s.M * s.K) * 2;
@@ -505,7 +514,7 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
                 pl->launches = 3;
             }
         }
-        pl->name = std::string("gemm_umma_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt) + "_bn" +
+        pl->name = std::string(pl->tf32x3 ? "gemm_umma_tf32x3_" : "gemm_umma_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt) + "_bn" +
                    std::to_string(pl->bn) + (pl->scratch ? "_dequant_prepass" : "");
     } else if (s.N == 1 && !s.trans_lhs) {
         pl->kernel = PK_GEMV_SIMT;
@@ -590,6 +599,13 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
         e = launch_matmul_simt(p, s.desc.lhs_dt, s.desc.rhs_dt, false, st);
         break;
     case PK_GEMM_UMMA: {
+        if (plan->tf32x3) {
+            if (scatter) return fail(RT_ERR_UNSUPPORTED, "scattered outputs are not taken by the f32 GEMM");
+            const void *P = plan->lhs_is_q ? rhs : lhs, *Q = plan->lhs_is_q ? lhs : rhs;
+            e = launch_gemm_umma_tf32x3(P, Q, out, plan->R, plan->S, (int)s.K, plan->u_stacks, plan->p_stack, plan->q_stack, p.bias,
+                                        p.bias_dt, s.has_bias ? BIAS_PER_N : BIAS_NONE, p.epilogue, plan->dev->sm_count, st);
+            break;
+        }
         const void *w = lhs;
         rt_dtype w_dt = s.desc.lhs_dt;
         if (plan->scratch) {

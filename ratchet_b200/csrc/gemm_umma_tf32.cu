@@ -1,0 +1,359 @@
+// Dense f32 GEMM on the 5th-generation tensor cores with f32-class accuracy (three TF32 MMAs per product).
+//
+// Takes the role of the reference's tiled GEMM shader (crates/ratchet-core/src/ops/gemm.rs, the generic
+// f32 path of build_gemm_scalar / vectorized) for nn::Linear-shaped f32 nodes: D[R][S] = P[R][K] . Q[S][K]^T,
+// both operands K-major.  The path's bar for f32 is rel-L2 <= 1e-5 against fp64, which one TF32 MMA
+// (10 explicit mantissa bits) misses by two orders of magnitude.  Every operand value is therefore
+// split in shared memory into hi = the value with its low 13 mantissa bits cleared (exactly a TF32
+// number, so the tensor core reads it without rounding) and lo = value - hi (exact in f32; the tensor
+// core keeps its leading 11 bits), and the product is accumulated as hi.hi + hi.lo + lo.hi in f32:
+// the dropped lo.lo term and the rounding of lo are below 2^-21 of the product.  The tensor core's own
+// f32 accumulation is not round-to-nearest, and its error grows with the number of MMAs added into one
+// accumulator (measured: 2.9e-5 rel-L2 at K = 4096); so an accumulator only ever takes CHUNK stages
+// (K = 128: 48 MMAs), and the chunks are added in registers with ordinary f32 adds.
+//
+//   warp 0      TMA producer: 128-byte-swizzled boxes of 128 x 32 f32 (P) and 128 x 32 f32 (Q) per stage
+//   warp 1      MMA issuer: per stage 3 x 4 tcgen05.mma kind::tf32 (128 x 128 x 8) into one of two accumulators
+//   warps 2-9   per stage: split the two raw tiles in place into hi and write the lo tiles beside them
+//               (element-wise, so the swizzled layout carries over unchanged); per chunk: add the finished
+//               accumulator into 64 registers per thread (one chunk behind the splitting, so the MMAs never
+//               wait for it); per output tile: bias / GELU, store f32 rows
+// Every wait is bounded; on expiry the kernel records the site, frees tensor memory and returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+#include "kernels.hpp"
+#include "umma_gemv.cuh"
+
+namespace rt {
+
+__device__ int g_umma_tf32_error = 0;
+
+namespace {
+
+using namespace umma_gemv; // smem_u32, mbarrier helpers, fences, encode_tiled_fn
+
+constexpr int BM = 128, BN = 128;
+constexpr int BK = 32;                 // 32 f32 = one 128-byte swizzle row
+constexpr int UMMA_K = 8;              // TF32: 8 elements = 32 bytes per instruction
+constexpr int STAGES = 3;
+constexpr int TILE_BYTES = BM * BK * 4;                   // 16 KB (P and Q tiles have the same size: BM == BN)
+constexpr int STAGE_BYTES = 4 * TILE_BYTES;               // P raw->hi, P lo, Q raw->hi, Q lo
+constexpr int SPLIT_WARPS = 8;
+constexpr int NUM_THREADS = 64 + SPLIT_WARPS * 32;
+constexpr int TMEM_COLS = 2 * BN;      // two accumulators: one collects a chunk while the other is drained
+constexpr int CHUNK = 4;               // stages per accumulator: K = 128
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+
+struct Tf32Params {
+    int R, S, K;
+    int stacks, p_stack, q_stack;
+    float *out;
+    const void *bias;
+    int bias_dt, bias_mode;
+    int epilogue;
+    int tiles_r, tiles_s;
+};
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site) {
+    return mbar_wait_flag(bar, parity, abort_flag, site, &g_umma_tf32_error);
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}\n"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const Tf32Params prm) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *tiles = smem;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
+    // bars: [0..S) full (TMA landed), [S..2S) split (hi/lo tiles ready), [2S..3S) empty, 2 accumulator complete, 2 accumulator drained
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * STAGES + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_full = smem_u32(bars), bar_split = smem_u32(bars + STAGES), bar_empty = smem_u32(bars + 2 * STAGES);
+    const uint32_t bar_tfull = smem_u32(bars + 3 * STAGES), bar_tempty = smem_u32(bars + 3 * STAGES + 2);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_split + 8 * s, SPLIT_WARPS);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tempty + 8 * a, SPLIT_WARPS);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_k = (prm.K + BK - 1) / BK;
+    const int tiles_per_batch = prm.tiles_r * prm.tiles_s;
+    const int total_tiles = tiles_per_batch * prm.stacks;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+                const int r0 = (rem % prm.tiles_r) * BM, s0 = (rem / prm.tiles_r) * BN;
+                const int bp = b % prm.p_stack, bq = b % prm.q_stack;
+                for (int kb = 0; kb < num_k; kb++) {
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, 1)) { ok = false; break; }
+                    const uint32_t dst = smem_u32(tiles + stage * STAGE_BYTES);
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_full + 8 * stage), "r"(2 * TILE_BYTES) : "memory");
+                    tma_load_3d(dst, &map_p, kb * BK, r0, bp, bar_full + 8 * stage);
+                    tma_load_3d(dst + 2 * TILE_BYTES, &map_q, kb * BK, s0, bq, bar_full + 8 * stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            // instruction descriptor: f32 accumulate, TF32 A and B, K-major, N >> 3 at bit 17, M >> 4 at bit 24
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            int stage = 0, chunk = 0; // chunk counts over all tiles: accumulator chunk & 1
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                for (int kb = 0; kb < num_k; kb++) {
+                    const int buf = chunk & 1;
+                    if (kb % CHUNK == 0) {
+                        // the accumulator's previous chunk has been added into registers
+                        if (!mbar_wait(bar_tempty + 8 * buf, ((chunk >> 1) & 1) ^ 1, abort_flag, 5)) { ok = false; break; }
+                        tc_fence_after();
+                    }
+                    if (!mbar_wait(bar_split + 8 * stage, phase, abort_flag, 3)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    const uint32_t p_hi = smem_u32(tiles + stage * STAGE_BYTES), p_lo = p_hi + TILE_BYTES;
+                    const uint32_t q_hi = p_hi + 2 * TILE_BYTES, q_lo = p_hi + 3 * TILE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        const uint32_t off = k * UMMA_K * 4;
+                        // small terms first, the dominant hi.hi last
+                        umma_tf32(d_tmem, umma_desc_sw128(p_lo + off, 1024), umma_desc_sw128(q_hi + off, 1024), idesc, ((kb % CHUNK) | k) != 0 ? 1u : 0u);
+                        umma_tf32(d_tmem, umma_desc_sw128(p_hi + off, 1024), umma_desc_sw128(q_lo + off, 1024), idesc, 1u);
+                        umma_tf32(d_tmem, umma_desc_sw128(p_hi + off, 1024), umma_desc_sw128(q_hi + off, 1024), idesc, 1u);
+                    }
+                    umma_commit(bar_empty + 8 * stage); // stage reusable once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (kb % CHUNK == CHUNK - 1 || kb == num_k - 1) {
+                        umma_commit(bar_tfull + 8 * buf); // chunk complete
+                        chunk++;
+                    }
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- split (per stage), epilogue (per tile)
+        const int q = warp & 3;             // the tensor-memory lane quarter this warp may read
+        const int half = (warp - 2) >> 2;   // which half of the tile's columns it stores
+        const int st_tid = threadIdx.x - 64; // 0..255
+        int stage = 0, chunk = 0; // chunk: the next chunk to be drained, counted over all tiles
+        uint32_t phase = 0;
+        bool ok = true;
+        // adds accumulator (chunk & 1), columns [half * 64, half * 64 + 64) of this thread's row, into racc and
+        // hands the accumulator back
+        auto drain = [&](float (&racc)[64]) -> bool {
+            const int buf = chunk & 1;
+            if (!mbar_wait(bar_tfull + 8 * buf, (chunk >> 1) & 1, abort_flag, 4)) return false;
+            tc_fence_after();
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + buf * BN + half * 64 + h * 32 + ((uint32_t)(q * 32) << 16), v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) racc[h * 32 + i] += __uint_as_float(v[i]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+            chunk++;
+            return true;
+        };
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+            const int r0 = (rem % prm.tiles_r) * BM, s0 = (rem / prm.tiles_r) * BN;
+            float racc[64];
+#pragma unroll
+            for (int i = 0; i < 64; i++) racc[i] = 0.f;
+            int pending = 0; // chunks of this tile whose stages are split but which are not drained yet
+            for (int kb = 0; kb < num_k; kb++) {
+                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 2)) { ok = false; break; }
+                // two raw tiles of 16 KB: thread t takes float4 number t, t + 256, ... of each
+                uint8_t *base = tiles + stage * STAGE_BYTES;
+#pragma unroll
+                for (int op = 0; op < 2; op++) {
+                    float4 *raw = reinterpret_cast<float4 *>(base + op * 2 * TILE_BYTES);
+                    float4 *lo = reinterpret_cast<float4 *>(base + op * 2 * TILE_BYTES + TILE_BYTES);
+#pragma unroll
+                    for (int i = 0; i < TILE_BYTES / 16 / (SPLIT_WARPS * 32); i++) {
+                        const int idx = st_tid + i * (SPLIT_WARPS * 32);
+                        const float4 v = raw[idx];
+                        float4 h, l;
+                        h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
+                        h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
+                        h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
+                        h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
+                        raw[idx] = h;
+                        lo[idx] = l;
+                    }
+                }
+                // the MMAs read the tiles through the async proxy
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_split + 8 * stage);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                if (kb % CHUNK == CHUNK - 1 || kb == num_k - 1) {
+                    // this chunk's MMAs are only being issued now: drain the one before it, which is long complete
+                    if (pending == 1 && !drain(racc)) { ok = false; break; }
+                    pending = 1;
+                }
+            }
+            if (!ok) break;
+            if (pending == 1 && !drain(racc)) break;
+            const int row = r0 + q * 32 + lane;
+            const bool has_bias = prm.bias_mode != BIAS_NONE;
+            float row_bias = 0.f;
+            if (prm.bias_mode == BIAS_PER_M && row < prm.R) row_bias = load_bias(prm.bias, prm.bias_dt, row);
+            float *orow = prm.out + (long long)b * prm.R * prm.S + (long long)row * prm.S;
+            const bool vec_ok = (prm.S % 4 == 0) && (reinterpret_cast<uintptr_t>(prm.out) % 16 == 0);
+#pragma unroll
+            for (int h = 0; h < 2; h++) { // 32 columns per round, two rounds per warp
+                const int col0 = s0 + half * 64 + h * 32;
+                if (row < prm.R && col0 < prm.S) {
+                    if (vec_ok && col0 + 32 <= prm.S) {
+#pragma unroll
+                        for (int g = 0; g < 8; g++) {
+                            float4 o;
+                            float *op = reinterpret_cast<float *>(&o);
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                const int i = g * 4 + j;
+                                const float bv = prm.bias_mode == BIAS_PER_N ? load_bias(prm.bias, prm.bias_dt, col0 + i) : row_bias;
+                                op[j] = epilogue_value<float>(racc[h * 32 + i], has_bias, bv, prm.epilogue);
+                            }
+                            *reinterpret_cast<float4 *>(orow + col0 + g * 4) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            if (col0 + i < prm.S) {
+                                const float bv = prm.bias_mode == BIAS_PER_N ? load_bias(prm.bias, prm.bias_dt, col0 + i) : row_bias;
+                                orow[col0 + i] = epilogue_value<float>(racc[h * 32 + i], has_bias, bv, prm.epilogue);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        const unsigned long long t0 = wait_clock();
+        while (wait_clock() - t0 < 400000ull) __nanosleep(1000);
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
+    }
+}
+
+// [stack][rows][K] f32 row-major -> boxes of 128 rows x 32 elements, 128-byte swizzle, zero fill
+bool make_map_f32(CUtensorMap *map, const void *base, long long K, long long rows, long long stack) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)stack};
+    cuuint64_t strides[2] = {(cuuint64_t)K * 4, (cuuint64_t)K * 4 * (cuuint64_t)rows};
+    cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)BM, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+} // namespace
+
+// K * 4 bytes must be a multiple of 16 (tensor-map strides), and the operands 16-byte aligned.
+bool umma_tf32_supported(long long K) { return K >= 4 && K % 4 == 0 && encode_tiled_fn() != nullptr; }
+
+// P: [p_stack][R][K] f32, Q: [q_stack][S][K] f32; out [stacks][R][S] f32.
+cudaError_t launch_gemm_umma_tf32x3(const void *P, const void *Q, void *out, int R, int S, int K, int stacks, int p_stack, int q_stack,
+                                    const void *bias, int bias_dt, int bias_mode, int epilogue, int sm_count, cudaStream_t stream) {
+    if ((reinterpret_cast<uintptr_t>(P) | reinterpret_cast<uintptr_t>(Q)) % 16 != 0) return cudaErrorInvalidValue;
+    CUtensorMap mp, mq;
+    if (!make_map_f32(&mp, P, K, R, p_stack) || !make_map_f32(&mq, Q, K, S, q_stack)) return cudaErrorInvalidValue;
+    Tf32Params prm{};
+    prm.R = R; prm.S = S; prm.K = K;
+    prm.stacks = stacks; prm.p_stack = p_stack; prm.q_stack = q_stack;
+    prm.out = static_cast<float *>(out);
+    prm.bias = bias; prm.bias_dt = bias_dt; prm.bias_mode = bias_mode;
+    prm.epilogue = epilogue;
+    prm.tiles_r = (R + BM - 1) / BM;
+    prm.tiles_s = (S + BN - 1) / BN;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_umma_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    const long long total = (long long)prm.tiles_r * prm.tiles_s * stacks;
+    const int grid = (int)(total < sm_count ? total : sm_count);
+    gemm_umma_tf32x3_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(mp, mq, prm);
+    return cudaGetLastError();
+}
+
+cudaError_t umma_tf32_take_error(int *site, cudaStream_t stream) {
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbolAsync(site, g_umma_tf32_error, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return e;
+    e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return e;
+    if (*site != 0) e = cudaMemcpyToSymbolAsync(g_umma_tf32_error, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream);
+    return e;
+}
+
+} // namespace rt

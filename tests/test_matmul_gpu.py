@@ -267,8 +267,9 @@ def test_q8_gemm_forms(gpu):
 
 def test_dense_f32_phi2_fc1(gpu):
     """BASELINE config 1: A f32 [1,128,2560], W f32 [10240,2560] N(0,0.02) rhs-transposed, b f32."""
-    err, _ = check_problem(Problem(F32, F32, (10240, 2560), (1, 128, 2560), (False, True, True), bias=True, seed=101,
-                                   w_std=0.02), gpu)
+    err, kernel = check_problem(Problem(F32, F32, (10240, 2560), (1, 128, 2560), (False, True, True), bias=True, seed=101,
+                                        w_std=0.02), gpu)
+    assert kernel.startswith("gemm_umma_tf32x3"), kernel
     assert err <= 1e-5
 
 
@@ -323,6 +324,22 @@ def test_umma_dense_forms(gpu):
     _, kernel = check_problem(Problem(F16, F16, (513, 1024), (1, 130, 1024), (False, True, True), bias=True, epilogue=1,
                                       seed=203, w_std=0.03), gpu)
     assert kernel.startswith("gemm_umma"), kernel
+
+
+def test_umma_tf32x3_dense_f32_forms(gpu):
+    """Dense f32 on the tensor cores (three TF32 MMAs per product) must keep the f32 bar of 1e-5: ragged
+    extents, K with a tail below one 32-wide step, both output orders, batches, bias, GELU."""
+    cases = [
+        Problem(F32, F32, (300, 520), (2, 700, 520), (False, True, True), bias=True, seed=301, w_std=0.05),
+        Problem(F32, F32, (300, 520), (2, 700, 520), (False, True, False), bias=True, seed=302, w_std=0.05),
+        Problem(F32, F32, (3, 257, 204), (3, 190, 204), (False, True, True), seed=303, w_std=0.05),
+        Problem(F32, F32, (513, 1024), (1, 131, 1024), (False, True, True), bias=True, epilogue=1, seed=304, w_std=0.03),
+        Problem(F32, F32, (1024, 4096), (1, 256, 4096), (False, True, True), seed=305, w_std=1.0),  # long sums, large values
+    ]
+    for p in cases:
+        err, kernel = check_problem(p, gpu)
+        assert kernel.startswith("gemm_umma_tf32x3"), kernel
+        assert err <= 1e-5, (kernel, err)
 
 
 def test_umma_takes_the_prefill_configs(gpu):
