@@ -730,6 +730,11 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
         return e;
     }
     cp.nodes = c->d_nodes;
+    {
+        // where the dispatch tags start (a test hook: the tag wraps from 65535 to 1)
+        const char *tv = getenv("RT_CHAIN_TAG_START");
+        if (tv) c->tag = (unsigned int)std::max(0, std::min(65535, atoi(tv)));
+    }
     cp.xbuf = c->d_xbuf;
     cp.pbuf = c->d_pbuf;
     c->name = "q8_gemv_chain_h_nodes" + std::to_string(cp.n_nodes) + "_grid" + std::to_string(grid) + "_maxsplit" + std::to_string(max_split) +

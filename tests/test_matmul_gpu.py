@@ -210,6 +210,28 @@ def test_q8_gemv_lists_chain_or_graph(gpu, shapes, kind):
         h = got.astype(np.float32)
 
 
+def test_q8_gemv_chain_tag_wraps(gpu, monkeypatch):
+    """The dispatch tag is 16 bits wide: dispatches across the wrap from 65535 to 1 stay correct."""
+    shapes = [(2560, 2560), (2560, 2560)]
+    x_dev, nodes, host = _decode_chain(gpu, shapes, 4400, [False, False])
+    nodes[-1].resolve()
+    monkeypatch.setenv("RT_CHAIN_TAG_START", "65532")
+    exe = rb.Executable(gpu, nodes, use_graph=True)
+    assert exe.kernel.startswith("q8_gemv_chain"), exe.kernel
+    for trial in range(8):
+        x = np.random.default_rng(4500 + trial).standard_normal(shapes[0][1]).astype(np.float16)
+        x_dev.write(x)
+        exe.dispatch()
+        gpu.sync()
+        h = x.astype(np.float32)
+        for i, (w_vals, b_vals, epi) in enumerate(host):
+            M, K = shapes[i]
+            got = nodes[i].to(Device.CPU).to_numpy().reshape(-1)
+            truth = oracle.matmul_truth(w_vals, h, b_vals, 1, 1, 1, M, 1, K, False, True, True, epi)
+            assert oracle.rel_l2(got.astype(np.float32), oracle.f64_to_f16(truth).astype(np.float32)) <= TOL[F16], (trial, i)
+            h = got.astype(np.float32)
+
+
 def test_q8_gemv_shapes_and_forms(gpu):
     for N, K in [(16, 32), (15, 64), (17, 96), (33, 2560), (1000, 352), (4096, 4096), (7, 8192)]:
         check_problem(Problem(Q8H, F16, (N, K), (1, K), (False, True, True), bias=True, seed=N + K, w_std=0.05), gpu)
