@@ -293,6 +293,31 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 int c0[MAX_TILES], c1[MAX_TILES];
 #pragma unroll
                 for (int t = 0; t < MAX_TILES; t++) { c0[t] = nd.c0[t]; c1[t] = nd.c1[t]; }
+                // where this thread's lane sits in the stage's row stream, tile by tile (worked out before the wait for the
+                // activations: afterwards the issuing warps need the schedulers)
+                int my_cl[MAX_TILES], my_row[MAX_TILES], my_k[MAX_TILES], col0[MAX_TILES];
+                bool mine[MAX_TILES], warp_has[MAX_TILES];
+                float acc[MAX_TILES];
+                int sc_off[MAX_TILES], xs_off[MAX_TILES];
+                const bool narrow = rb8 >= 32; // a warp's 32 lanes then belong to at most two chunks: two column pairs do
+#pragma unroll
+                for (int t = 0; t < MAX_TILES; t++) {
+                    const int pos = 128 * t + row_local, pos_w = 128 * t + q * 32;
+                    my_cl[t] = pos / rb8;
+                    my_row[t] = pos - my_cl[t] * rb8;
+                    warp_has[t] = t < tiles && pos_w < S * rb8;
+                    mine[t] = t < tiles && pos < S * rb8 && my_row[t] < rows_here;
+                    // first of the column pairs this warp loads: two pairs (narrow) or four, inside the MMA's cstride columns
+                    const int d_first = min(pos_w / rb8 - c0[t], cstride / 2 - (narrow ? 2 : 4));
+                    col0[t] = 2 * d_first;
+                    my_k[t] = my_cl[t] - c0[t] - d_first;
+                    acc[t] = 0.f;
+                    // where this lane's scales and activation scales are (lanes outside the stage read some valid
+                    // place: their sums are dropped)
+                    const int cl_in = min(my_cl[t], S - 1), row_in = min(my_row[t], rb8 - 1);
+                    sc_off[t] = row_in * (ks / 16) + (cl_in * 4 + half * 2) * 2;
+                    xs_off[t] = cl_in * 4 + half * 2;
+                }
                 {
                     const int sub = et & 3; // 4 threads per block of 32 elements, 8 elements each
                     constexpr int MAX_IT = (MAX_KS / 32 + 63) / 64;
@@ -363,30 +388,6 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 if (*abort_flag) break;
                 if (lane == 0) mbar_arrive(bar_x);
 
-                // where this thread's lane sits in the stage's row stream, tile by tile
-                int my_cl[MAX_TILES], my_row[MAX_TILES], my_k[MAX_TILES], col0[MAX_TILES];
-                bool mine[MAX_TILES], warp_has[MAX_TILES];
-                float acc[MAX_TILES];
-                int sc_off[MAX_TILES], xs_off[MAX_TILES];
-                const bool narrow = rb8 >= 32; // a warp's 32 lanes then belong to at most two chunks: two column pairs do
-#pragma unroll
-                for (int t = 0; t < MAX_TILES; t++) {
-                    const int pos = 128 * t + row_local, pos_w = 128 * t + q * 32;
-                    my_cl[t] = pos / rb8;
-                    my_row[t] = pos - my_cl[t] * rb8;
-                    warp_has[t] = t < tiles && pos_w < S * rb8;
-                    mine[t] = t < tiles && pos < S * rb8 && my_row[t] < rows_here;
-                    // first of the column pairs this warp loads: two pairs (narrow) or four, inside the MMA's cstride columns
-                    const int d_first = min(pos_w / rb8 - c0[t], cstride / 2 - (narrow ? 2 : 4));
-                    col0[t] = 2 * d_first;
-                    my_k[t] = my_cl[t] - c0[t] - d_first;
-                    acc[t] = 0.f;
-                    // where this lane's scales and activation scales are (lanes outside the stage read some valid
-                    // place: their sums are dropped)
-                    const int cl_in = min(my_cl[t], S - 1), row_in = min(my_row[t], rb8 - 1);
-                    sc_off[t] = row_in * (ks / 16) + (cl_in * 4 + half * 2) * 2;
-                    xs_off[t] = cl_in * 4 + half * 2;
-                }
                 const uint8_t *scales_n = scales_s + (size_t)sbuf * cp.scale_buf_bytes;
                 const int srow = ks / 16; // bytes per row of the node's scales
                 if (!mbar_wait(bar_sfull + 8 * sbuf, sphase, abort_flag, 10)) break;

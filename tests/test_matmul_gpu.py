@@ -210,6 +210,26 @@ def test_q8_gemv_lists_chain_or_graph(gpu, shapes, kind):
         h = got.astype(np.float32)
 
 
+def test_q8_gemv_chain_is_deterministic(gpu):
+    """Same input, same bits, dispatch after dispatch: the CTAs hand rows on through polled words and K slices
+    meet in a fixed order, so nothing may depend on which CTA is early."""
+    shapes = [(10240, 2560), (2560, 10240), (10240, 2560), (2560, 10240), (10240, 2560), (2560, 10240)]
+    x_dev, nodes, host = _decode_chain(gpu, shapes, 4600, [True, False, False, True, False, False])
+    nodes[-1].resolve()
+    exe = rb.Executable(gpu, nodes, use_graph=True)
+    assert exe.kernel.startswith("q8_gemv_chain"), exe.kernel
+    exe.dispatch()
+    gpu.sync()
+    first = [n.to(Device.CPU).to_numpy().reshape(-1).copy() for n in nodes]
+    for trial in range(12):
+        for _ in range(25):
+            exe.dispatch()
+        gpu.sync()
+        for i, n in enumerate(nodes):
+            got = n.to(Device.CPU).to_numpy().reshape(-1)
+            assert np.array_equal(got.view(np.uint16), first[i].view(np.uint16)), f"dispatch {25 * (trial + 1)}: node {i} changed"
+
+
 def test_q8_gemv_chain_tag_wraps(gpu, monkeypatch):
     """The dispatch tag is 16 bits wide: dispatches across the wrap from 65535 to 1 stay correct."""
     shapes = [(2560, 2560), (2560, 2560)]
