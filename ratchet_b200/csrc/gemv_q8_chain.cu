@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                         // Copies are spread over the node's time instead of bursting when the MMAs free the slots:
                         // MMA operand reads (about 100 bytes per cycle) and copy writes share the shared-memory port.
                         if (cp.pace > 0) {
-                            while (clock64() - last_copy < cp.pace) {}
+                            while (clock64() - last_copy < cp.pace) __nanosleep(40); // no hot spin: the scheduler is shared with epilogue warps
                             last_copy = clock64();
                         }
                         tma_load_2d(st + c * rb8 * 128, map_w, kb + c * CHUNK_K, row_begin, full);
