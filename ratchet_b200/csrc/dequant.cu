@@ -37,6 +37,50 @@ __global__ void __launch_bounds__(256) dequant_q8h_f16_vec_kernel(const uint4 *c
 // bf16 -> f16, eight values per thread.  Exact for 2^-14 <= |x| <= 65504 (bf16 has 8 significant
 // bits, f16 has 11); larger magnitudes saturate to +-65504, smaller ones round into the f16
 // subnormals (absolute error below 2^-25).
+// Q4_K -> f16, sixteen quant bytes per thread: their low nibbles are sixteen values of sub-block 2p, their
+// high nibbles sixteen values of sub-block 2p + 1 (GGUF block_q4_K: d, dmin, 12 bytes of 6-bit scales and
+// mins, 128 bytes of nibbles).  Same arithmetic, value by value, as q4k_element: (d * sc) * q - dmin * m
+// with every step rounded to f32, then one rounding to f16.
+__global__ void __launch_bounds__(256) dequant_q4k_f16_vec_kernel(const uint8_t *src, __half *dst, long long n_units) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < n_units; u += stride) {
+        const long long blk_i = u >> 3;           // super-block of 256 values
+        const int p = (int)(u & 7) >> 1;          // pair of sub-blocks
+        const int h = (int)(u & 1);               // which sixteen of the pair's thirty-two bytes
+        const uint8_t *blk = src + blk_i * 144;
+        const uint4 head = __ldg(reinterpret_cast<const uint4 *>(blk));
+        const uint4 qs = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + 32 * p + 16 * h));
+        const __half2 dd = *reinterpret_cast<const __half2 *>(&head.x);
+        const float d = __low2float(dd), dmin = __high2float(dd);
+        const uint8_t *sb = reinterpret_cast<const uint8_t *>(&head) + 4;
+        int sc0, m0, sc1, m1;
+        q4k_scale_min(2 * p, sb, sc0, m0);
+        q4k_scale_min(2 * p + 1, sb, sc1, m1);
+        const float ds0 = __fmul_rn(d, (float)sc0), dm0 = __fmul_rn(dmin, (float)m0);
+        const float ds1 = __fmul_rn(d, (float)sc1), dm1 = __fmul_rn(dmin, (float)m1);
+        const uint32_t w[4] = {qs.x, qs.y, qs.z, qs.w};
+        uint32_t lo[8], hi[8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+#pragma unroll
+            for (int b = 0; b < 4; b += 2) {
+                const uint32_t q0 = (w[i] >> (8 * b)) & 0xFFu, q1 = (w[i] >> (8 * b + 8)) & 0xFFu;
+                const __half2 l2 = __halves2half2(__float2half_rn(__fsub_rn(__fmul_rn(ds0, (float)(q0 & 15u)), dm0)),
+                                                  __float2half_rn(__fsub_rn(__fmul_rn(ds0, (float)(q1 & 15u)), dm0)));
+                const __half2 h2 = __halves2half2(__float2half_rn(__fsub_rn(__fmul_rn(ds1, (float)(q0 >> 4)), dm1)),
+                                                  __float2half_rn(__fsub_rn(__fmul_rn(ds1, (float)(q1 >> 4)), dm1)));
+                lo[i * 2 + b / 2] = *reinterpret_cast<const uint32_t *>(&l2);
+                hi[i * 2 + b / 2] = *reinterpret_cast<const uint32_t *>(&h2);
+            }
+        }
+        __half *o = dst + blk_i * 256 + (2 * p) * 32 + 16 * h;
+        reinterpret_cast<uint4 *>(o)[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        reinterpret_cast<uint4 *>(o)[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+        reinterpret_cast<uint4 *>(o + 32)[0] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        reinterpret_cast<uint4 *>(o + 32)[1] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+    }
+}
+
 __global__ void __launch_bounds__(256) cast_bf16_f16_kernel(const uint4 *src, uint4 *dst, long long n8) {
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
@@ -95,7 +139,14 @@ cudaError_t launch_dequant(rt_dtype dt, long long numel, const void *src, const 
     } else if (dt == RT_Q4_K && out_dt == RT_F32) {
         dequant_kernel<LK_Q4K, float><<<blocks, threads, 0, stream>>>(src, scales, (float *)dst, numel);
     } else if (dt == RT_Q4_K && out_dt == RT_F16) {
-        dequant_kernel<LK_Q4K, __half><<<blocks, threads, 0, stream>>>(src, scales, (__half *)dst, numel);
+        if (numel % 256 == 0 && (reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) % 16 == 0) {
+            const long long n_units = numel / 32;
+            const long long w2 = (n_units + threads - 1) / threads;
+            const int b2 = (int)(w2 < (long long)sm_count * 16 ? w2 : (long long)sm_count * 16);
+            dequant_q4k_f16_vec_kernel<<<b2, threads, 0, stream>>>((const uint8_t *)src, (__half *)dst, n_units);
+        } else {
+            dequant_kernel<LK_Q4K, __half><<<blocks, threads, 0, stream>>>(src, scales, (__half *)dst, numel);
+        }
     } else {
         return cudaErrorInvalidValue;
     }

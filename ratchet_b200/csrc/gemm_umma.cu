@@ -416,8 +416,10 @@ cudaError_t launch_bn(const CUtensorMap &mp, const CUtensorMap &mq, UmmaParams p
 bool umma_gemm_supported(long long K) { return K >= 8 && K % 8 == 0 && encode_fn() != nullptr; }
 
 int umma_pick_bn(long long R, long long S, long long stacks, int sm_count) {
+    // 128 x 256 tiles need 96 bytes of operands per MMA cycle, 128 x 128 tiles 128: the narrow tile is bound by
+    // the copies into shared memory, so the wide one is taken as soon as it fills half of the SMs
     const long long t256 = ((R + BM - 1) / BM) * ((S + 255) / 256) * stacks;
-    return t256 >= sm_count ? 256 : 128;
+    return 2 * t256 >= sm_count ? 256 : 128;
 }
 
 // P: [p_stack][R][K] of p_dt, Q: [q_stack][S][K] of q_dt (f16 or bf16 each); out [stacks][R][S] of out_dt.
