@@ -110,6 +110,7 @@ struct ChainParams {
     unsigned long long *pbuf;    // K-sliced nodes: the slices' row sums as {f32 sum, 32-bit tag} words
     unsigned int tag;            // this dispatch's tag: 1..65535, never the previous dispatch's
     int pace;            // least number of cycles between two chunk copies of the producer (0: none)
+    int skip_tempty;     // no node has more stages than tensor-memory regions: a region is only reused by a later node
 };
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site) {
@@ -142,7 +143,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
     if (threadIdx.x == 0) {
         for (int s = 0; s < cp.ring; s++) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_done + 8 * s, 1); // the commit of the stage's issuer
+            mbar_init(bar_done + 8 * s, cp.n_issue); // one commit per issuer
         }
         for (int a = 0; a < TGROUPS; a++) {
             mbar_init(bar_tempty + 8 * a, 8);
@@ -219,7 +220,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
             // instruction descriptor: s32 accumulate, signed 8-bit A and B, K-major, N = 16, M = 128
             const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
             const uint64_t a_desc_ring = umma_desc_sw128(smem_u32(ring), 1024);
-            int slot = 0, tg = 0, turn = 0;
+            int slot = 0, tg = 0;
             uint32_t phase = 0, tphase = 0, xphase = 0;
             bool ok = true;
             for (int l = 0; l < cp.n_nodes && ok; l++) {
@@ -234,28 +235,28 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 if (!has_rows) continue;
                 // 16-row digit tiles are two 8-row groups 1024 bytes apart; 8-row tiles repeat their group (stride 0)
                 const uint64_t b_desc_base = umma_desc_sw128(smem_u32(b_tiles), btb == 2048 ? 1024 : 0);
+                const int tile_cols = 4 * cstride + (cstride == 8 ? 8 : 0);
                 for (int s = 0; s < nstages; s++) {
-                    if (turn == issuer) { // a stage is one issuer's: its single commit covers all of the stage's MMAs
-                        if (!mbar_wait(bar_tempty + 8 * tg, tphase ^ 1, abort_flag, 3)) { ok = false; break; }
-                        if (!mbar_wait(bar_full + 8 * slot, phase, abort_flag, 4)) { ok = false; break; }
-                        tc_fence_after();
-                        const uint64_t a_desc = a_desc_ring + (uint64_t)((uint32_t)(slot * cp.slot_bytes) >> 4);
-                        const uint32_t d0 = tmem_base + tg * TG_COLS;
-                        for (int t = 0; t < tiles; t++) {
-                            // tile t: 128 stream rows; block j of the chunks: 32 bytes further along K in both operands,
-                            // its own 16 columns
-                            const uint64_t at = a_desc + (uint64_t)(t * (128 * 128 >> 4));
-                            const uint64_t bt = b_desc_base + (uint64_t)((uint32_t)((s * tiles + t) * btb) >> 4);
+                    // the region's previous sums have been read (when a node has no more stages than there are regions,
+                    // the previous user was an earlier node, which the epilogue warps had left before this node's digits)
+                    if (!cp.skip_tempty && !mbar_wait(bar_tempty + 8 * tg, tphase ^ 1, abort_flag, 3)) { ok = false; break; }
+                    if (!mbar_wait(bar_full + 8 * slot, phase, abort_flag, 4)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t a_desc = a_desc_ring + (uint64_t)((uint32_t)(slot * cp.slot_bytes) >> 4);
+                    const uint32_t d0 = tmem_base + tg * TG_COLS;
+                    // The issuers share a stage tile by tile.  Tile t: 128 stream rows; block j of the chunks: 32 bytes
+                    // further along K in both operands.  An MMA writes 16 columns, of which at most the first
+                    // 2 * (chunks of the tile) are ever read; with a stride of 8 the next MMA of the same thread
+                    // overwrites the unread upper half (the tensor pipe runs one thread's MMAs in issue order), and a
+                    // gap of 8 columns behind a tile keeps another thread's tile out of reach.  So four stages fit into
+                    // tensor memory and no stage of a node waits for the epilogue of another.
+                    for (int t = issuer; t < tiles; t += cp.n_issue) {
+                        const uint64_t at = a_desc + (uint64_t)(t * (128 * 128 >> 4));
+                        const uint64_t bt = b_desc_base + (uint64_t)((uint32_t)((s * tiles + t) * btb) >> 4);
 #pragma unroll
-                            // An MMA writes 16 columns, of which at most the first 2 * (chunks of the tile) are ever read.
-                            // With a stride of 8 the next MMA of this thread overwrites the unread upper half (the tensor
-                            // pipe runs one thread's MMAs in issue order), which fits four stages into tensor memory, so
-                            // that no stage of a node waits for the epilogue of another.
-                            for (int j = 0; j < 4; j++) umma_i8(d0 + (t * 4 + j) * cstride, at + 2 * j, bt + 2 * j, idesc);
-                        }
-                        umma_commit(bar_done + 8 * slot);
+                        for (int j = 0; j < 4; j++) umma_i8(d0 + t * tile_cols + j * cstride, at + 2 * j, bt + 2 * j, idesc);
                     }
-                    if (++turn == cp.n_issue) turn = 0;
+                    umma_commit(bar_done + 8 * slot); // this issuer's part of the stage (possibly nothing)
                     if (++slot == cp.ring) { slot = 0; phase ^= 1; }
                     if (++tg == TGROUPS) { tg = 0; tphase ^= 1; }
                 }
@@ -395,6 +396,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                     if (!mbar_wait(bar_done + 8 * slot, phase, abort_flag, 6)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t t0 = tmem_base + tg * TG_COLS + ((uint32_t)(q * 32) << 16) + half * 2 * cstride;
+                    const int tile_cols = 4 * cstride + (cstride == 8 ? 8 : 0);
                     // all of the stage's loads first (one wait), then the arithmetic
                     int v[MAX_TILES][2][8] = {};
                     if (narrow) {
@@ -402,14 +404,14 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                         for (int t = 0; t < MAX_TILES; t++) {
                             if (!warp_has[t]) continue;
 #pragma unroll
-                            for (int j = 0; j < 2; j++) tmem_ld4_nowait(t0 + (t * 4 + j) * cstride + col0[t], v[t][j]);
+                            for (int j = 0; j < 2; j++) tmem_ld4_nowait(t0 + t * tile_cols + j * cstride + col0[t], v[t][j]);
                         }
                     } else {
 #pragma unroll
                         for (int t = 0; t < MAX_TILES; t++) {
                             if (!warp_has[t]) continue;
 #pragma unroll
-                            for (int j = 0; j < 2; j++) tmem_ld8_nowait(t0 + (t * 4 + j) * cstride + col0[t], v[t][j]);
+                            for (int j = 0; j < 2; j++) tmem_ld8_nowait(t0 + t * tile_cols + j * cstride + col0[t], v[t][j]);
                         }
                     }
                     tmem_ld_wait();
@@ -565,7 +567,7 @@ bool pick_stage(ChainNodeDev &nd) {
         int span = 1;
         for (int t = 0; t < tiles; t++) span = std::max(span, std::min(S - 1, (128 * t + 127) / nd.rb8) - (128 * t) / nd.rb8 + 1);
         if (span > 8) continue;
-        if ((span <= 4 ? tiles * 4 * 8 + 8 : tiles * 4 * 16) > TG_COLS) continue;
+        if ((span <= 4 ? tiles * (4 * 8 + 8) : tiles * 4 * 16) > TG_COLS) continue;
         const int cost = (nchunks / S) * tiles;
         if (cost < best_cost) { best_cost = cost; nd.S = S; }
     }
@@ -653,6 +655,7 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
     std::vector<ChainNodeDev> host(nodes.size());
     int slot_bytes = 0, b_bytes = GUARD_BYTES, scale_buf_bytes = 0, mmas = 0;
     size_t x_words = 0, p_words = 0;
+    int max_stages = 0;
     for (size_t i = 0; i < nodes.size(); i++) {
         const MatmulParams &p = nodes[i];
         ChainNodeDev &nd = host[i];
@@ -669,6 +672,7 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
         b_bytes = std::max(b_bytes, nd.nstages * nd.tiles * nd.b_tile_bytes);
         scale_buf_bytes = std::max(scale_buf_bytes, nd.rb8 * (nd.ks / 16));
         mmas = std::max(mmas, nd.nstages * nd.tiles * 4);
+        max_stages = std::max(max_stages, nd.nstages);
         nd.x_off = (int)x_words;
         x_words += (size_t)((p.M + 31) & ~31);
         nd.p_off = (int)p_words;
@@ -703,9 +707,10 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
     cp.n_nodes = (int)nodes.size();
     {
         const char *v = getenv("RT_CHAIN_ISSUERS");
-        cp.n_issue = v ? std::max(1, std::min(N_ISSUE, atoi(v))) : 2;
+        cp.n_issue = v ? std::max(1, std::min(N_ISSUE, atoi(v))) : 3;
         const char *pv = getenv("RT_CHAIN_PACE");
         cp.pace = pv ? std::max(0, atoi(pv)) : 300;
+        cp.skip_tempty = max_stages <= TGROUPS ? 1 : 0;
 
     }
     cp.slot_bytes = (slot_bytes + 1023) & ~1023;
