@@ -24,12 +24,13 @@
 //    memory, but clusters of four leave 16 of the 148 SMs without a CTA).  The products are those of
 //    launching the nodes one by one; the f32 sums are taken in another order;
 //  * with the SM to itself a CTA owns all 512 tensor-memory columns: four regions of 128, one per stage in
-//    flight, so no stage of a node waits for the epilogue of another; stages alternate between the issuing
-//    warps, and one tcgen05.commit per stage signals both "sums ready" and "slot free";
+//    flight, so no stage of a node waits for the epilogue of another.  Up to four warps issue a stage's MMAs,
+//    tile by tile (a single thread issues a tcgen05.mma every 54 cycles; the pipe takes this shape every 41),
+//    each with one tcgen05.commit per stage onto one barrier that says both "sums ready" and "slot free";
 //  * a node's MMAs take 128 consecutive rows of the stage's row stream, whichever 128-byte chunks of K they
 //    belong to (see ChainNodeDev): every MMA is full, 48 per Phi-2 node instead of 80;
 //  * the producer spaces its copies (cp.pace): bursts of copy writes and the MMAs' operand reads would meet
-//    at the shared-memory port.
+//    at the shared-memory port; it sleeps in between, because it shares a scheduler with epilogue warps.
 // The dispatch is only legal as a cooperative launch: CTAs wait for one another, so all must be resident.
 // Every wait is bounded; a wait that runs out records its site, raises the CTA's abort flag and the CTA
 // leaves its loops, frees tensor memory and returns; the other CTAs run into their own limits.
@@ -53,7 +54,7 @@ namespace {
 
 using namespace umma_gemv;
 
-constexpr int N_ISSUE = 4;                               // MMA-issuing warps at most: stage g belongs to issuer g % n_issue
+constexpr int N_ISSUE = 4;                               // MMA-issuing warps at most: tile t of a stage belongs to issuer t % n_issue
 constexpr int THREADS = 64 + 256 + 32 * (N_ISSUE - 1);   // warp 0 producer, warp 1 issuer 0, warps 2-9 epilogue, warps 10.. issuers 1..
 constexpr int CHUNK_K = 128;                             // bytes of K per sub-tile row (one swizzle row) = 4 Q8_0 blocks
 constexpr int MAX_S = 8;                                 // sub-tiles (chunks) per ring stage
