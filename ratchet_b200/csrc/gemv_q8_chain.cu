@@ -399,7 +399,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                     const uint32_t t0 = tmem_base + tg * TG_COLS + ((uint32_t)(q * 32) << 16) + half * 2 * cstride;
                     const int tile_cols = 4 * cstride + (cstride == 8 ? 8 : 0);
                     // all of the stage's loads first (one wait), then the arithmetic
-                    int v[MAX_TILES][2][8] = {};
+                    int v[MAX_TILES][2][8]; // tiles the warp has no rows in stay unset: their sums are dropped
                     if (narrow) {
 #pragma unroll
                         for (int t = 0; t < MAX_TILES; t++) {
