@@ -394,6 +394,14 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 const int srow = ks / 16; // bytes per row of the node's scales
                 if (!mbar_wait(bar_sfull + 8 * sbuf, sphase, abort_flag, 10)) break;
                 for (int s = 0; s < nstages; s++) {
+                    // the stage's weight scales and activation scales do not wait for the MMAs
+                    __half2 d2[MAX_TILES];
+                    float2 xv[MAX_TILES];
+#pragma unroll
+                    for (int t = 0; t < MAX_TILES; t++) {
+                        d2[t] = *reinterpret_cast<const __half2 *>(scales_n + sc_off[t] + s * S * 8);
+                        xv[t] = *reinterpret_cast<const float2 *>(xs + xs_off[t] + s * S * 4);
+                    }
                     if (!mbar_wait(bar_done + 8 * slot, phase, abort_flag, 6)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t t0 = tmem_base + tg * TG_COLS + ((uint32_t)(q * 32) << 16) + half * 2 * cstride;
@@ -420,13 +428,6 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_tempty + 8 * tg); // the sums are in registers: the MMAs may reuse the columns
                     // no branches from here to the end of the stage: three independent chains the scheduler can interleave
-                    __half2 d2[MAX_TILES];
-                    float2 xv[MAX_TILES];
-#pragma unroll
-                    for (int t = 0; t < MAX_TILES; t++) {
-                        d2[t] = *reinterpret_cast<const __half2 *>(scales_n + sc_off[t] + s * S * 8);
-                        xv[t] = *reinterpret_cast<const float2 *>(xs + xs_off[t] + s * S * 4);
-                    }
 #pragma unroll
                     for (int t = 0; t < MAX_TILES; t++) {
                         const int k = my_k[t];
