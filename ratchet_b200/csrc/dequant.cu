@@ -18,6 +18,9 @@ __global__ void __launch_bounds__(256) dequant_kernel(const void *src, const voi
 // Q8_0H -> f16, 16 codes per thread: the pre-pass form (same values as the element-wise kernel).
 __global__ void __launch_bounds__(256) dequant_q8h_f16_vec_kernel(const uint4 *codes, const __half *scales, uint4 *dst,
                                                                  long long n16) {
+    // the next kernel may start its prologue now; this one's stream predecessor may still be reading what it writes
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
         const uint4 w = __ldg(codes + i);
@@ -42,6 +45,9 @@ __global__ void __launch_bounds__(256) dequant_q8h_f16_vec_kernel(const uint4 *c
 // mins, 128 bytes of nibbles).  Same arithmetic, value by value, as q4k_element: (d * sc) * q - dmin * m
 // with every step rounded to f32, then one rounding to f16.
 __global__ void __launch_bounds__(256) dequant_q4k_f16_vec_kernel(const uint8_t *src, __half *dst, long long n_units) {
+    // the next kernel may start its prologue now; this one's stream predecessor may still be reading what it writes
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < n_units; u += stride) {
         const long long blk_i = u >> 3;           // super-block of 256 values
@@ -82,6 +88,9 @@ __global__ void __launch_bounds__(256) dequant_q4k_f16_vec_kernel(const uint8_t 
 }
 
 __global__ void __launch_bounds__(256) cast_bf16_f16_kernel(const uint4 *src, uint4 *dst, long long n8) {
+    // the next kernel may start its prologue now; this one's stream predecessor may still be reading what it writes
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
         uint4 v = __ldg(src + i);
@@ -110,7 +119,8 @@ cudaError_t launch_cast_bf16_f16(const void *src, void *dst, long long numel, in
     if (n8 > 0) {
         const long long want = (n8 + 255) / 256;
         const int blocks = (int)(want < (long long)sm_count * 16 ? want : (long long)sm_count * 16);
-        cast_bf16_f16_kernel<<<blocks, 256, 0, stream>>>((const uint4 *)src, (uint4 *)dst, n8);
+        cudaError_t e = launch_pdl(cast_bf16_f16_kernel, dim3(blocks), dim3(256), 0, stream, (const uint4 *)src, (uint4 *)dst, n8);
+        if (e != cudaSuccess) return e;
     }
     if (numel % 8)
         cast_bf16_f16_tail_kernel<<<1, 256, 0, stream>>>((const __nv_bfloat16 *)src, (__half *)dst, n8 * 8, numel);
@@ -128,7 +138,7 @@ cudaError_t launch_dequant(rt_dtype dt, long long numel, const void *src, const 
             long long n16 = numel / 16;
             long long w2 = (n16 + threads - 1) / threads;
             const int b2 = (int)(w2 < (long long)sm_count * 16 ? w2 : (long long)sm_count * 16);
-            dequant_q8h_f16_vec_kernel<<<b2, threads, 0, stream>>>((const uint4 *)src, (const __half *)scales, (uint4 *)dst, n16);
+            return launch_pdl(dequant_q8h_f16_vec_kernel, dim3(b2), dim3(threads), 0, stream, (const uint4 *)src, (const __half *)scales, (uint4 *)dst, n16);
         } else {
             dequant_kernel<LK_Q8H, __half><<<blocks, threads, 0, stream>>>(src, scales, (__half *)dst, numel);
         }
@@ -143,7 +153,7 @@ cudaError_t launch_dequant(rt_dtype dt, long long numel, const void *src, const 
             const long long n_units = numel / 32;
             const long long w2 = (n_units + threads - 1) / threads;
             const int b2 = (int)(w2 < (long long)sm_count * 16 ? w2 : (long long)sm_count * 16);
-            dequant_q4k_f16_vec_kernel<<<b2, threads, 0, stream>>>((const uint8_t *)src, (__half *)dst, n_units);
+            return launch_pdl(dequant_q4k_f16_vec_kernel, dim3(b2), dim3(threads), 0, stream, (const uint8_t *)src, (__half *)dst, n_units);
         } else {
             dequant_kernel<LK_Q4K, __half><<<blocks, threads, 0, stream>>>(src, scales, (__half *)dst, numel);
         }

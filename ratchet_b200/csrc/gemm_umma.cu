@@ -200,6 +200,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything so far touched no global data: it ran beside the stream predecessor (programmatic dependent
+    // launch).  Operands, bias and output wait for it; the successor may start its own prologue.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int num_k = (prm.K + BK - 1) / BK;
     const int tiles_per_batch = prm.tiles_r * prm.tiles_s;
@@ -407,8 +411,7 @@ cudaError_t launch_bn(const CUtensorMap &mp, const CUtensorMap &mq, UmmaParams p
     prm.idesc |= (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     const long long total = (long long)prm.tiles_r * prm.tiles_s * prm.stacks;
     const int grid = (int)(total < sm_count ? total : sm_count);
-    kernel<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(mp, mq, prm);
-    return cudaGetLastError();
+    return launch_pdl(kernel, dim3(grid), dim3(NUM_THREADS), C::SMEM_BYTES, stream, mp, mq, prm);
 }
 
 } // namespace
