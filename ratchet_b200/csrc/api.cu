@@ -662,6 +662,11 @@ rt_status rt_executable_create(rt_device *dev, const rt_dispatch *nodes, int32_t
             delete x;
             return fail(RT_ERR_ARG, "rt_executable_create: node without a plan of this device");
         }
+        if (nodes[i].out && (nodes[i].out == nodes[i].lhs || nodes[i].out == nodes[i].rhs ||
+                             (nodes[i].plan->spec.has_bias && nodes[i].out == nodes[i].bias))) {
+            delete x;
+            return fail(RT_ERR_INVARIANT, "Matmul is never in place: out aliases an operand");
+        }
         x->nodes.push_back(nodes[i]);
         x->launches += nodes[i].plan->launches;
     }

@@ -111,6 +111,12 @@ def test_launch_rejects_aliasing_and_null(gpu):
     plan = gpu.plan_for(out.op.desc)
     assert lib.rt_matmul_launch(plan, a.ptr, a.ptr, None, a.ptr, None) == rb._lib.RT_ERR_INVARIANT
     assert lib.rt_matmul_launch(plan, None, a.ptr, None, a.ptr, None) == rb._lib.RT_ERR_ARG
+    # the same invariant when the node is bound into an executable
+    from ctypes import byref, c_void_p
+    node = (rb._lib.rt_dispatch * 1)()
+    node[0].plan, node[0].lhs, node[0].rhs, node[0].out = plan, a.ptr, a.ptr, a.ptr
+    exe = c_void_p()
+    assert lib.rt_executable_create(gpu._h, node, 1, 0, byref(exe)) == rb._lib.RT_ERR_INVARIANT
 
 
 # ----------------------------------------------------------------------------- Q8_0 GEMV (decode)
