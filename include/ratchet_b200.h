@@ -300,6 +300,78 @@ rt_status rt_shard_rows(rt_dtype dt, const void *src, uint64_t rows, uint64_t k,
  * checked on the device.  Arithmetic: quant.rs:114-120; gemm.rs:400-406 for the f16 form. */
 rt_status rt_dequantize_device(rt_device *dev, rt_dtype dt, uint64_t numel, const void *src, void *dst, void *stream);
 
+/* ------------------------------------------------------------------ GGUF files (weight load) */
+
+/* The loader that feeds the Matmul its weights: crates/ratchet-loader/src/gguf/gguf.rs.
+ * rt_gguf_open = Header::read (gguf.rs:409-480): magic "GGUF" in either byte order, versions
+ * 1-3 (32-bit lengths in v1, 64-bit after), metadata key/values, tensor infos with the
+ * dimensions REVERSED so the outermost comes first (gguf.rs:452), and the tensor data offset
+ * rounded up to `general.alignment` (default 32).  Errors (RT_ERR_ARG with the reference's
+ * message): unknown magic, unsupported version, unrecognized value type, a bool that is not
+ * 0/1; plus, which the reference leaves to its reader, any length that runs past the end of
+ * the file.  A ggml type id outside lib.rs:57-80 is RT_ERR_DTYPE. */
+typedef struct rt_gguf rt_gguf;
+
+/* gguf.rs:183-216 (ValueType); the numbers are the file's. */
+typedef enum rt_gguf_type {
+    RT_GGUF_U8 = 0, RT_GGUF_I8 = 1, RT_GGUF_U16 = 2, RT_GGUF_I16 = 3, RT_GGUF_U32 = 4,
+    RT_GGUF_I32 = 5, RT_GGUF_F32 = 6, RT_GGUF_BOOL = 7, RT_GGUF_STRING = 8, RT_GGUF_ARRAY = 9,
+    RT_GGUF_U64 = 10, RT_GGUF_I64 = 11, RT_GGUF_F64 = 12
+} rt_gguf_type;
+
+/* gguf.rs:218-232 (Value), flattened for C.  Integers and bools fill u64, i64 and f64 alike;
+ * floats fill f64 only.  `str` (strings; NUL-terminated, trailing NULs of the file dropped as
+ * in read_string, gguf.rs:165-180) and `node` stay valid until rt_gguf_close. */
+typedef struct rt_gguf_value {
+    int32_t type;       /* rt_gguf_type */
+    int32_t elem_type;  /* arrays: the elements' rt_gguf_type; else -1 */
+    uint64_t len;       /* strings: bytes; arrays: elements; else 1 */
+    uint64_t u64;
+    int64_t i64;
+    double f64;
+    const char *str;
+    const void *node;   /* opaque; what rt_gguf_array_item walks */
+} rt_gguf_value;
+
+/* gguf.rs:56-60 (TensorInfo) plus size_in_bytes (93-98). */
+typedef struct rt_gguf_tensor_info {
+    const char *name;   /* valid until rt_gguf_close */
+    uint32_t ggml_type; /* lib.rs:57-80: 0 F32, 1 F16, 8 Q8_0, 12 Q4_K, ... */
+    rt_shape shape;     /* outermost first */
+    uint64_t offset;    /* from the start of the tensor data */
+    uint64_t nbytes;    /* numel / block_numel * type_size */
+} rt_gguf_tensor_info;
+
+rt_status rt_gguf_open(const char *path, rt_gguf **out);
+rt_status rt_gguf_close(rt_gguf *g);
+int32_t rt_gguf_version(const rt_gguf *g);
+uint64_t rt_gguf_alignment(const rt_gguf *g);
+uint64_t rt_gguf_tensor_data_offset(const rt_gguf *g);   /* Header::tensor_data_offset */
+uint64_t rt_gguf_tensor_count(const rt_gguf *g);
+uint64_t rt_gguf_metadata_count(const rt_gguf *g);
+/* Entries in file order.  rt_gguf_metadata_find = Metadata::get (gguf.rs:149-153): an absent
+ * key is RT_ERR_ARG "missing key <key>". */
+rt_status rt_gguf_metadata_at(const rt_gguf *g, uint64_t index, const char **key, rt_gguf_value *value);
+rt_status rt_gguf_metadata_find(const rt_gguf *g, const char *key, rt_gguf_value *value);
+rt_status rt_gguf_array_item(const rt_gguf_value *array, uint64_t index, rt_gguf_value *item);
+/* An absent name is RT_ERR_ARG "cannot find tensor info for <name>" (gguf.rs:490-493). */
+rt_status rt_gguf_tensor_at(const rt_gguf *g, uint64_t index, rt_gguf_tensor_info *info);
+rt_status rt_gguf_tensor_find(const rt_gguf *g, const char *name, rt_gguf_tensor_info *info);
+/* ratchet_from_gguf (gguf.rs:113-141): the dtype a tensor loads as.  F32 and F16 as they are;
+ * Q8_0 as RT_Q8_0H (the f16-capable-device branch, gguf.rs:130-136; RT_Q8_0F may be asked for
+ * instead); Q4_K as RT_Q4_K (extension: the reference rejects it); every other ggml type is
+ * RT_ERR_UNSUPPORTED "unsupported ggml dtype". */
+rt_status rt_gguf_tensor_dtype(const rt_gguf *g, const char *name, rt_dtype *dt);
+/* TensorInfo::read (gguf.rs:62-84) + GGUFInterop::transcode (gguf/dtype.rs:44-110) on the host:
+ * writes the tensor in the device layout of `dt` (rt_dtype_segments) to `out`.  RT_ERR_SHAPE when
+ * the element count does not divide by the block size, RT_ERR_DTYPE when the tensor cannot load
+ * as `dt`. */
+rt_status rt_gguf_read_tensor(rt_gguf *g, const char *name, rt_dtype dt, void *out, uint64_t out_bytes);
+/* The same checks without reading: the bytes rt_gguf_read_tensor would write. */
+rt_status rt_gguf_tensor_nbytes(const rt_gguf *g, const char *name, rt_dtype dt, uint64_t *nbytes);
+/* The same, uploaded into a new device buffer (freed by the caller); *shape may be NULL. */
+rt_status rt_gguf_load_tensor(rt_gguf *g, rt_device *dev, const char *name, rt_dtype dt, rt_buffer **buf, rt_shape *shape);
+
 #ifdef __cplusplus
 }
 #endif

@@ -12,7 +12,8 @@ from .tensor import (Device, DeviceRequest, DType, Executable, GpuBuffer, Linear
                      Tensor, bf16_bits_to_f32, f32_to_bf16_bits, transcode_gguf_q8_0)
 
 from .sharded import Comm, ShardedLinear, shard_bounds, shard_rows
+from .gguf import GGUF, TensorInfo
 
-__all__ = ["Comm", "ShardedLinear", "shard_bounds", "shard_rows", "Device", "DeviceRequest", "DType", "Executable", "GpuBuffer", "Linear", "Matmul", "PinnedArray", "Quantization",
+__all__ = ["GGUF", "TensorInfo", "Comm", "ShardedLinear", "shard_bounds", "shard_rows", "Device", "DeviceRequest", "DType", "Executable", "GpuBuffer", "Linear", "Matmul", "PinnedArray", "Quantization",
            "Quantizer", "Tensor", "RatchetError", "ShapeError", "InvariantError", "EPILOGUE_NONE",
            "EPILOGUE_GELU_TANH", "bf16_bits_to_f32", "f32_to_bf16_bits", "transcode_gguf_q8_0"]

@@ -72,6 +72,16 @@ class rt_dispatch(Structure):
                 ("opts", rt_launch_opts)]
 
 
+class rt_gguf_value(Structure):
+    _fields_ = [("type", c_int32), ("elem_type", c_int32), ("len", c_uint64), ("u64", c_uint64),
+                ("i64", c_int64), ("f64", ctypes.c_double), ("str", c_void_p), ("node", c_void_p)]
+
+
+class rt_gguf_tensor_info(Structure):
+    _fields_ = [("name", c_char_p), ("ggml_type", ctypes.c_uint32), ("shape", rt_shape),
+                ("offset", c_uint64), ("nbytes", c_uint64)]
+
+
 class RatchetError(RuntimeError):
     """A non-OK rt_status.  `.status` is the code, `.status_name` its name."""
 
@@ -156,6 +166,22 @@ def load() -> ctypes.CDLL:
         "rt_ipc_close": (c_int32, [V, V]),
         "rt_shard_rows": (c_int32, [c_int32, V, c_uint64, c_uint64, c_uint64, c_uint64, V]),
         "rt_dequantize_device": (c_int32, [V, c_int32, c_uint64, V, V, V]),
+        "rt_gguf_open": (c_int32, [c_char_p, POINTER(V)]),
+        "rt_gguf_close": (c_int32, [V]),
+        "rt_gguf_version": (c_int32, [V]),
+        "rt_gguf_alignment": (c_uint64, [V]),
+        "rt_gguf_tensor_data_offset": (c_uint64, [V]),
+        "rt_gguf_tensor_count": (c_uint64, [V]),
+        "rt_gguf_metadata_count": (c_uint64, [V]),
+        "rt_gguf_metadata_at": (c_int32, [V, c_uint64, POINTER(c_char_p), POINTER(rt_gguf_value)]),
+        "rt_gguf_metadata_find": (c_int32, [V, c_char_p, POINTER(rt_gguf_value)]),
+        "rt_gguf_array_item": (c_int32, [POINTER(rt_gguf_value), c_uint64, POINTER(rt_gguf_value)]),
+        "rt_gguf_tensor_at": (c_int32, [V, c_uint64, POINTER(rt_gguf_tensor_info)]),
+        "rt_gguf_tensor_find": (c_int32, [V, c_char_p, POINTER(rt_gguf_tensor_info)]),
+        "rt_gguf_tensor_dtype": (c_int32, [V, c_char_p, POINTER(c_int32)]),
+        "rt_gguf_read_tensor": (c_int32, [V, c_char_p, c_int32, V, c_uint64]),
+        "rt_gguf_tensor_nbytes": (c_int32, [V, c_char_p, c_int32, POINTER(c_uint64)]),
+        "rt_gguf_load_tensor": (c_int32, [V, V, c_char_p, c_int32, POINTER(V), POINTER(rt_shape)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

@@ -19,6 +19,7 @@ INCLUDE = os.path.join(ROOT, "include")
 SOURCES = [
     "spec.cpp",
     "quant_host.cpp",
+    "gguf_reader.cpp",
     "comm.cpp",
     "api.cu",
     "matmul_simt.cu",

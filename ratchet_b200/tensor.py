@@ -174,6 +174,16 @@ class GpuBuffer:
         self.ptr = int(_lib.load().rt_buffer_ptr(self._h) or 0)
         self.size = int(_lib.load().rt_buffer_size(self._h))
 
+    @classmethod
+    def adopt(cls, device: Device, handle: c_void_p) -> "GpuBuffer":
+        """Take ownership of an rt_buffer the library allocated (e.g. rt_gguf_load_tensor)."""
+        b = cls.__new__(cls)
+        b.device = device
+        b._h = handle
+        b.ptr = int(_lib.load().rt_buffer_ptr(handle) or 0)
+        b.size = int(_lib.load().rt_buffer_size(handle))
+        return b
+
     def __del__(self):
         try:
             if self._h:

@@ -81,6 +81,35 @@ def test_reference_regression_shapes(gpu):
     check_problem(Problem(Q8H, F16, (51865, 384), (1, 1, 384), (False, True, True), seed=34, w_std=0.02), gpu)
 
 
+def test_every_matmul_call_site_of_the_models(gpu):
+    """The forms and shape families of each `matmul` / `gemm` call in the reference's models."""
+    nn = (False, False, False)
+    # attention scores q·kT (k permuted beforehand, so plain matmul) in f32 after .full(), then
+    # softmax(w)·v in the cache dtype: phi2/attn.rs:139-151, phi3/attn.rs:144-155,
+    # moondream/text_model.rs:87-98 -- rank 4, all stacks equal; prefill (S = T) and decode (S = 1)
+    for heads, hd, S, T in [(32, 80, 48, 48), (32, 80, 1, 200), (32, 96, 1, 64)]:
+        check_problem(Problem(F32, F32, (1, heads, S, hd), (1, heads, hd, T), nn, seed=51), gpu)
+        check_problem(Problem(F16, F16, (1, heads, S, T), (1, heads, T, hd), nn, seed=52), gpu)
+    # whisper/mha.rs:109-124: scores and values both in the activation dtype, encoder length 1500
+    for dt in (F32, F16):
+        check_problem(Problem(dt, dt, (1, 6, 1500, 64), (1, 6, 64, 1500), nn, seed=53), gpu)
+        check_problem(Problem(dt, dt, (1, 6, 1500, 1500), (1, 6, 1500, 64), nn, seed=54), gpu)
+        check_problem(Problem(dt, dt, (1, 6, 1, 64), (1, 6, 64, 1500), nn, seed=55), gpu)  # decoder cross-attention
+    # moondream/vision_encoder.rs:58-61: 729 patches, 16 heads of 72
+    check_problem(Problem(F32, F32, (1, 16, 729, 72), (1, 16, 72, 729), nn, seed=56), gpu)
+    check_problem(Problem(F16, F16, (1, 16, 729, 729), (1, 16, 729, 72), nn, seed=57), gpu)
+    # crates/ratchet-core/tests/attn_tests.rs:56-65,129-153
+    check_problem(Problem(F32, F32, (1, 128, 256), (256, 256), nn, seed=58), gpu)
+    check_problem(Problem(F32, F32, (1, 64, 384), (1, 384, 384), nn, seed=59), gpu)
+    # nn::Linear (linear.rs:23) at the shapes the configs do not name
+    lin = (False, True, True)
+    check_problem(Problem(Q8H, F16, (51200, 2560), (1, 1, 2560), lin, bias=True, seed=60, w_std=0.02), gpu)  # Phi-2 lm_head
+    check_problem(Problem(Q8H, F16, (16384, 3072), (1, 1, 3072), lin, seed=61, w_std=0.02), gpu)             # Phi-3 gate_up
+    check_problem(Problem(Q8H, F16, (3072, 8192), (1, 7, 8192), lin, seed=62, w_std=0.02), gpu)              # Phi-3 down, short prompt
+    check_problem(Problem(Q8H, F16, (2048, 1152), (1, 729, 1152), lin, bias=True, seed=63, w_std=0.02), gpu)  # Moondream projection
+    check_problem(Problem(F16, F16, (384, 384), (1, 1500, 384), lin, seed=64, w_std=0.05), gpu)              # Whisper k (no bias)
+
+
 def test_rank_and_broadcast_forms(gpu):
     check_problem(Problem(F32, F32, (7, 5), (5,), (False, False, False), seed=41), gpu)           # implicit n
     check_problem(Problem(F32, F32, (5,), (5, 9), (False, False, False), seed=42), gpu)           # implicit m
