@@ -471,11 +471,13 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
                    "_split" + std::to_string(pl->split);
     } else if (desc->lhs_dt == RT_Q4_K && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.N >= 1 && s.N <= 16 &&
                (s.N == 1 || s.trans_rhs) && !empty && !force_simt() &&
-               q4k_gemv_pick_split(p.M, p.K, (int)s.N, dev->sm_count) > 0) {
+               q4k_gemv_pick_split(p.M, p.K, (int)s.N, (int)s.stacks, dev->sm_count) > 0) {
         pl->kernel = PK_Q4K_GEMV;
         pl->nv = (int)s.N;
-        pl->split = q4k_gemv_pick_split(p.M, p.K, (int)s.N, dev->sm_count);
-        pl->name = std::string("q4k_gemv_mma_nv") + std::to_string(pl->nv) + "_split" + std::to_string(pl->split);
+        pl->split = q4k_gemv_pick_split(p.M, p.K, (int)s.N, (int)s.stacks, dev->sm_count); // split | groups per CTA << 8 | buffers << 16
+        pl->name = std::string("q4k_gemv_mma_nv") + std::to_string(pl->nv) + "_split" + std::to_string(pl->split & 0xff) +
+                   (((pl->split >> 8) & 0xff) > 1 ? "_walk" + std::to_string((pl->split >> 8) & 0xff) + "x" + std::to_string((pl->split >> 16) & 0xff) + "buf"
+                                                   : std::string());
     } else if (umma_eligible(*desc, s)) {
         pl->kernel = PK_GEMM_UMMA;
         pl->lhs_is_q = s.trans_out;

@@ -19,7 +19,12 @@
 //    sum_k (s1*q - dmin*m) x = s1 * sum_k (1024+q) x - s3 * sum_k x;
 //  * warps are reduced through shared memory in a fixed order and K slices through distributed
 //    shared memory in rank order: deterministic results;
+//  * with more than four vectors the staged activations outweigh one row group's weights, so a CTA
+//    then keeps them and walks several row groups, the next group's super-blocks already in flight
+//    into a second buffer while the current one is multiplied;
 //  * epilogue = the reference's: f16(acc) + bias in f16, optional fused GELU.
+#include <algorithm>
+#include <cstdlib>
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -34,8 +39,8 @@ __device__ int g_gemv_q4k_error = 0;
 
 namespace {
 
-constexpr int WARPS = 8;
-constexpr int THREADS = WARPS * 32;
+constexpr int WARPS_ONCE = 8;  // a CTA that handles one row group (up to four such CTAs per SM)
+constexpr int WARPS_WALK = 16; // a CTA that walks several row groups (one or two per SM)
 constexpr int ROWS = 16;
 constexpr int SB_BYTES = 144;
 constexpr unsigned long long WAIT_LIMIT_CYCLES = 4000000000ull;
@@ -57,63 +62,90 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __host__ __device__ inline int row_stride(int nsb) { const int b = nsb * SB_BYTES; return b + ((32 - b % 128) + 128) % 128; }
 
 struct Q4kLayout {
-    int codes, table, x, xsum, red, bar, total; // byte offsets
+    int codes, table, slot, x, xsum, red, bar, total; // byte offsets (slot: bytes per half-CTA table)
 };
-__host__ __device__ inline Q4kLayout layout(int nsb, int nv) {
+__host__ __device__ inline Q4kLayout layout(int nsb, int nv, int nbuf) {
+    const int WARPS = nbuf > 1 ? WARPS_WALK : WARPS_ONCE;
     Q4kLayout l;
-    l.codes = 0;
-    l.table = ROWS * row_stride(nsb);                       // float2 [ROWS][nsb*8 + 1]
-    l.x = l.table + ROWS * (nsb * 8 + 1) * 8;                // half [nv][nsb*256], permuted
+    l.codes = 0;                                             // nbuf buffers of ROWS padded rows
     const int cols = nv <= 8 ? 8 : 16;
+    l.slot = ROWS * (nsb * 8 + 1) * 8;                       // float2 [ROWS][nsb*8 + 1]
+    l.table = nbuf * ROWS * row_stride(nsb);                 // one table per half-CTA when walking
+    l.x = l.table + (nbuf > 1 ? 2 : 1) * l.slot;             // half [nv][nsb*256], permuted
     l.xsum = l.x + ((nv * nsb * 256 * 2 + 15) & ~15);        // float [nsb*8][cols]
     l.red = l.xsum + nsb * 8 * cols * 4;                     // float [WARPS][ROWS][cols]
     l.bar = l.red + WARPS * ROWS * cols * 4;
-    l.total = l.bar + 16;
+    l.total = l.bar + 8 * 4; // up to four buffers, one barrier each
     return l;
 }
 
 // NVG: groups of 8 activation vectors (1 or 2).  SPLIT: K is split over a cluster of gridDim.y CTAs.
-template <int NVG, bool SPLIT>
-__global__ void __launch_bounds__(THREADS) q4k_gemv_kernel(MatmulParams p, int nv, int sb_per_cta, int lhs_constant) {
+// WARPS: WARPS_WALK when the CTA walks gpc > 1 row groups through nbuf buffers, else WARPS_ONCE.
+// HALVES: 2 = the two halves of the CTA's warps work on alternate row groups at the same time,
+// each with its own header table, partial sums and named barrier, sharing the activations and the
+// buffers (like two CTAs per SM, without staging the activations twice); not with SPLIT, whose
+// cluster barrier needs the whole CTA.
+template <int NVG, bool SPLIT, int WARPS, int HALVES>
+__global__ void __launch_bounds__(WARPS * 32) q4k_gemv_kernel(MatmulParams p, int nv, int sb_per_cta, int lhs_constant, int gpc, int nbuf) {
+    static_assert(HALVES == 1 || !SPLIT, "the cluster barrier needs every thread");
+    constexpr int THREADS = WARPS * 32;
+    constexpr int WH = WARPS / HALVES, TH = WH * 32; // warps and threads that share a row group
     extern __shared__ __align__(128) uint8_t smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31;
+    const int half = HALVES == 2 ? (int)(threadIdx.x / TH) : 0;
+    const int t = (int)threadIdx.x - half * TH;       // thread index within the half
+    const int warp = t >> 5;                          // warp index within the half
+    auto half_sync = [&]() {
+        if (HALVES == 1) __syncthreads();
+        else asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "r"(TH) : "memory");
+    };
     const int g = lane >> 2, c = lane & 3;
     const int batch = blockIdx.z;
     const int nsb_total = p.K >> 8;
     const int split = SPLIT ? (int)blockIdx.y : 0;
     const int sb_begin = split * sb_per_cta;
     const int nsb = max(0, min(nsb_total, sb_begin + sb_per_cta) - sb_begin);
-    const Q4kLayout L = layout(sb_per_cta, nv);
+    const Q4kLayout L = layout(sb_per_cta, nv, nbuf);
     const int rstride = row_stride(sb_per_cta);
     uint8_t *codes_s = smem + L.codes;
-    float2 *table = reinterpret_cast<float2 *>(smem + L.table);
     const int tstride = sb_per_cta * 8 + 1;
+    float2 *table = reinterpret_cast<float2 *>(smem + L.table + half * L.slot);
     __half *x_s = reinterpret_cast<__half *>(smem + L.x);
     float *xsum = reinterpret_cast<float *>(smem + L.xsum);
-    float *red = reinterpret_cast<float *>(smem + L.red);
-    const uint32_t bar_addr = smem_u32(smem + L.bar);
     constexpr int COLS = NVG * 8;
+    float *red = reinterpret_cast<float *>(smem + L.red) + half * WH * ROWS * COLS;
+    const uint32_t bar_addr = smem_u32(smem + L.bar); // one barrier per buffer, 8 bytes apart
 
-    const int row_base = blockIdx.x * ROWS;
-    const int rows_here = min(ROWS, p.M - row_base);
+    // this CTA's row groups: gpc consecutive groups of ROWS rows
+    const int group0 = blockIdx.x * gpc;
+    const int my_groups = max(0, min(gpc, (p.M + ROWS - 1) / ROWS - group0));
     const uint8_t *w = (const uint8_t *)p.lhs + (long long)(batch % p.lhs_stack) * p.M * nsb_total * SB_BYTES;
+    const uint32_t row_bytes = (uint32_t)nsb * SB_BYTES;
+
+    // one thread: ask for row group `it` of this CTA (into buffer it % nbuf)
+    auto request = [&](int it) {
+        const int buf = it % nbuf;
+        const int rb = (group0 + it) * ROWS;
+        const int rows = min(ROWS, p.M - rb);
+        const uint32_t bar = bar_addr + 8u * buf;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(row_bytes * (uint32_t)rows) : "memory");
+        for (int r = 0; r < rows; r++) {
+            const uint8_t *src = w + ((long long)(rb + r) * nsb_total + sb_begin) * SB_BYTES;
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(codes_s + (buf * ROWS + r) * rstride)), "l"(src), "r"(row_bytes), "r"(bar) : "memory");
+        }
+    };
 
     if (threadIdx.x == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_addr) : "memory");
+        for (int b = 0; b < nbuf; b++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_addr + 8u * b) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (!lhs_constant) asm volatile("griddepcontrol.wait;" ::: "memory");
     __syncthreads();
 
-    const uint32_t row_bytes = (uint32_t)nsb * SB_BYTES;
     if (threadIdx.x == 0 && row_bytes > 0) {
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_addr), "r"(row_bytes * (uint32_t)rows_here) : "memory");
-        for (int r = 0; r < rows_here; r++) {
-            const uint8_t *src = w + ((long long)(row_base + r) * nsb_total + sb_begin) * SB_BYTES;
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                         ::"r"(smem_u32(codes_s + r * rstride)), "l"(src), "r"(row_bytes), "r"(bar_addr) : "memory");
-        }
+        for (int it = 0; it < min(nbuf, my_groups); it++) request(it);
     }
     if (lhs_constant) asm volatile("griddepcontrol.wait;" ::: "memory");
 
@@ -122,27 +154,57 @@ __global__ void __launch_bounds__(THREADS) q4k_gemv_kernel(MatmulParams p, int n
     // nibbles of two 32-bit words leave the AND / shift sequence below as f16 pairs.
     const int kslice = nsb * 256;
     const long long rbatch = batch % p.rhs_stack;
-    for (int i = threadIdx.x; i < nv * (kslice / 8); i += THREADS) {
-        const int v = i / (kslice / 8), o = i - v * (kslice / 8);
-        const __half *src = (const __half *)p.rhs + (rbatch * nv + v) * (long long)p.K + (long long)sb_begin * 256 + o * 8;
-        const uint4 raw = *reinterpret_cast<const uint4 *>(src);
-        const __half *h = reinterpret_cast<const __half *>(&raw);
-        __half out[8] = {h[0], h[2], h[1], h[3], h[4], h[6], h[5], h[7]};
-        *reinterpret_cast<uint4 *>(x_s + (long long)v * sb_per_cta * 256 + o * 8) = *reinterpret_cast<const uint4 *>(out);
-        float s = 0.f;
+    // eight independent 16-byte loads per thread are in flight at a time: the activations come from L2
+    // and a dependent load per iteration would cost one L2 round trip each.  kslice / 8 is a multiple
+    // of 32, so a warp is either wholly inside or wholly outside the range.
+    constexpr int XU = 8;
+    const int x_items = nv * (kslice / 8);
+    for (int i0 = threadIdx.x; i0 < x_items; i0 += THREADS * XU) {
+        uint4 raw[XU];
 #pragma unroll
-        for (int j = 0; j < 8; j++) s += __half2float(h[j]);
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        if ((o & 3) == 0) xsum[(o >> 2) * COLS + v] = s; // four consecutive 8-element groups = one sub-block
+        for (int u = 0; u < XU; u++) {
+            const int i = i0 + u * THREADS;
+            if (i < x_items) {
+                const int v = i / (kslice / 8), o = i - v * (kslice / 8);
+                raw[u] = *reinterpret_cast<const uint4 *>((const __half *)p.rhs + (rbatch * nv + v) * (long long)p.K +
+                                                          (long long)sb_begin * 256 + o * 8);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < XU; u++) {
+            const int i = i0 + u * THREADS;
+            if (i < x_items) {
+                const int v = i / (kslice / 8), o = i - v * (kslice / 8);
+                const __half *h = reinterpret_cast<const __half *>(&raw[u]);
+                __half out[8] = {h[0], h[2], h[1], h[3], h[4], h[6], h[5], h[7]};
+                *reinterpret_cast<uint4 *>(x_s + (long long)v * sb_per_cta * 256 + o * 8) = *reinterpret_cast<const uint4 *>(out);
+                float s = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) s += __half2float(h[j]);
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                if ((o & 3) == 0) xsum[(o >> 2) * COLS + v] = s; // four consecutive 8-element groups = one sub-block
+            }
+        }
     }
     // vectors past nv (the MMA has 8 or 16 columns) read vector nv-1 and a zero sum is not needed: their outputs are dropped
 
-    // ---- wait for the super-blocks (bounded)
+    if (HALVES == 2) __syncthreads(); // the activations are staged by all warps and read by both halves
+
     bool ok = true;
-    if (row_bytes > 0 && !mbar_try_wait(bar_addr, 0)) {
+#pragma unroll 1
+    for (int it = half; it < my_groups; it += HALVES) {
+    const int buf = it % nbuf;
+    const uint32_t bar = bar_addr + 8u * buf;
+    const uint32_t parity = (uint32_t)(it / nbuf) & 1u; // how often this buffer has been filled before
+    const int row_base = (group0 + it) * ROWS;
+    const int rows_here = min(ROWS, p.M - row_base);
+    const uint8_t *codes_b = codes_s + buf * ROWS * rstride;
+
+    // ---- wait for the super-blocks (bounded)
+    if (ok && row_bytes > 0 && !mbar_try_wait(bar, parity)) {
         const unsigned long long t0 = (unsigned long long)clock64();
-        while (!mbar_try_wait(bar_addr, 0)) {
+        while (!mbar_try_wait(bar, parity)) {
             if ((unsigned long long)clock64() - t0 > WAIT_LIMIT_CYCLES) {
                 ok = false;
                 atomicCAS(&g_gemv_q4k_error, 0, 1);
@@ -153,12 +215,12 @@ __global__ void __launch_bounds__(THREADS) q4k_gemv_kernel(MatmulParams p, int n
 
     // ---- header table: (s1, s3) per (row, sub-block)
     if (ok) {
-        const int r = threadIdx.x >> 4;
-        for (int i = threadIdx.x & 15; i < nsb * 8; i += 16) {
+        const int r = (t >> 4) & 15;
+        for (int i = (t & 15) + 16 * (t >> 8); i < nsb * 8; i += 16 * (TH / 256)) {
             const int sb = i >> 3, j = i & 7;
             float2 e = make_float2(0.f, 0.f);
             if (r < rows_here) {
-                const uint8_t *blk = codes_s + r * rstride + sb * SB_BYTES;
+                const uint8_t *blk = codes_b + r * rstride + sb * SB_BYTES;
                 const float d = __half2float(*reinterpret_cast<const __half *>(blk));
                 const float dmin = __half2float(*reinterpret_cast<const __half *>(blk + 2));
                 int sc, m;
@@ -169,7 +231,7 @@ __global__ void __launch_bounds__(THREADS) q4k_gemv_kernel(MatmulParams p, int n
             table[r * tstride + i] = e;
         }
     }
-    __syncthreads();
+    half_sync();
 
     float acc[NVG][4];
 #pragma unroll
@@ -178,8 +240,8 @@ __global__ void __launch_bounds__(THREADS) q4k_gemv_kernel(MatmulParams p, int n
         for (int i = 0; i < 4; i++) acc[n][i] = 0.f;
 
     if (ok) {
-        const uint8_t *qa = codes_s + g * rstride + 16 + c * 8;
-        const uint8_t *qb = codes_s + (g + 8) * rstride + 16 + c * 8;
+        const uint8_t *qa = codes_b + g * rstride + 16 + c * 8;
+        const uint8_t *qb = codes_b + (g + 8) * rstride + 16 + c * 8;
         const float2 *ta = table + g * tstride, *tb = table + (g + 8) * tstride;
         // B fragment column n = g <-> activation vector (clamped); one pointer per group of 8 vectors
         const __half *xl[NVG];
@@ -187,7 +249,7 @@ __global__ void __launch_bounds__(THREADS) q4k_gemv_kernel(MatmulParams p, int n
         for (int n = 0; n < NVG; n++) xl[n] = x_s + (long long)min(n * 8 + g, nv - 1) * sb_per_cta * 256 + c * 8;
         const uint32_t magic = 0x64006400u, mask = 0x000F000Fu;
 #pragma unroll 1
-        for (int pr = warp; pr < nsb * 4; pr += WARPS) { // a pair = sub-blocks 2*pr (low nibbles) and 2*pr+1 (high nibbles)
+        for (int pr = warp; pr < nsb * 4; pr += WH) { // a pair = sub-blocks 2*pr (low nibbles) and 2*pr+1 (high nibbles)
             const int sb = pr >> 2, jp = pr & 3;
             const int off = sb * SB_BYTES + jp * 32;
             const uint2 wa = *reinterpret_cast<const uint2 *>(qa + off);
@@ -230,13 +292,19 @@ __global__ void __launch_bounds__(THREADS) q4k_gemv_kernel(MatmulParams p, int n
         red[(warp * ROWS + g + 8) * COLS + n * 8 + 2 * c] = acc[n][2];
         red[(warp * ROWS + g + 8) * COLS + n * 8 + 2 * c + 1] = acc[n][3];
     }
-    __syncthreads();
-    const int r = threadIdx.x >> 4, v = threadIdx.x & 15; // one (row, vector) per thread
+    half_sync();
+    // every warp is done with this buffer and with the table: refill the buffer for nbuf groups ahead
+    if (t == 0 && ok && row_bytes > 0 && it + nbuf < my_groups) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        request(it + nbuf);
+    }
+    const int r = (t >> 4) & 15, v = t < 256 ? (t & 15) : COLS; // one (row, vector) per thread of the first 256
     float sum = 0.f;
     if (v < COLS) {
 #pragma unroll
-        for (int w8 = 0; w8 < WARPS; w8++) sum += red[(w8 * ROWS + r) * COLS + v];
+        for (int w8 = 0; w8 < WH; w8++) sum += red[(w8 * ROWS + r) * COLS + v];
     }
+    bool writer = true;
     if (SPLIT) {
         cg::cluster_group cluster = cg::this_cluster();
         __syncthreads();
@@ -247,9 +315,9 @@ __global__ void __launch_bounds__(THREADS) q4k_gemv_kernel(MatmulParams p, int n
             for (unsigned k = 1; k < n; k++) sum += cluster.map_shared_rank(red, k)[r * COLS + v];
         }
         cluster.sync(); // keep every CTA's shared memory alive until rank 0 has read it
-        if (cluster.block_rank() != 0) return;
+        writer = cluster.block_rank() == 0;
     }
-    if (v < nv && ok) {
+    if (writer && v < nv && ok) {
         const int row = row_base + r;
         if (row < p.M) {
             const bool has_bias = p.bias_mode != BIAS_NONE;
@@ -260,23 +328,28 @@ __global__ void __launch_bounds__(THREADS) q4k_gemv_kernel(MatmulParams p, int n
             ((__half *)p.out)[p.trans_out ? ob + (long long)v * p.M + row : ob + (long long)row * nv + v] = o;
         }
     }
+    } // row groups
 }
 
 template <int NVG>
-cudaError_t launch_g(const MatmulParams &p, int nv, int split, bool lhs_constant, cudaStream_t stream) {
+cudaError_t launch_g(const MatmulParams &p, int nv, int split, int gpc, int nbuf, bool lhs_constant, cudaStream_t stream) {
     const int nsb_total = p.K / 256;
     const int spc = (nsb_total + split - 1) / split;
-    const size_t smem = (size_t)layout(spc, nv).total;
-    auto kernel = split == 1 ? q4k_gemv_kernel<NVG, false> : q4k_gemv_kernel<NVG, true>;
-    static size_t configured[2] = {0, 0};
-    if (smem > 48 * 1024 && configured[split != 1] < smem) {
+    const size_t smem = (size_t)layout(spc, nv, nbuf).total;
+    const bool walk = nbuf > 1;
+    auto kernel = walk ? (split == 1 ? q4k_gemv_kernel<NVG, false, WARPS_WALK, 2> : q4k_gemv_kernel<NVG, true, WARPS_WALK, 1>)
+                       : (split == 1 ? q4k_gemv_kernel<NVG, false, WARPS_ONCE, 1> : q4k_gemv_kernel<NVG, true, WARPS_ONCE, 1>);
+    static size_t configured[4] = {0, 0, 0, 0};
+    const int slot = (walk ? 2 : 0) + (split != 1 ? 1 : 0);
+    if (smem > 48 * 1024 && configured[slot] < smem) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        configured[split != 1] = smem;
+        configured[slot] = smem;
     }
+    const int groups = (p.M + ROWS - 1) / ROWS;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((p.M + ROWS - 1) / ROWS, split, p.stacks);
-    cfg.blockDim = dim3(THREADS);
+    cfg.gridDim = dim3((groups + gpc - 1) / gpc, split, p.stacks);
+    cfg.blockDim = dim3((walk ? WARPS_WALK : WARPS_ONCE) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -293,26 +366,47 @@ cudaError_t launch_g(const MatmulParams &p, int nv, int split, bool lhs_constant
     }
     cfg.attrs = attr;
     cfg.numAttrs = n;
-    return cudaLaunchKernelEx(&cfg, kernel, p, nv, spc, lhs_constant ? 1 : 0);
+    return cudaLaunchKernelEx(&cfg, kernel, p, nv, spc, lhs_constant ? 1 : 0, gpc, nbuf);
 }
 
 } // namespace
 
-// K split over a cluster (1, 2, 4 or 8), or 0 when the shape does not fit the kernel.
-int q4k_gemv_pick_split(int M, int K, int nv, int sm_count) {
+// The launch shape for [M][K] x nv vectors: the K split over a cluster (1, 2, 4 or 8) in bits 0-7,
+// the row groups one CTA walks in bits 8-15 and its weight buffers in bits 16-23; 0 when the shape
+// does not fit the kernel.
+int q4k_gemv_pick_split(int M, int K, int nv, int stacks, int sm_count) {
     if (K < 256 || K % 256 != 0 || nv < 1 || nv > 16 || M < 1) return 0;
     const int nsb = K / 256;
     const int groups = (M + ROWS - 1) / ROWS;
-    const size_t target = 56 * 1024, limit = 200 * 1024; // four CTAs per SM
+    const size_t limit = 200 * 1024, whole_sm = 226 * 1024;
+    static const int walk_from = [] { const char *e = std::getenv("RT_Q4K_WALK_FROM"); return e ? std::atoi(e) : 2; }();
+    if (nv >= walk_from) {
+        // keep the activations and walk row groups, one CTA of WARPS_WALK warps per SM (its registers
+        // leave no room for a second): the smallest split that fits at least two weight buffers,
+        // then as many buffers (up to four) as fit, since the bytes in flight hide the DRAM latency
+        for (int split = 1; split <= 8 && nsb / split >= 1; split *= 2) {
+            const int spc = (nsb + split - 1) / split;
+            if ((size_t)layout(spc, nv, 2).total > whole_sm) continue;
+            const int clusters = std::max(1, sm_count / split / std::max(1, stacks));
+            const int gpc = std::min(255, (groups + clusters - 1) / clusters);
+            if (gpc < 2) break;
+            int nbuf = std::min(4, gpc);
+            while (nbuf > 2 && (size_t)layout(spc, nv, nbuf).total > whole_sm) nbuf--;
+            return split | (gpc << 8) | (nbuf << 16);
+        }
+    }
+    const size_t target = 56 * 1024; // four CTAs per SM
     int split = 1;
-    while (split < 8 && (size_t)layout((nsb + split - 1) / split, nv).total > target) split *= 2;
+    while (split < 8 && (size_t)layout((nsb + split - 1) / split, nv, 1).total > target) split *= 2;
     while (split < 8 && groups * split < 3 * sm_count && nsb / (split * 2) >= 2) split *= 2;
-    if ((size_t)layout((nsb + split - 1) / split, nv).total > limit) return 0;
-    return split;
+    if ((size_t)layout((nsb + split - 1) / split, nv, 1).total > limit) return 0;
+    return split | (1 << 8) | (1 << 16);
 }
 
-cudaError_t launch_q4k_gemv(const MatmulParams &p, int nv, int split, bool lhs_constant, cudaStream_t stream) {
-    return nv <= 8 ? launch_g<1>(p, nv, split, lhs_constant, stream) : launch_g<2>(p, nv, split, lhs_constant, stream);
+cudaError_t launch_q4k_gemv(const MatmulParams &p, int nv, int config, bool lhs_constant, cudaStream_t stream) {
+    const int split = config & 0xff, gpc = std::max(1, (config >> 8) & 0xff), nbuf = std::max(1, (config >> 16) & 0xff);
+    return nv <= 8 ? launch_g<1>(p, nv, split, gpc, nbuf, lhs_constant, stream)
+                   : launch_g<2>(p, nv, split, gpc, nbuf, lhs_constant, stream);
 }
 
 cudaError_t gemv_q4k_take_error(int *site, cudaStream_t stream) {

@@ -56,8 +56,8 @@ const char *gemv_chain_name(const GemvChain *chain);
 cudaError_t gemv_chain_take_error(int *site, cudaStream_t stream);
 
 // Q4_K x f16 GEMV / skinny GEMM on warp MMAs.  nv = columns of op(rhs), 1..16 (rhs stored [nv][K]).
-int q4k_gemv_pick_split(int M, int K, int nv, int sm_count);
-cudaError_t launch_q4k_gemv(const MatmulParams &p, int nv, int split, bool lhs_constant, cudaStream_t stream);
+int q4k_gemv_pick_split(int M, int K, int nv, int stacks, int sm_count); // split | groups per CTA << 8 | weight buffers << 16, or 0
+cudaError_t launch_q4k_gemv(const MatmulParams &p, int nv, int config, bool lhs_constant, cudaStream_t stream);
 cudaError_t gemv_q4k_take_error(int *site, cudaStream_t stream);
 
 // Dense f32 GEMM on the tensor cores, three TF32 MMAs per product (f32-class accuracy): D[R][S] = P[R][K] . Q[S][K]^T.

@@ -372,6 +372,23 @@ def test_q4k_gemv_shapes_and_vectors(gpu):
     check_problem(Problem(Q4K, F16, (64, 512), (4, 1, 512), (False, True, True), seed=92, w_std=0.02), gpu)     # broadcast weight
 
 
+def test_q4k_skinny_gemm_walks_row_groups(gpu):
+    """More row groups than SMs and 2..16 vectors: a CTA keeps the activations and walks several row
+    groups (two at a time, one per half of its warps).  Ragged last group, a last CTA with fewer
+    groups, both output orders, bias + GELU, K split over a cluster, batched weights."""
+    for nv in (2, 5, 8, 9, 16):
+        for to in (True, False):
+            _, kernel = check_problem(Problem(Q4K, F16, (2405, 768), (1, nv, 768), (False, True, to), bias=True, epilogue=1,
+                                              seed=190 + nv, w_std=0.02), gpu)
+            assert f"nv{nv}_split1_walk2" in kernel, kernel
+    _, kernel = check_problem(Problem(Q4K, F16, (4100, 8192), (1, 16, 8192), (False, True, True), seed=196, w_std=0.02), gpu)
+    assert "nv16_split4_walk7" in kernel, kernel
+    _, kernel = check_problem(Problem(Q4K, F16, (3, 2405, 512), (3, 4, 512), (False, True, True), bias=True, seed=197, w_std=0.02), gpu)
+    assert "walk4" in kernel, kernel
+    _, kernel = check_problem(Problem(Q4K, F16, (8192, 3072), (1, 8, 3072), (False, True, True), seed=198, w_std=0.02), gpu)
+    assert "nv8_split1_walk4x4buf" in kernel, kernel
+
+
 def test_q4k_forms(gpu):
     check_problem(Problem(Q4K, F16, (40, 256), (1, 256), (False, True, True), bias=True, seed=81, w_std=0.02), gpu)
     check_problem(Problem(Q4K, F16, (2, 33, 512), (2, 512, 7), (False, False, False), seed=82, w_std=0.02), gpu)
