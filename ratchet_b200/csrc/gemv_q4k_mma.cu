@@ -61,6 +61,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // row stride of the staged super-blocks: a multiple of 16 that is 32 mod 128 (conflict-free 8-byte reads by 8 rows)
 __host__ __device__ inline int row_stride(int nsb) { const int b = nsb * SB_BYTES; return b + ((32 - b % 128) + 128) % 128; }
 
+// halves between two staged activation vectors: 64 bytes past a multiple of 128, so that the 16-byte
+// reads of the two vectors (B-fragment columns) in one quarter-warp fall in different banks
+__host__ __device__ inline int x_stride(int nsb) { return nsb * 256 + 32; }
+
 struct Q4kLayout {
     int codes, table, slot, x, xsum, red, bar, total; // byte offsets (slot: bytes per half-CTA table)
 };
@@ -71,8 +75,8 @@ __host__ __device__ inline Q4kLayout layout(int nsb, int nv, int nbuf) {
     const int cols = nv <= 8 ? 8 : 16;
     l.slot = ROWS * (nsb * 8 + 1) * 8;                       // float2 [ROWS][nsb*8 + 1]
     l.table = nbuf * ROWS * row_stride(nsb);                 // one table per half-CTA when walking
-    l.x = l.table + (nbuf > 1 ? 2 : 1) * l.slot;             // half [nv][nsb*256], permuted
-    l.xsum = l.x + ((nv * nsb * 256 * 2 + 15) & ~15);        // float [nsb*8][cols]
+    l.x = l.table + (nbuf > 1 ? 2 : 1) * l.slot;             // half [nv][x_stride], permuted
+    l.xsum = l.x + nv * x_stride(nsb) * 2;                   // float [nsb*8][cols]
     l.red = l.xsum + nsb * 8 * cols * 4;                     // float [WARPS][ROWS][cols]
     l.bar = l.red + WARPS * ROWS * cols * 4;
     l.total = l.bar + 8 * 4; // up to four buffers, one barrier each
@@ -177,7 +181,7 @@ __global__ void __launch_bounds__(WARPS * 32) q4k_gemv_kernel(MatmulParams p, in
                 const int v = i / (kslice / 8), o = i - v * (kslice / 8);
                 const __half *h = reinterpret_cast<const __half *>(&raw[u]);
                 __half out[8] = {h[0], h[2], h[1], h[3], h[4], h[6], h[5], h[7]};
-                *reinterpret_cast<uint4 *>(x_s + (long long)v * sb_per_cta * 256 + o * 8) = *reinterpret_cast<const uint4 *>(out);
+                *reinterpret_cast<uint4 *>(x_s + (long long)v * x_stride(sb_per_cta) + o * 8) = *reinterpret_cast<const uint4 *>(out);
                 float s = 0.f;
 #pragma unroll
                 for (int j = 0; j < 8; j++) s += __half2float(h[j]);
@@ -246,7 +250,7 @@ __global__ void __launch_bounds__(WARPS * 32) q4k_gemv_kernel(MatmulParams p, in
         // B fragment column n = g <-> activation vector (clamped); one pointer per group of 8 vectors
         const __half *xl[NVG];
 #pragma unroll
-        for (int n = 0; n < NVG; n++) xl[n] = x_s + (long long)min(n * 8 + g, nv - 1) * sb_per_cta * 256 + c * 8;
+        for (int n = 0; n < NVG; n++) xl[n] = x_s + (long long)min(n * 8 + g, nv - 1) * x_stride(sb_per_cta) + c * 8;
         const uint32_t magic = 0x64006400u, mask = 0x000F000Fu;
 #pragma unroll 1
         for (int pr = warp; pr < nsb * 4; pr += WH) { // a pair = sub-blocks 2*pr (low nibbles) and 2*pr+1 (high nibbles)
