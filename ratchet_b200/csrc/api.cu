@@ -405,7 +405,7 @@ static bool umma_eligible(const rt_matmul_desc &d, const Spec &s) {
         if (!dense && d.lhs_dt != RT_Q8_0H && d.lhs_dt != RT_Q4_K) return false;
         if (!umma_gemm_supported(s.K)) return false;
     }
-    if (s.M < 1 || s.N < 16 || s.stacks < 1) return false;
+    if (s.M < 1 || s.N < 9 || s.stacks < 1) return false; // up to 8 columns: the streaming GEMV kernels
     if ((double)s.M * (double)s.N * (double)s.K * (double)s.stacks < (double)(1 << 21)) return false;
     return true;
 }

@@ -436,6 +436,17 @@ def test_umma_tf32x3_dense_f32_forms(gpu):
         assert err <= 1e-5, (kernel, err)
 
 
+def test_short_prompts_take_the_tensor_core_gemm(gpu):
+    """9..15 activation rows (more than the streaming GEMV kernels take, fewer than one MMA column
+    block): the tensor-core GEMM with the missing rows zero-filled by the tile loads."""
+    for nv in (9, 15):
+        for lhs, dt in ((Q8H, F16), (F16, F16), (BF16, BF16), (F32, F32)):
+            for to in (True, False):
+                _, kernel = check_problem(Problem(lhs, dt, (1000, 512), (1, nv, 512), (False, True, to), bias=True,
+                                                  epilogue=0 if dt == F32 else 1, seed=200 + nv, w_std=0.02), gpu)
+                assert kernel.startswith("gemm_umma"), kernel
+
+
 def test_umma_takes_the_prefill_configs(gpu):
     lib = rb._lib.load()
     for lhs_dt, act, wshape, xshape in [(Q8H, F16, (1536, 384), (1, 1500, 384)), (Q8H, F16, (384, 1536), (1, 1500, 1536)),
