@@ -489,8 +489,27 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
         pl->p_stack = s.trans_out ? rhs_st : lhs_st;
         pl->q_stack = s.trans_out ? lhs_st : rhs_st;
         pl->tf32x3 = desc->rhs_dt == RT_F32;
-        pl->bn = pl->tf32x3 ? 128 : umma_pick_bn(pl->R, pl->S, pl->u_stacks, dev->sm_count);
+        pl->bn = pl->tf32x3 ? umma_tf32_pick_bn(pl->R, pl->S, pl->u_stacks, dev->sm_count)
+                            : umma_pick_bn(pl->R, pl->S, pl->u_stacks, dev->sm_count);
         pl->launches = 1;
+        if (pl->tf32x3 && umma_tf32_presplit_pays(pl->S, pl->bn)) {
+            // P (the operand whose 128-row tiles every tile column reads) is split into hi and lo once
+            // per launch, into this scratch, rather than by every CTA of its tile row.  A problem whose
+            // P is too large for that keeps the split inside the GEMM.
+            const uint64_t bytes = (uint64_t)pl->p_stack * (uint64_t)pl->R * (uint64_t)s.K * 8;
+            if (bytes <= (1ull << 30)) {
+                cudaError_t e = cudaSetDevice(dev->ordinal);
+                if (e == cudaSuccess) e = cudaMalloc(&pl->scratch, bytes);
+                if (e != cudaSuccess) {
+                    pl->scratch = nullptr;
+                    delete pl;
+                    return fail(e == cudaErrorMemoryAllocation ? RT_ERR_NOMEM : RT_ERR_CUDA,
+                                std::string("plan scratch: ") + cudaGetErrorString(e));
+                }
+                pl->scratch_bytes = bytes;
+                pl->launches = 2;
+            }
+        }
         if (is_quantized(desc->lhs_dt)) {
             pl->scratch_bytes = (uint64_t)(s.lhs_stack * s.M * s.K) * 2;
             cudaError_t e = cudaSetDevice(dev->ordinal);
@@ -517,7 +536,7 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
             }
         }
         pl->name = std::string(pl->tf32x3 ? "gemm_umma_tf32x3_" : "gemm_umma_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt) + "_bn" +
-                   std::to_string(pl->bn) + (pl->scratch ? "_dequant_prepass" : "");
+                   std::to_string(pl->bn) + (pl->scratch ? (pl->tf32x3 ? "_presplit" : "_dequant_prepass") : "");
     } else if (s.N == 1 && !s.trans_lhs) {
         pl->kernel = PK_GEMV_SIMT;
         pl->name = std::string("gemv_simt_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt);
@@ -605,7 +624,8 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
             if (scatter) return fail(RT_ERR_UNSUPPORTED, "scattered outputs are not taken by the f32 GEMM");
             const void *P = plan->lhs_is_q ? rhs : lhs, *Q = plan->lhs_is_q ? lhs : rhs;
             e = launch_gemm_umma_tf32x3(P, Q, out, plan->R, plan->S, (int)s.K, plan->u_stacks, plan->p_stack, plan->q_stack, p.bias,
-                                        p.bias_dt, s.has_bias ? BIAS_PER_N : BIAS_NONE, p.epilogue, plan->dev->sm_count, st);
+                                        p.bias_dt, s.has_bias ? BIAS_PER_N : BIAS_NONE, p.epilogue, plan->bn, plan->scratch,
+                                        plan->dev->sm_count, st);
             break;
         }
         const void *w = lhs;

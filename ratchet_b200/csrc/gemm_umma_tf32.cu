@@ -12,16 +12,24 @@
 // accumulator (measured: 2.9e-5 rel-L2 at K = 4096); so an accumulator only ever takes CHUNK stages
 // (K = 128: 48 MMAs), and the chunks are added in registers with ordinary f32 adds.
 //
-//   warp 0      TMA producer: 128-byte-swizzled boxes of 128 x 32 f32 (P) and 128 x 32 f32 (Q) per stage
-//   warp 1      MMA issuer: per stage 3 x 4 tcgen05.mma kind::tf32 (128 x 128 x 8) into one of two accumulators
-//   warps 2-9   per stage: split the two raw tiles in place into hi and write the lo tiles beside them
+//   warp 0      TMA producer: 128-byte-swizzled boxes of 128 x 32 f32 (P) and BN x 32 f32 (Q) per stage
+//   warp 1      MMA issuer: per stage 3 x 4 tcgen05.mma kind::tf32 (128 x BN x 8) into one of two accumulators
+//   warps 2-9   per stage: split the raw tiles in place into hi and write the lo tiles beside them
 //               (element-wise, so the swizzled layout carries over unchanged); per chunk: add the finished
-//               accumulator into 64 registers per thread (one chunk behind the splitting, so the MMAs never
-//               wait for it); per output tile: bias / GELU, store f32 rows
+//               accumulator into BN / 2 registers per thread (one chunk behind the splitting, so the MMAs
+//               never wait for it); per output tile: bias / GELU, store f32 rows
+// Two things keep the SMs busy on Linear-shaped problems (few rows of P, many of Q).  The tile width BN
+// (128, 96, 80 or 64 rows of Q) is the one whose tiles take the fewest waves x width: 10240 rows are 80
+// tiles of 128 on 148 SMs, but 128 tiles of 80.  And when P spans more than one tile column its split is
+// done once, by a pass of its own into a scratch pair (hi, lo) that the TMA producer then loads directly,
+// instead of by every CTA of the tile row again: the per-stage split then only covers the BN rows of Q.
 // Every wait is bounded; on expiry the kernel records the site, frees tensor memory and returns.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.hpp"
@@ -35,17 +43,25 @@ namespace {
 
 using namespace umma_gemv; // smem_u32, mbarrier helpers, fences, encode_tiled_fn
 
-constexpr int BM = 128, BN = 128;
+constexpr int BM = 128;                // rows of P per tile (the MMA's M)
 constexpr int BK = 32;                 // 32 f32 = one 128-byte swizzle row
 constexpr int UMMA_K = 8;              // TF32: 8 elements = 32 bytes per instruction
-constexpr int STAGES = 3;
-constexpr int TILE_BYTES = BM * BK * 4;                   // 16 KB (P and Q tiles have the same size: BM == BN)
-constexpr int STAGE_BYTES = 4 * TILE_BYTES;               // P raw->hi, P lo, Q raw->hi, Q lo
+constexpr int P_TILE = BM * BK * 4;    // 16 KB
 constexpr int SPLIT_WARPS = 8;
 constexpr int NUM_THREADS = 64 + SPLIT_WARPS * 32;
-constexpr int TMEM_COLS = 2 * BN;      // two accumulators: one collects a chunk while the other is drained
+constexpr int ACC_STRIDE = 128;        // tensor-memory columns between the two accumulators
+constexpr int TMEM_COLS = 2 * ACC_STRIDE; // two accumulators: one collects a chunk while the other is drained
 constexpr int CHUNK = 4;               // stages per accumulator: K = 128
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+
+// BN: rows of Q per tile (the MMA's N), a multiple of 16 up to 128.  A stage holds P hi, P lo, Q hi, Q lo.
+template <int BN> struct TileCfg {
+    static_assert(BN % 16 == 0 && BN >= 32 && BN <= 128, "BN");
+    static constexpr int Q_TILE = BN * BK * 4;
+    static constexpr int STAGE_BYTES = 2 * P_TILE + 2 * Q_TILE;
+    static constexpr int STAGES_FIT = (227 * 1024 - 1024 - 256) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_FIT < 6 ? STAGES_FIT : 6;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
 
 struct Tf32Params {
     int R, S, K;
@@ -56,6 +72,14 @@ struct Tf32Params {
     int epilogue;
     int tiles_r, tiles_s;
 };
+
+// tcgen05.ld of 8 consecutive columns of this warp's 32 lanes, no wait
+__device__ __forceinline__ void tmem_ld8_f32(uint32_t taddr, uint32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
+}
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site) {
     return mbar_wait_flag(bar, parity, abort_flag, site, &g_umma_tf32_error);
@@ -74,22 +98,14 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint
                  : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
+// P_PRE: P arrives already split (map_p = its hi parts, map_plo = its lo parts, written by
+// split_tf32_kernel): every CTA of a tile row would otherwise repeat the same split.
+template <int BN, bool P_PRE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const Tf32Params prm) {
+gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_plo,
+                        const __grid_constant__ CUtensorMap map_q, const Tf32Params prm) {
+    using Cfg = TileCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, Q_TILE = Cfg::Q_TILE;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *tiles = smem;
@@ -140,9 +156,11 @@ gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
                 for (int kb = 0; kb < num_k; kb++) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, 1)) { ok = false; break; }
                     const uint32_t dst = smem_u32(tiles + stage * STAGE_BYTES);
-                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_full + 8 * stage), "r"(2 * TILE_BYTES) : "memory");
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_full + 8 * stage),
+                                 "r"((P_PRE ? 2 : 1) * P_TILE + Q_TILE) : "memory");
                     tma_load_3d(dst, &map_p, kb * BK, r0, bp, bar_full + 8 * stage);
-                    tma_load_3d(dst + 2 * TILE_BYTES, &map_q, kb * BK, s0, bq, bar_full + 8 * stage);
+                    if (P_PRE) tma_load_3d(dst + P_TILE, &map_plo, kb * BK, r0, bp, bar_full + 8 * stage);
+                    tma_load_3d(dst + 2 * P_TILE, &map_q, kb * BK, s0, bq, bar_full + 8 * stage);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -165,9 +183,9 @@ gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
                     }
                     if (!mbar_wait(bar_split + 8 * stage, phase, abort_flag, 3)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + buf * BN;
-                    const uint32_t p_hi = smem_u32(tiles + stage * STAGE_BYTES), p_lo = p_hi + TILE_BYTES;
-                    const uint32_t q_hi = p_hi + 2 * TILE_BYTES, q_lo = p_hi + 3 * TILE_BYTES;
+                    const uint32_t d_tmem = tmem_base + buf * ACC_STRIDE;
+                    const uint32_t p_hi = smem_u32(tiles + stage * STAGE_BYTES), p_lo = p_hi + P_TILE;
+                    const uint32_t q_hi = p_hi + 2 * P_TILE, q_lo = q_hi + Q_TILE;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; k++) {
                         const uint32_t off = k * UMMA_K * 4;
@@ -193,19 +211,22 @@ gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
         int stage = 0, chunk = 0; // chunk: the next chunk to be drained, counted over all tiles
         uint32_t phase = 0;
         bool ok = true;
-        // adds accumulator (chunk & 1), columns [half * 64, half * 64 + 64) of this thread's row, into racc and
+        constexpr int HC = BN / 2; // columns of a row that one thread keeps
+        // adds accumulator (chunk & 1), columns [half * HC, half * HC + HC) of this thread's row, into racc and
         // hands the accumulator back
-        auto drain = [&](float (&racc)[64]) -> bool {
+        auto drain = [&](float (&racc)[HC]) -> bool {
             const int buf = chunk & 1;
             if (!mbar_wait(bar_tfull + 8 * buf, (chunk >> 1) & 1, abort_flag, 4)) return false;
             tc_fence_after();
+            uint32_t v[HC / 8][8];
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + buf * BN + half * 64 + h * 32 + ((uint32_t)(q * 32) << 16), v);
+            for (int j = 0; j < HC / 8; j++)
+                tmem_ld8_f32(tmem_base + buf * ACC_STRIDE + half * HC + j * 8 + ((uint32_t)(q * 32) << 16), v[j]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < 32; i++) racc[h * 32 + i] += __uint_as_float(v[i]);
-            }
+            for (int j = 0; j < HC / 8; j++)
+#pragma unroll
+                for (int i = 0; i < 8; i++) racc[j * 8 + i] += __uint_as_float(v[j][i]);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
@@ -215,21 +236,23 @@ gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
             const int r0 = (rem % prm.tiles_r) * BM, s0 = (rem / prm.tiles_r) * BN;
-            float racc[64];
+            float racc[HC];
 #pragma unroll
-            for (int i = 0; i < 64; i++) racc[i] = 0.f;
+            for (int i = 0; i < HC; i++) racc[i] = 0.f;
             int pending = 0; // chunks of this tile whose stages are split but which are not drained yet
             for (int kb = 0; kb < num_k; kb++) {
                 if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 2)) { ok = false; break; }
-                // two raw tiles of 16 KB: thread t takes float4 number t, t + 256, ... of each
+                // the raw tiles (P unless it came split, and Q): thread t takes float4 number t, t + 256, ... of each
                 uint8_t *base = tiles + stage * STAGE_BYTES;
 #pragma unroll
-                for (int op = 0; op < 2; op++) {
-                    float4 *raw = reinterpret_cast<float4 *>(base + op * 2 * TILE_BYTES);
-                    float4 *lo = reinterpret_cast<float4 *>(base + op * 2 * TILE_BYTES + TILE_BYTES);
+                for (int op = P_PRE ? 1 : 0; op < 2; op++) {
+                    float4 *raw = reinterpret_cast<float4 *>(base + op * 2 * P_TILE);
+                    float4 *lo = reinterpret_cast<float4 *>(base + op * 2 * P_TILE + (op == 0 ? P_TILE : Q_TILE));
+                    const int n4 = (op == 0 ? P_TILE : Q_TILE) / 16;
 #pragma unroll
-                    for (int i = 0; i < TILE_BYTES / 16 / (SPLIT_WARPS * 32); i++) {
+                    for (int i = 0; i < (P_TILE / 16 + SPLIT_WARPS * 32 - 1) / (SPLIT_WARPS * 32); i++) {
                         const int idx = st_tid + i * (SPLIT_WARPS * 32);
+                        if (idx >= n4) break;
                         const float4 v = raw[idx];
                         float4 h, l;
                         h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
@@ -259,29 +282,28 @@ gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
             if (prm.bias_mode == BIAS_PER_M && row < prm.R) row_bias = load_bias(prm.bias, prm.bias_dt, row);
             float *orow = prm.out + (long long)b * prm.R * prm.S + (long long)row * prm.S;
             const bool vec_ok = (prm.S % 4 == 0) && (reinterpret_cast<uintptr_t>(prm.out) % 16 == 0);
-#pragma unroll
-            for (int h = 0; h < 2; h++) { // 32 columns per round, two rounds per warp
-                const int col0 = s0 + half * 64 + h * 32;
+            {
+                const int col0 = s0 + half * HC;
                 if (row < prm.R && col0 < prm.S) {
-                    if (vec_ok && col0 + 32 <= prm.S) {
+                    if (vec_ok && col0 + HC <= prm.S) {
 #pragma unroll
-                        for (int g = 0; g < 8; g++) {
+                        for (int g = 0; g < HC / 4; g++) {
                             float4 o;
                             float *op = reinterpret_cast<float *>(&o);
 #pragma unroll
                             for (int j = 0; j < 4; j++) {
                                 const int i = g * 4 + j;
                                 const float bv = prm.bias_mode == BIAS_PER_N ? load_bias(prm.bias, prm.bias_dt, col0 + i) : row_bias;
-                                op[j] = epilogue_value<float>(racc[h * 32 + i], has_bias, bv, prm.epilogue);
+                                op[j] = epilogue_value<float>(racc[i], has_bias, bv, prm.epilogue);
                             }
                             *reinterpret_cast<float4 *>(orow + col0 + g * 4) = o;
                         }
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 32; i++) {
+                        for (int i = 0; i < HC; i++) {
                             if (col0 + i < prm.S) {
                                 const float bv = prm.bias_mode == BIAS_PER_N ? load_bias(prm.bias, prm.bias_dt, col0 + i) : row_bias;
-                                orow[col0 + i] = epilogue_value<float>(racc[h * 32 + i], has_bias, bv, prm.epilogue);
+                                orow[col0 + i] = epilogue_value<float>(racc[i], has_bias, bv, prm.epilogue);
                             }
                         }
                     }
@@ -303,16 +325,46 @@ gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
     }
 }
 
-// [stack][rows][K] f32 row-major -> boxes of 128 rows x 32 elements, 128-byte swizzle, zero fill
-bool make_map_f32(CUtensorMap *map, const void *base, long long K, long long rows, long long stack) {
+// hi = the value with the 13 low mantissa bits cleared (what a TF32 operand keeps), lo = value - hi
+__global__ void split_tf32_kernel(const float4 *__restrict__ in, float4 *__restrict__ hi, float4 *__restrict__ lo, long long n4) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+        const float4 v = in[i];
+        float4 h, l;
+        h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
+        h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
+        h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
+        h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
+        hi[i] = h;
+        lo[i] = l;
+    }
+}
+
+// [stack][rows][K] f32 row-major -> boxes of box_rows rows x 32 elements, 128-byte swizzle, zero fill
+bool make_map_f32(CUtensorMap *map, const void *base, long long K, long long rows, long long stack, int box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)stack};
     cuuint64_t strides[2] = {(cuuint64_t)K * 4, (cuuint64_t)K * 4 * (cuuint64_t)rows};
-    cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)BM, 1};
+    cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, bool P_PRE>
+cudaError_t launch_t(const CUtensorMap &mp, const CUtensorMap &mplo, const CUtensorMap &mq, Tf32Params prm, int sm_count, cudaStream_t stream) {
+    auto kernel = gemm_umma_tf32x3_kernel<BN, P_PRE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TileCfg<BN>::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    prm.tiles_s = (prm.S + BN - 1) / BN;
+    const long long total = (long long)prm.tiles_r * prm.tiles_s * prm.stacks;
+    const int grid = (int)(total < sm_count ? total : sm_count);
+    kernel<<<grid, NUM_THREADS, TileCfg<BN>::SMEM_BYTES, stream>>>(mp, mplo, mq, prm);
+    return cudaGetLastError();
 }
 
 } // namespace
@@ -320,12 +372,48 @@ bool make_map_f32(CUtensorMap *map, const void *base, long long K, long long row
 // K * 4 bytes must be a multiple of 16 (tensor-map strides), and the operands 16-byte aligned.
 bool umma_tf32_supported(long long K) { return K >= 4 && K % 4 == 0 && encode_tiled_fn() != nullptr; }
 
-// P: [p_stack][R][K] f32, Q: [q_stack][S][K] f32; out [stacks][R][S] f32.
+// Rows of Q per tile: the width whose tiles take the fewest waves x width on sm_count SMs (each SM
+// holds one CTA); ties go to the wider tile.
+int umma_tf32_pick_bn(int R, int S, int stacks, int sm_count) {
+    static const int forced = [] { const char *e = std::getenv("RT_TF32_BN"); return e ? std::atoi(e) : 0; }();
+    if (forced == 128 || forced == 96 || forced == 80 || forced == 64) return forced;
+    static const int widths[] = {128, 96, 80, 64};
+    int best = 128;
+    long long best_cost = -1;
+    for (int bn : widths) {
+        const long long tiles = (long long)((R + BM - 1) / BM) * ((S + bn - 1) / bn) * stacks;
+        const long long cost = ((tiles + sm_count - 1) / sm_count) * bn;
+        if (best_cost < 0 || cost < best_cost) best = bn, best_cost = cost;
+    }
+    return best;
+}
+
+// Whether splitting P ahead of the GEMM pays: every tile column repeats P's split otherwise.
+bool umma_tf32_presplit_pays(int S, int bn) { return (S + bn - 1) / bn >= 2; }
+
+// P: [p_stack][R][K] f32, Q: [q_stack][S][K] f32; out [stacks][R][S] f32.  p_split: nullptr, or room for
+// 2 * p_stack * R * K floats, in which P is split into its hi and lo parts by a pass of its own.
 cudaError_t launch_gemm_umma_tf32x3(const void *P, const void *Q, void *out, int R, int S, int K, int stacks, int p_stack, int q_stack,
-                                    const void *bias, int bias_dt, int bias_mode, int epilogue, int sm_count, cudaStream_t stream) {
-    if ((reinterpret_cast<uintptr_t>(P) | reinterpret_cast<uintptr_t>(Q)) % 16 != 0) return cudaErrorInvalidValue;
-    CUtensorMap mp, mq;
-    if (!make_map_f32(&mp, P, K, R, p_stack) || !make_map_f32(&mq, Q, K, S, q_stack)) return cudaErrorInvalidValue;
+                                    const void *bias, int bias_dt, int bias_mode, int epilogue, int bn, void *p_split, int sm_count,
+                                    cudaStream_t stream) {
+    if ((reinterpret_cast<uintptr_t>(P) | reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(p_split)) % 16 != 0)
+        return cudaErrorInvalidValue;
+    const long long p_elems = (long long)p_stack * R * K;
+    const float *p_hi = static_cast<const float *>(P), *p_lo = p_hi;
+    if (p_split) {
+        float *hi = static_cast<float *>(p_split), *lo = hi + p_elems;
+        const long long n4 = p_elems / 4; // K % 4 == 0
+        const int blocks = (int)std::min<long long>((n4 + 255) / 256, (long long)sm_count * 8);
+        split_tf32_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float4 *>(P), reinterpret_cast<float4 *>(hi),
+                                                      reinterpret_cast<float4 *>(lo), n4);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        p_hi = hi, p_lo = lo;
+    }
+    CUtensorMap mp, mplo, mq;
+    if (!make_map_f32(&mp, p_hi, K, R, p_stack, BM) || !make_map_f32(&mplo, p_lo, K, R, p_stack, BM) ||
+        !make_map_f32(&mq, Q, K, S, q_stack, bn))
+        return cudaErrorInvalidValue;
     Tf32Params prm{};
     prm.R = R; prm.S = S; prm.K = K;
     prm.stacks = stacks; prm.p_stack = p_stack; prm.q_stack = q_stack;
@@ -333,17 +421,14 @@ cudaError_t launch_gemm_umma_tf32x3(const void *P, const void *Q, void *out, int
     prm.bias = bias; prm.bias_dt = bias_dt; prm.bias_mode = bias_mode;
     prm.epilogue = epilogue;
     prm.tiles_r = (R + BM - 1) / BM;
-    prm.tiles_s = (S + BN - 1) / BN;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_umma_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return e;
-        configured = true;
+    const bool pre = p_split != nullptr;
+    switch (bn) {
+    case 128: return pre ? launch_t<128, true>(mp, mplo, mq, prm, sm_count, stream) : launch_t<128, false>(mp, mplo, mq, prm, sm_count, stream);
+    case 96: return pre ? launch_t<96, true>(mp, mplo, mq, prm, sm_count, stream) : launch_t<96, false>(mp, mplo, mq, prm, sm_count, stream);
+    case 80: return pre ? launch_t<80, true>(mp, mplo, mq, prm, sm_count, stream) : launch_t<80, false>(mp, mplo, mq, prm, sm_count, stream);
+    case 64: return pre ? launch_t<64, true>(mp, mplo, mq, prm, sm_count, stream) : launch_t<64, false>(mp, mplo, mq, prm, sm_count, stream);
+    default: return cudaErrorInvalidValue;
     }
-    const long long total = (long long)prm.tiles_r * prm.tiles_s * stacks;
-    const int grid = (int)(total < sm_count ? total : sm_count);
-    gemm_umma_tf32x3_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(mp, mq, prm);
-    return cudaGetLastError();
 }
 
 cudaError_t umma_tf32_take_error(int *site, cudaStream_t stream) {

@@ -62,8 +62,11 @@ cudaError_t gemv_q4k_take_error(int *site, cudaStream_t stream);
 
 // Dense f32 GEMM on the tensor cores, three TF32 MMAs per product (f32-class accuracy): D[R][S] = P[R][K] . Q[S][K]^T.
 bool umma_tf32_supported(long long K);
+int umma_tf32_pick_bn(int R, int S, int stacks, int sm_count);
+bool umma_tf32_presplit_pays(int S, int bn);
 cudaError_t launch_gemm_umma_tf32x3(const void *P, const void *Q, void *out, int R, int S, int K, int stacks, int p_stack, int q_stack,
-                                    const void *bias, int bias_dt, int bias_mode, int epilogue, int sm_count, cudaStream_t stream);
+                                    const void *bias, int bias_dt, int bias_mode, int epilogue, int bn, void *p_split, int sm_count,
+                                    cudaStream_t stream);
 cudaError_t umma_tf32_take_error(int *site, cudaStream_t stream);
 
 // Tensor-core GEMM (tcgen05): D[R][S] = P[R][K] . Q[S][K]^T, 16-bit K-major operands, bias along S.

@@ -436,6 +436,19 @@ def test_umma_tf32x3_dense_f32_forms(gpu):
         assert err <= 1e-5, (kernel, err)
 
 
+@pytest.mark.parametrize("w_rows,x_rows,name", [
+    (128, 18944, "bn128"), (96, 18944, "bn96"), (80, 18944, "bn80"), (40, 500, "bn64"),  # one tile column: split in the GEMM
+    (256, 9472, "bn128_presplit"), (192, 9472, "bn96_presplit"), (10240, 128, "bn80_presplit"), (300, 1400, "bn64_presplit"),
+])
+def test_umma_tf32x3_tile_widths(gpu, w_rows, x_rows, name):
+    """Every tile width of the f32 tensor-core GEMM, with the activations split inside the GEMM (one tile
+    column) and by the pass ahead of it (several)."""
+    err, kernel = check_problem(Problem(F32, F32, (w_rows, 328), (1, x_rows, 328), (False, True, True), bias=True,
+                                        seed=310 + w_rows % 97, w_std=0.05), gpu)
+    assert kernel == "gemm_umma_tf32x3_F32_F32_" + name, kernel
+    assert err <= 1e-5, (kernel, err)
+
+
 def test_short_prompts_take_the_tensor_core_gemm(gpu):
     """9..15 activation rows (more than the streaming GEMV kernels take, fewer than one MMA column
     block): the tensor-core GEMM with the missing rows zero-filled by the tile loads."""
