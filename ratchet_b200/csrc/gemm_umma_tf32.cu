@@ -48,9 +48,11 @@ constexpr int BK = 32;                 // 32 f32 = one 128-byte swizzle row
 constexpr int UMMA_K = 8;              // TF32: 8 elements = 32 bytes per instruction
 constexpr int P_TILE = BM * BK * 4;    // 16 KB
 constexpr int SPLIT_WARPS = 8;
-constexpr int NUM_THREADS = 64 + SPLIT_WARPS * 32;
-constexpr int ACC_STRIDE = 128;        // tensor-memory columns between the two accumulators
-constexpr int TMEM_COLS = 2 * ACC_STRIDE; // two accumulators: one collects a chunk while the other is drained
+constexpr int ISSUERS = 2;             // MMA-issuing threads (warp 1 and the last warp), each with accumulators of its own
+constexpr int NUM_THREADS = 64 + SPLIT_WARPS * 32 + 32;
+constexpr int ISSUER_B_WARP = 2 + SPLIT_WARPS;
+constexpr int ACC_STRIDE = 128;        // tensor-memory columns between accumulators
+constexpr int TMEM_COLS = 2 * ISSUERS * ACC_STRIDE; // per chunk parity one accumulator per issuer: one pair collects a chunk while the other is drained
 constexpr int CHUNK = 4;               // stages per accumulator: K = 128
 
 // BN: rows of Q per tile (the MMA's N), a multiple of 16 up to 128.  A stage holds P hi, P lo, Q hi, Q lo.
@@ -121,10 +123,10 @@ gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
         for (int s = 0; s < STAGES; s++) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_split + 8 * s, SPLIT_WARPS);
-            mbar_init(bar_empty + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, ISSUERS);
         }
         for (int a = 0; a < 2; a++) {
-            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tfull + 8 * a, ISSUERS);
             mbar_init(bar_tempty + 8 * a, SPLIT_WARPS);
         }
         *abort_flag = 0;
@@ -165,45 +167,51 @@ gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer
+    } else if (warp == 1 || warp == ISSUER_B_WARP) {
+        // ---------------------------------------------------------------- MMA issuers
+        // One thread issues a tcgen05.mma about every 75 cycles here (descriptors included), so the twelve
+        // MMAs of a stage would take longer to issue than to run.  Two threads issue six each, into
+        // accumulators of their own (the first MMA of a chunk overwrites its accumulator, and nothing
+        // orders the MMAs of two threads); the drain adds the two.
         if (lane == 0) {
+            const int who = warp == 1 ? 0 : 1;
             // instruction descriptor: f32 accumulate, TF32 A and B, K-major, N >> 3 at bit 17, M >> 4 at bit 24
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            int stage = 0, chunk = 0; // chunk counts over all tiles: accumulator chunk & 1
+            int stage = 0, chunk = 0; // chunk counts over all tiles: accumulator pair chunk & 1
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 for (int kb = 0; kb < num_k; kb++) {
                     const int buf = chunk & 1;
                     if (kb % CHUNK == 0) {
-                        // the accumulator's previous chunk has been added into registers
+                        // the accumulators' previous chunk has been added into registers
                         if (!mbar_wait(bar_tempty + 8 * buf, ((chunk >> 1) & 1) ^ 1, abort_flag, 5)) { ok = false; break; }
                         tc_fence_after();
                     }
                     if (!mbar_wait(bar_split + 8 * stage, phase, abort_flag, 3)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + buf * ACC_STRIDE;
+                    const uint32_t d_tmem = tmem_base + (buf * ISSUERS + who) * ACC_STRIDE;
                     const uint32_t p_hi = smem_u32(tiles + stage * STAGE_BYTES), p_lo = p_hi + P_TILE;
                     const uint32_t q_hi = p_hi + 2 * P_TILE, q_lo = q_hi + Q_TILE;
+                    // the stage's twelve MMAs in the order lo.hi (k = 0..3), hi.lo (0..3), hi.hi (0..3): small terms
+                    // first; issuer 0 takes the first six, issuer 1 the last six
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++) {
+                    for (int i = 0; i < 6; i++) {
+                        const int j = who * 6 + i, term = j >> 2, k = j & 3;
                         const uint32_t off = k * UMMA_K * 4;
-                        // small terms first, the dominant hi.hi last
-                        umma_tf32(d_tmem, umma_desc_sw128(p_lo + off, 1024), umma_desc_sw128(q_hi + off, 1024), idesc, ((kb % CHUNK) | k) != 0 ? 1u : 0u);
-                        umma_tf32(d_tmem, umma_desc_sw128(p_hi + off, 1024), umma_desc_sw128(q_lo + off, 1024), idesc, 1u);
-                        umma_tf32(d_tmem, umma_desc_sw128(p_hi + off, 1024), umma_desc_sw128(q_hi + off, 1024), idesc, 1u);
+                        const uint32_t pa = (term == 0 ? p_lo : p_hi) + off, qa = (term == 1 ? q_lo : q_hi) + off;
+                        umma_tf32(d_tmem, umma_desc_sw128(pa, 1024), umma_desc_sw128(qa, 1024), idesc, ((kb % CHUNK) | i) != 0 ? 1u : 0u);
                     }
-                    umma_commit(bar_empty + 8 * stage); // stage reusable once these MMAs have read it
+                    umma_commit(bar_empty + 8 * stage); // stage reusable once both issuers' MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     if (kb % CHUNK == CHUNK - 1 || kb == num_k - 1) {
-                        umma_commit(bar_tfull + 8 * buf); // chunk complete
+                        umma_commit(bar_tfull + 8 * buf); // chunk complete (both issuers)
                         chunk++;
                     }
                 }
             }
         }
-    } else {
+    } else if (warp >= 2 && warp < 2 + SPLIT_WARPS) {
         // ---------------------------------------------------------------- split (per stage), epilogue (per tile)
         const int q = warp & 3;             // the tensor-memory lane quarter this warp may read
         const int half = (warp - 2) >> 2;   // which half of the tile's columns it stores
@@ -218,15 +226,18 @@ gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
             const int buf = chunk & 1;
             if (!mbar_wait(bar_tfull + 8 * buf, (chunk >> 1) & 1, abort_flag, 4)) return false;
             tc_fence_after();
-            uint32_t v[HC / 8][8];
 #pragma unroll
-            for (int j = 0; j < HC / 8; j++)
-                tmem_ld8_f32(tmem_base + buf * ACC_STRIDE + half * HC + j * 8 + ((uint32_t)(q * 32) << 16), v[j]);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            for (int who = 0; who < ISSUERS; who++) {
+                uint32_t v[HC / 8][8];
 #pragma unroll
-            for (int j = 0; j < HC / 8; j++)
+                for (int j = 0; j < HC / 8; j++)
+                    tmem_ld8_f32(tmem_base + (buf * ISSUERS + who) * ACC_STRIDE + half * HC + j * 8 + ((uint32_t)(q * 32) << 16), v[j]);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < 8; i++) racc[j * 8 + i] += __uint_as_float(v[j][i]);
+                for (int j = 0; j < HC / 8; j++)
+#pragma unroll
+                    for (int i = 0; i < 8; i++) racc[j * 8 + i] += __uint_as_float(v[j][i]);
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
@@ -389,7 +400,10 @@ int umma_tf32_pick_bn(int R, int S, int stacks, int sm_count) {
 }
 
 // Whether splitting P ahead of the GEMM pays: every tile column repeats P's split otherwise.
-bool umma_tf32_presplit_pays(int S, int bn) { return (S + bn - 1) / bn >= 2; }
+bool umma_tf32_presplit_pays(int S, int bn) {
+    static const int allow = [] { const char *e = std::getenv("RT_TF32_PRESPLIT"); return e ? std::atoi(e) : 1; }();
+    return allow != 0 && (S + bn - 1) / bn >= 2;
+}
 
 // P: [p_stack][R][K] f32, Q: [q_stack][S][K] f32; out [stacks][R][S] f32.  p_split: nullptr, or room for
 // 2 * p_stack * R * K floats, in which P is split into its hi and lo parts by a pass of its own.
