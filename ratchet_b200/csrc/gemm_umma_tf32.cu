@@ -140,6 +140,10 @@ gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // programmatic dependent launch: everything above overlapped the stream predecessor (the split pass or the
+    // previous node); its results are read, and this kernel's output written, only after this wait
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int num_k = (prm.K + BK - 1) / BK;
     const int tiles_per_batch = prm.tiles_r * prm.tiles_s;
@@ -338,6 +342,10 @@ gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
 
 // hi = the value with the 13 low mantissa bits cleared (what a TF32 operand keeps), lo = value - hi
 __global__ void split_tf32_kernel(const float4 *__restrict__ in, float4 *__restrict__ hi, float4 *__restrict__ lo, long long n4) {
+    // programmatic dependent launch: the GEMM behind this pass may set itself up now; this pass reads what its
+    // own stream predecessor wrote (and overwrites the scratch that predecessor's GEMM may still read)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
         const float4 v = in[i];
         float4 h, l;
@@ -374,8 +382,7 @@ cudaError_t launch_t(const CUtensorMap &mp, const CUtensorMap &mplo, const CUten
     prm.tiles_s = (prm.S + BN - 1) / BN;
     const long long total = (long long)prm.tiles_r * prm.tiles_s * prm.stacks;
     const int grid = (int)(total < sm_count ? total : sm_count);
-    kernel<<<grid, NUM_THREADS, TileCfg<BN>::SMEM_BYTES, stream>>>(mp, mplo, mq, prm);
-    return cudaGetLastError();
+    return launch_pdl(kernel, dim3(grid), dim3(NUM_THREADS), TileCfg<BN>::SMEM_BYTES, stream, mp, mplo, mq, prm);
 }
 
 } // namespace
@@ -418,9 +425,8 @@ cudaError_t launch_gemm_umma_tf32x3(const void *P, const void *Q, void *out, int
         float *hi = static_cast<float *>(p_split), *lo = hi + p_elems;
         const long long n4 = p_elems / 4; // K % 4 == 0
         const int blocks = (int)std::min<long long>((n4 + 255) / 256, (long long)sm_count * 8);
-        split_tf32_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float4 *>(P), reinterpret_cast<float4 *>(hi),
-                                                      reinterpret_cast<float4 *>(lo), n4);
-        cudaError_t e = cudaGetLastError();
+        cudaError_t e = launch_pdl(split_tf32_kernel, dim3(blocks), dim3(256), 0, stream, static_cast<const float4 *>(P),
+                                   reinterpret_cast<float4 *>(hi), reinterpret_cast<float4 *>(lo), n4);
         if (e != cudaSuccess) return e;
         p_hi = hi, p_lo = lo;
     }
