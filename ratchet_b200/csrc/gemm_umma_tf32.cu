@@ -13,11 +13,13 @@
 // (K = 128: 48 MMAs), and the chunks are added in registers with ordinary f32 adds.
 //
 //   warp 0      TMA producer: 128-byte-swizzled boxes of 128 x 32 f32 (P) and BN x 32 f32 (Q) per stage
-//   warp 1      MMA issuer: per stage 3 x 4 tcgen05.mma kind::tf32 (128 x BN x 8) into one of two accumulators
+//   warps 1, 10 MMA issuers: per stage 3 x 4 tcgen05.mma kind::tf32 (128 x BN x 8), six per issuer, each issuer
+//               into accumulators of its own (one thread issues an MMA about every 75 cycles, which for twelve
+//               is longer than they run); two accumulator pairs alternate by chunk
 //   warps 2-9   per stage: split the raw tiles in place into hi and write the lo tiles beside them
 //               (element-wise, so the swizzled layout carries over unchanged); per chunk: add the finished
-//               accumulator into BN / 2 registers per thread (one chunk behind the splitting, so the MMAs
-//               never wait for it); per output tile: bias / GELU, store f32 rows
+//               accumulator pair into BN / 2 registers per thread (one chunk behind the splitting, so the
+//               MMAs never wait for it); per output tile: bias / GELU, store f32 rows
 // Two things keep the SMs busy on Linear-shaped problems (few rows of P, many of Q).  The tile width BN
 // (128, 96, 80 or 64 rows of Q) is the one whose tiles take the fewest waves x width: 10240 rows are 80
 // tiles of 128 on 148 SMs, but 128 tiles of 80.  And when P spans more than one tile column its split is
@@ -199,12 +201,24 @@ gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
                     const uint32_t q_hi = p_hi + 2 * P_TILE, q_lo = q_hi + Q_TILE;
                     // the stage's twelve MMAs in the order lo.hi (k = 0..3), hi.lo (0..3), hi.hi (0..3): small terms
                     // first; issuer 0 takes the first six, issuer 1 the last six
-#pragma unroll
-                    for (int i = 0; i < 6; i++) {
-                        const int j = who * 6 + i, term = j >> 2, k = j & 3;
-                        const uint32_t off = k * UMMA_K * 4;
-                        const uint32_t pa = (term == 0 ? p_lo : p_hi) + off, qa = (term == 1 ? q_lo : q_hi) + off;
-                        umma_tf32(d_tmem, umma_desc_sw128(pa, 1024), umma_desc_sw128(qa, 1024), idesc, ((kb % CHUNK) | i) != 0 ? 1u : 0u);
+                    // descriptors of the four tiles at k = 0; a step of 8 elements (32 bytes) adds 2 to the address field
+                    const uint64_t d_phi = umma_desc_sw128(p_hi, 1024), d_plo = umma_desc_sw128(p_lo, 1024);
+                    const uint64_t d_qhi = umma_desc_sw128(q_hi, 1024), d_qlo = umma_desc_sw128(q_lo, 1024);
+                    const uint32_t first = (kb % CHUNK) != 0 ? 1u : 0u;
+                    if (who == 0) {
+                        umma_tf32(d_tmem, d_plo + 0, d_qhi + 0, idesc, first);
+                        umma_tf32(d_tmem, d_plo + 2, d_qhi + 2, idesc, 1u);
+                        umma_tf32(d_tmem, d_plo + 4, d_qhi + 4, idesc, 1u);
+                        umma_tf32(d_tmem, d_plo + 6, d_qhi + 6, idesc, 1u);
+                        umma_tf32(d_tmem, d_phi + 0, d_qlo + 0, idesc, 1u);
+                        umma_tf32(d_tmem, d_phi + 2, d_qlo + 2, idesc, 1u);
+                    } else {
+                        umma_tf32(d_tmem, d_phi + 4, d_qlo + 4, idesc, first);
+                        umma_tf32(d_tmem, d_phi + 6, d_qlo + 6, idesc, 1u);
+                        umma_tf32(d_tmem, d_phi + 0, d_qhi + 0, idesc, 1u);
+                        umma_tf32(d_tmem, d_phi + 2, d_qhi + 2, idesc, 1u);
+                        umma_tf32(d_tmem, d_phi + 4, d_qhi + 4, idesc, 1u);
+                        umma_tf32(d_tmem, d_phi + 6, d_qhi + 6, idesc, 1u);
                     }
                     umma_commit(bar_empty + 8 * stage); // stage reusable once both issuers' MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
