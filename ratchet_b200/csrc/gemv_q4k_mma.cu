@@ -163,8 +163,7 @@ __global__ void __launch_bounds__(WARPS * 32) q4k_gemv_kernel(MatmulParams p, in
     // of 32, so a warp is either wholly inside or wholly outside the range.
     constexpr int XU = 8;
     const int x_items = nv * (kslice / 8);
-    for (int i0 = threadIdx.x; i0 < x_items; i0 += THREADS * XU) {
-        uint4 raw[XU];
+    auto x_load = [&](int i0, uint4 (&raw)[XU]) {
 #pragma unroll
         for (int u = 0; u < XU; u++) {
             const int i = i0 + u * THREADS;
@@ -174,6 +173,8 @@ __global__ void __launch_bounds__(WARPS * 32) q4k_gemv_kernel(MatmulParams p, in
                                                           (long long)sb_begin * 256 + o * 8);
             }
         }
+    };
+    auto x_store = [&](int i0, const uint4 (&raw)[XU]) {
 #pragma unroll
         for (int u = 0; u < XU; u++) {
             const int i = i0 + u * THREADS;
@@ -190,51 +191,73 @@ __global__ void __launch_bounds__(WARPS * 32) q4k_gemv_kernel(MatmulParams p, in
                 if ((o & 3) == 0) xsum[(o >> 2) * COLS + v] = s; // four consecutive 8-element groups = one sub-block
             }
         }
+    };
+
+    bool ok = true;
+    // waits (bounded) for row group `it` and builds its header table: (s1, s3) per (row, sub-block).
+    // One thread per (row, super-block): the 16-byte header in one load, its eight 6-bit (scale, min)
+    // pairs unpacked in registers (the packing of q4k_scale_min, decode.cuh).
+    auto prepare = [&](int it) {
+        const int buf = it % nbuf;
+        const uint32_t bar = bar_addr + 8u * buf;
+        const uint32_t parity = (uint32_t)(it / nbuf) & 1u; // how often this buffer has been filled before
+        const int rows_here = min(ROWS, p.M - (group0 + it) * ROWS);
+        const uint8_t *codes_b = codes_s + buf * ROWS * rstride;
+        if (ok && row_bytes > 0 && !mbar_try_wait(bar, parity)) {
+            const unsigned long long t0 = (unsigned long long)clock64();
+            while (!mbar_try_wait(bar, parity)) {
+                if ((unsigned long long)clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                    ok = false;
+                    atomicCAS(&g_gemv_q4k_error, 0, 1);
+                    break;
+                }
+            }
+        }
+        if (!ok) return;
+        for (int item = t; item < ROWS * nsb; item += TH) {
+            const int r = item / nsb, sb = item - r * nsb;
+            float2 *dst = table + r * tstride + sb * 8;
+            if (r < rows_here) {
+                const uint4 h = *reinterpret_cast<const uint4 *>(codes_b + r * rstride + sb * SB_BYTES);
+                const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xFFFFu)));
+                const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
+                // scale bytes s[0..3] = h.y, s[4..7] = h.z, s[8..11] = h.w
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint32_t a = (h.y >> (8 * j)) & 0xFFu, b = (h.z >> (8 * j)) & 0xFFu, c8 = (h.w >> (8 * j)) & 0xFFu;
+                    const float s_lo = d * (float)(a & 63u);                          // sub-block j
+                    dst[j] = make_float2(s_lo, fmaf(1024.f, s_lo, dmin * (float)(b & 63u)));
+                    const float s_hi = d * (float)((c8 & 0x0Fu) | ((a >> 6) << 4));   // sub-block j + 4
+                    dst[j + 4] = make_float2(s_hi, fmaf(1024.f, s_hi, dmin * (float)((c8 >> 4) | ((b >> 6) << 4))));
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++) dst[j] = make_float2(0.f, 0.f);
+            }
+        }
+    };
+
+    {
+        uint4 raw[XU];
+        x_load(threadIdx.x, raw);
+        // a CTA with one row group builds its table while the first activation loads are in flight
+        if (WARPS == WARPS_ONCE && my_groups > 0) prepare(0);
+        x_store(threadIdx.x, raw);
+        for (int i0 = threadIdx.x + THREADS * XU; i0 < x_items; i0 += THREADS * XU) {
+            x_load(i0, raw);
+            x_store(i0, raw);
+        }
     }
     // vectors past nv (the MMA has 8 or 16 columns) read vector nv-1 and a zero sum is not needed: their outputs are dropped
 
     if (HALVES == 2) __syncthreads(); // the activations are staged by all warps and read by both halves
 
-    bool ok = true;
 #pragma unroll 1
     for (int it = half; it < my_groups; it += HALVES) {
     const int buf = it % nbuf;
-    const uint32_t bar = bar_addr + 8u * buf;
-    const uint32_t parity = (uint32_t)(it / nbuf) & 1u; // how often this buffer has been filled before
     const int row_base = (group0 + it) * ROWS;
-    const int rows_here = min(ROWS, p.M - row_base);
     const uint8_t *codes_b = codes_s + buf * ROWS * rstride;
-
-    // ---- wait for the super-blocks (bounded)
-    if (ok && row_bytes > 0 && !mbar_try_wait(bar, parity)) {
-        const unsigned long long t0 = (unsigned long long)clock64();
-        while (!mbar_try_wait(bar, parity)) {
-            if ((unsigned long long)clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                ok = false;
-                atomicCAS(&g_gemv_q4k_error, 0, 1);
-                break;
-            }
-        }
-    }
-
-    // ---- header table: (s1, s3) per (row, sub-block)
-    if (ok) {
-        const int r = (t >> 4) & 15;
-        for (int i = (t & 15) + 16 * (t >> 8); i < nsb * 8; i += 16 * (TH / 256)) {
-            const int sb = i >> 3, j = i & 7;
-            float2 e = make_float2(0.f, 0.f);
-            if (r < rows_here) {
-                const uint8_t *blk = codes_b + r * rstride + sb * SB_BYTES;
-                const float d = __half2float(*reinterpret_cast<const __half *>(blk));
-                const float dmin = __half2float(*reinterpret_cast<const __half *>(blk + 2));
-                int sc, m;
-                q4k_scale_min(j, blk + 4, sc, m);
-                const float s1 = d * (float)sc;
-                e = make_float2(s1, fmaf(1024.f, s1, dmin * (float)m));
-            }
-            table[r * tstride + i] = e;
-        }
-    }
+    if (WARPS != WARPS_ONCE) prepare(it);
     half_sync();
 
     float acc[NVG][4];
