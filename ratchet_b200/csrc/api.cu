@@ -75,6 +75,7 @@ struct rt_plan {
     bool lhs_is_q = false; // the lhs is the kernel's Q operand (trans_out), else its P operand
     int R = 0, S = 0, u_stacks = 1, p_stack = 1, q_stack = 1, bn = 128;
     bool tf32x3 = false;   // dense f32 on the tensor cores: three TF32 MMAs per product
+    bool rhs_transpose = false; // rhs is stored [K][N]: transposed into act_scratch ahead of the GEMM
     void *scratch = nullptr;     // dequantised weights (f16)
     uint64_t scratch_bytes = 0;
     void *act_scratch = nullptr; // bf16 activations cast to f16 (quantised weights only)
@@ -394,9 +395,19 @@ static bool force_simt() {
 }
 
 // The tensor-core GEMM takes nn::Linear-shaped nodes: both operands K-major, 16-bit activations.
+// The tensor-core GEMMs take both operands K-major: op(lhs) [M][K] as stored, and op(rhs) as [N][K], which
+// is how trans_rhs stores it (the Linear form).  A dense rhs stored [K][N] (the attention products
+// q.kT and softmax.v of the models, rank 4, no transposes) is made K-major by a transposing pass first.
 static bool umma_eligible(const rt_matmul_desc &d, const Spec &s) {
     if (force_simt()) return false;
-    if (s.trans_lhs || !s.trans_rhs) return false;
+    if (s.trans_lhs) return false;
+    if (!s.trans_rhs) {
+        if (d.lhs_dt != d.rhs_dt || s.trans_out) return false;
+        // only where the GEMM's vector stores apply (output rows of whole 16-byte groups), and for f32
+        // not below 16 rows, where three launches cost more than the CUDA-core kernel
+        if (s.N % (d.rhs_dt == RT_F32 ? 4 : 8) != 0) return false;
+        if (d.rhs_dt == RT_F32 && s.M < 16) return false;
+    }
     if (d.rhs_dt == RT_F32) {
         if (d.lhs_dt != RT_F32 || !umma_tf32_supported(s.K)) return false;
     } else {
@@ -492,6 +503,19 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
         pl->bn = pl->tf32x3 ? umma_tf32_pick_bn(pl->R, pl->S, pl->u_stacks, dev->sm_count)
                             : umma_pick_bn(pl->R, pl->S, pl->u_stacks, dev->sm_count);
         pl->launches = 1;
+        if (!s.trans_rhs) {
+            pl->rhs_transpose = true;
+            pl->act_scratch_bytes = (uint64_t)(s.rhs_stack * s.N * s.K) * dtype_size(desc->rhs_dt);
+            cudaError_t e = cudaSetDevice(dev->ordinal);
+            if (e == cudaSuccess) e = cudaMalloc(&pl->act_scratch, pl->act_scratch_bytes);
+            if (e != cudaSuccess) {
+                pl->act_scratch = nullptr;
+                delete pl;
+                return fail(e == cudaErrorMemoryAllocation ? RT_ERR_NOMEM : RT_ERR_CUDA,
+                            std::string("plan scratch: ") + cudaGetErrorString(e));
+            }
+            pl->launches++;
+        }
         if (pl->tf32x3 && umma_tf32_presplit_pays(pl->S, pl->bn)) {
             // P (the operand whose 128-row tiles every tile column reads) is split into hi and lo once
             // per launch, into this scratch, rather than by every CTA of its tile row.  A problem whose
@@ -507,7 +531,7 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
                                 std::string("plan scratch: ") + cudaGetErrorString(e));
                 }
                 pl->scratch_bytes = bytes;
-                pl->launches = 2;
+                pl->launches++;
             }
         }
         if (is_quantized(desc->lhs_dt)) {
@@ -536,7 +560,8 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
             }
         }
         pl->name = std::string(pl->tf32x3 ? "gemm_umma_tf32x3_" : "gemm_umma_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt) + "_bn" +
-                   std::to_string(pl->bn) + (pl->scratch ? (pl->tf32x3 ? "_presplit" : "_dequant_prepass") : "");
+                   std::to_string(pl->bn) + (pl->scratch ? (pl->tf32x3 ? "_presplit" : "_dequant_prepass") : "") +
+                   (pl->rhs_transpose ? "_rhs_transposed" : "");
     } else if (s.N == 1 && !s.trans_lhs) {
         pl->kernel = PK_GEMV_SIMT;
         pl->name = std::string("gemv_simt_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt);
@@ -622,7 +647,13 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
     case PK_GEMM_UMMA: {
         if (plan->tf32x3) {
             if (scatter) return fail(RT_ERR_UNSUPPORTED, "scattered outputs are not taken by the f32 GEMM");
-            const void *P = plan->lhs_is_q ? rhs : lhs, *Q = plan->lhs_is_q ? lhs : rhs;
+            const void *r32 = rhs;
+            if (plan->rhs_transpose) {
+                e = launch_transpose(rhs, plan->act_scratch, (int)s.rhs_stack, (int)s.K, (int)s.N, 4, st);
+                if (e != cudaSuccess) break;
+                r32 = plan->act_scratch;
+            }
+            const void *P = plan->lhs_is_q ? r32 : lhs, *Q = plan->lhs_is_q ? lhs : r32;
             e = launch_gemm_umma_tf32x3(P, Q, out, plan->R, plan->S, (int)s.K, plan->u_stacks, plan->p_stack, plan->q_stack, p.bias,
                                         p.bias_dt, s.has_bias ? BIAS_PER_N : BIAS_NONE, p.epilogue, plan->bn, plan->scratch,
                                         plan->dev->sm_count, st);
@@ -639,7 +670,11 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
         }
         const void *x = rhs;
         rt_dtype x_dt = s.desc.rhs_dt;
-        if (plan->act_scratch) {
+        if (plan->rhs_transpose) {
+            e = launch_transpose(rhs, plan->act_scratch, (int)s.rhs_stack, (int)s.K, (int)s.N, 2, st);
+            if (e != cudaSuccess) break;
+            x = plan->act_scratch;
+        } else if (plan->act_scratch) {
             e = launch_cast_bf16_f16(rhs, plan->act_scratch, (long long)(s.rhs_stack * s.N * s.K), plan->dev->sm_count, st);
             if (e != cudaSuccess) break;
             x = plan->act_scratch;

@@ -111,7 +111,42 @@ __global__ void __launch_bounds__(256) cast_bf16_f16_tail_kernel(const __nv_bflo
     if (i < n) dst[i] = __float2half_rn(fminf(fmaxf(__bfloat162float(src[i]), -65504.f), 65504.f));
 }
 
+// [stack][rows][cols] -> [stack][cols][rows], 32 x 32 tiles through padded shared memory so that both
+// the reads and the writes run along the contiguous dimension.  T: a 2- or 4-byte element.
+template <typename T>
+__global__ void __launch_bounds__(256) transpose_kernel(const T *__restrict__ src, T *__restrict__ dst, int rows, int cols) {
+    __shared__ T tile[32][33];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const long long base = (long long)blockIdx.z * rows * cols;
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+        const int r = r0 + ty + j, c = c0 + tx;
+        if (r < rows && c < cols) tile[ty + j][tx] = src[base + (long long)r * cols + c];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+        const int c = c0 + ty + j, r = r0 + tx;
+        if (c < cols && r < rows) dst[base + (long long)c * rows + r] = tile[tx][ty + j];
+    }
+}
+
 } // namespace
+
+// src [stacks][rows][cols] -> dst [stacks][cols][rows]; elem_size 2 or 4.
+cudaError_t launch_transpose(const void *src, void *dst, int stacks, int rows, int cols, int elem_size, cudaStream_t stream) {
+    if (stacks <= 0 || rows <= 0 || cols <= 0) return cudaSuccess;
+    if (stacks > 65535 || (rows + 31) / 32 > 65535) return cudaErrorInvalidValue;
+    const dim3 grid((cols + 31) / 32, (rows + 31) / 32, stacks);
+    if (elem_size == 2)
+        return launch_pdl(transpose_kernel<uint16_t>, grid, dim3(256), 0, stream, (const uint16_t *)src, (uint16_t *)dst, rows, cols);
+    if (elem_size == 4)
+        return launch_pdl(transpose_kernel<uint32_t>, grid, dim3(256), 0, stream, (const uint32_t *)src, (uint32_t *)dst, rows, cols);
+    return cudaErrorInvalidValue;
+}
 
 cudaError_t launch_cast_bf16_f16(const void *src, void *dst, long long numel, int sm_count, cudaStream_t stream) {
     if (numel == 0) return cudaSuccess;

@@ -91,5 +91,7 @@ cudaError_t launch_dequant(rt_dtype dt, long long numel, const void *src, const 
 
 // bf16 -> f16 (saturating) for the activations of a quantised-weight tensor-core GEMM.
 cudaError_t launch_cast_bf16_f16(const void *src, void *dst, long long numel, int sm_count, cudaStream_t stream);
+// [stacks][rows][cols] -> [stacks][cols][rows], elements of 2 or 4 bytes (the pass that makes an operand K-major)
+cudaError_t launch_transpose(const void *src, void *dst, int stacks, int rows, int cols, int elem_size, cudaStream_t stream);
 
 } // namespace rt
