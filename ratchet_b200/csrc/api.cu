@@ -69,6 +69,7 @@ struct rt_plan {
     int split = 1;
     int nv = 1;
     GemvUmmaConfig gemv_umma{};
+    bool chain_ok = false; // a Q8_0H x f16 GEMV the persistent chain kernel can take as a node
     MatmulParams params{}; // everything but the pointers
     uint64_t lhs_scale_offset = 0;
     // tensor-core GEMM: operand roles, tile width, and the scratch that holds dequantised weights
@@ -470,9 +471,14 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
         pl->split = gemv_split;
         // one vector against f16-scaled Q8_0 at a size that fills the machine: the tensor-memory GEMV
         const char *env_gu = getenv("RT_GEMV_UMMA");
-        const bool umma_ok = !(env_gu && env_gu[0] == '0') && desc->lhs_dt == RT_Q8_0H && s.N == 1 && s.stacks == 1 &&
-                             s.lhs_stack == 1 && s.rhs_stack == 1 &&
-                             q8_gemv_umma_config(p.M, p.K, dev->sm_count, &pl->gemv_umma) && pl->gemv_umma.rb >= 8;
+        pl->chain_ok = !(env_gu && env_gu[0] == '0') && desc->lhs_dt == RT_Q8_0H && s.N == 1 && s.stacks == 1 &&
+                       s.lhs_stack == 1 && s.rhs_stack == 1 &&
+                       q8_gemv_umma_config(p.M, p.K, dev->sm_count, &pl->gemv_umma) && pl->gemv_umma.rb >= 8;
+        // launched on its own, the tensor-memory kernel only pays from about 22 rows per CTA: below that its
+        // fixed cost (tensor-memory allocation, digits of x, the MMA pipeline's depth) outweighs the streaming
+        // kernel's (measured on [2560,2560]: 13.2 us against 5.2 us; equal at [3072,3072]; 7.1 against 10.4 us
+        // at [4096,4096])
+        const bool umma_ok = pl->chain_ok && pl->gemv_umma.rb >= 22;
         pl->kernel = umma_ok ? PK_Q8_GEMV_UMMA : PK_Q8_GEMV_MMA;
         if (umma_ok)
             pl->name = std::string("q8_gemv_umma_h_rb") + std::to_string(pl->gemv_umma.rb) + "_split" +
@@ -732,7 +738,7 @@ rt_status rt_executable_create(rt_device *dev, const rt_dispatch *nodes, int32_t
         bool all = true;
         std::vector<MatmulParams> ps;
         for (const rt_dispatch &n : x->nodes) {
-            if (n.plan->kernel != PK_Q8_GEMV_UMMA || !(n.opts.flags & RT_LAUNCH_LHS_CONSTANT) || n.opts.n_out > 0 || !n.lhs || !n.rhs ||
+            if (!n.plan->chain_ok || !(n.opts.flags & RT_LAUNCH_LHS_CONSTANT) || n.opts.n_out > 0 || !n.lhs || !n.rhs ||
                 !n.out || (n.plan->spec.has_bias && !n.bias)) {
                 all = false;
                 break;
