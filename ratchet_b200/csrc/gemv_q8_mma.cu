@@ -295,7 +295,9 @@ int q8_gemv_mma_pick_split(int M, int K, int sm_count, int scale_size) {
     const size_t per_cta_target = 44 * 1024, per_cta_max = 200 * 1024;
     int split = 1;
     while (split < 8 && smem_bytes((nblk + split - 1) / split, scale_size) > per_cta_target) split *= 2;
-    while (split < 8 && groups * split < 4 * sm_count && nblk / (split * 2) >= 2 * WARPS) split *= 2;
+    // more K slices while the machine is not full, but never past the CTAs that are resident at once (five
+    // per SM): a second wave costs more than the finer split gains ([3072,3072]: 768 CTAs on 740 slots)
+    while (split < 8 && groups * split < 4 * sm_count && groups * split * 2 <= 5 * sm_count && nblk / (split * 2) >= 2 * WARPS) split *= 2;
     if (smem_bytes((nblk + split - 1) / split, scale_size) > per_cta_max) return 0;
     return split;
 }
