@@ -404,9 +404,9 @@ static bool umma_eligible(const rt_matmul_desc &d, const Spec &s) {
     if (s.trans_lhs) return false;
     if (!s.trans_rhs) {
         if (d.lhs_dt != d.rhs_dt || s.trans_out) return false;
-        // only where the GEMM's vector stores apply (output rows of whole 16-byte groups), and for f32
-        // not below 16 rows, where three launches cost more than the CUDA-core kernel
-        if (s.N % (d.rhs_dt == RT_F32 ? 4 : 8) != 0) return false;
+        // f32: only where the GEMM's vector stores apply (output rows of whole 16-byte groups) and not
+        // below 16 rows, where three launches cost more than the CUDA-core kernel
+        if (d.rhs_dt == RT_F32 && s.N % 4 != 0) return false;
         if (d.rhs_dt == RT_F32 && s.M < 16) return false;
     }
     if (d.rhs_dt == RT_F32) {

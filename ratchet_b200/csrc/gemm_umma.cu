@@ -265,7 +265,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
         int acc = 0;
         uint32_t acc_phase = 0;
         bool vec_ok = (prm.S % 8 == 0) && (prm.out_ld % 8 == 0) && (prm.out_col % 8 == 0) && (prm.out_batch_stride % 8 == 0);
-        for (int d = 0; d < prm.n_out; d++) vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(prm.outs[d]) % 16 == 0);
+        bool pair_ok = (prm.S % 2 == 0) && (prm.out_ld % 2 == 0) && (prm.out_col % 2 == 0) && (prm.out_batch_stride % 2 == 0);
+        for (int d = 0; d < prm.n_out; d++) {
+            vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(prm.outs[d]) % 16 == 0);
+            pair_ok = pair_ok && (reinterpret_cast<uintptr_t>(prm.outs[d]) % 4 == 0);
+        }
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
             const int r0 = (rem % prm.tiles_r) * BM, s0 = (rem / prm.tiles_r) * BN;
@@ -283,7 +287,6 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             const bool has_bias = prm.bias_mode != BIAS_NONE;
             float row_bias = 0.f;
             if (prm.bias_mode == BIAS_PER_M && row < prm.R) row_bias = load_bias(prm.bias, prm.bias_dt, row);
-            const long long row_off = (long long)b * prm.out_batch_stride + (long long)row * prm.out_ld + prm.out_col;
             // 64 columns per round: two tensor-memory loads, the epilogue arithmetic, then through a
             // per-warp staging buffer so that global stores run along rows: 8 lanes x 16 B = one full
             // 128-byte line per row (this matters most when the destination is a peer GPU over NVLink)
@@ -302,8 +305,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                         __syncwarp();
                         if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
                     }
-                    const int col0 = s0 + c * 32;
-                    if (vec_ok) {
+                    {
 #pragma unroll
                         for (int g = 0; g < 4; g++) {
                             uint32_t w[4];
@@ -318,19 +320,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                             }
                             *reinterpret_cast<uint4 *>(stg + lane * STG_ROW_BYTES + (((h * 4 + g) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
-                    } else if (row < prm.R && col0 < prm.S) {
-#pragma unroll
-                        for (int i = 0; i < 32; i++) {
-                            if (col0 + i < prm.S) {
-                                const float bv = prm.bias_mode == BIAS_PER_N ? bias_s[c * 32 + i] : row_bias;
-                                const OutT o = epilogue_value<OutT>(__uint_as_float(v[i]), has_bias, bv, prm.epilogue);
-                                for (int d = 0; d < prm.n_out; d++) reinterpret_cast<OutT *>(prm.outs[d])[row_off + col0 + i] = o;
-                            }
-                        }
                     }
                 }
+                __syncwarp();
                 if (vec_ok) {
-                    __syncwarp();
                     const int colv = colbase + (lane & 7) * 8;
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
@@ -342,8 +335,38 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                             for (int d = 0; d < prm.n_out; d++) *reinterpret_cast<uint4 *>(reinterpret_cast<OutT *>(prm.outs[d]) + off) = pk;
                         }
                     }
-                    __syncwarp();
+                } else if (pair_ok) {
+                    // rows that start on 4-byte but not on 16-byte boundaries: a warp writes the round's 64
+                    // columns of one row as 32 element pairs per instruction
+#pragma unroll 4
+                    for (int rl = 0; rl < 32; rl++) {
+                        const int rg = r0 + q * 32 + rl;
+                        if (rg >= prm.R) break;
+                        const int col = 2 * lane;
+                        if (colbase + col < prm.S) {
+                            const uint32_t o2 = *reinterpret_cast<const uint32_t *>(stg + rl * STG_ROW_BYTES + (((col >> 3) ^ (rl & 7)) << 4) + (col & 7) * 2);
+                            const long long off = (long long)b * prm.out_batch_stride + (long long)rg * prm.out_ld + prm.out_col + colbase + col;
+                            for (int d = 0; d < prm.n_out; d++) *reinterpret_cast<uint32_t *>(reinterpret_cast<OutT *>(prm.outs[d]) + off) = o2;
+                        }
+                    }
+                } else {
+                    // any other row alignment: element stores, still along the rows
+#pragma unroll 4
+                    for (int rl = 0; rl < 32; rl++) {
+                        const int rg = r0 + q * 32 + rl;
+                        if (rg >= prm.R) break;
+                        const long long off = (long long)b * prm.out_batch_stride + (long long)rg * prm.out_ld + prm.out_col + colbase;
+#pragma unroll
+                        for (int k = 0; k < 2; k++) {
+                            const int col = lane + 32 * k;
+                            if (colbase + col < prm.S) {
+                                const OutT o = *reinterpret_cast<const OutT *>(stg + rl * STG_ROW_BYTES + (((col >> 3) ^ (rl & 7)) << 4) + (col & 7) * 2);
+                                for (int d = 0; d < prm.n_out; d++) reinterpret_cast<OutT *>(prm.outs[d])[off + col] = o;
+                            }
+                        }
+                    }
                 }
+                __syncwarp();
             }
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }

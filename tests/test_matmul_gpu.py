@@ -451,8 +451,7 @@ def test_umma_tf32x3_tile_widths(gpu, w_rows, x_rows, name):
 
 def test_attention_products_take_the_tensor_core_gemm(gpu):
     """q.kT and softmax.v of the models: rank 4, no transposes, rhs stored [K][N].  A transposing pass makes
-    the rhs K-major for the tensor-core GEMMs; shapes whose output rows are not whole 16-byte groups, or whose
-    K the tile loads cannot take, stay on the CUDA cores."""
+    the rhs K-major for the tensor-core GEMMs; shapes whose K the tile loads cannot take stay on the CUDA cores."""
     nn = (False, False, False)
     cases = [
         (Problem(F16, F16, (1, 32, 1, 1024), (1, 32, 1024, 80), nn, seed=401), "gemm_umma_F16_F16", "_rhs_transposed"),      # decode, values
@@ -461,7 +460,8 @@ def test_attention_products_take_the_tensor_core_gemm(gpu):
         (Problem(F32, F32, (1, 32, 512, 80), (1, 32, 80, 512), nn, seed=404), "gemm_umma_tf32x3", "_rhs_transposed"),        # prefill, scores
         (Problem(F16, F16, (3, 300, 96), (1, 96, 200), nn, bias=True, seed=405), "gemm_umma_F16_F16", "_rhs_transposed"),      # broadcast rhs, bias
         (Problem(F32, F32, (1, 32, 1, 80), (1, 32, 80, 1024), nn, seed=406), "gemm_simt", ""),                               # decode scores in f32
-        (Problem(F16, F16, (1, 6, 300, 64), (1, 6, 64, 300), nn, seed=407), "gemm_simt", ""),                                # 300 % 8 != 0
+        (Problem(F16, F16, (1, 6, 300, 64), (1, 6, 64, 300), nn, seed=407), "gemm_umma_F16_F16", "_rhs_transposed"),         # rows of 300: element stores
+        (Problem(BF16, BF16, (1, 2, 130, 64), (1, 2, 64, 1501), nn, bias=True, seed=409), "gemm_umma_BF16_BF16", "_rhs_transposed"),  # odd row length
         (Problem(F16, F16, (1, 6, 64, 300), (1, 6, 300, 64), nn, seed=408), "gemm_simt", ""),                                # K % 8 != 0
     ]
     for prob, prefix, suffix in cases:
