@@ -69,6 +69,7 @@ struct rt_plan {
     int split = 1;
     int nv = 1;
     GemvUmmaConfig gemv_umma{};
+    int nv2 = 0;           // streaming Q8_0 kernel: vectors beyond the first launch's 8, taken 8 at a time (9..24 in all)
     bool chain_ok = false; // a Q8_0H x f16 GEMV the persistent chain kernel can take as a node
     MatmulParams params{}; // everything but the pointers
     uint64_t lhs_scale_offset = 0;
@@ -486,6 +487,19 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
         else
         pl->name = std::string("q8_gemv_mma_") + (desc->lhs_dt == RT_Q8_0H ? "h" : "f") + "_nv" + std::to_string(pl->nv) +
                    "_split" + std::to_string(pl->split);
+    } else if (gemv_split > 0 && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.trans_rhs && s.trans_out && s.N >= 9 && s.N <= 24 &&
+               s.stacks == 1 && s.K > 0 && !empty) {
+        // 9..24 vectors against Q8_0: two or three passes of the streaming kernel, 8 vectors at a time.  The
+        // weights are read again by each pass (from L2 where they fit), which still is well under the
+        // dequantise + tensor-core GEMM route ([10240,2560] x 12 rows: 37 -> 15.6 us); with trans_out each
+        // vector's outputs are contiguous, so a later pass is the same problem on offset pointers.
+        pl->kernel = PK_Q8_GEMV_MMA;
+        pl->nv = 8;
+        pl->nv2 = (int)s.N - 8;
+        pl->split = gemv_split;
+        pl->launches = 1 + (pl->nv2 + 7) / 8;
+        pl->name = std::string("q8_gemv_mma_") + (desc->lhs_dt == RT_Q8_0H ? "h" : "f") + "_nv8+" + std::to_string(pl->nv2) +
+                   "_split" + std::to_string(pl->split);
     } else if (desc->lhs_dt == RT_Q4_K && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.N >= 1 && s.N <= 16 &&
                (s.N == 1 || s.trans_rhs) && !empty && !force_simt() &&
                q4k_gemv_pick_split(p.M, p.K, (int)s.N, (int)s.stacks, dev->sm_count) > 0) {
@@ -633,6 +647,13 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
     switch (plan->kernel) {
     case PK_Q8_GEMV_MMA:
         e = launch_q8_gemv_mma(p, s.desc.lhs_dt == RT_Q8_0F, plan->nv, plan->split, (flags & RT_LAUNCH_LHS_CONSTANT) != 0, st);
+        for (int done = plan->nv; e == cudaSuccess && done < plan->nv + plan->nv2; done += 8) {
+            MatmulParams p2 = p; // vectors done.. : rhs rows and (trans_out) output rows of the same problem
+            p2.rhs = (const char *)rhs + (size_t)done * (size_t)s.K * 2;
+            p2.out = (char *)out + (size_t)done * (size_t)s.M * 2;
+            const int nv = std::min(8, plan->nv + plan->nv2 - done);
+            e = launch_q8_gemv_mma(p2, s.desc.lhs_dt == RT_Q8_0F, nv, plan->split, (flags & RT_LAUNCH_LHS_CONSTANT) != 0, st);
+        }
         break;
     case PK_Q4K_GEMV:
         if ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) % 16 != 0)

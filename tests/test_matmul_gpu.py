@@ -477,7 +477,16 @@ def test_short_prompts_take_the_tensor_core_gemm(gpu):
             for to in (True, False):
                 _, kernel = check_problem(Problem(lhs, dt, (1000, 512), (1, nv, 512), (False, True, to), bias=True,
                                                   epilogue=0 if dt == F32 else 1, seed=200 + nv, w_std=0.02), gpu)
-                assert kernel.startswith("gemm_umma"), kernel
+                if lhs == Q8H and to:  # the Linear form: two passes of the streaming kernel, 8 vectors then the rest
+                    assert kernel.startswith(f"q8_gemv_mma_h_nv8+{nv - 8}"), kernel
+                else:
+                    assert kernel.startswith("gemm_umma"), kernel
+    # the same at a decode shape, with bias and GELU, f32 scales too
+    for lhs in (Q8H, Q8F):
+        for nv in (9, 12, 16, 17, 24):
+            _, kernel = check_problem(Problem(lhs, F16, (10240, 2560), (1, nv, 2560), (False, True, True), bias=True, epilogue=1,
+                                              seed=230 + nv, w_std=0.02), gpu)
+            assert "_nv8+" in kernel, kernel
 
 
 def test_umma_takes_the_prefill_configs(gpu):
