@@ -152,30 +152,36 @@ def tensor_peaks():
     return 1590.0, 1400.0, "fallback"
 
 
-def time_node(gpu, stream, make_node, copies: int, iters: int, warmup: int = 3):
-    """Times one Matmul node: `copies` independent operand sets are rotated so that a memory-bound
-    node never finds its weights in L2.  Returns microseconds per launch."""
+def time_nodes(gpu, stream, nodes, reps: int, warmup: int = 3):
+    """Times a list of resolved Matmul nodes dispatched as one executable (the way a step runs: one CUDA
+    graph, weights flagged constant), `reps` dispatches between two events.  Returns microseconds per
+    dispatch, the kernels' names and the launches per dispatch."""
     import torch
     import ratchet_b200 as rb
     lib = rb._lib.load()
-    nodes = [make_node(i) for i in range(copies)]
     for n in nodes:
         n.resolve()
-    args = [(gpu.plan_for(n.op.desc), n.op.lhs.ptr, n.op.rhs.ptr, n.op.bias.ptr if n.op.bias is not None else None, n.ptr)
-            for n in nodes]
-    for i in range(warmup * copies):
-        rb._lib.check(lib.rt_matmul_launch(*args[i % copies], None))
+    exe = rb.Executable(gpu, nodes)
+    for _ in range(warmup):
+        exe.dispatch()
     gpu.sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
-    for i in range(iters):
-        rb._lib.check(lib.rt_matmul_launch(*args[i % copies], None))
+    for _ in range(reps):
+        exe.dispatch()
     e1.record(stream)
     gpu.sync()
     torch.cuda.synchronize()
-    kernel = lib.rt_plan_kernel(args[0][0]).decode()
-    launches = int(lib.rt_plan_launches(args[0][0]))
-    return e0.elapsed_time(e1) * 1e3 / iters, kernel, launches
+    kernels = [lib.rt_plan_kernel(gpu.plan_for(n.op.desc)).decode() for n in nodes]
+    return e0.elapsed_time(e1) * 1e3 / reps, kernels, exe.launches
+
+
+def time_node(gpu, stream, make_node, copies: int, iters: int, warmup: int = 3):
+    """Times one Matmul node: `copies` independent operand sets are rotated inside one executable so
+    that a memory-bound node never finds its weights in L2.  Returns microseconds per node."""
+    nodes = [make_node(i) for i in range(copies)]
+    us, kernels, launches = time_nodes(gpu, stream, nodes, max(1, iters // copies), warmup)
+    return us / copies, kernels[0], launches // copies
 
 
 def run_extras(which, gpu, stream):
@@ -222,11 +228,10 @@ def run_extras(which, gpu, stream):
         b1, b2 = weight((1536,), DType.F16, 2103).to(gpu), weight((384,), DType.F16, 2104).to(gpu)
         x = act((1, 1500, 384), DType.F16, 103).to(gpu)
         h = linear_node(w1, x, b1, rb.EPILOGUE_GELU_TANH)
-        us1, k1, l1 = time_node(gpu, stream, lambda i: linear_node(w1, x, b1, rb.EPILOGUE_GELU_TANH), 1, 200)
-        h.resolve()
-        us2, k2, l2 = time_node(gpu, stream, lambda i: linear_node(w2, h, b2), 1, 200)
-        record("c3_whisper_tiny_mlp_q8_0_m1500", us1 + us2, k1 + " + " + k2, l1 + l2, 2 * 1500 * 384 * 1536 * 2, 12777216,
-               "tensor", "fc1+GELU then fc2, back-to-back launches; latency-bound (one wave)")
+        y = linear_node(w2, h, b2)
+        us, ks, l = time_nodes(gpu, stream, [h, y], 200)
+        record("c3_whisper_tiny_mlp_q8_0_m1500", us, " + ".join(ks), l, 2 * 1500 * 384 * 1536 * 2, 12777216,
+               "tensor", "fc1+GELU then fc2 as one executable; latency-bound (one wave)")
     if "c4" in which:
         hw = weight((8192, 3072), DType.Q4_K, 1104)
         copies = 20  # 20 x 14.2 MB of weights: larger than L2
