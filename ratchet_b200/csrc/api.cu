@@ -78,6 +78,8 @@ struct rt_plan {
     int R = 0, S = 0, u_stacks = 1, p_stack = 1, q_stack = 1, bn = 128;
     bool tf32x3 = false;   // dense f32 on the tensor cores: three TF32 MMAs per product
     bool rhs_transpose = false; // rhs is stored [K][N]: transposed into act_scratch ahead of the GEMM
+    int k_pad = 0;              // with rhs_transpose, 16-bit: K rounded up to a multiple of 8 when it is not one
+                                // (lhs rows are then copied, zero-padded, into `scratch`); 0 = K as it is
     void *scratch = nullptr;     // dequantised weights (f16)
     uint64_t scratch_bytes = 0;
     void *act_scratch = nullptr; // bf16 activations cast to f16 (quantised weights only)
@@ -416,7 +418,10 @@ static bool umma_eligible(const rt_matmul_desc &d, const Spec &s) {
         if (d.rhs_dt != RT_F16 && d.rhs_dt != RT_BF16) return false;
         const bool dense = d.lhs_dt == d.rhs_dt;
         if (!dense && d.lhs_dt != RT_Q8_0H && d.lhs_dt != RT_Q4_K) return false;
-        if (!umma_gemm_supported(s.K)) return false;
+        // a dense 16-bit product with rhs [K][N] whose K is not a multiple of 8 (Whisper's softmax.v, K = 1500):
+        // both operands are repacked anyway or cheaply, with K zero-padded to the next multiple of 8
+        const long long k_eff = (!s.trans_rhs && dense) ? (s.K + 7) / 8 * 8 : s.K;
+        if (!umma_gemm_supported(k_eff)) return false;
     }
     if (s.M < 1 || s.N < 9 || s.stacks < 1) return false; // up to 8 columns: the streaming GEMV kernels
     if ((double)s.M * (double)s.N * (double)s.K * (double)s.stacks < (double)(1 << 21)) return false;
@@ -525,16 +530,24 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
         pl->launches = 1;
         if (!s.trans_rhs) {
             pl->rhs_transpose = true;
-            pl->act_scratch_bytes = (uint64_t)(s.rhs_stack * s.N * s.K) * dtype_size(desc->rhs_dt);
+            const uint64_t k_eff = pl->tf32x3 ? (uint64_t)s.K : (uint64_t)(s.K + 7) / 8 * 8;
+            if (k_eff != (uint64_t)s.K) pl->k_pad = (int)k_eff;
+            pl->act_scratch_bytes = (uint64_t)(s.rhs_stack * s.N) * k_eff * dtype_size(desc->rhs_dt);
             cudaError_t e = cudaSetDevice(dev->ordinal);
             if (e == cudaSuccess) e = cudaMalloc(&pl->act_scratch, pl->act_scratch_bytes);
+            if (e == cudaSuccess && pl->k_pad) {
+                pl->scratch_bytes = (uint64_t)(s.lhs_stack * s.M) * k_eff * 2;
+                e = cudaMalloc(&pl->scratch, pl->scratch_bytes);
+            }
             if (e != cudaSuccess) {
+                if (pl->act_scratch) cudaFree(pl->act_scratch);
                 pl->act_scratch = nullptr;
+                pl->scratch = nullptr;
                 delete pl;
                 return fail(e == cudaErrorMemoryAllocation ? RT_ERR_NOMEM : RT_ERR_CUDA,
                             std::string("plan scratch: ") + cudaGetErrorString(e));
             }
-            pl->launches++;
+            pl->launches += pl->k_pad ? 2 : 1;
         }
         if (pl->tf32x3 && umma_tf32_presplit_pays(pl->S, pl->bn)) {
             // P (the operand whose 128-row tiles every tile column reads) is split into hi and lo once
@@ -580,8 +593,8 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
             }
         }
         pl->name = std::string(pl->tf32x3 ? "gemm_umma_tf32x3_" : "gemm_umma_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt) + "_bn" +
-                   std::to_string(pl->bn) + (pl->scratch ? (pl->tf32x3 ? "_presplit" : "_dequant_prepass") : "") +
-                   (pl->rhs_transpose ? "_rhs_transposed" : "");
+                   std::to_string(pl->bn) + (pl->scratch && !pl->k_pad ? (pl->tf32x3 ? "_presplit" : "_dequant_prepass") : "") +
+                   (pl->rhs_transpose ? "_rhs_transposed" : "") + (pl->k_pad ? "_kpad" + std::to_string(pl->k_pad) : "");
     } else if (s.N == 1 && !s.trans_lhs) {
         pl->kernel = PK_GEMV_SIMT;
         pl->name = std::string("gemv_simt_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt);
@@ -676,7 +689,7 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
             if (scatter) return fail(RT_ERR_UNSUPPORTED, "scattered outputs are not taken by the f32 GEMM");
             const void *r32 = rhs;
             if (plan->rhs_transpose) {
-                e = launch_transpose(rhs, plan->act_scratch, (int)s.rhs_stack, (int)s.K, (int)s.N, 4, st);
+                e = launch_transpose(rhs, plan->act_scratch, (int)s.rhs_stack, (int)s.K, (int)s.N, (int)s.K, 4, st);
                 if (e != cudaSuccess) break;
                 r32 = plan->act_scratch;
             }
@@ -688,7 +701,12 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
         }
         const void *w = lhs;
         rt_dtype w_dt = s.desc.lhs_dt;
-        if (plan->scratch) {
+        const int k_eff = plan->k_pad ? plan->k_pad : (int)s.K;
+        if (plan->k_pad) {
+            e = launch_pad_rows16(lhs, plan->scratch, (long long)(s.lhs_stack * s.M), (int)s.K, plan->k_pad, plan->dev->sm_count, st);
+            if (e != cudaSuccess) break;
+            w = plan->scratch;
+        } else if (plan->scratch) {
             e = launch_dequant(s.desc.lhs_dt, (long long)(s.lhs_stack * s.M * s.K), lhs, p.lhs_scales, plan->scratch, RT_F16,
                                plan->dev->sm_count, st);
             if (e != cudaSuccess) break;
@@ -698,7 +716,7 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
         const void *x = rhs;
         rt_dtype x_dt = s.desc.rhs_dt;
         if (plan->rhs_transpose) {
-            e = launch_transpose(rhs, plan->act_scratch, (int)s.rhs_stack, (int)s.K, (int)s.N, 2, st);
+            e = launch_transpose(rhs, plan->act_scratch, (int)s.rhs_stack, (int)s.K, (int)s.N, k_eff, 2, st);
             if (e != cudaSuccess) break;
             x = plan->act_scratch;
         } else if (plan->act_scratch) {
@@ -718,7 +736,7 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
             sc.out_ld = opts->out_ld;
             sc.out_col = opts->out_col;
         }
-        e = launch_gemm_umma(P, p_dt, Q, q_dt, out, s.out_dt, plan->R, plan->S, (int)s.K, plan->u_stacks, plan->p_stack,
+        e = launch_gemm_umma(P, p_dt, Q, q_dt, out, s.out_dt, plan->R, plan->S, k_eff, plan->u_stacks, plan->p_stack,
                              plan->q_stack, p.bias, p.bias_dt, s.has_bias ? BIAS_PER_N : BIAS_NONE, p.epilogue, plan->bn,
                              plan->dev->sm_count, st, scatter ? &sc : nullptr);
         break;

@@ -1,6 +1,8 @@
 // Dequantise a block-format tensor on the device: the parity hook for "bit-exact dequantised
 // weights" and the weight pre-pass of the large-M tensor-core GEMM.
 // Arithmetic per element: see decode.cuh (quant.rs:114-120, gemm.rs:400-406 of the reference).
+#include <algorithm>
+
 #include "decode.cuh"
 #include "kernels.hpp"
 
@@ -111,41 +113,69 @@ __global__ void __launch_bounds__(256) cast_bf16_f16_tail_kernel(const __nv_bflo
     if (i < n) dst[i] = __float2half_rn(fminf(fmaxf(__bfloat162float(src[i]), -65504.f), 65504.f));
 }
 
-// [stack][rows][cols] -> [stack][cols][rows], 32 x 32 tiles through padded shared memory so that both
-// the reads and the writes run along the contiguous dimension.  T: a 2- or 4-byte element.
+// [stack][rows][cols] -> [stack][cols][dst_ld], 32 x 32 tiles through padded shared memory so that both
+// the reads and the writes run along the contiguous dimension; dst_ld >= rows, the columns past `rows`
+// of every output row are zero.  T: a 2- or 4-byte element.
 template <typename T>
-__global__ void __launch_bounds__(256) transpose_kernel(const T *__restrict__ src, T *__restrict__ dst, int rows, int cols) {
+__global__ void __launch_bounds__(256) transpose_kernel(const T *__restrict__ src, T *__restrict__ dst, int rows, int cols, int dst_ld) {
     __shared__ T tile[32][33];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const long long base = (long long)blockIdx.z * rows * cols;
+    const long long base = (long long)blockIdx.z * rows * cols, dbase = (long long)blockIdx.z * cols * dst_ld;
     const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8
 #pragma unroll
     for (int j = 0; j < 32; j += 8) {
         const int r = r0 + ty + j, c = c0 + tx;
-        if (r < rows && c < cols) tile[ty + j][tx] = src[base + (long long)r * cols + c];
+        tile[ty + j][tx] = (r < rows && c < cols) ? src[base + (long long)r * cols + c] : T(0);
     }
     __syncthreads();
 #pragma unroll
     for (int j = 0; j < 32; j += 8) {
         const int c = c0 + ty + j, r = r0 + tx;
-        if (c < cols && r < rows) dst[base + (long long)c * rows + r] = tile[tx][ty + j];
+        if (c < cols && r < dst_ld) dst[dbase + (long long)c * dst_ld + r] = tile[tx][ty + j];
+    }
+}
+
+// rows of `k` 16-bit elements -> rows of `k_pad` (a multiple of 8), zero filled: one 16-byte store per thread
+__global__ void __launch_bounds__(256) pad_rows16_kernel(const uint16_t *__restrict__ src, uint4 *__restrict__ dst, long long rows, int k, int k_pad) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int groups = k_pad / 8;
+    const long long total = rows * groups;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / groups;
+        const int c0 = (int)(i - r * groups) * 8;
+        const uint16_t *s = src + r * k + c0;
+        uint16_t v[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = c0 + j < k ? s[j] : (uint16_t)0;
+        dst[i] = make_uint4(v[0] | ((uint32_t)v[1] << 16), v[2] | ((uint32_t)v[3] << 16), v[4] | ((uint32_t)v[5] << 16),
+                            v[6] | ((uint32_t)v[7] << 16));
     }
 }
 
 } // namespace
 
-// src [stacks][rows][cols] -> dst [stacks][cols][rows]; elem_size 2 or 4.
-cudaError_t launch_transpose(const void *src, void *dst, int stacks, int rows, int cols, int elem_size, cudaStream_t stream) {
+// src [stacks][rows][cols] -> dst [stacks][cols][dst_ld], dst_ld >= rows (zero filled beyond rows); elem_size 2 or 4.
+cudaError_t launch_transpose(const void *src, void *dst, int stacks, int rows, int cols, int dst_ld, int elem_size, cudaStream_t stream) {
     if (stacks <= 0 || rows <= 0 || cols <= 0) return cudaSuccess;
-    if (stacks > 65535 || (rows + 31) / 32 > 65535) return cudaErrorInvalidValue;
-    const dim3 grid((cols + 31) / 32, (rows + 31) / 32, stacks);
+    if (dst_ld < rows || stacks > 65535 || (dst_ld + 31) / 32 > 65535) return cudaErrorInvalidValue;
+    const dim3 grid((cols + 31) / 32, (dst_ld + 31) / 32, stacks);
     if (elem_size == 2)
-        return launch_pdl(transpose_kernel<uint16_t>, grid, dim3(256), 0, stream, (const uint16_t *)src, (uint16_t *)dst, rows, cols);
+        return launch_pdl(transpose_kernel<uint16_t>, grid, dim3(256), 0, stream, (const uint16_t *)src, (uint16_t *)dst, rows, cols, dst_ld);
     if (elem_size == 4)
-        return launch_pdl(transpose_kernel<uint32_t>, grid, dim3(256), 0, stream, (const uint32_t *)src, (uint32_t *)dst, rows, cols);
+        return launch_pdl(transpose_kernel<uint32_t>, grid, dim3(256), 0, stream, (const uint32_t *)src, (uint32_t *)dst, rows, cols, dst_ld);
     return cudaErrorInvalidValue;
+}
+
+// [rows][k] 16-bit -> [rows][k_pad], k_pad a multiple of 8 and >= k, zero filled; dst 16-byte aligned.
+cudaError_t launch_pad_rows16(const void *src, void *dst, long long rows, int k, int k_pad, int sm_count, cudaStream_t stream) {
+    if (rows <= 0 || k <= 0) return cudaSuccess;
+    if (k_pad < k || k_pad % 8 != 0) return cudaErrorInvalidValue;
+    const long long total = rows * (k_pad / 8);
+    const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count * 16);
+    return launch_pdl(pad_rows16_kernel, dim3(blocks), dim3(256), 0, stream, (const uint16_t *)src, (uint4 *)dst, rows, k, k_pad);
 }
 
 cudaError_t launch_cast_bf16_f16(const void *src, void *dst, long long numel, int sm_count, cudaStream_t stream) {

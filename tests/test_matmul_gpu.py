@@ -451,7 +451,7 @@ def test_umma_tf32x3_tile_widths(gpu, w_rows, x_rows, name):
 
 def test_attention_products_take_the_tensor_core_gemm(gpu):
     """q.kT and softmax.v of the models: rank 4, no transposes, rhs stored [K][N].  A transposing pass makes
-    the rhs K-major for the tensor-core GEMMs; shapes whose K the tile loads cannot take stay on the CUDA cores."""
+    the rhs K-major for the tensor-core GEMMs (16-bit operands whose K is not a multiple of 8 are zero-padded on the way)."""
     nn = (False, False, False)
     cases = [
         (Problem(F16, F16, (1, 32, 1, 1024), (1, 32, 1024, 80), nn, seed=401), "gemm_umma_F16_F16", "_rhs_transposed"),      # decode, values
@@ -462,7 +462,9 @@ def test_attention_products_take_the_tensor_core_gemm(gpu):
         (Problem(F32, F32, (1, 32, 1, 80), (1, 32, 80, 1024), nn, seed=406), "gemm_simt", ""),                               # decode scores in f32
         (Problem(F16, F16, (1, 6, 300, 64), (1, 6, 64, 300), nn, seed=407), "gemm_umma_F16_F16", "_rhs_transposed"),         # rows of 300: element stores
         (Problem(BF16, BF16, (1, 2, 130, 64), (1, 2, 64, 1501), nn, bias=True, seed=409), "gemm_umma_BF16_BF16", "_rhs_transposed"),  # odd row length
-        (Problem(F16, F16, (1, 6, 64, 300), (1, 6, 300, 64), nn, seed=408), "gemm_simt", ""),                                # K % 8 != 0
+        (Problem(F16, F16, (1, 6, 64, 300), (1, 6, 300, 64), nn, seed=408), "gemm_umma_F16_F16", "_rhs_transposed_kpad304"),  # K % 8 != 0: zero-padded
+        (Problem(BF16, BF16, (2, 3, 200, 1501), (2, 3, 1501, 64), nn, bias=True, seed=410), "gemm_umma_BF16_BF16", "_kpad1504"),    # odd K
+        (Problem(F32, F32, (1, 6, 64, 302), (1, 6, 302, 64), nn, seed=411), "gemm_simt", ""),                                # f32: K % 4 != 0
     ]
     for prob, prefix, suffix in cases:
         _, kernel = check_problem(prob, gpu)
