@@ -520,3 +520,29 @@ def test_q8_bf16_prefill_config5_full_size_sampled(gpu):
     assert oracle.rel_l2(got[rows], truth_r) <= 1e-3
     # a checksum over everything else: column sums of the output against the sampled rows' scale
     assert np.all(np.isfinite(got))
+
+
+def test_repeated_dispatch_is_bitwise_stable(gpu):
+    """The kernels with scratch passes, walking CTAs or several issuers give the same bits on every dispatch:
+    their reductions run in a fixed order and their scratch is rewritten each time."""
+    rng = np.random.default_rng(77)
+    cases = [
+        (Q4K, F16, (8192, 3072), (1, 16, 3072), (False, True, True)),      # row-walking Q4_K kernel
+        (Q8H, F16, (10240, 2560), (1, 12, 2560), (False, True, True)),     # two passes of the streaming kernel
+        (F32, F32, (10240, 2560), (1, 128, 2560), (False, True, True)),    # pre-split + two issuers
+        (F16, F16, (1, 6, 200, 1500), (1, 6, 1500, 64), (False, False, False)),  # transposed + K-padded
+    ]
+    for lhs_dt, act_dt, lsh, rsh, tr in cases:
+        w, _ = make_lhs(lhs_dt, lsh, rng, 0.02)
+        x = Tensor.from_data(rng.standard_normal(rsh).astype(np.float32), gpu, act_dt)
+        y = w.to(gpu).gemm(x, None, *tr)
+        y.resolve()
+        exe = rb.Executable(gpu, [y])
+        first = None
+        for _ in range(25):
+            exe.dispatch()
+            gpu.sync()
+            got = y.to(Device.CPU).storage.copy()
+            if first is None:
+                first = got
+            assert np.array_equal(got, first), (lhs_dt, lsh)
