@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(MatmulParams p) {
 // warp keep that many independent 16-byte loads in flight per lane and share the loads of x: with one row per
 // warp a short row (the Whisper logits, K = 384) is one or two dependent loads and a shuffle reduction, and the
 // kernel ran at the same 16.5 us for 40 MB (f16) as for 80 MB (f32).
-constexpr int GEMV_ROWS = 4;
+constexpr int GEMV_ROWS = 8;
 template <int KIND, typename ActT>
 __global__ void __launch_bounds__(256) gemv_simt_kernel(MatmulParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
