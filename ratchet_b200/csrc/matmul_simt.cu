@@ -173,6 +173,56 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(MatmulParams p) {
     }
 }
 
+// y[n] = sum_k x[k] * B[k][n] per stack: one row of op(lhs) against a dense rhs stored [K][N] (the decode step's
+// attention products: q.kT with one query row, softmax.v with one row of weights).  A CTA takes ROWVEC_COLS
+// columns; its eight warps take the k rows 8 apart, every lane four adjacent columns of a row (one 8- or
+// 16-byte load, a warp reads a contiguous run of B), and the warps' sums meet in shared memory in warp order.
+constexpr int ROWVEC_COLS = 128;
+template <typename T>
+__global__ void __launch_bounds__(256) rowvec_mat_kernel(MatmulParams p) {
+    __shared__ float part[8][ROWVEC_COLS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int batch = blockIdx.y;
+    const int n0 = blockIdx.x * ROWVEC_COLS + lane * 4;
+    const T *x = (const T *)p.lhs + (long long)(batch % p.lhs_stack) * p.K;
+    const T *B = (const T *)p.rhs + (long long)(batch % p.rhs_stack) * p.K * p.N;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool vec = (p.N % 4 == 0) && (reinterpret_cast<uintptr_t>(p.rhs) % 16 == 0) && n0 + 3 < p.N;
+    if (vec) {
+#pragma unroll 4
+        for (int k = warp; k < p.K; k += 8) {
+            const float xk = to_f32(x[k]);
+            T v[4];
+            if (sizeof(T) == 2) *reinterpret_cast<uint2 *>(v) = __ldg(reinterpret_cast<const uint2 *>(B + (long long)k * p.N + n0));
+            else *reinterpret_cast<uint4 *>(v) = __ldg(reinterpret_cast<const uint4 *>(B + (long long)k * p.N + n0));
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[j] = fmaf(xk, to_f32(v[j]), acc[j]);
+        }
+    } else {
+        for (int k = warp; k < p.K; k += 8) {
+            const float xk = to_f32(x[k]);
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (n0 + j < p.N) acc[j] = fmaf(xk, to_f32(B[(long long)k * p.N + n0 + j]), acc[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; j++) part[warp][lane * 4 + j] = acc[j];
+    __syncthreads();
+    if (threadIdx.x < ROWVEC_COLS) {
+        const int n = blockIdx.x * ROWVEC_COLS + threadIdx.x;
+        if (n < p.N) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; w++) sum += part[w][threadIdx.x];
+            const bool has_bias = p.bias_mode != BIAS_NONE;
+            float bias = 0.f;
+            if (has_bias) bias = load_bias(p.bias, p.bias_dt, p.bias_mode == BIAS_PER_N ? n : 0);
+            ((T *)p.out)[(long long)batch * p.N + n] = epilogue_value<T>(sum, has_bias, bias, p.epilogue);
+        }
+    }
+}
+
 template <int KIND, typename ActT>
 cudaError_t launch_kind_act(const MatmulParams &p, bool gemv, cudaStream_t stream) {
     if (gemv) {
@@ -196,6 +246,20 @@ cudaError_t launch_kind(const MatmulParams &p, rt_dtype act, bool gemv, cudaStre
 }
 
 } // namespace
+
+// One row of a dense lhs against a dense rhs [K][N] of the same dtype (M == 1, no transposes; with M == 1 the
+// output is the same memory with or without trans_out).
+cudaError_t launch_rowvec_mat(const MatmulParams &p, rt_dtype dt, cudaStream_t stream) {
+    if (p.M != 1 || p.stacks > 65535) return cudaErrorInvalidValue;
+    const dim3 grid((p.N + ROWVEC_COLS - 1) / ROWVEC_COLS, p.stacks);
+    switch (dt) {
+    case RT_F32: rowvec_mat_kernel<float><<<grid, 256, 0, stream>>>(p); break;
+    case RT_F16: rowvec_mat_kernel<__half><<<grid, 256, 0, stream>>>(p); break;
+    case RT_BF16: rowvec_mat_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p); break;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
 
 cudaError_t launch_matmul_simt(const MatmulParams &p, rt_dtype lhs_dt, rt_dtype act_dt, bool gemv, cudaStream_t stream) {
     switch (lhs_dt) {

@@ -455,11 +455,16 @@ def test_attention_products_take_the_tensor_core_gemm(gpu):
     nn = (False, False, False)
     cases = [
         (Problem(F16, F16, (1, 32, 1, 1024), (1, 32, 1024, 80), nn, seed=401), "gemm_umma_F16_F16", "_rhs_transposed"),      # decode, values
+        (Problem(F16, F16, (1, 32, 1, 80), (1, 32, 80, 1024), nn, seed=415), "rowvec_mat_F16", ""),                          # decode, scores: one row
+        (Problem(F16, F16, (1, 32, 16, 1024), (1, 32, 1024, 80), nn, seed=412), "gemm_umma_F16_F16", "_rhs_transposed"),     # 16 rows, values
         (Problem(F16, F16, (1, 32, 512, 512), (1, 32, 512, 80), nn, seed=402), "gemm_umma_F16_F16", "_rhs_transposed"),      # prefill, values
         (Problem(BF16, BF16, (2, 4, 100, 64), (2, 4, 64, 72), nn, seed=403), "gemm_umma_BF16_BF16", "_rhs_transposed"),
         (Problem(F32, F32, (1, 32, 512, 80), (1, 32, 80, 512), nn, seed=404), "gemm_umma_tf32x3", "_rhs_transposed"),        # prefill, scores
         (Problem(F16, F16, (3, 300, 96), (1, 96, 200), nn, bias=True, seed=405), "gemm_umma_F16_F16", "_rhs_transposed"),      # broadcast rhs, bias
-        (Problem(F32, F32, (1, 32, 1, 80), (1, 32, 80, 1024), nn, seed=406), "gemm_simt", ""),                               # decode scores in f32
+        (Problem(F32, F32, (1, 32, 1, 80), (1, 32, 80, 1024), nn, seed=406), "rowvec_mat_F32", ""),                          # decode scores in f32: one row
+        (Problem(BF16, BF16, (3, 1, 77), (1, 77, 131), nn, bias=True, epilogue=1, seed=413), "rowvec_mat_BF16", ""),          # odd N, broadcast rhs, bias + GELU
+        (Problem(F32, F32, (77,), (77, 260), nn, bias=True, seed=416), "rowvec_mat_F32", ""),                               # vector lhs
+        (Problem(F32, F32, (2, 5, 8, 80), (2, 5, 80, 256), nn, seed=414), "gemm_simt", ""),                                  # f32 below 16 rows
         (Problem(F16, F16, (1, 6, 300, 64), (1, 6, 64, 300), nn, seed=407), "gemm_umma_F16_F16", "_rhs_transposed"),         # rows of 300: element stores
         (Problem(BF16, BF16, (1, 2, 130, 64), (1, 2, 64, 1501), nn, bias=True, seed=409), "gemm_umma_BF16_BF16", "_rhs_transposed"),  # odd row length
         (Problem(F16, F16, (1, 6, 64, 300), (1, 6, 300, 64), nn, seed=408), "gemm_umma_F16_F16", "_rhs_transposed_kpad304"),  # K % 8 != 0: zero-padded
