@@ -514,13 +514,26 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
         pl->name = std::string("q4k_gemv_mma_nv") + std::to_string(pl->nv) + "_split" + std::to_string(pl->split & 0xff) +
                    (((pl->split >> 8) & 0xff) > 1 ? "_walk" + std::to_string((pl->split >> 8) & 0xff) + "x" + std::to_string((pl->split >> 16) & 0xff) + "buf"
                                                    : std::string());
-    } else if (s.M == 1 && s.N >= 128 && !s.trans_lhs && !s.trans_rhs && desc->lhs_dt == desc->rhs_dt && !is_quantized(desc->lhs_dt) &&
+    } else if (s.M == 1 && s.N >= 2 && !s.trans_lhs && !s.trans_rhs && desc->lhs_dt == desc->rhs_dt && !is_quantized(desc->lhs_dt) &&
                (desc->rhs_dt == RT_F32 || desc->rhs_dt == RT_F16 || desc->rhs_dt == RT_BF16) && !empty && !force_simt() &&
                s.stacks <= 65535) {
-        // one row against a dense [K][N] matrix of at least 128 columns (q.kT of a decode step): with fewer
-        // columns the kernel's lanes and CTAs stay idle (softmax.v, N = 80: 28.8 us against 14.4 us on the GEMM route)
+        // one row against a dense [K][N] matrix (q.kT and softmax.v of a decode step); with few columns and many
+        // k rows (softmax.v: 80 columns) the k rows are split over CTAs that leave f32 partial sums in act_scratch
         pl->kernel = PK_ROWVEC_MAT;
-        pl->name = std::string("rowvec_mat_") + dtype_name(desc->rhs_dt);
+        pl->split = rowvec_mat_chunks((int)s.N, (int)s.K, (int)s.stacks, dev->sm_count);
+        if (pl->split > 1) {
+            pl->act_scratch_bytes = (uint64_t)s.stacks * (uint64_t)pl->split * (uint64_t)s.N * 4;
+            cudaError_t e = cudaSetDevice(dev->ordinal);
+            if (e == cudaSuccess) e = cudaMalloc(&pl->act_scratch, pl->act_scratch_bytes);
+            if (e != cudaSuccess) {
+                pl->act_scratch = nullptr;
+                delete pl;
+                return fail(e == cudaErrorMemoryAllocation ? RT_ERR_NOMEM : RT_ERR_CUDA,
+                            std::string("plan scratch: ") + cudaGetErrorString(e));
+            }
+            pl->launches = 2;
+        }
+        pl->name = std::string("rowvec_mat_") + dtype_name(desc->rhs_dt) + (pl->split > 1 ? "_ksplit" + std::to_string(pl->split) : "");
     } else if (umma_eligible(*desc, s)) {
         pl->kernel = PK_GEMM_UMMA;
         pl->lhs_is_q = s.trans_out;
@@ -689,7 +702,7 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
         e = launch_matmul_simt(p, s.desc.lhs_dt, s.desc.rhs_dt, true, st);
         break;
     case PK_ROWVEC_MAT:
-        e = launch_rowvec_mat(p, s.desc.rhs_dt, st);
+        e = launch_rowvec_mat(p, s.desc.rhs_dt, plan->split, static_cast<float *>(plan->act_scratch), st);
         break;
     case PK_GEMM_SIMT:
         e = launch_matmul_simt(p, s.desc.lhs_dt, s.desc.rhs_dt, false, st);

@@ -28,7 +28,8 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
 // General CUDA-core kernels: any legal node.
 cudaError_t launch_matmul_simt(const MatmulParams &p, rt_dtype lhs_dt, rt_dtype act_dt, bool gemv, cudaStream_t stream);
 // one row of a dense lhs against a dense rhs stored [K][N] of the same dtype (M == 1, no transposes)
-cudaError_t launch_rowvec_mat(const MatmulParams &p, rt_dtype dt, cudaStream_t stream);
+int rowvec_mat_chunks(int N, int K, int stacks, int sm_count); // CTAs that share the k rows (1: no partial sums)
+cudaError_t launch_rowvec_mat(const MatmulParams &p, rt_dtype dt, int chunks, float *partial, cudaStream_t stream);
 
 // Q8_0 x f16 GEMV / skinny GEMM on warp MMAs.  nv = columns of op(rhs), 1..8 (rhs stored [nv][K]).
 // pick_split returns the K split (cluster size), or 0 when the shape does not fit the kernel.

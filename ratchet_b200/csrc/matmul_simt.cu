@@ -5,6 +5,8 @@
 //
 // Roles in the reference: the scalar GEMM of crates/ratchet-core/src/ops/gemm.rs:342-492 and the
 // workgroup GEMV of crates/ratchet-core/src/ops/gemv.rs:181-331.
+#include <algorithm>
+
 #include "decode.cuh"
 #include "kernels.hpp"
 
@@ -177,12 +179,19 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(MatmulParams p) {
 // attention products: q.kT with one query row, softmax.v with one row of weights).  A CTA takes ROWVEC_COLS
 // columns; its eight warps take the k rows 8 apart, every lane four adjacent columns of a row (one 8- or
 // 16-byte load, a warp reads a contiguous run of B), and the warps' sums meet in shared memory in warp order.
+// With few columns and many k rows (softmax.v of a decode step: 80 columns, K = the cache length) the k rows
+// are also split over gridDim.z CTAs, which leave f32 partial sums in `partial` [stack][chunk][N] for
+// rowvec_reduce_kernel to add in chunk order (deterministic) and finish.
 constexpr int ROWVEC_COLS = 128;
-template <typename T>
-__global__ void __launch_bounds__(256) rowvec_mat_kernel(MatmulParams p) {
+template <typename T, bool PARTIAL>
+__global__ void __launch_bounds__(256) rowvec_mat_kernel(MatmulParams p, float *partial, int k_chunk) {
     __shared__ float part[8][ROWVEC_COLS];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int batch = blockIdx.y;
+    const int k_begin = PARTIAL ? (int)blockIdx.z * k_chunk : 0;
+    const int k_end = PARTIAL ? min(p.K, k_begin + k_chunk) : p.K;
     const int n0 = blockIdx.x * ROWVEC_COLS + lane * 4;
     const T *x = (const T *)p.lhs + (long long)(batch % p.lhs_stack) * p.K;
     const T *B = (const T *)p.rhs + (long long)(batch % p.rhs_stack) * p.K * p.N;
@@ -190,7 +199,7 @@ __global__ void __launch_bounds__(256) rowvec_mat_kernel(MatmulParams p) {
     const bool vec = (p.N % 4 == 0) && (reinterpret_cast<uintptr_t>(p.rhs) % 16 == 0) && n0 + 3 < p.N;
     if (vec) {
 #pragma unroll 4
-        for (int k = warp; k < p.K; k += 8) {
+        for (int k = k_begin + warp; k < k_end; k += 8) {
             const float xk = to_f32(x[k]);
             T v[4];
             if (sizeof(T) == 2) *reinterpret_cast<uint2 *>(v) = __ldg(reinterpret_cast<const uint2 *>(B + (long long)k * p.N + n0));
@@ -199,7 +208,7 @@ __global__ void __launch_bounds__(256) rowvec_mat_kernel(MatmulParams p) {
             for (int j = 0; j < 4; j++) acc[j] = fmaf(xk, to_f32(v[j]), acc[j]);
         }
     } else {
-        for (int k = warp; k < p.K; k += 8) {
+        for (int k = k_begin + warp; k < k_end; k += 8) {
             const float xk = to_f32(x[k]);
 #pragma unroll
             for (int j = 0; j < 4; j++)
@@ -215,12 +224,31 @@ __global__ void __launch_bounds__(256) rowvec_mat_kernel(MatmulParams p) {
             float sum = 0.f;
 #pragma unroll
             for (int w = 0; w < 8; w++) sum += part[w][threadIdx.x];
-            const bool has_bias = p.bias_mode != BIAS_NONE;
-            float bias = 0.f;
-            if (has_bias) bias = load_bias(p.bias, p.bias_dt, p.bias_mode == BIAS_PER_N ? n : 0);
-            ((T *)p.out)[(long long)batch * p.N + n] = epilogue_value<T>(sum, has_bias, bias, p.epilogue);
+            if (PARTIAL) {
+                partial[((long long)batch * gridDim.z + blockIdx.z) * p.N + n] = sum;
+            } else {
+                const bool has_bias = p.bias_mode != BIAS_NONE;
+                float bias = 0.f;
+                if (has_bias) bias = load_bias(p.bias, p.bias_dt, p.bias_mode == BIAS_PER_N ? n : 0);
+                ((T *)p.out)[(long long)batch * p.N + n] = epilogue_value<T>(sum, has_bias, bias, p.epilogue);
+            }
         }
     }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) rowvec_reduce_kernel(MatmulParams p, const float *partial, int chunks) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)p.stacks * p.N) return;
+    const int batch = (int)(i / p.N), n = (int)(i - (long long)batch * p.N);
+    float sum = 0.f;
+    for (int c = 0; c < chunks; c++) sum += partial[((long long)batch * chunks + c) * p.N + n];
+    const bool has_bias = p.bias_mode != BIAS_NONE;
+    float bias = 0.f;
+    if (has_bias) bias = load_bias(p.bias, p.bias_dt, p.bias_mode == BIAS_PER_N ? n : 0);
+    ((T *)p.out)[i] = epilogue_value<T>(sum, has_bias, bias, p.epilogue);
 }
 
 template <int KIND, typename ActT>
@@ -245,20 +273,37 @@ cudaError_t launch_kind(const MatmulParams &p, rt_dtype act, bool gemv, cudaStre
     }
 }
 
+template <typename T>
+cudaError_t launch_rowvec_t(const MatmulParams &p, int chunks, float *partial, cudaStream_t stream) {
+    const int col_blocks = (p.N + ROWVEC_COLS - 1) / ROWVEC_COLS;
+    if (chunks <= 1)
+        return launch_pdl(rowvec_mat_kernel<T, false>, dim3(col_blocks, p.stacks, 1), dim3(256), 0, stream, p, (float *)nullptr, p.K);
+    const int k_chunk = ((p.K + chunks - 1) / chunks + 7) & ~7;
+    cudaError_t e = launch_pdl(rowvec_mat_kernel<T, true>, dim3(col_blocks, p.stacks, chunks), dim3(256), 0, stream, p, partial, k_chunk);
+    if (e != cudaSuccess) return e;
+    const long long total = (long long)p.stacks * p.N;
+    return launch_pdl(rowvec_reduce_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, p, (const float *)partial, chunks);
+}
+
 } // namespace
 
+// How many CTAs share the k rows of one column block: enough to put about two CTAs on every SM, at least 64 rows each.
+int rowvec_mat_chunks(int N, int K, int stacks, int sm_count) {
+    const long long col_ctas = (long long)((N + ROWVEC_COLS - 1) / ROWVEC_COLS) * stacks;
+    const long long want = (2LL * sm_count + col_ctas - 1) / col_ctas;
+    return (int)std::max<long long>(1, std::min<long long>(want, K / 64));
+}
+
 // One row of a dense lhs against a dense rhs [K][N] of the same dtype (M == 1, no transposes; with M == 1 the
-// output is the same memory with or without trans_out).
-cudaError_t launch_rowvec_mat(const MatmulParams &p, rt_dtype dt, cudaStream_t stream) {
-    if (p.M != 1 || p.stacks > 65535) return cudaErrorInvalidValue;
-    const dim3 grid((p.N + ROWVEC_COLS - 1) / ROWVEC_COLS, p.stacks);
+// output is the same memory with or without trans_out).  chunks > 1: `partial` holds stacks * chunks * N floats.
+cudaError_t launch_rowvec_mat(const MatmulParams &p, rt_dtype dt, int chunks, float *partial, cudaStream_t stream) {
+    if (p.M != 1 || p.stacks > 65535 || chunks > 65535 || (chunks > 1 && !partial)) return cudaErrorInvalidValue;
     switch (dt) {
-    case RT_F32: rowvec_mat_kernel<float><<<grid, 256, 0, stream>>>(p); break;
-    case RT_F16: rowvec_mat_kernel<__half><<<grid, 256, 0, stream>>>(p); break;
-    case RT_BF16: rowvec_mat_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p); break;
+    case RT_F32: return launch_rowvec_t<float>(p, chunks, partial, stream);
+    case RT_F16: return launch_rowvec_t<__half>(p, chunks, partial, stream);
+    case RT_BF16: return launch_rowvec_t<__nv_bfloat16>(p, chunks, partial, stream);
     default: return cudaErrorInvalidValue;
     }
-    return cudaGetLastError();
 }
 
 cudaError_t launch_matmul_simt(const MatmulParams &p, rt_dtype lhs_dt, rt_dtype act_dt, bool gemv, cudaStream_t stream) {

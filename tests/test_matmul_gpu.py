@@ -454,7 +454,8 @@ def test_attention_products_take_the_tensor_core_gemm(gpu):
     the rhs K-major for the tensor-core GEMMs (16-bit operands whose K is not a multiple of 8 are zero-padded on the way)."""
     nn = (False, False, False)
     cases = [
-        (Problem(F16, F16, (1, 32, 1, 1024), (1, 32, 1024, 80), nn, seed=401), "gemm_umma_F16_F16", "_rhs_transposed"),      # decode, values
+        (Problem(F16, F16, (1, 32, 1, 1024), (1, 32, 1024, 80), nn, seed=401), "rowvec_mat_F16", "_ksplit10"),               # decode, values: k rows split
+        (Problem(F32, F32, (1, 1, 1000), (3, 1000, 50), nn, bias=True, seed=417), "rowvec_mat_F32", "_ksplit15"),           # ragged chunks, broadcast lhs
         (Problem(F16, F16, (1, 32, 1, 80), (1, 32, 80, 1024), nn, seed=415), "rowvec_mat_F16", ""),                          # decode, scores: one row
         (Problem(F16, F16, (1, 32, 16, 1024), (1, 32, 1024, 80), nn, seed=412), "gemm_umma_F16_F16", "_rhs_transposed"),     # 16 rows, values
         (Problem(F16, F16, (1, 32, 512, 512), (1, 32, 512, 80), nn, seed=402), "gemm_umma_F16_F16", "_rhs_transposed"),      # prefill, values
