@@ -471,6 +471,8 @@ def test_attention_products_take_the_tensor_core_gemm(gpu):
         (Problem(F16, F16, (1, 6, 64, 300), (1, 6, 300, 64), nn, seed=408), "gemm_umma_F16_F16", "_rhs_transposed_kpad304"),  # K % 8 != 0: zero-padded
         (Problem(BF16, BF16, (2, 3, 200, 1501), (2, 3, 1501, 64), nn, bias=True, seed=410), "gemm_umma_BF16_BF16", "_kpad1504"),    # odd K
         (Problem(F32, F32, (1, 6, 64, 302), (1, 6, 302, 64), nn, seed=411), "gemm_simt", ""),                                # f32: K % 4 != 0
+        (Problem(F16, F16, (1, 4, 300, 12), (1, 4, 12, 601), nn, bias=True, seed=418), "gemm_umma_F16_F16", "_kpad16"),      # K below one tile step, odd N
+        (Problem(F16, F16, (2, 129, 8), (2, 8, 1024), nn, seed=419), "gemm_umma_F16_F16", "_rhs_transposed"),               # K = 8
     ]
     for prob, prefix, suffix in cases:
         _, kernel = check_problem(prob, gpu)
