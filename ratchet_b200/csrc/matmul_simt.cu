@@ -98,8 +98,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(MatmulParams p) {
 // warp keep that many independent 16-byte loads in flight per lane and share the loads of x: with one row per
 // warp a short row (the Whisper logits, K = 384) is one or two dependent loads and a shuffle reduction, and the
 // kernel ran at the same 16.5 us for 40 MB (f16) as for 80 MB (f32).
-constexpr int GEMV_ROWS = 8;
-template <int KIND, typename ActT>
+// GEMV_ROWS is 8 when that still gives two CTAs per SM, else 2 (a [2560, 10240] node has only 2560 rows).
+template <int KIND, typename ActT, int GEMV_ROWS>
 __global__ void __launch_bounds__(256) gemv_simt_kernel(MatmulParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = (blockIdx.x * 8 + warp) * GEMV_ROWS;
@@ -149,6 +149,37 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(MatmulParams p) {
                     acc[r] = fmaf(wv[r].y, xv.y, acc[r]);
                     acc[r] = fmaf(wv[r].z, xv.z, acc[r]);
                     acc[r] = fmaf(wv[r].w, xv.w, acc[r]);
+                }
+            }
+        }
+    } else if ((KIND == LK_Q8H || KIND == LK_Q8F) && p.K % 32 == 0 && lbase % 16 == 0 &&
+               (reinterpret_cast<uintptr_t>(p.lhs) | reinterpret_cast<uintptr_t>(x)) % 16 == 0) {
+        // Q8_0 against activations this file's tensor-core kernels do not take (f32, the reference's
+        // (Q8_0F, F32) pair; bf16): a lane takes 16 codes of a row per step (one 16-byte load, half a block),
+        // the 16 activations are loaded once for all the warp's rows, and every element is dequantised with
+        // the rounding of lhs_element before it meets its activation.
+        const int8_t *codes = (const int8_t *)p.lhs;
+        for (int k = lane * 16; k < p.K; k += 512) {
+            uint4 qv[GEMV_ROWS];
+            float d[GEMV_ROWS];
+#pragma unroll
+            for (int r = 0; r < GEMV_ROWS; r++) {
+                qv[r] = __ldg(reinterpret_cast<const uint4 *>(codes + abase[r] + k));
+                const long long blk = (abase[r] + k) >> 5;
+                d[r] = KIND == LK_Q8F ? __ldg((const float *)p.lhs_scales + blk) : __half2float(__ldg((const __half *)p.lhs_scales + blk));
+            }
+            ActT xv[16];
+#pragma unroll
+            for (int j = 0; j < (int)(16 * sizeof(ActT) / 16); j++)
+                reinterpret_cast<uint4 *>(xv)[j] = __ldg(reinterpret_cast<const uint4 *>(x + k) + j);
+#pragma unroll
+            for (int r = 0; r < GEMV_ROWS; r++) {
+                const int8_t *q = reinterpret_cast<const int8_t *>(&qv[r]);
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const float qd = __fmul_rn((float)q[i], d[r]);
+                    const float v = KIND == LK_Q8F ? qd : __half2float(__float2half_rn(qd));
+                    acc[r] = fmaf(v, to_f32(xv[i]), acc[r]);
                 }
             }
         }
@@ -254,8 +285,16 @@ __global__ void __launch_bounds__(256) rowvec_reduce_kernel(MatmulParams p, cons
 template <int KIND, typename ActT>
 cudaError_t launch_kind_act(const MatmulParams &p, bool gemv, cudaStream_t stream) {
     if (gemv) {
-        dim3 grid((p.M + 8 * GEMV_ROWS - 1) / (8 * GEMV_ROWS), 1, p.stacks);
-        gemv_simt_kernel<KIND, ActT><<<grid, 256, 0, stream>>>(p);
+        int sms = 148;
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if ((long long)((p.M + 63) / 64) * p.stacks >= 2LL * sms) {
+            dim3 grid((p.M + 63) / 64, 1, p.stacks);
+            gemv_simt_kernel<KIND, ActT, 8><<<grid, 256, 0, stream>>>(p);
+        } else {
+            dim3 grid((p.M + 15) / 16, 1, p.stacks);
+            gemv_simt_kernel<KIND, ActT, 2><<<grid, 256, 0, stream>>>(p);
+        }
     } else {
         dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, p.stacks);
         gemm_simt_kernel<KIND, ActT><<<grid, 256, 0, stream>>>(p);
