@@ -472,7 +472,10 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
     const bool empty = s.M == 0 || s.N == 0 || s.stacks == 0;
     const int gemv_split = (q8 && s.K > 0 && !empty && !force_simt())
                                ? q8_gemv_mma_pick_split(p.M, p.K, dev->sm_count, desc->lhs_dt == RT_Q8_0H ? 2 : 4) : 0;
-    if (gemv_split > 0 && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.N >= 1 && s.N <= 8 && (s.N == 1 || s.trans_rhs) && s.K > 0 && !empty) {
+    // short rows against very many of them (the Whisper logits, [51865, 384]): the 16-row CTAs of the streaming
+    // kernel come to 3,242 tiny CTAs; the CUDA-core GEMV with 8 rows per warp is faster there (12.6 against 16.4 us)
+    const bool short_rows = q8 && s.N == 1 && s.K <= 512 && s.M >= 16384 && s.K % 32 == 0;
+    if (gemv_split > 0 && !short_rows && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.N >= 1 && s.N <= 8 && (s.N == 1 || s.trans_rhs) && s.K > 0 && !empty) {
         pl->nv = (int)s.N;
         pl->split = gemv_split;
         // one vector against f16-scaled Q8_0 at a size that fills the machine: the tensor-memory GEMV
