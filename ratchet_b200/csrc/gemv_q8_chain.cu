@@ -97,6 +97,8 @@ static_assert(sizeof(ChainNodeInfo) == 128, "ChainNodeInfo is copied as 32 words
 struct alignas(64) ChainNodeDev : ChainNodeInfo {
     CUtensorMap map_w; // codes  [M][K] u8, box 128 x rb, 128-byte swizzle
     CUtensorMap map_s; // scales [M][K/32] f16, box (ks/32) x rb
+    const void *lhs;   // the same tensors as plain pointers: only the path for NaN / infinite activations reads them
+    const void *lhs_scales;
 };
 
 struct ChainParams {
@@ -136,6 +138,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
     const int n_bars = 2 * cp.ring + 2 * TGROUPS + 1 + 4;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + n_bars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    unsigned int *badmask = tmem_slot + 2; // [2][4]: blocks of the K slice with a NaN or an infinity, by node parity; then [2]: any
     const uint32_t bar_full = smem_u32(bars), bar_done = smem_u32(bars + cp.ring);
     const uint32_t bar_tempty = smem_u32(bars + 2 * cp.ring + TGROUPS);
     const uint32_t bar_x = smem_u32(bars + 2 * cp.ring + 2 * TGROUPS);
@@ -155,6 +158,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
             mbar_init(bar_sempty + 8 * a, 8);
         }
         *abort_flag = 0;
+        for (int i = 0; i < 10; i++) badmask[i] = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -282,9 +286,11 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
             // the next node's description, fetched while this node waits and computes (nobody reads the other
             // copy any more: node l-1 is over for every warp of this CTA once its sums were taken)
             int next_word = 0;
-            if (warp == 2 && l + 1 < cp.n_nodes) next_word = reinterpret_cast<const int *>(static_cast<const ChainNodeInfo *>(cp.nodes + l + 1))[lane];
-            if (warp == 2 && l + 1 < cp.n_nodes) reinterpret_cast<int *>(info + ((l + 1) & 1))[lane] = next_word;
+            // (asked for here, stored after the digits: a warp issues in order, and a store right behind the load would
+            // hold up the whole warp, and with it the node's digits, until the word has come from memory)
+            if (warp == 2 && l + 1 < cp.n_nodes) next_word = __ldcg(reinterpret_cast<const int *>(static_cast<const ChainNodeInfo *>(cp.nodes + l + 1)) + lane);
             if (!has_rows) {
+                if (warp == 2 && l + 1 < cp.n_nodes) reinterpret_cast<int *>(info + ((l + 1) & 1))[lane] = next_word;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_x);
             }
@@ -368,8 +374,15 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                         if (blk >= ks / 32) break;
                         uint2 hi8, lo8;
                         float inv;
-                        quantize_quarter_block(pre[it], hi8, lo8, inv);
-                        if (sub == 0) xs[blk] = inv;
+                        bool nonfinite;
+                        quantize_quarter_block(pre[it], hi8, lo8, inv, nonfinite);
+                        if (sub == 0) {
+                            xs[blk] = inv;
+                            if (nonfinite) {
+                                atomicOr(badmask + (l & 1) * 4 + (blk >> 5), 1u << (blk & 31));
+                                badmask[8 + (l & 1)] = 1u;
+                            }
+                        }
                         // the chunk's digits go into every MMA tile that holds some of the chunk's rows
                         const int chunk = blk >> 2, stage = (chunk * inv_S) >> 16, cl = chunk - stage * S;
                         const int kpos = (blk & 3) * 32 + sub * 8;
@@ -389,6 +402,9 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 asm volatile("bar.sync 1, 256;" ::: "memory"); // xs visible to all epilogue warps
                 if (*abort_flag) break;
                 if (lane == 0) mbar_arrive(bar_x);
+                if (warp == 2 && l + 1 < cp.n_nodes) reinterpret_cast<int *>(info + ((l + 1) & 1))[lane] = next_word;
+                if (et < 4) badmask[((l + 1) & 1) * 4 + et] = 0u; // the next node's mask and flag (node l-1's readers are two barriers back)
+                if (et == 4) badmask[8 + ((l + 1) & 1)] = 0u;
 
                 const uint8_t *scales_n = scales_s + (size_t)sbuf * cp.scale_buf_bytes;
                 const int srow = ks / 16; // bytes per row of the node's scales
@@ -462,6 +478,23 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 float sum = 0.f;
                 if (my_rows) {
                     for (int c = 0; c < S; c++) sum += part[c * rb8 + et] + part[MAX_TILES * 128 + c * rb8 + et];
+                    // blocks of the activations that hold NaN or infinities were left out above (zero digits): their
+                    // products over this CTA's K slice, formed as the reference forms them
+                    if (badmask[8 + (l & 1)]) {
+                        const ChainNodeDev &dev = cp.nodes[l];
+                        const int row = row_begin + et;
+                        for (int w = 0; w < (ks / 32 + 31) / 32; w++) {
+                            unsigned int m = badmask[(l & 1) * 4 + w];
+                            while (m) {
+                                const int blk = w * 32 + __ffs(m) - 1;
+                                m &= m - 1;
+                                const __half d = ((const __half *)dev.lhs_scales)[(size_t)row * (nd.K / 32) + k_begin / 32 + blk];
+                                sum += nonfinite_block_products((const int8_t *)dev.lhs + (size_t)row * nd.K + k_begin + blk * 32, d,
+                                                                l == 0 ? (const __half *)nd.rhs + k_begin + blk * 32 : nullptr,
+                                                                l == 0 ? nullptr : cp.xbuf + prev_x_off + k_begin + blk * 32);
+                            }
+                        }
+                    }
                 }
                 bool writes_rows = true;
                 if (split > 1) {
@@ -669,6 +702,7 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
         nd.ks = p.K / splits[i];
         if (!pick_stage(nd)) { *why = "no stage shape for this node"; return cudaSuccess; }
         nd.rhs = p.rhs; nd.out = p.out; nd.bias = p.bias;
+        nd.lhs = p.lhs; nd.lhs_scales = p.lhs_scales;
         nd.bias_mode = p.bias_mode; nd.bias_dt = p.bias_dt; nd.epilogue = p.epilogue;
         slot_bytes = std::max(slot_bytes, nd.S * nd.rb8 * 128);
         b_bytes = std::max(b_bytes, nd.nstages * nd.tiles * nd.b_tile_bytes);

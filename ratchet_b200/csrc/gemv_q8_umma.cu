@@ -93,6 +93,7 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // bars: [0..R) full, [R..2R) empty, then TGROUPS tmem_full, TGROUPS tmem_empty, digits ready, K-slice sums arrived
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * up.ring + 2 * TGROUPS + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    unsigned int *badmask = tmem_slot + 2; // [4]: blocks of this CTA's K slice that hold a NaN or an infinity, then [1]: any
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + up.ring);
     const uint32_t bar_tfull = smem_u32(bars + 2 * up.ring), bar_tempty = smem_u32(bars + 2 * up.ring + TGROUPS);
     const uint32_t bar_x = smem_u32(bars + 2 * up.ring + 2 * TGROUPS), bar_red = smem_u32(bars + 2 * up.ring + 2 * TGROUPS + 1);
@@ -109,6 +110,7 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         mbar_init(bar_x, 4);
         mbar_init(bar_red, (up.split > 1 ? up.split - 1 : 1) * 128); // one arrival per row of every other K slice
         *abort_flag = 0;
+        for (int i = 0; i < 5; i++) badmask[i] = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -203,7 +205,10 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int it = 0; it < MAX_IT; it++) {
                 const int blk = (et >> 2) + it * 32;
                 if (blk >= up.ks / 32) break;
-                digits_of_quarter_block(pre[it], blk, sub, b_tiles, xs);
+                if (digits_of_quarter_block(pre[it], blk, sub, b_tiles, xs) && sub == 0) {
+                    atomicOr(badmask + (blk >> 5), 1u << (blk & 31));
+                    badmask[4] = 1u;
+                }
             }
         }
         // the MMAs read the tiles through the async proxy
@@ -238,6 +243,21 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
             if (++slot == up.ring) { slot = 0; phase ^= 1; }
             if (++tg == TGROUPS) { tg = 0; tphase ^= 1; }
+        }
+        // blocks of the activations that hold NaN or infinities were left out above (zero digits): their
+        // products, formed as the reference forms them
+        if (badmask[4] && row_local < rows_here) {
+            const int row = row_begin + row_local;
+            for (int w = 0; w < (up.ks / 32 + 31) / 32; w++) {
+                unsigned int m = badmask[w];
+                while (m) {
+                    const int blk = w * 32 + __ffs(m) - 1;
+                    m &= m - 1;
+                    const __half d = ((const __half *)p.lhs_scales)[(size_t)row * (p.K / 32) + k_begin / 32 + blk];
+                    acc += nonfinite_block_products((const int8_t *)p.lhs + (size_t)row * p.K + k_begin + blk * 32, d,
+                                                    (const __half *)p.rhs + k_begin + blk * 32, nullptr);
+                }
+            }
         }
         red[row_local] = acc;
     }

@@ -115,7 +115,11 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // Eight consecutive activations (one quarter of a Q8_0 block; the four threads of a quad hold one
 // block) -> their hi / lo int8 digits (eight bytes each) and the block's power-of-two scale.
 //   m = round(x / xs), |m| <= 16383, m = 256 * hi + lo with lo in [-128, 127];  x ~ m * xs.
-__device__ __forceinline__ void quantize_quarter_block(const uint4 raw, uint2 &hi8, uint2 &lo8, float &xs_of_block) {
+// A block that holds a NaN or an infinity cannot be written as digits: it gets zero digits and a zero
+// scale (it then adds nothing to any row) and `nonfinite` is set for all four threads of the quad, so
+// that the caller can add the block's products the way the reference forms them (nonfinite_block_products).
+__device__ __forceinline__ void quantize_quarter_block(const uint4 raw, uint2 &hi8, uint2 &lo8, float &xs_of_block, bool &nonfinite) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
     const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
     float v[8];
 #pragma unroll
@@ -124,11 +128,18 @@ __device__ __forceinline__ void quantize_quarter_block(const uint4 raw, uint2 &h
         v[2 * i] = f.x;
         v[2 * i + 1] = f.y;
     }
-    float amax = 0.f;
+    // the largest magnitude as a bit pattern (f16 magnitudes order like integers; NaN and infinities, whose
+    // exponent field is all ones, come out on top, which a floating-point maximum would not guarantee)
+    uint32_t amax_bits = 0u;
 #pragma unroll
-    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    for (int i = 0; i < 4; i++) {
+        const uint32_t a = w[i] & 0x7FFF7FFFu;
+        amax_bits = max(amax_bits, max(a & 0xFFFFu, a >> 16));
+    }
+    amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, 1));
+    amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, 2));
+    nonfinite = amax_bits >= 0x7C00u;
+    const float amax = nonfinite ? 0.f : __half2float(__ushort_as_half((unsigned short)amax_bits));
     // amax < 2^(E-126) for its exponent field E: scale it below 2^14
     const int E = (int)((__float_as_uint(amax) >> 23) & 0xFFu);
     const float scale = amax > 0.f ? __uint_as_float((uint32_t)(140 - E + 127) << 23) : 0.f;
@@ -147,6 +158,21 @@ __device__ __forceinline__ void quantize_quarter_block(const uint4 raw, uint2 &h
     lo8 = make_uint2(lo_w[0], lo_w[1]);
 }
 
+// One 32-wide block's contribution to one weight row, formed the way the reference's GEMV forms it
+// (crates/ratchet-core/src/ops/gemv.rs:470-480: code times scale rounded to f16, times x in f16, widened to
+// f32 and added), so that NaN and infinities in x come out as IEEE arithmetic gives them.  Only blocks that
+// quantize_quarter_block flagged take this path.  The activations are either plain f16 (`x_plain`) or the
+// low halves of 32-bit words (`x_words`, the chain kernels' exchange format); the other pointer is null.
+__device__ __forceinline__ float nonfinite_block_products(const int8_t *codes, __half d, const __half *x_plain, const unsigned int *x_words) {
+    float sum = 0.f;
+    for (int i = 0; i < 32; i++) {
+        const __half xv = x_plain ? x_plain[i] : __ushort_as_half((unsigned short)(__ldcg(x_words + i) & 0xFFFFu));
+        const __half w = __hmul(__int2half_rn((int)codes[i]), d);
+        sum += __half2float(__hmul(w, xv));
+    }
+    return sum;
+}
+
 // Stores eight digit bytes at byte `kpos` (a multiple of 8 below 128) of row `row` (0..7) of a K-major
 // 8-row x 128-byte operand tile with the 128-byte swizzle: 16-byte chunks XOR the row index.
 __device__ __forceinline__ void store_digits8(uint8_t *tile, int row, int kpos, uint2 v) {
@@ -156,15 +182,17 @@ __device__ __forceinline__ void store_digits8(uint8_t *tile, int row, int kpos, 
 
 // The single-launch kernel's layout: one 8-row tile per 128 bytes of K, row 0 = hi, row 1 = lo, rows
 // 2..7 zero.  `blk` is the block index inside the CTA's K slice, `sub` the quarter (0..3).
-__device__ __forceinline__ void digits_of_quarter_block(const uint4 raw, int blk, int sub, uint8_t *b_tiles, float *xs) {
+__device__ __forceinline__ bool digits_of_quarter_block(const uint4 raw, int blk, int sub, uint8_t *b_tiles, float *xs) {
     uint2 hi8, lo8;
     float inv;
-    quantize_quarter_block(raw, hi8, lo8, inv);
+    bool nonfinite;
+    quantize_quarter_block(raw, hi8, lo8, inv, nonfinite);
     uint8_t *tile = b_tiles + (size_t)(blk >> 2) * 1024;
     const int kpos = (blk & 3) * 32 + sub * 8;
     store_digits8(tile, 0, kpos, hi8);
     store_digits8(tile, 1, kpos, lo8);
     if (sub == 0) xs[blk] = inv;
+    return nonfinite;
 }
 
 // One block's contribution to a row: d = weight scale, xsv = activation scale, (hi, lo) = the MMA's two sums.

@@ -245,6 +245,71 @@ def test_q8_gemv_lists_chain_or_graph(gpu, shapes, kind):
         h = got.astype(np.float32)
 
 
+def _reference_gemv_f16(w_codes, w_scales, x16):
+    """The reference's Q8_0H GEMV arithmetic in numpy (gemv.rs:470-480): code times scale rounded to f16, times x
+    in f16, widened to f32 and summed.  IEEE semantics for NaN and infinities come with numpy's float16."""
+    with np.errstate(all="ignore"):
+        inter = (w_codes.astype(np.float16).reshape(w_codes.shape[0], -1, 32) * w_scales[:, :, None]).astype(np.float16)
+        prod = (inter.reshape(w_codes.shape[0], -1) * x16[None, :]).astype(np.float16)
+        return prod.astype(np.float32).sum(axis=1, dtype=np.float32)
+
+
+@pytest.mark.parametrize("as_list", [True, False], ids=["executable", "single_launch"])
+def test_q8_gemv_propagates_nan_and_infinities(gpu, as_list):
+    """NaN, +inf, -inf and a 60000-magnitude outlier among N(0,1) activations: every output row is NaN, +inf, -inf or
+    finite exactly where the reference's f16 arithmetic makes it so, and the finite rows meet the usual bar."""
+    M, K = 4096, 2560
+    rng = np.random.default_rng(4700)
+    w = (rng.standard_normal((M, K)) * 0.02).astype(np.float32)
+    w[7, 64:96] = 0.0            # a row whose weights are zero where an infinity sits: 0 * inf = NaN
+    buf = oracle.q8_quantize_h(w)
+    codes = buf[:M * K].view(np.int8).reshape(M, K)
+    scales = buf[(M * K + 255) // 256 * 256:][:M * K // 32 * 2].view(np.float16).reshape(M, K // 32)
+    wv = oracle.q8_dequantize_h(buf, M * K).astype(np.float32).reshape(M, K)
+    w_t = Tensor.from_quantized(buf, Q8H, (M, K), gpu)
+    w2_t, w2v = make_lhs(Q8H, (M, M), np.random.default_rng(4701), 0.02)
+    w2_t = w2_t.to(gpu)
+    cases = {
+        "outlier": [(100, 60000.0)],
+        "nan": [(5, np.nan)],
+        "pos_inf": [(70, np.inf)],
+        "two_inf_one_block": [(64, np.inf), (65, -np.inf)],
+        "inf_and_nan_far_apart": [(33, -np.inf), (2000, np.nan)],
+    }
+    for name, edits in cases.items():
+        x = rng.standard_normal(K).astype(np.float16)
+        for pos, val in edits:
+            x[pos] = np.float16(val)
+        xd = Tensor.from_data(x, gpu)
+        y1 = w_t.gemm(xd, None, False, True, True)
+        if as_list:
+            y2 = w2_t.gemm(y1, None, False, True, True)
+            y2.resolve()
+            exe = rb.Executable(gpu, [y1, y2])
+            assert exe.kernel.startswith("q8_gemv_chain"), exe.kernel
+            y1.write(np.zeros(M, dtype=np.float16))
+            exe.dispatch()
+            gpu.sync()
+        else:
+            y1.resolve()
+        got = y1.to(Device.CPU).to_numpy().reshape(-1).astype(np.float32)
+        want = _reference_gemv_f16(codes, scales, x)
+        for kind, f in (("nan", np.isnan), ("+inf", np.isposinf), ("-inf", np.isneginf)):
+            assert np.array_equal(f(got), f(want)), (name, kind, int(f(got).sum()), int(f(want).sum()))
+        fin = np.isfinite(want)
+        if fin.any():
+            truth = oracle.matmul_truth(wv, x.astype(np.float32), None, 1, 1, 1, M, 1, K, False, True, True)
+            assert oracle.rel_l2(got[fin], oracle.f64_to_f16(truth).astype(np.float32)[fin]) <= TOL[F16], name
+        if as_list:
+            # the second node reads the first one's rows: whatever is not finite there spreads the same way
+            got2 = y2.to(Device.CPU).to_numpy().reshape(-1).astype(np.float32)
+            codes2 = w2_t.to(Device.CPU).to_numpy()[:M * M].view(np.int8).reshape(M, M)
+            scales2 = w2_t.to(Device.CPU).to_numpy()[(M * M + 255) // 256 * 256:][:M * M // 32 * 2].view(np.float16).reshape(M, M // 32)
+            want2 = _reference_gemv_f16(codes2, scales2, y1.to(Device.CPU).to_numpy().reshape(-1))
+            for kind, f in (("nan", np.isnan), ("+inf", np.isposinf), ("-inf", np.isneginf)):
+                assert np.array_equal(f(got2), f(want2)), (name, "node 2", kind)
+
+
 def test_q8_gemv_chain_is_deterministic(gpu):
     """Same input, same bits, dispatch after dispatch: the CTAs hand rows on through polled words and K slices
     meet in a fixed order, so nothing may depend on which CTA is early."""
