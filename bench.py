@@ -11,13 +11,18 @@ launches per step, 27,878,400 algorithmic bytes each (codes + f16 scales + x + y
 (1.78 GB) exceed the 126 MB L2, so every launch streams from HBM.  Synthetic data: weights
 N(0, 0.02) (fc2: N(0, 0.01), see make_weights) quantised with sint8_quantize, input N(0, 1), seeded.
 
+A "step" is REPEATS (50) decode steps in a row, so that a run of a few steps is long enough to time.
+
 Legs, all in one JSON line printed by rank 0:
-  value         device-timed GB/s, operands resident, one Executable dispatch per step
+  value         device-timed GB/s, operands resident, one Executable dispatch per decode step
   e2e           the same step through the public host API (Tensor.to / gemm / resolve / to):
                 host->device copy of the step's input vector from pinned memory and
                 device->host read of the step's output inside the timed region
   roofline      algorithmic bytes per launch / average launch time, against the measured HBM peak
   cpu_baseline  the shader-faithful CPU oracle on all host cores, bounded sample (rank 0, N=1)
+  dispatch_forms   the same GEMVs launched one kernel per node, and as two-node fc1 -> fc2 executables
+  extras        the other workloads on one GPU (dense f32, Whisper MLP, Q4_K, bf16 prefill), each with its roofline
+  sharded       the N-sharded bf16 prefill Linear (at N = 1: the compute-only point of the curve), with a parity check
 `--impl reference` times that CPU oracle alone (the reference has no CPU Matmul and its WebGPU
 backend cannot run on this box; the oracle is the restated reference arithmetic).
 """
@@ -42,6 +47,7 @@ UNIT = "GB/s"
 LAYERS = 32
 D_MODEL, D_FF = 2560, 10240
 NCU_TRAFFIC_PER_GEMV = 27_900_000     # measured DRAM bytes per GEMV (27.88 MB per node of the chain kernel; 27.89 / 27.91 MB single launches)
+REPEATS = 50                          # decode steps per timed "step"
 BYTES_PER_GEMV = D_FF * D_MODEL + 2 * (D_FF * D_MODEL // 32) + 2 * D_MODEL + 2 * D_FF  # 27,878,400
 WORKLOAD = "phi2_mlp_q8_0_gemv_decode"
 
@@ -49,16 +55,16 @@ WORKLOAD = "phi2_mlp_q8_0_gemv_decode"
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=300)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=20, help="timed steps; one step = %d decode steps" % REPEATS)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="MLP blocks per step (default: Phi-2's 32)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="dispatch node by node instead of one CUDA graph")
     ap.add_argument("--no-lazy", action="store_true", help="skip the node-by-node lazy-graph leg reported beside e2e")
     ap.add_argument("--no-sharded", action="store_true", help="with --gpus > 1: skip the N-sharded prefill GEMM section")
-    ap.add_argument("--extras", default="", help="comma list of the other configurations to time on one GPU and "
-                    "report under \"extras\": c1,c3,c4,c5,c5long or all")
+    ap.add_argument("--extras", default="all", help="comma list of the other workloads to time on one GPU and "
+                    "report under \"extras\": c1,c3,c4,c5,c5long, all (default) or none")
     return ap.parse_args()
 
 
@@ -74,20 +80,33 @@ def peaks():
 UNIQUE_LAYERS = 4
 
 
-def make_weights(layers: int, seed: int):
-    """Per layer (fc1 [D_FF, D_MODEL], fc2 [D_MODEL, D_FF]) Q8_0H host tensors, built with the library's
-    quantiser.  Four distinct layers are generated and repeated: every layer still gets its own device
-    buffer, and bandwidth does not depend on the values.  fc1 ~ N(0, 0.02); fc2 ~ N(0, 0.01) so that the
-    chained activations keep a constant scale and stay inside the f16 range over 32 layers."""
-    import ratchet_b200 as rb
-    qz = rb.Quantizer(rb.Quantization.SInt8)
+def make_weights_f32(layers: int, seed: int):
+    """Per layer (fc1 [D_FF, D_MODEL], fc2 [D_MODEL, D_FF]) f32 weights.  Four distinct layers are generated and
+    repeated: every layer still gets its own device buffer, and bandwidth does not depend on the values.
+    fc1 ~ N(0, 0.02); fc2 ~ N(0, 0.01) so that the chained activations keep a constant scale and stay inside the
+    f16 range over 32 layers."""
     uniq = []
     for l in range(min(layers, UNIQUE_LAYERS)):
         rng = np.random.default_rng(seed + 1000 + l)
-        w1 = (rng.standard_normal((D_FF, D_MODEL), dtype=np.float32) * np.float32(0.02))
-        w2 = (rng.standard_normal((D_MODEL, D_FF), dtype=np.float32) * np.float32(0.01))
-        uniq.append((qz.sint8_quantize(rb.Tensor.from_data(w1), rb.DType.Q8_0H),
-                     qz.sint8_quantize(rb.Tensor.from_data(w2), rb.DType.Q8_0H)))
+        uniq.append((rng.standard_normal((D_FF, D_MODEL), dtype=np.float32) * np.float32(0.02),
+                     rng.standard_normal((D_MODEL, D_FF), dtype=np.float32) * np.float32(0.01)))
+    return uniq
+
+
+def make_weights(layers: int, seed: int):
+    """The same as Q8_0H host tensors, built with the library's quantiser (our arm)."""
+    import ratchet_b200 as rb
+    qz = rb.Quantizer(rb.Quantization.SInt8)
+    uniq = [(qz.sint8_quantize(rb.Tensor.from_data(w1), rb.DType.Q8_0H), qz.sint8_quantize(rb.Tensor.from_data(w2), rb.DType.Q8_0H))
+            for w1, w2 in make_weights_f32(layers, seed)]
+    return [uniq[l % len(uniq)] for l in range(layers)]
+
+
+def make_weights_oracle(layers: int, seed: int):
+    """The same as raw Q8_0H byte buffers, built with the oracle's quantiser: the reference arm's process never
+    loads the CUDA library."""
+    import oracle
+    uniq = [(oracle.q8_quantize_h(w1), oracle.q8_quantize_h(w2)) for w1, w2 in make_weights_f32(layers, seed)]
     return [uniq[l % len(uniq)] for l in range(layers)]
 
 
@@ -184,8 +203,15 @@ def time_node(gpu, stream, make_node, copies: int, iters: int, warmup: int = 3):
     return us / copies, kernels[0], launches // copies
 
 
+# measured DRAM bytes per call (ncu dram__bytes_read.sum + dram__bytes_write.sum, profiles/), where a capture exists
+NCU_TRAFFIC = {
+    "c1_dense_f32_phi2_fc1_m128": 111.4e6,            # profiles/gemm_umma_tf32x3_dense_f32_c1.md
+    "c4_q4_k_phi3_m1": 14.21e6,                       # profiles/q4k_gemv_mma_phi3_decode.md
+}
+
+
 def run_extras(which, gpu, stream):
-    """The other workload configurations (1, 3, 4, 5) on one GPU: time, TFLOP/s or GB/s, roofline fraction."""
+    """The other workloads on one GPU: time, TFLOP/s or GB/s, roofline object each."""
     import ratchet_b200 as rb
     from ratchet_b200 import DType, Tensor
     hbm, hbm_kind = peaks()
@@ -210,9 +236,11 @@ def run_extras(which, gpu, stream):
         peak = tf_burst if bound == "tensor" else hbm
         ach = tfs if bound == "tensor" else gbs
         out.append({"workload": name, "us_per_call": us, "kernel": kernel, "launches_per_call": launches,
-                    "tflops": tfs, "gbs": gbs, "roofline": {"bound": bound, "achieved": ach, "peak": peak,
-                    "unit": "TFLOP/s" if bound == "tensor" else "GB/s", "frac": ach / peak,
-                    "peak_kind": f"of {tf_kind if bound == 'tensor' else hbm_kind}"}, "note": note})
+                    "tflops": tfs, "gbs": gbs, "algorithmic_flops": flops, "algorithmic_bytes": nbytes,
+                    "roofline": {"bound": bound, "achieved": ach, "peak": peak,
+                                 "unit": "TFLOP/s" if bound == "tensor" else "GB/s", "frac": ach / peak,
+                                 "peak_kind": f"of {tf_kind if bound == 'tensor' else hbm_kind}",
+                                 "traffic": NCU_TRAFFIC.get(name)}, "note": note})
 
     def linear_node(w_dev, x_dev, b_dev, epilogue=0):
         return w_dev.gemm(x_dev, b_dev, False, True, True, epilogue=epilogue)
@@ -254,17 +282,80 @@ def run_extras(which, gpu, stream):
     return out
 
 
-def run_sharded(rank, world, gpu, stream, dist, torch, rows_per_batch=2048, iters=10):
-    """BASELINE config 5 on `world` GPUs: A bf16 [4, rows, 2560] replicated, W Q8_0H [10240, 2560] split along N,
-    f16 bias, fused GELU.  Times the local slice alone, slice + NCCL all-gather, and the peer-store epilogue
-    (every rank ends with the full [4*rows, 10240]); device events, max over ranks."""
-    import ratchet_b200 as rb
-    from ratchet_b200 import DType, GpuBuffer, Tensor
+def sharded_operands(rows_per_batch):
+    """Seeded operands of the sharded prefill Linear: W f32 [10240, 2560] ~ N(0, 0.02), f16 bias, bf16 activations."""
     N, K, rows = 10240, 2560, 4 * rows_per_batch
+    w = np.random.default_rng(1105).standard_normal((N, K), dtype=np.float32) * np.float32(0.02)
+    b = (np.random.default_rng(2105).standard_normal(N, dtype=np.float32) * np.float32(0.02)).astype(np.float16)
+    x = np.random.default_rng(105).standard_normal((rows, K), dtype=np.float32)
+    return N, K, rows, w, b, x
+
+
+def sharded_parity(got_bf16_bits, rows_idx, w_q, b16, x_bf16_f32, N, K):
+    """rel-L2 of sampled rows of a gathered bf16 output against the fp64 oracle over the dequantised weights
+    (the oracle is the checker here, outside every timed region)."""
+    import oracle
+    wv = oracle.q8_dequantize_h(w_q, N * K).astype(np.float32).reshape(N, K)
+    truth = oracle.matmul_truth(wv, x_bf16_f32[rows_idx], b16.astype(np.float32), 1, 1, 1, N, len(rows_idx), K, False, True, True, 1)
+    want = oracle.bf16_bits_to_f32(oracle.f64_to_bf16_bits(truth)).reshape(len(rows_idx), N)
+    got = oracle.bf16_bits_to_f32(got_bf16_bits[rows_idx].reshape(-1)).reshape(len(rows_idx), N)
+    return oracle.rel_l2(got, want)
+
+
+def run_sharded(rank, world, gpu, stream, dist, torch, rows_per_batch=2048, iters=10):
+    """The N-sharded bf16 prefill Linear on `world` GPUs: A bf16 [4, rows, 2560] replicated, W Q8_0H [10240, 2560] split
+    along N, f16 bias, fused GELU.  Times the local slice alone, slice + NCCL all-gather, and the peer-store epilogue
+    (every rank ends with the full [4*rows, 10240]); device events, max over ranks.  After the timed regions a sample of
+    rows of every gathered output is compared with the oracle.  With one GPU only the compute leg exists."""
+    import ratchet_b200 as rb
+    from ratchet_b200 import DType, Device, GpuBuffer, Tensor
+    N, K, rows, w32, b16, x32 = sharded_operands(rows_per_batch)
     qz = rb.Quantizer(rb.Quantization.SInt8)
-    w = qz.sint8_quantize(Tensor.from_data(np.random.default_rng(1105).standard_normal((N, K), dtype=np.float32) * np.float32(0.02)), DType.Q8_0H)
-    b = Tensor.from_data(np.random.default_rng(2105).standard_normal(N, dtype=np.float32) * np.float32(0.02), dt=DType.F16)
-    x = Tensor.from_data(np.random.default_rng(105).standard_normal((rows, K), dtype=np.float32), gpu, DType.BF16)
+    w = qz.sint8_quantize(Tensor.from_data(w32), DType.Q8_0H)
+    b = Tensor.from_data(b16)
+    x = Tensor.from_data(x32, gpu, DType.BF16)
+    x_vals = rb.bf16_bits_to_f32(rb.f32_to_bf16_bits(x32)).reshape(rows, K)
+    sample = np.concatenate([np.random.default_rng(5).choice(rows, size=12, replace=False), [0, rows - 1]])
+    lib = rb._lib.load()
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        gpu.sync()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            fn()
+        e1.record(stream)
+        gpu.sync()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        if world > 1:
+            t = torch.tensor([ms], device=f"cuda:{gpu.ordinal}", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms * 1e3  # us
+
+    flops = 2.0 * rows * N * K
+    res = {"workload": f"c5_q8_0_prefill_bf16_4x{rows_per_batch}_n_sharded", "n_gpus": world, "rows": rows,
+           "out_bytes_gathered_per_gpu": rows * N * 2}
+    if world == 1:
+        node = w.to(gpu).gemm(x, b.to(gpu), False, True, True, epilogue=rb.EPILOGUE_GELU_TANH)
+        node.resolve()
+        plan = gpu.plan_for(node.op.desc)
+        opts = rb._lib.rt_launch_opts()
+        opts.flags = rb._lib.RT_LAUNCH_LHS_CONSTANT
+        from ctypes import byref
+        us = timed(lambda: rb._lib.check(lib.rt_matmul_launch_ex(plan, node.op.lhs.ptr, x.ptr, node.op.bias.ptr, node.ptr, None, byref(opts))))
+        got = node.to(Device.CPU).to_numpy().reshape(rows, N)
+        res.update({"compute_only_us": us, "tflops_compute_only": flops / us / 1e6, "kernel": lib.rt_plan_kernel(plan).decode(),
+                    "parity_rel_l2": sharded_parity(got, sample, w.to_numpy(), b16, x_vals, N, K)})
+        return res
 
     def exchange(obj):
         out = [None] * world
@@ -276,40 +367,40 @@ def run_sharded(rank, world, gpu, stream, dist, torch, rows_per_batch=2048, iter
     local = GpuBuffer(gpu, rows * per * 2)
     gathered = GpuBuffer(gpu, rows * N * 2)
     comm = rb.Comm(gpu, rank, world, exchange)
-    lin.bind_outputs(rows, DType.BF16, exchange)
+    out_t = lin.bind_outputs(rows, DType.BF16, exchange)
     node = lin._node(x)
     plan = gpu.plan_for(node.op.desc)
-    lib = rb._lib.load()
+
+    from ctypes import byref
+    const_opts = rb._lib.rt_launch_opts()
+    const_opts.flags = rb._lib.RT_LAUNCH_LHS_CONSTANT
 
     def compute_only():
-        rb._lib.check(lib.rt_matmul_launch(plan, lin.w.ptr, x.ptr, lin.b.ptr, local.ptr, None))
-
-    def timed(fn):
-        for _ in range(3):
-            fn()
-        gpu.sync(); dist.barrier(); torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(iters):
-            fn()
-        e1.record(stream)
-        gpu.sync(); dist.barrier(); torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / iters], device=f"cuda:{gpu.ordinal}", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()) * 1e3  # us
+        rb._lib.check(lib.rt_matmul_launch_ex(plan, lin.w.ptr, x.ptr, lin.b.ptr, local.ptr, None, byref(const_opts)))
 
     us_compute = timed(compute_only)
     us_nccl = timed(lambda: lin.launch_nccl(x, comm, local, gathered))
+    # the NCCL leg gathers [world][rows][N / world]: rank r's column window of row i
+    g = Tensor([world, rows, per], DType.BF16, gpu, gathered).to(Device.CPU).to_numpy()
+    parity_nccl = sharded_parity(np.ascontiguousarray(np.transpose(g, (1, 0, 2))).reshape(rows, N), sample, w.to_numpy(), b16, x_vals, N, K)
     us_peer = timed(lambda: lin.launch_peer(x))
+    gpu.sync()
+    dist.barrier()
+    full = out_t.to(Device.CPU).to_numpy().reshape(rows, N)
+    parity_peer = sharded_parity(full, sample, w.to_numpy(), b16, x_vals, N, K)
+    par = torch.tensor([parity_nccl, parity_peer], device=f"cuda:{gpu.ordinal}", dtype=torch.float64)
+    dist.all_reduce(par, op=dist.ReduceOp.MAX)  # the worst rank's
     dist.barrier()
     lin.close_peers()
     comm.close()
-    flops = 2.0 * rows * N * K
-    return {"workload": f"c5_q8_0_prefill_bf16_4x{rows_per_batch}_n_sharded", "n_gpus": world, "rows": rows,
-            "out_bytes_gathered_per_gpu": rows * N * 2,
-            "compute_only_us": us_compute, "gemm_plus_nccl_all_gather_us": us_nccl, "peer_store_epilogue_us": us_peer,
-            "tflops_compute_only": flops / us_compute / 1e6, "tflops_nccl": flops / us_nccl / 1e6, "tflops_peer": flops / us_peer / 1e6,
-            "kernel": lib.rt_plan_kernel(plan).decode()}
+    link_bytes = rows * N * 2 * (world - 1) / world  # what every GPU has to receive
+    res.update({"compute_only_us": us_compute, "gemm_plus_nccl_all_gather_us": us_nccl, "peer_store_epilogue_us": us_peer,
+                "tflops_compute_only": flops / us_compute / 1e6, "tflops_nccl": flops / us_nccl / 1e6, "tflops_peer": flops / us_peer / 1e6,
+                "link_ingress_bytes_per_gpu": link_bytes, "link_ingress_gbs_peer": link_bytes / us_peer / 1e3,
+                "link_ingress_gbs_nccl": link_bytes / max(us_nccl - us_compute, 1e-3) / 1e3,
+                "parity_rel_l2": float(par[1].item()), "parity_rel_l2_nccl": float(par[0].item()),
+                "kernel": lib.rt_plan_kernel(plan).decode()})
+    return res
 
 
 def cpu_step(weights_raw, x16, layers):
@@ -338,18 +429,27 @@ def time_cpu(weights_raw, x16, budget_s: float, max_layers: int):
     return gbs, layers, dt
 
 
+def base_config(layers):
+    """The `config` object both arms print: the workload, not how an arm runs it."""
+    gemvs = 2 * layers
+    return {"workload": WORKLOAD, "layers": layers, "gemv_per_decode_step": gemvs, "decode_steps_per_step": REPEATS,
+            "shapes": "W Q8_0H [10240,2560] and [2560,10240], x f16, M=1",
+            "l2": f"inputs larger than L2: {gemvs * BYTES_PER_GEMV / 1e6:.0f} MB of distinct weights per decode step vs 126 MB L2"}
+
+
 def run_reference(args, rank):
-    """The reference arm: the restated reference arithmetic on the host cores (rank 0 only)."""
+    """The reference arm: the restated reference arithmetic on the host cores (rank 0 only).  Everything here,
+    the quantiser included, is the oracle's: this process never loads the CUDA library."""
     if rank != 0:
         return
     import oracle
     oracle.use_all_cores()
-    raw = [(t1.to_numpy(), t2.to_numpy()) for t1, t2 in make_weights(args.layers, 102)]
+    raw = make_weights_oracle(args.layers, 102)
     x16 = np.random.default_rng(102).standard_normal(D_MODEL).astype(np.float16)
     t0 = time.perf_counter()
     cpu_step(raw, x16, 1)
     per_layer = time.perf_counter() - t0
-    # a bounded sample of the step: as many of its layers as keep the whole run near two minutes
+    # a bounded sample of the step: as many of one decode step's layers as keep the whole run near two minutes
     layers = int(max(1, min(args.layers, 120.0 / max(args.steps + min(args.warmup, 2), 1) / max(per_layer, 1e-6))))
     for _ in range(max(1, min(args.warmup, 2))):
         cpu_step(raw, x16, layers)
@@ -359,12 +459,13 @@ def run_reference(args, rank):
     dt = time.perf_counter() - t0
     ms = dt / args.steps * 1e3
     gbs = layers * 2 * BYTES_PER_GEMV / (dt / args.steps) / 1e9
-    sample = f"{layers} of {args.layers} layers per step ({2 * layers} GEMVs), C oracle with OpenMP"
+    sample = (f"{layers} of the {args.layers} layers of ONE decode step per timed step ({2 * layers} GEMVs; our arm's step is "
+              f"{REPEATS} decode steps), C oracle with OpenMP")
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers": layers, "note": "reference has no CPU Matmul and its WebGPU backend is unavailable on this box; this is the CPU restatement of its shader arithmetic"},
+        "dtype": "f16", "data": "synthetic", "config": base_config(args.layers),
+        "note": "the reference has no CPU Matmul and its WebGPU backend is unavailable on this box; this is the CPU restatement of its shader arithmetic",
         "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -411,13 +512,13 @@ def main():
             nodes.append(h)
         return h, nodes
 
-    # ---- device-timed leg: buffers bound once, one dispatch per step
+    # ---- device-timed leg: buffers bound once, one dispatch per decode step
     x_dev = Tensor.from_data(x_pin.array, gpu)
     y, nodes = build_graph(x_dev)
     y.resolve()
     kernel_names = sorted({rb._lib.load().rt_plan_kernel(gpu.plan_for(t.op.desc)).decode() for t in nodes})
     exe = Executable(gpu, nodes, use_graph=not args.no_graph)
-    launches_per_step = exe.launches
+    launches_per_decode = exe.launches
 
     def barrier():
         gpu.sync()
@@ -425,26 +526,31 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def device_timed(fn, steps, warmup):
+        """`steps` timed steps of REPEATS calls each, between two events on the launching stream."""
+        for _ in range(warmup * REPEATS):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps * REPEATS):
+            fn()
+        e1.record(stream)
+        barrier()
+        return e0.elapsed_time(e1)
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.6)  # nvidia-smi needs a moment before its first sample
-    for _ in range(max(args.warmup, 3)):
-        exe.dispatch()
-    barrier()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record(stream)
-    for _ in range(args.steps):
-        exe.dispatch()
-    ev1.record(stream)
-    barrier()
-    dev_ms = ev0.elapsed_time(ev1)
+    warmup = max(args.warmup, 3)
+    dev_ms = device_timed(exe.dispatch, args.steps, warmup)
 
-    # ---- end-to-end leg: the public host API, H2D of the input and D2H of the result every step.
+    # ---- end-to-end leg: the public host API, H2D of the input and D2H of the result every decode step.
     # A decode loop keeps its Executable (the reference's models keep their compiled ops) and feeds it:
     def e2e_step():
         x_dev.write(x_pin.array)                              # H2D from pinned memory into the bound input
-        exe.dispatch()                                        # the step
+        exe.dispatch()                                        # the decode step
         y.to(Device.CPU, out=y_pin.array)                     # D2H of the step's result (waits)
 
     # the same step with the lazy graph rebuilt and resolved node by node every time (reported beside it)
@@ -454,20 +560,20 @@ def main():
         out.resolve(sync=False)                               # plan lookup + one launch per node
         out.to(Device.CPU, out=y_pin.array)                   # D2H of the step's result (waits)
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(warmup * REPEATS):
         e2e_step()
     barrier()
     t0 = time.perf_counter()
     ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev2.record(stream)
-    for _ in range(args.steps):
+    for _ in range(args.steps * REPEATS):
         e2e_step()
     ev3.record(stream)
     barrier()
     e2e_ms = ev2.elapsed_time(ev3)                 # device timeline, host gaps included
     e2e_wall_ms = (time.perf_counter() - t0) * 1e3  # the host's view of the same region
     y_e2e = y_pin.array.reshape(-1).copy()
-    lazy_steps = 1 if args.no_lazy else max(3, min(args.steps, 30))
+    lazy_steps = 1 if args.no_lazy else 30
     for _ in range(0 if args.no_lazy else 3):
         lazy_step()
     barrier()
@@ -488,10 +594,40 @@ def main():
     # with the depth (2e-4 after three nodes, 2e-3 after 64); per-node parity is what the tests check
     assert rel <= 2e-2, f"executable and node-by-node results differ: rel-L2 {rel:.3e}"
 
+    # ---- the same GEMVs in the forms a real graph dispatches them in (rank 0, one GPU): one launch per node, and
+    # fc1 -> fc2 pairs (the longest chain of Matmul nodes in the reference's MLPs) as two-node executables
+    forms = None
+    if world == 1 and rank == 0:
+        os.environ["RT_GEMV_CHAIN"] = "0"
+        exe_nodes = Executable(gpu, nodes, use_graph=True)
+        del os.environ["RT_GEMV_CHAIN"]
+        ms_nodes = device_timed(exe_nodes.dispatch, max(2, args.steps // 4), 1)
+        n_nodes_steps = max(2, args.steps // 4) * REPEATS
+        pairs = []
+        for w1, w2 in dev_w:
+            h1 = w1.gemm(x_dev, None, False, True, True)
+            h2 = w2.gemm(h1, None, False, True, True)
+            h2.resolve()
+            pairs.append(Executable(gpu, [h1, h2], use_graph=True))
+
+        def all_pairs():
+            for p in pairs:
+                p.dispatch()
+        ms_pairs = device_timed(all_pairs, max(2, args.steps // 4), 1)
+        peak_hbm, _ = peaks()
+        us_node = ms_nodes * 1e3 / n_nodes_steps / (2 * layers)
+        us_pair = ms_pairs * 1e3 / n_nodes_steps / (2 * layers)
+        forms = {
+            "one_launch_per_node": {"us_per_gemv": us_node, "gbs": BYTES_PER_GEMV / us_node / 1e3, "frac": BYTES_PER_GEMV / us_node / 1e3 / peak_hbm,
+                                    "dispatch": exe_nodes.kernel, "kernels": kernel_names},
+            "two_node_fc1_fc2_executables": {"us_per_gemv": us_pair, "gbs": BYTES_PER_GEMV / us_pair / 1e3, "frac": BYTES_PER_GEMV / us_pair / 1e3 / peak_hbm,
+                                             "dispatch": pairs[0].kernel, "launches_per_pair": pairs[0].launches},
+        }
+        del exe_nodes, pairs
+
     sharded = None
-    if world > 1 and not args.no_sharded:
-        res = [run_sharded(rank, world, gpu, stream, dist, torch, rows_per_batch=r) for r in (2048, 8192)]
-        sharded = res
+    if not args.no_sharded and (world > 1 or args.extras != "none"):
+        sharded = [run_sharded(rank, world, gpu, stream, dist, torch, rows_per_batch=r) for r in ((2048, 8192) if world > 1 else (2048,))]
     if world > 1:
         t = torch.tensor([dev_ms, e2e_ms, e2e_wall_ms], device=f"cuda:{local_rank}", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -500,48 +636,49 @@ def main():
     if rank == 0:
         peak, peak_kind = peaks()
         gemvs = 2 * layers
-        step_bytes = gemvs * BYTES_PER_GEMV
+        decode_bytes = gemvs * BYTES_PER_GEMV
         ms_per_step = dev_ms / args.steps
-        value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
-        launch_us = ms_per_step * 1e3 / gemvs
+        ms_per_decode = ms_per_step / REPEATS
+        value = world * decode_bytes / (ms_per_decode * 1e-3) / 1e9
+        launch_us = ms_per_decode * 1e3 / gemvs
         achieved = BYTES_PER_GEMV / (launch_us * 1e-6) / 1e9
         e2e_ms_step = max(e2e_ms, e2e_wall_ms) / args.steps
+        gemv_per_launch = gemvs // max(launches_per_decode, 1)
+        config = base_config(layers)
+        run_info = {"dispatch": exe.kernel, "kernels": kernel_names,
+                    "parallelism": "replicas only (independent decode streams)" if world > 1 else "single GPU"}
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "layers": layers, "gemv_per_step": gemvs,
-                       "shapes": "W Q8_0H [10240,2560] and [2560,10240], x f16, M=1",
-                       "l2": f"inputs larger than L2: {gemvs * BYTES_PER_GEMV / 1e6:.0f} MB of distinct weights per step vs 126 MB L2",
-                       "dispatch": exe.kernel,
-                       "parallelism": "replicas only (independent decode streams)" if world > 1 else "single GPU",
-                       "kernels": kernel_names},
+            "dtype": "f16", "data": "synthetic", "config": config, "run": run_info,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": f"of {peak_kind}", "kernel": exe.kernel.split("_h_")[0] if exe.kernel.startswith("q8_gemv_chain") else kernel_names[0],
-                         "gemv_per_launch": gemvs // max(launches_per_step, 1), "launch_us": launch_us * (gemvs // max(launches_per_step, 1)),
+                         "peak_kind": f"of {peak_kind}", "kernel": exe.kernel.split("_h_")[0] if exe.kernel.startswith("q8_gemv_") else kernel_names[0],
+                         "gemv_per_launch": gemv_per_launch, "launch_us": launch_us * gemv_per_launch,
                          "us_per_gemv": launch_us, "bytes_per_gemv": BYTES_PER_GEMV,
-                         "bytes_per_launch": BYTES_PER_GEMV * (gemvs // max(launches_per_step, 1)),
-                         "traffic": NCU_TRAFFIC_PER_GEMV * (gemvs // max(launches_per_step, 1)), "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, "
+                         "bytes_per_launch": BYTES_PER_GEMV * gemv_per_launch,
+                         "traffic": NCU_TRAFFIC_PER_GEMV * gemv_per_launch, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, "
                          "mean of the two shapes, from the captures summarised in profiles/q8_gemv_chain_phi2_decode.md and profiles/q8_gemv_umma_phi2_decode.md"},
-            "e2e": {"value": world * step_bytes / (e2e_ms_step * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms_step,
-                    "h2d_bytes_per_step": int(x_pin.nbytes), "d2h_bytes_per_step": int(y_pin.nbytes),
-                    "api": "Tensor.write(x) + Executable.dispatch() + Tensor.to(CPU)",
-                    "lazy_graph_resolve": {"value": world * step_bytes / (lazy_ms_step * 1e-3) / 1e9, "unit": UNIT,
-                                           "ms_per_step": lazy_ms_step, "steps": lazy_steps,
+            "e2e": {"value": world * decode_bytes * REPEATS / (e2e_ms_step * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms_step,
+                    "h2d_bytes_per_step": int(x_pin.nbytes) * REPEATS, "d2h_bytes_per_step": int(y_pin.nbytes) * REPEATS,
+                    "api": "per decode step: Tensor.write(x) + Executable.dispatch() + Tensor.to(CPU)",
+                    "lazy_graph_resolve": {"value": world * decode_bytes / (lazy_ms_step * 1e-3) / 1e9, "unit": UNIT,
+                                           "ms_per_decode_step": lazy_ms_step, "decode_steps": lazy_steps,
                                            "api": "Tensor.from_data(x) + 64 x gemm() + resolve() + to(CPU), one launch per node"}},
-            "gpu_launches": args.steps * launches_per_step,
+            "gpu_launches": args.steps * REPEATS * launches_per_decode,
             "clocks": clocks,
         }
+        if forms is not None:
+            line["dispatch_forms"] = forms
         if world == 1 and not args.no_cpu_baseline:
             import oracle
             oracle.use_all_cores()
             raw = [(a.to_numpy(), b.to_numpy()) for a, b in host_w]
             gbs, l_used, dt = time_cpu(raw, x_pin.array.reshape(-1).copy(), budget_s=15.0, max_layers=layers)
             line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
-                                    "sample": f"{l_used} of {layers} layers ({2 * l_used} GEMVs) in {dt:.2f} s, C oracle with OpenMP"}
+                                    "sample": f"{l_used} of {layers} layers of one decode step ({2 * l_used} GEMVs) in {dt:.2f} s, C oracle with OpenMP"}
         if sharded is not None:
             line["sharded"] = sharded
-        if args.extras and world == 1:
+        if args.extras != "none" and world == 1:
             which = {"c1", "c3", "c4", "c5", "c5long"} if args.extras == "all" else set(args.extras.split(","))
             line["extras"] = run_extras(which, gpu, stream)
         print(json.dumps(line), flush=True)

@@ -114,6 +114,9 @@ const char *rt_last_error(void);
 const char *rt_status_name(rt_status s);
 /* "ratchet_b200 <semver> sm_100a"; lets a binding check what it loaded. */
 const char *rt_version(void);
+/* sizeof / offsetof of the public structs above and below, in the order the implementation
+ * documents (api.cu), so that a binding can check its mirror of them; returns the entry count. */
+int32_t rt_abi_layout(uint64_t *out, int32_t n);
 
 /* ------------------------------------------------------------------ dtypes and layouts (host) */
 
@@ -169,7 +172,10 @@ int32_t rt_device_sm_count(rt_device *dev);
 int32_t rt_device_ordinal(rt_device *dev);
 
 /* GPUBuffer::from_bytes / BufferPool allocation (storage/gpu_buffer.rs:46-61,
- * gpu/pools/buffer_pool.rs:82-95): sizes are rounded up to 4 B, minimum 16 B. */
+ * gpu/pools/buffer_pool.rs:82-95): sizes are rounded up to 4 B, minimum 16 B.  A freed block
+ * goes back to the device's pool and may be handed out again at once: that is safe for work
+ * queued on the device's own stream (it runs in order); work on other streams that still uses
+ * the block must have finished before rt_buffer_free. */
 rt_status rt_buffer_alloc(rt_device *dev, uint64_t nbytes, rt_buffer **buf);
 rt_status rt_buffer_free(rt_buffer *buf);
 void *rt_buffer_ptr(rt_buffer *buf);
@@ -187,10 +193,19 @@ rt_status rt_host_free(void *ptr);
 
 /* MetaOperation::compile for Matmul (op.rs:304-362, ops/matmul.rs:480-647): validates the
  * node, routes GEMV vs GEMM (ops/matmul.rs:540-592), picks the kernel and its launch shape
- * and allocates whatever scratch the kernel needs.  Plans are immutable and may be launched
- * any number of times; creating plans is thread-safe. */
+ * and allocates whatever scratch the kernel needs.  Equal descriptions on one device share one
+ * plan (the role of the KernelKey lookup, ops/matmul.rs:485-524, op.rs:169-196): the device keeps
+ * a cache, the call is thread-safe, and rt_plan_destroy only gives the caller's hold back.
+ * A plan may be launched any number of times, with these limits: it owns ONE scratch area
+ * (dequantised weights, transposed or padded operands, the f32 pre-split, partial sums), so only
+ * one launch of a plan may be in flight at a time unless its launches are ordered on one stream;
+ * two streams, or two graphs replayed concurrently, that launch the same plan race on it. */
 rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **plan);
 rt_status rt_plan_destroy(rt_plan *plan);
+/* Drops the dequantised copies a plan keeps of weights launched with RT_LAUNCH_LHS_CONSTANT (see
+ * there).  rt_buffer_free does this by itself for buffers of this library; call it before reusing
+ * the memory of a weight that came from another allocator. */
+rt_status rt_plan_forget_weights(rt_plan *plan);
 /* GEMMSpec of the planned node. */
 rt_status rt_plan_spec(const rt_plan *plan, rt_gemm_spec *spec);
 /* Name of the kernel the plan launches (the role of KernelKey, ops/matmul.rs:485-524). */
@@ -209,7 +224,12 @@ rt_status rt_matmul_launch(rt_plan *plan, const void *lhs, const void *rhs, cons
  * bytes (a weight uploaded earlier: the leaf tensors of the reference's graph, tensor.rs:589-599).
  * A kernel may then request the weights before it waits for its stream predecessor (programmatic
  * dependent launch), which overlaps one layer's weight streaming with the previous layer's tail.
- * Never set it for an lhs that an earlier node of the same stream produces (attention scores). */
+ * A tensor-core GEMM over block-format weights also keeps the weight's dequantised f16 copy with
+ * the plan, keyed by the lhs pointer (2 bytes per weight of device memory, allocated at the first
+ * launch with that weight: make that launch outside any stream capture): later launches skip the
+ * dequantising pass.  The copy is filled on the stream of that first launch; launches on other
+ * streams must be ordered after it.  RT_KEEP_WEIGHTS=0 in the environment turns this off.
+ * Never set the flag for an lhs that an earlier node of the same stream produces (attention scores). */
 #define RT_LAUNCH_LHS_CONSTANT 1u
 /* n_out > 0 places the result somewhere else than `out`: element (r, s) of the node's [R][S]
  * output goes to outs[d][r*out_ld + out_col + s] for every d < n_out.  This is the N-sharded
@@ -244,9 +264,10 @@ typedef struct rt_dispatch {
  * compute pass and submits once).  With `use_graph` != 0 the list is captured once into a CUDA
  * graph at creation (on a private stream; capturing executes nothing) and each dispatch is one
  * graph launch.  A list of two or more single-vector Q8_0H GEMVs whose weights are all flagged
- * RT_LAUNCH_LHS_CONSTANT becomes ONE persistent kernel instead (grid barriers between the nodes,
- * weights of later nodes streamed while earlier ones compute; same products as node-by-node
- * dispatch, f32 sums in another order);
+ * RT_LAUNCH_LHS_CONSTANT, each reading its predecessor's output, becomes ONE persistent kernel
+ * instead (rows are handed from node to node as tagged words that the readers poll; weights of
+ * later nodes are streamed while earlier ones compute; same products as node-by-node dispatch,
+ * f32 sums in another order);
  * only one dispatch of such an executable may be in flight at a time.  Plans and buffers must
  * outlive the executable. */
 rt_status rt_executable_create(rt_device *dev, const rt_dispatch *nodes, int32_t n_nodes, int32_t use_graph, rt_executable **exe);

@@ -146,6 +146,8 @@ def load() -> ctypes.CDLL:
         "rt_host_free": (c_int32, [V]),
         "rt_matmul_plan": (c_int32, [V, POINTER(rt_matmul_desc), POINTER(V)]),
         "rt_plan_destroy": (c_int32, [V]),
+        "rt_plan_forget_weights": (c_int32, [V]),
+        "rt_abi_layout": (c_int32, [POINTER(c_uint64), c_int32]),
         "rt_plan_spec": (c_int32, [V, POINTER(rt_gemm_spec)]),
         "rt_plan_kernel": (c_char_p, [V]),
         "rt_plan_launches": (c_int32, [V]),

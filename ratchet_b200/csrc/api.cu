@@ -4,6 +4,7 @@
 // executable.rs:25-54 of the reference).
 #include <cuda_runtime.h>
 
+#include <cstddef>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -39,6 +40,12 @@ struct rt_device {
     std::mutex pool_mu;
     std::unordered_map<uint64_t, std::vector<void *>> pool; // size class -> free blocks
     uint64_t pooled_bytes = 0;
+    // compiled-op cache: one plan per distinct node description (the role of the reference's KernelKey lookup,
+    // crates/ratchet-core/src/ops/matmul.rs:485-524 and op.rs:169-196)
+    std::mutex plan_mu;
+    std::unordered_map<std::string, rt_plan *> plans;
+    std::mutex kept_mu;
+    std::unordered_map<const void *, int> kept_ptrs; // weight pointers some plan keeps a dequantised copy of
 };
 
 static inline uint64_t size_class(uint64_t n) {
@@ -84,12 +91,40 @@ struct rt_plan {
     uint64_t scratch_bytes = 0;
     void *act_scratch = nullptr; // bf16 activations cast to f16 (quantised weights only)
     uint64_t act_scratch_bytes = 0;
+    int refs = 1;                // holders: the device's cache and every rt_matmul_plan call that returned this plan
+    std::string key;             // its entry in the device's cache
+    // Dequantised copies of weights the caller flagged RT_LAUNCH_LHS_CONSTANT, by weight pointer: the pre-pass then
+    // runs once per weight instead of once per launch, and plans shared by many same-shaped layers do not share scratch.
+    std::mutex weights_mu;
+    std::unordered_map<const void *, void *> kept_weights;
     ~rt_plan() {
-        if (scratch || act_scratch) cudaSetDevice(dev->ordinal);
+        if (scratch || act_scratch || !kept_weights.empty()) cudaSetDevice(dev->ordinal);
         if (scratch) cudaFree(scratch);
         if (act_scratch) cudaFree(act_scratch);
+        for (auto &kv : kept_weights) cudaFree(kv.second);
     }
 };
+
+// Everything of a node description that routing looks at, field by field (the struct has padding bytes), plus the
+// debugging switches that change routing.
+static std::string plan_key(const rt_matmul_desc &d) {
+    std::string k;
+    auto put = [&k](long long v) { k.append(reinterpret_cast<const char *>(&v), sizeof(v)); };
+    auto put_shape = [&](const rt_shape &s) {
+        put(s.rank);
+        for (int i = 0; i < s.rank && i < RT_MAX_RANK; i++) put(s.dims[i]);
+    };
+    put(d.lhs_dt); put(d.rhs_dt); put(d.has_bias ? d.bias_dt : -1);
+    put_shape(d.lhs_shape); put_shape(d.rhs_shape);
+    if (d.has_bias) put_shape(d.bias_shape);
+    put(d.has_bias != 0); put(d.trans_lhs != 0); put(d.trans_rhs != 0); put(d.trans_out != 0); put(d.epilogue);
+    for (const char *name : {"RT_FORCE_KERNEL", "RT_GEMV_UMMA", "RT_TF32_BN", "RT_TF32_PRESPLIT", "RT_Q4K_WALK_FROM", "RT_KEEP_WEIGHTS"}) {
+        const char *v = getenv(name);
+        k += '|';
+        if (v) k += v;
+    }
+    return k;
+}
 
 struct rt_executable {
     rt_device *dev = nullptr;
@@ -256,6 +291,9 @@ rt_status rt_device_destroy(rt_device *dev) {
     if (!dev) return RT_OK;
     cudaSetDevice(dev->ordinal);
     if (dev->stream) cudaStreamSynchronize(dev->stream);
+    for (auto &kv : dev->plans)
+        if (--kv.second->refs <= 0) delete kv.second;
+    dev->plans.clear();
     for (auto &kv : dev->pool)
         for (void *p : kv.second) cudaFree(p);
     if (dev->stream) cudaStreamDestroy(dev->stream);
@@ -342,6 +380,27 @@ rt_status rt_buffer_free(rt_buffer *buf) {
     if (!buf) return RT_OK;
     rt_device *dev = buf->dev;
     {
+        // a weight that goes away takes the dequantised copies plans keep of it along: the block may come back
+        // from the pool holding another tensor
+        bool kept = false;
+        {
+            std::lock_guard<std::mutex> lk(dev->kept_mu);
+            kept = dev->kept_ptrs.erase(buf->ptr) > 0;
+        }
+        if (kept) {
+            cudaSetDevice(dev->ordinal);
+            std::lock_guard<std::mutex> lk(dev->plan_mu);
+            for (auto &kv : dev->plans) {
+                std::lock_guard<std::mutex> wl(kv.second->weights_mu);
+                auto it = kv.second->kept_weights.find(buf->ptr);
+                if (it != kv.second->kept_weights.end()) {
+                    cudaFree(it->second);
+                    kv.second->kept_weights.erase(it);
+                }
+            }
+        }
+    }
+    {
         std::lock_guard<std::mutex> lk(dev->pool_mu);
         dev->pool[buf->klass].push_back(buf->ptr);
         dev->pooled_bytes += buf->klass;
@@ -393,6 +452,12 @@ static bool chain_enabled() {
 
 // RT_FORCE_KERNEL=simt keeps every node on the CUDA-core kernels (a debugging switch in the
 // spirit of the reference's RATCHET_* variables, gpu/device.rs:92-99).
+// RT_KEEP_WEIGHTS=0: dequantise on every launch even for weights flagged constant (A/B timing, memory-tight callers).
+static bool keep_weights_enabled() {
+    const char *v = getenv("RT_KEEP_WEIGHTS");
+    return !(v && v[0] == '0');
+}
+
 static bool force_simt() {
     const char *v = getenv("RT_FORCE_KERNEL");
     return v && std::string(v) == "simt";
@@ -428,8 +493,32 @@ static bool umma_eligible(const rt_matmul_desc &d, const Spec &s) {
     return true;
 }
 
+static rt_status build_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **plan);
+
 rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **plan) {
     if (!dev || !desc || !plan) return fail(RT_ERR_ARG, "rt_matmul_plan: null argument");
+    if (desc->lhs_shape.rank < 0 || desc->lhs_shape.rank > RT_MAX_RANK || desc->rhs_shape.rank < 0 || desc->rhs_shape.rank > RT_MAX_RANK ||
+        (desc->has_bias && (desc->bias_shape.rank < 0 || desc->bias_shape.rank > RT_MAX_RANK)))
+        return fail(RT_ERR_ARG, "rank out of range");
+    const std::string key = plan_key(*desc);
+    std::lock_guard<std::mutex> lk(dev->plan_mu); // one plan is built at a time per device: equal descriptions share it
+    auto it = dev->plans.find(key);
+    if (it != dev->plans.end()) {
+        it->second->refs++;
+        *plan = it->second;
+        return RT_OK;
+    }
+    rt_plan *pl = nullptr;
+    rt_status st = build_plan(dev, desc, &pl);
+    if (st != RT_OK) return st;
+    pl->key = key;
+    pl->refs = 2; // the cache and the caller
+    dev->plans.emplace(key, pl);
+    *plan = pl;
+    return RT_OK;
+}
+
+static rt_status build_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **plan) {
     rt_plan *pl = new (std::nothrow) rt_plan();
     if (!pl) return fail(RT_ERR_NOMEM, "out of host memory");
     Status st = resolve_spec(*desc, &pl->spec);
@@ -630,9 +719,45 @@ rt_status rt_matmul_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan **p
     return RT_OK;
 }
 
+// Gives the caller's hold on the plan back; the device's cache keeps its own until rt_device_destroy.
 rt_status rt_plan_destroy(rt_plan *plan) {
-    delete plan;
+    if (!plan) return RT_OK;
+    rt_device *dev = plan->dev;
+    std::lock_guard<std::mutex> lk(dev->plan_mu);
+    if (--plan->refs <= 0) {
+        dev->plans.erase(plan->key);
+        delete plan;
+    }
     return RT_OK;
+}
+
+rt_status rt_plan_forget_weights(rt_plan *plan) {
+    if (!plan) return fail(RT_ERR_ARG, "rt_plan_forget_weights: null plan");
+    CUDA_TRY(cudaSetDevice(plan->dev->ordinal));
+    std::lock_guard<std::mutex> lk(plan->weights_mu);
+    for (auto &kv : plan->kept_weights) cudaFree(kv.second);
+    plan->kept_weights.clear();
+    return RT_OK;
+}
+
+// sizeof / offsetof of the public structs, for bindings to check their mirrors against: the entries are
+// {sizeof(rt_shape), offsetof dims, sizeof(rt_segment), sizeof(rt_matmul_desc), offsetof lhs_shape, rhs_shape, bias_shape,
+//  has_bias, epilogue, sizeof(rt_gemm_spec), offsetof out_dt, lhs_stack, dim_inner, is_gemv, sizeof(rt_launch_opts), offsetof
+//  outs, out_ld, out_col, sizeof(rt_dispatch), offsetof opts, sizeof(rt_gguf_value), offsetof str,
+//  sizeof(rt_gguf_tensor_info), offsetof shape, nbytes}
+int32_t rt_abi_layout(uint64_t *out, int32_t n) {
+    const uint64_t v[] = {
+        sizeof(rt_shape), offsetof(rt_shape, dims), sizeof(rt_segment),
+        sizeof(rt_matmul_desc), offsetof(rt_matmul_desc, lhs_shape), offsetof(rt_matmul_desc, rhs_shape), offsetof(rt_matmul_desc, bias_shape),
+        offsetof(rt_matmul_desc, has_bias), offsetof(rt_matmul_desc, epilogue),
+        sizeof(rt_gemm_spec), offsetof(rt_gemm_spec, out_dt), offsetof(rt_gemm_spec, lhs_stack), offsetof(rt_gemm_spec, dim_inner), offsetof(rt_gemm_spec, is_gemv),
+        sizeof(rt_launch_opts), offsetof(rt_launch_opts, outs), offsetof(rt_launch_opts, out_ld), offsetof(rt_launch_opts, out_col),
+        sizeof(rt_dispatch), offsetof(rt_dispatch, opts),
+        sizeof(rt_gguf_value), offsetof(rt_gguf_value, str),
+        sizeof(rt_gguf_tensor_info), offsetof(rt_gguf_tensor_info, shape), offsetof(rt_gguf_tensor_info, nbytes)};
+    const int32_t count = (int32_t)(sizeof(v) / sizeof(v[0]));
+    for (int32_t i = 0; i < count && i < n; i++) out[i] = v[i];
+    return count;
 }
 
 rt_status rt_plan_spec(const rt_plan *plan, rt_gemm_spec *spec) {
@@ -682,6 +807,9 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
     cudaError_t e = cudaSuccess;
     switch (plan->kernel) {
     case PK_Q8_GEMV_MMA:
+        // the kernel fetches weight rows with bulk copies and activations with 16-byte loads
+        if ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) % 16 != 0)
+            return fail(RT_ERR_ARG, "rt_matmul_launch: lhs and rhs must be 16-byte aligned");
         e = launch_q8_gemv_mma(p, s.desc.lhs_dt == RT_Q8_0F, plan->nv, plan->split, (flags & RT_LAUNCH_LHS_CONSTANT) != 0, st);
         for (int done = plan->nv; e == cudaSuccess && done < plan->nv + plan->nv2; done += 8) {
             MatmulParams p2 = p; // vectors done.. : rhs rows and (trans_out) output rows of the same problem
@@ -733,10 +861,39 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
             if (e != cudaSuccess) break;
             w = plan->scratch;
         } else if (plan->scratch) {
-            e = launch_dequant(s.desc.lhs_dt, (long long)(s.lhs_stack * s.M * s.K), lhs, p.lhs_scales, plan->scratch, RT_F16,
-                               plan->dev->sm_count, st);
-            if (e != cudaSuccess) break;
-            w = plan->scratch;
+            // A weight flagged constant is dequantised once and its f16 copy kept with the plan (the first launch with a
+            // new weight allocates: make it outside any stream capture); any other lhs goes through the plan's own scratch
+            // on every launch.
+            void *dst = plan->scratch;
+            bool have = false;
+            if ((flags & RT_LAUNCH_LHS_CONSTANT) && keep_weights_enabled()) {
+                std::lock_guard<std::mutex> lk(plan->weights_mu);
+                auto it = plan->kept_weights.find(lhs);
+                if (it != plan->kept_weights.end()) {
+                    dst = it->second;
+                    have = true;
+                } else {
+                    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+                    void *kept = nullptr;
+                    if (cudaStreamIsCapturing(st, &cs) == cudaSuccess && cs == cudaStreamCaptureStatusNone &&
+                        cudaMalloc(&kept, plan->scratch_bytes) == cudaSuccess) {
+                        plan->kept_weights.emplace(lhs, kept);
+                        {
+                            std::lock_guard<std::mutex> dl(plan->dev->kept_mu);
+                            plan->dev->kept_ptrs[lhs]++;
+                        }
+                        dst = kept;
+                    } else {
+                        cudaGetLastError(); // no room, or capturing: this launch uses the plan's scratch
+                    }
+                }
+            }
+            if (!have) {
+                e = launch_dequant(s.desc.lhs_dt, (long long)(s.lhs_stack * s.M * s.K), lhs, p.lhs_scales, dst, RT_F16,
+                                   plan->dev->sm_count, st);
+                if (e != cudaSuccess) break;
+            }
+            w = dst;
             w_dt = RT_F16;
         }
         const void *x = rhs;

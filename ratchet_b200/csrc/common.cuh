@@ -91,6 +91,16 @@ __device__ __forceinline__ void codes4_to_half2(uint32_t w, __half2 &lo, __half2
     hi = __hsub2(*reinterpret_cast<__half2 *>(&b), bias);
 }
 
+// Named barrier `id` over `nthreads` threads that also returns the OR of every thread's `pred`: all of them
+// take the same decision (to leave a loop after a bounded wait ran out, say), so none is left behind at the
+// next barrier.
+__device__ __forceinline__ bool bar_red_or(int id, int nthreads, bool pred) {
+    int r;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.s32 p, %3, 0;\n\tbarrier.cta.red.or.pred q, %1, %2, p;\n\tselp.s32 %0, 1, 0, q;\n\t}\n"
+                 : "=r"(r) : "r"(id), "r"(nthreads), "r"((int)pred) : "memory");
+    return r != 0;
+}
+
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 
 } // namespace rt

@@ -270,18 +270,20 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(prm.outs[d]) % 16 == 0);
             pair_ok = pair_ok && (reinterpret_cast<uintptr_t>(prm.outs[d]) % 4 == 0);
         }
+        bool gave_up = false; // a wait of this warp ran out: it skips its work but stays in step with the other warps
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
             const int r0 = (rem % prm.tiles_r) * BM, s0 = (rem / prm.tiles_r) * BN;
-            if (*abort_flag) break;
-            // bias values of this tile's columns, shared by the four epilogue warps
-            asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+            // The eight warps leave together: the barrier hands every thread the OR of what each of them saw, so
+            // none is left waiting at a barrier for a warp that has gone.
+            if (bar_red_or(1, EPI_WARPS * 32, gave_up || *abort_flag != 0)) break;
+            // bias values of this tile's columns, shared by the epilogue warps
             if (prm.bias_mode == BIAS_PER_N) {
                 for (int j = ep_tid; j < BN; j += EPI_WARPS * 32)
                     bias_s[j] = (s0 + j < prm.S) ? load_bias(prm.bias, prm.bias_dt, s0 + j) : 0.f;
             }
             asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
-            if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, 4)) break;
+            if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, 4)) { gave_up = true; continue; }
             tc_fence_after();
             const int row = r0 + q * 32 + lane;
             const bool has_bias = prm.bias_mode != BIAS_NONE;
@@ -421,12 +423,11 @@ bool make_map(CUtensorMap *map, const void *base, rt_dtype dt, long long K, long
 template <int BN, typename OutT>
 cudaError_t launch_bn(const CUtensorMap &mp, const CUtensorMap &mq, UmmaParams prm, int sm_count, cudaStream_t stream) {
     using C = Cfg<BN>;
-    static bool configured = false;
+    static SmemAttr smem_attr;
     auto kernel = gemm_umma_kernel<BN, OutT>;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    {
+        cudaError_t e = smem_attr.ensure(kernel, C::SMEM_BYTES);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     prm.tiles_r = (prm.R + BM - 1) / BM;
     prm.tiles_s = (prm.S + BN - 1) / BN;

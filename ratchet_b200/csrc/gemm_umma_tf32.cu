@@ -387,11 +387,10 @@ bool make_map_f32(CUtensorMap *map, const void *base, long long K, long long row
 template <int BN, bool P_PRE>
 cudaError_t launch_t(const CUtensorMap &mp, const CUtensorMap &mplo, const CUtensorMap &mq, Tf32Params prm, int sm_count, cudaStream_t stream) {
     auto kernel = gemm_umma_tf32x3_kernel<BN, P_PRE>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TileCfg<BN>::SMEM_BYTES);
+    static SmemAttr smem_attr;
+    {
+        cudaError_t e = smem_attr.ensure(kernel, TileCfg<BN>::SMEM_BYTES);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     prm.tiles_s = (prm.S + BN - 1) / BN;
     const long long total = (long long)prm.tiles_r * prm.tiles_s * prm.stacks;

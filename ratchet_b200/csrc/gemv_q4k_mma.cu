@@ -366,12 +366,11 @@ cudaError_t launch_g(const MatmulParams &p, int nv, int split, int gpc, int nbuf
     const bool walk = nbuf > 1;
     auto kernel = walk ? (split == 1 ? q4k_gemv_kernel<NVG, false, WARPS_WALK, 2> : q4k_gemv_kernel<NVG, true, WARPS_WALK, 1>)
                        : (split == 1 ? q4k_gemv_kernel<NVG, false, WARPS_ONCE, 1> : q4k_gemv_kernel<NVG, true, WARPS_ONCE, 1>);
-    static size_t configured[4] = {0, 0, 0, 0};
+    static SmemAttr smem_attr[4];
     const int slot = (walk ? 2 : 0) + (split != 1 ? 1 : 0);
-    if (smem > 48 * 1024 && configured[slot] < smem) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (smem > 48 * 1024) {
+        cudaError_t e = smem_attr[slot].ensure(kernel, smem);
         if (e != cudaSuccess) return e;
-        configured[slot] = smem;
     }
     const int groups = (p.M + ROWS - 1) / ROWS;
     cudaLaunchConfig_t cfg = {};

@@ -112,6 +112,8 @@ struct ChainParams {
     unsigned int *xbuf;          // every node's output rows as {f16 value, 16-bit tag} words
     unsigned long long *pbuf;    // K-sliced nodes: the slices' row sums as {f32 sum, 32-bit tag} words
     unsigned int tag;            // this dispatch's tag: 1..65535, never the previous dispatch's
+    unsigned int publish_tag;    // the tag written with the rows: `tag`, except under the bounded-wait test hook
+    unsigned long long poll_limit; // cycles the readers wait for rows and K-slice sums
     int pace;            // least number of cycles between two chunk copies of the producer (0: none)
     int skip_tempty;     // no node has more stages than tensor-memory regions: a region is only reused by a later node
 };
@@ -277,8 +279,8 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
         const int row_local = q * 32 + lane;  // this thread's tensor-memory lane
         int tg = 0, sbuf = 0, prev_x_off = 0, slot = 0;
         uint32_t sphase = 0, phase = 0;
-        bool ok = true;
-        for (int l = 0; l < cp.n_nodes && ok; l++) {
+        bool gave_up = false; // a wait of this warp ran out: it skips work but stays in step with the others up to the next barrier
+        for (int l = 0; l < cp.n_nodes; l++) {
             const ChainNodeInfo &nd = info[l & 1];
             const int split = nd.split, unit = (int)blockIdx.x / split, rank = (int)blockIdx.x % split;
             const int row_begin = unit * nd.rb;
@@ -360,7 +362,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                                     break;
                                 }
                                 if (*abort_flag) break;
-                                if (wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
+                                if (wait_clock() - t0 > cp.poll_limit) {
                                     *abort_flag = 1;
                                     atomicCAS(&g_gemv_chain_error, 0, 8);
                                     break;
@@ -399,8 +401,9 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 }
                 // the MMAs read the tiles through the async proxy
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                asm volatile("bar.sync 1, 256;" ::: "memory"); // xs visible to all epilogue warps
-                if (*abort_flag) break;
+                // xs visible to all epilogue warps; and the warps leave together (the barrier returns the OR of what every
+                // thread saw), so that none waits at a later barrier for one that has gone
+                if (bar_red_or(1, 256, gave_up || *abort_flag != 0)) break;
                 if (lane == 0) mbar_arrive(bar_x);
                 if (warp == 2 && l + 1 < cp.n_nodes) reinterpret_cast<int *>(info + ((l + 1) & 1))[lane] = next_word;
                 if (et < 4) badmask[((l + 1) & 1) * 4 + et] = 0u; // the next node's mask and flag (node l-1's readers are two barriers back)
@@ -408,8 +411,8 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
 
                 const uint8_t *scales_n = scales_s + (size_t)sbuf * cp.scale_buf_bytes;
                 const int srow = ks / 16; // bytes per row of the node's scales
-                if (!mbar_wait(bar_sfull + 8 * sbuf, sphase, abort_flag, 10)) break;
-                for (int s = 0; s < nstages; s++) {
+                if (!mbar_wait(bar_sfull + 8 * sbuf, sphase, abort_flag, 10)) gave_up = true;
+                for (int s = 0; s < nstages && !gave_up; s++) {
                     // the stage's weight scales and activation scales do not wait for the MMAs
                     __half2 d2[MAX_TILES];
                     float2 xv[MAX_TILES];
@@ -418,7 +421,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                         d2[t] = *reinterpret_cast<const __half2 *>(scales_n + sc_off[t] + s * S * 8);
                         xv[t] = *reinterpret_cast<const float2 *>(xs + xs_off[t] + s * S * 4);
                     }
-                    if (!mbar_wait(bar_done + 8 * slot, phase, abort_flag, 6)) { ok = false; break; }
+                    if (!mbar_wait(bar_done + 8 * slot, phase, abort_flag, 6)) { gave_up = true; break; }
                     tc_fence_after();
                     const uint32_t t0 = tmem_base + tg * TG_COLS + ((uint32_t)(q * 32) << 16) + half * 2 * cstride;
                     const int tile_cols = 4 * cstride + (cstride == 8 ? 8 : 0);
@@ -464,7 +467,6 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                     if (++tg == TGROUPS) tg = 0;
                     if (++slot == cp.ring) { slot = 0; phase ^= 1; }
                 }
-                if (!ok) break;
                 // the scales buffer is free for the node after the next one
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_sempty + 8 * sbuf);
@@ -473,7 +475,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
 #pragma unroll
                 for (int t = 0; t < MAX_TILES; t++)
                     if (mine[t]) part[half * (MAX_TILES * 128) + 128 * t + row_local] = acc[t];
-                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (bar_red_or(1, 256, gave_up || *abort_flag != 0)) break;
                 const bool my_rows = et < rows_here; // from here on thread et of the first four warps owns row et
                 float sum = 0.f;
                 if (my_rows) {
@@ -517,7 +519,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                                 asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w3) : "l"(pw + (size_t)3 * nd.M) : "memory");
                                 if ((unsigned int)(w1 >> 32) == cp.tag && (unsigned int)(w2 >> 32) == cp.tag && (unsigned int)(w3 >> 32) == cp.tag) break;
                                 if (*abort_flag) break;
-                                if (wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
+                                if (wait_clock() - t0 > cp.poll_limit) {
                                     *abort_flag = 1;
                                     atomicCAS(&g_gemv_chain_error, 0, 7);
                                     break;
@@ -536,7 +538,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                                         break;
                                     }
                                     if (*abort_flag) break;
-                                    if (wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
+                                    if (wait_clock() - t0 > cp.poll_limit) {
                                         *abort_flag = 1;
                                         atomicCAS(&g_gemv_chain_error, 0, 7);
                                         break;
@@ -553,16 +555,14 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                     if (has_bias) bias = load_bias(nd.bias, nd.bias_dt, nd.bias_mode == BIAS_PER_M ? row : 0);
                     const __half y = epilogue_value<__half>(sum, has_bias, bias, nd.epilogue);
                     // for the next node: value and tag in one word, so the word is its own "ready" flag
-                    const unsigned int word = (cp.tag << 16) | (unsigned int)__half_as_ushort(y);
+                    const unsigned int word = (cp.publish_tag << 16) | (unsigned int)__half_as_ushort(y);
                     asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(cp.xbuf + nd.x_off + row), "r"(word) : "memory");
                     ((__half *)nd.out)[row] = y; // for the caller, after the kernel
                 }
             }
             prev_x_off = nd.x_off;
             // every warp is done with node l's description, digits scales and sums before the next node's are written
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-
-            if (*abort_flag) break;
+            if (bar_red_or(1, 256, gave_up || *abort_flag != 0)) break;
         }
     }
 
@@ -638,6 +638,7 @@ struct GemvChain {
     unsigned int *d_xbuf = nullptr;        // {f16, tag} words of every node's output rows
     unsigned long long *d_pbuf = nullptr;  // {f32, tag} words of the K slices' row sums
     unsigned int tag = 0;                  // the last dispatch's tag
+    bool wrong_tag_once = false;           // bounded-wait test hook: the next dispatch publishes a tag nobody waits for
     int grid = 0;
     size_t smem = 0;
     std::string name;
@@ -776,6 +777,12 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
         // where the dispatch tags start (a test hook: the tag wraps from 65535 to 1)
         const char *tv = getenv("RT_CHAIN_TAG_START");
         if (tv) c->tag = (unsigned int)std::max(0, std::min(65535, atoi(tv)));
+        // two more test hooks: a short budget for the readers' waits, and one dispatch whose rows carry a tag no
+        // reader waits for, so that those waits run out (nothing faults or spins past the budget)
+        const char *wv = getenv("RT_CHAIN_WAIT_CYCLES");
+        cp.poll_limit = wv ? (unsigned long long)std::max(1000ll, atoll(wv)) : WAIT_LIMIT_CYCLES;
+        const char *bv = getenv("RT_CHAIN_TEST_WRONG_TAG");
+        c->wrong_tag_once = bv && bv[0] == '1';
     }
     cp.xbuf = c->d_xbuf;
     cp.pbuf = c->d_pbuf;
@@ -789,6 +796,11 @@ cudaError_t gemv_chain_create(const std::vector<MatmulParams> &nodes, int device
 cudaError_t gemv_chain_launch(GemvChain *c, cudaStream_t stream) {
     c->tag = c->tag >= 65535u ? 1u : c->tag + 1u;
     c->cp.tag = c->tag;
+    c->cp.publish_tag = c->tag;
+    if (c->wrong_tag_once) {
+        c->cp.publish_tag = c->tag ^ 0x8000u;
+        c->wrong_tag_once = false;
+    }
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(c->grid);
     lc.blockDim = dim3(THREADS);

@@ -241,11 +241,10 @@ cudaError_t launch_nv(const MatmulParams &p, int split, bool lhs_constant, cudaS
     const int bpc = (nblk + split - 1) / split;
     const size_t smem = smem_bytes(bpc, (int)sizeof(ScaleT));
     auto kernel = split == 1 ? q8_gemv_bulk_kernel<ScaleT, NV, false> : q8_gemv_bulk_kernel<ScaleT, NV, true>;
-    static size_t configured[2] = {0, 0};
-    if (smem > 48 * 1024 && configured[split != 1] < smem) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static SmemAttr smem_attr[2];
+    if (smem > 48 * 1024) {
+        cudaError_t e = smem_attr[split != 1].ensure(kernel, smem);
         if (e != cudaSuccess) return e;
-        configured[split != 1] = smem;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((p.M + ROWS - 1) / ROWS, split, p.stacks);

@@ -377,11 +377,10 @@ cudaError_t launch_q8_gemv_umma(const MatmulParams &p, const GemvUmmaConfig &cfg
     up.p = p;
     up.rb = cfg.rb; up.rb8 = cfg.rb8; up.ks = cfg.ks; up.nstages_k = cfg.ks / STAGE_K; up.ring = cfg.ring;
     up.stage_bytes = cfg.stage_bytes; up.b_bytes = cfg.b_bytes; up.split = cfg.split; up.lhs_constant = lhs_constant ? 1 : 0;
-    static size_t configured = 0;
-    if (cfg.smem_bytes > configured) {
-        cudaError_t e = cudaFuncSetAttribute(q8_gemv_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.smem_bytes);
+    static SmemAttr smem_attr;
+    {
+        cudaError_t e = smem_attr.ensure(q8_gemv_umma_kernel, cfg.smem_bytes);
         if (e != cudaSuccess) return e;
-        configured = cfg.smem_bytes;
     }
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(cfg.clusters * cfg.split);

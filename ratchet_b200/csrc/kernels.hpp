@@ -1,5 +1,6 @@
 // Launchers of the device kernels (one translation unit each).
 #pragma once
+#include <mutex>
 #include <string>
 #include <vector>
 #include <cuda_runtime.h>
@@ -24,6 +25,26 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     lc.numAttrs = 1;
     return cudaLaunchKernelEx(&lc, kernel, static_cast<KArgs>(args)...);
 }
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) acts on the current device only, and launches may come from
+// several host threads: one record per device ordinal of the largest size set so far, under a mutex.
+class SmemAttr {
+    std::mutex mu_;
+    size_t set_[64] = {};
+
+  public:
+    template <typename Kernel> cudaError_t ensure(Kernel kernel, size_t bytes) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+        std::lock_guard<std::mutex> lk(mu_);
+        if (bytes <= set_[dev]) return cudaSuccess;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e == cudaSuccess) set_[dev] = bytes;
+        return e;
+    }
+};
 
 // General CUDA-core kernels: any legal node.
 cudaError_t launch_matmul_simt(const MatmulParams &p, rt_dtype lhs_dt, rt_dtype act_dt, bool gemv, cudaStream_t stream);

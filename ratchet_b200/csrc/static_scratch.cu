@@ -36,7 +36,7 @@ extern "C" rt_status rt_linear_q8_0_static_scratch(rt_device *dev, const void *w
     if (!dev || !w || !x || !out) return fail(RT_ERR_ARG, "rt_linear_q8_0_static_scratch: null argument");
     if (epilogue != RT_EPILOGUE_NONE && epilogue != RT_EPILOGUE_GELU_TANH)
         return fail(RT_ERR_ARG, "rt_linear_q8_0_static_scratch: invalid epilogue");
-    if (rows < 1 || n < 1 || k < 32 || k % 32 != 0 || rows >= (int64_t(1) << 31) || n >= (int64_t(1) << 31))
+    if (rows < 1 || n < 1 || k < 32 || k % 32 != 0 || rows >= (int64_t(1) << 31) || n >= (int64_t(1) << 31) || k >= (int64_t(1) << 31))
         return fail(RT_ERR_SHAPE, "rt_linear_q8_0_static_scratch: rows, n >= 1 and k a positive multiple of 32 are required");
     const uint64_t need = (uint64_t)n * (uint64_t)k * 2;
     if (need > (uint64_t)RT_STATIC_SCRATCH_BYTES)

@@ -40,6 +40,28 @@ def test_device_dequant_matches_gguf_fixtures(gpu):
     assert np.array_equal(t4.dequantize_on_device().reshape(-1).view(np.uint32), g4["dequant"].reshape(-1).view(np.uint32))
 
 
+def test_quantised_matmul_fixtures_from_gguf_py_and_torch(gpu):
+    """GGUF blocks through the library's loader path (transcode for Q8_0, raw super-blocks for Q4_K) and kernels,
+    against values that gguf-py's decoder and torch.matmul in float64 produced (tests/golden/make_qmatmul_golden.py):
+    GEMV, skinny and GEMM shapes, with bias and GELU."""
+    z = np.load(os.path.join(GOLDEN, "qmatmul.npz"))
+    for name in z["quant_cases"]:
+        name = str(name)
+        N, K, M, has_bias, gelu = (int(v) for v in z[name + "_meta"])
+        if name.startswith("q8"):
+            w = rb.transcode_gguf_q8_0(z[name + "_blocks"], [N, K], Q8H, gpu)
+        else:
+            w = Tensor.from_quantized(z[name + "_blocks"].reshape(-1), Q4K, [N, K], gpu)
+        bias = Tensor.from_data(z[name + "_bias"], gpu) if has_bias else None
+        y = w.gemm(Tensor.from_data(z[name + "_x"], gpu), bias, False, True, True, epilogue=gelu).resolve().to(Device.CPU)
+        want = z[name + "_y"].astype(np.float32)
+        assert y.shape == list(want.shape)
+        assert oracle.rel_l2(y.to_f32().reshape(-1), want.reshape(-1)) <= TOL[F16], name
+    for name in ("f16_a", "f16_b"):
+        y = Tensor.from_data(z[name + "_a"], gpu).matmul(Tensor.from_data(z[name + "_b"], gpu)).resolve().to(Device.CPU)
+        assert oracle.rel_l2(y.to_f32().reshape(-1), z[name + "_c"].astype(np.float32).reshape(-1)) <= TOL[F16], name
+
+
 # ----------------------------------------------------------------------------- dense f32: the reference's own test space
 
 @pytest.mark.parametrize("i", range(int(np.load(os.path.join(GOLDEN, "sgemm.npz"))["n_cases"][0])))
@@ -148,11 +170,57 @@ def test_launch_rejects_aliasing_and_null(gpu):
     assert lib.rt_executable_create(gpu._h, node, 1, 0, byref(exe)) == rb._lib.RT_ERR_INVARIANT
 
 
+def test_streaming_gemv_rejects_misaligned_operands(gpu):
+    """The Q8_0 streaming kernel fetches rows with bulk copies and activations with 16-byte loads: an offset device
+    pointer is refused with an error code, not handed to the kernel."""
+    lib = rb._lib.load()
+    w, _ = make_lhs(Q8H, (1000, 2560), np.random.default_rng(1), 0.02)
+    w = w.to(gpu)
+    x = Tensor.from_data(np.zeros((1, 2, 2560), dtype=np.float16), gpu)
+    node = w.gemm(x, None, False, True, True)
+    plan = gpu.plan_for(node.op.desc)
+    assert lib.rt_plan_kernel(plan).decode().startswith("q8_gemv_mma")
+    out = rb.GpuBuffer(gpu, 2 * 1000 * 2)
+    assert lib.rt_matmul_launch(plan, w.ptr, x.ptr + 4, None, out.ptr, None) == rb._lib.RT_ERR_ARG
+    assert lib.rt_matmul_launch(plan, w.ptr + 8, x.ptr, None, out.ptr, None) == rb._lib.RT_ERR_ARG
+    assert b"16-byte aligned" in lib.rt_last_error()
+    assert lib.rt_matmul_launch(plan, w.ptr, x.ptr, None, out.ptr, None) == rb._lib.RT_OK
+    gpu.sync()
+
+
+def test_plans_are_cached_by_the_library_and_kept_weights_follow_their_buffers(gpu):
+    """rt_matmul_plan hands equal descriptions the same plan (the KernelKey cache's role).  A quantised weight
+    flagged constant is dequantised once and the copy kept by pointer; when the weight's buffer is freed and its
+    block reused for another weight, the stale copy must not be used."""
+    from ctypes import byref, c_void_p
+    lib = rb._lib.load()
+    shape, rows = (512, 256), 64
+    x = round_to(F16, np.random.default_rng(7).standard_normal((1, rows, 256)))
+    xd = Tensor.from_data(x, gpu, F16)
+    results = []
+    for seed in (11, 12):
+        w_t, wv = make_lhs(Q8H, shape, np.random.default_rng(seed), 0.02)
+        w_dev = w_t.to(gpu)
+        node = w_dev.gemm(xd, None, False, True, True)
+        h1, h2 = c_void_p(), c_void_p()
+        rb._lib.check(lib.rt_matmul_plan(gpu._h, byref(node.op.desc), byref(h1)))
+        rb._lib.check(lib.rt_matmul_plan(gpu._h, byref(node.op.desc), byref(h2)))
+        assert h1.value == h2.value
+        assert lib.rt_plan_kernel(h1).decode().endswith("_dequant_prepass")
+        for _ in range(2):  # the second launch takes the kept copy
+            y = w_dev.gemm(xd, None, False, True, True).resolve().to(Device.CPU)
+            truth = oracle.matmul_truth(wv, x, None, 1, 1, 1, shape[0], rows, shape[1], False, True, True)
+            assert oracle.rel_l2(y.to_f32().reshape(-1), oracle.f64_to_f16(truth).astype(np.float32)) <= TOL[F16], seed
+        results.append(w_dev.ptr)
+        del w_dev, node, y  # the buffer goes back to the pool: the next weight of this size gets the same block
+    assert results[0] == results[1], "the pool did not reuse the block: the test did not exercise the stale-copy case"
+
+
 # ----------------------------------------------------------------------------- Q8_0 GEMV (decode)
 
 @pytest.mark.parametrize("shape,seed", [((10240, 2560), 102), ((2560, 10240), 112)])
 def test_q8_gemv_phi2_shapes(gpu, shape, seed):
-    """BASELINE config 2: x f16 [1,1,K], W Q8_0H [N,K] from N(0,0.02), out f16 [1,1,N]."""
+    """The Phi-2 MLP decode GEMVs: x f16 [1,1,K], W Q8_0H [N,K] from N(0,0.02), out f16 [1,1,N]."""
     N, K = shape
     for bias in (False, True):
         p = Problem(Q8H, F16, shape, (1, 1, K), (False, True, True), bias=bias, seed=seed, w_std=0.02)
@@ -161,7 +229,7 @@ def test_q8_gemv_phi2_shapes(gpu, shape, seed):
         err = oracle.rel_l2(got, truth_r)
         err_ref = oracle.rel_l2(faithful, truth_r)
         assert err <= 1e-3, (kernel, err)
-        assert err <= err_ref + 1e-4  # exact products: at least as close to the truth as the reference's arithmetic
+        assert err <= err_ref + 1e-4  # int8 products of 15-bit activation digits: at least as close to the truth as the reference's f16 arithmetic
     # f32 scales with f16 activations (extension) and the reference's (Q8_0F, F32) pair
     _, kernel = check_problem(Problem(Q8F, F16, shape, (1, 1, K), (False, True, True), bias=True, seed=seed, w_std=0.02), gpu)
     assert kernel.startswith("q8_gemv_mma_f")
@@ -191,8 +259,8 @@ def _decode_chain(gpu, shapes, seed, with_bias):
     [(10240, 2560), (2560, 10240), (8192, 2560), (2560, 8192)],        # fc1 / fc2: K split four ways on every second node
 ], ids=["square_x3", "phi2_mlp_x2"])
 def test_q8_gemv_chain_is_one_kernel_and_matches_node_by_node(gpu, monkeypatch, shapes):
-    """A decode step's GEMVs as ONE persistent kernel (grid barriers between the nodes): every node's
-    output agrees with node-by-node dispatch and meets the bar against the fp64 oracle."""
+    """A decode step's GEMVs as ONE persistent kernel (rows handed from node to node as tagged words): every
+    node's output agrees with node-by-node dispatch and meets the bar against the fp64 oracle."""
     x_dev, nodes, host = _decode_chain(gpu, shapes, 4100, [True, False, False, True][:len(shapes)])
     nodes[-1].resolve()
     exe = rb.Executable(gpu, nodes, use_graph=True)
@@ -210,7 +278,7 @@ def test_q8_gemv_chain_is_one_kernel_and_matches_node_by_node(gpu, monkeypatch, 
         for n in nodes:
             n.write(np.zeros(n.numel(), dtype=np.float16))
         exe.dispatch()
-        exe.dispatch()  # back to back: the barrier counter is reset between dispatches
+        exe.dispatch()  # back to back: every dispatch has its own tag
         gpu.sync()
         got = [n.to(Device.CPU).to_numpy().reshape(-1).copy() for n in nodes]
         h = x.astype(np.float32)
@@ -352,6 +420,35 @@ def test_q8_gemv_chain_tag_wraps(gpu, monkeypatch):
             h = got.astype(np.float32)
 
 
+def test_q8_gemv_chain_bounded_wait_runs_out_and_the_next_dispatch_is_right(gpu, monkeypatch):
+    """A wait that can never be satisfied: one dispatch publishes its rows under a tag no reader waits for, with the
+    readers' budget cut to about a millisecond.  The kernel must come back by itself (nothing faults or spins on),
+    the next synchronisation must name the failure, and the dispatch after that must be correct again."""
+    shapes = [(2560, 2560), (2560, 2560), (2560, 2560)]
+    x_dev, nodes, host = _decode_chain(gpu, shapes, 4800, [False, False, False])
+    nodes[-1].resolve()
+    monkeypatch.setenv("RT_CHAIN_WAIT_CYCLES", "2000000")
+    monkeypatch.setenv("RT_CHAIN_TEST_WRONG_TAG", "1")
+    exe = rb.Executable(gpu, nodes, use_graph=True)
+    assert exe.kernel.startswith("q8_gemv_chain"), exe.kernel
+    exe.dispatch()
+    with pytest.raises(rb.RatchetError) as err:
+        gpu.sync()
+    assert err.value.status == rb._lib.RT_ERR_CUDA and "gave up a bounded wait" in str(err.value)
+    gpu.sync()  # the flag was taken: the device is usable
+    x = np.random.default_rng(4801).standard_normal(shapes[0][1]).astype(np.float16)
+    x_dev.write(x)
+    exe.dispatch()
+    gpu.sync()
+    h = x.astype(np.float32)
+    for i, (w_vals, b_vals, epi) in enumerate(host):
+        M, K = shapes[i]
+        got = nodes[i].to(Device.CPU).to_numpy().reshape(-1)
+        truth = oracle.matmul_truth(w_vals, h, b_vals, 1, 1, 1, M, 1, K, False, True, True, epi)
+        assert oracle.rel_l2(got.astype(np.float32), oracle.f64_to_f16(truth).astype(np.float32)) <= TOL[F16], i
+        h = got.astype(np.float32)
+
+
 def test_q8_gemv_shapes_and_forms(gpu):
     for N, K in [(16, 32), (15, 64), (17, 96), (33, 2560), (1000, 352), (4096, 4096), (7, 8192)]:
         check_problem(Problem(Q8H, F16, (N, K), (1, K), (False, True, True), bias=True, seed=N + K, w_std=0.05), gpu)
@@ -376,7 +473,7 @@ def test_q8_skinny_gemm_streams_weights_once(gpu, nv):
 # ----------------------------------------------------------------------------- Q8_0 GEMM (prefill)
 
 def test_q8_gemm_whisper_mlp_chain(gpu):
-    """BASELINE config 3: A f16 [1,1500,384] -> Q8_0 [1536,384] + b -> GELU -> Q8_0 [384,1536] + b."""
+    """The Whisper-tiny encoder MLP: A f16 [1,1500,384] -> Q8_0 [1536,384] + b -> GELU -> Q8_0 [384,1536] + b."""
     rng = np.random.default_rng(103)
     w1_t, w1 = make_lhs(Q8H, (1536, 384), np.random.default_rng(1103), 0.02)
     w2_t, w2 = make_lhs(Q8H, (384, 1536), np.random.default_rng(1104), 0.02)
@@ -408,7 +505,7 @@ def test_q8_gemm_forms(gpu):
 
 
 def test_dense_f32_phi2_fc1(gpu):
-    """BASELINE config 1: A f32 [1,128,2560], W f32 [10240,2560] N(0,0.02) rhs-transposed, b f32."""
+    """Dense f32 Phi-2 fc1 prefill: A f32 [1,128,2560], W f32 [10240,2560] N(0,0.02) rhs-transposed, b f32."""
     err, kernel = check_problem(Problem(F32, F32, (10240, 2560), (1, 128, 2560), (False, True, True), bias=True, seed=101,
                                         w_std=0.02), gpu)
     assert kernel.startswith("gemm_umma_tf32x3"), kernel
@@ -419,7 +516,7 @@ def test_dense_f32_phi2_fc1(gpu):
 
 @pytest.mark.parametrize("M", [1, 16, 512])
 def test_q4k_phi3_shapes(gpu, M):
-    """BASELINE config 4: W Q4_K [8192,3072] from N(0,0.02), x f16 [M,3072], out f16 [M,8192]."""
+    """The Phi-3 shaped Q4_K projection: W Q4_K [8192,3072] from N(0,0.02), x f16 [M,3072], out f16 [M,8192]."""
     check_problem(Problem(Q4K, F16, (8192, 3072), (1, M, 3072), (False, True, True), seed=104, w_std=0.02), gpu)
 
 
@@ -462,8 +559,8 @@ def test_q4k_forms(gpu):
 
 # ----------------------------------------------------------------------------- bf16 prefill at reduced rows
 
-def test_q8_bf16_prefill_rows_of_config5(gpu):
-    """BASELINE config 5 on a slice of the rows: A bf16 [1,256,2560], W Q8_0H [10240,2560], f16 bias, GELU."""
+def test_q8_bf16_prefill_row_slice(gpu):
+    """A slice of the rows of the bf16 prefill Linear: A bf16 [1,256,2560], W Q8_0H [10240,2560], f16 bias, GELU."""
     check_problem(Problem(Q8H, BF16, (10240, 2560), (1, 256, 2560), (False, True, True), bias=True, epilogue=1,
                           seed=105, w_std=0.02, bias_dt=F16), gpu)
 
@@ -574,10 +671,12 @@ def test_umma_takes_the_prefill_configs(gpu):
         assert lib.rt_plan_kernel(gpu.plan_for(node.op.desc)).decode().startswith("gemm_umma"), (lhs_dt, wshape)
 
 
-def test_q8_bf16_prefill_config5_full_size_sampled(gpu):
-    """BASELINE config 5 at full size: A bf16 [4,2048,2560], W Q8_0H [10240,2560], f16 bias, fused GELU.
-    The oracle finishes a sample of the 8192 output rows in seconds; every sampled row is compared."""
-    B, M, K, N = 4, 2048, 2560, 10240
+@pytest.mark.parametrize("M", [2048, 8192], ids=["4x2048", "4x8192"])
+def test_q8_bf16_prefill_full_size_sampled(gpu, M):
+    """The sharded prefill workload at full size on one GPU: A bf16 [4,M,2560], W Q8_0H [10240,2560], f16 bias,
+    fused GELU, with M = 2048 and the long form M = 8192 (32768 rows).  The oracle finishes a sample of the output
+    rows in seconds; every sampled row is compared."""
+    B, K, N = 4, 2560, 10240
     w_t, wv = make_lhs(Q8H, (N, K), np.random.default_rng(1105), 0.02)
     x = round_to(BF16, np.random.default_rng(105).standard_normal((B, M, K)).astype(np.float32))
     bias = round_to(F16, np.random.default_rng(2105).standard_normal(N) * 0.02)

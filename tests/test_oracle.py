@@ -149,3 +149,38 @@ def test_bf16_rounding_single():
     import torch
     want = torch.tensor(x, dtype=torch.float64).to(torch.float32).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
     assert np.array_equal(bits, want)
+
+
+def _qmatmul_cases():
+    z = np.load(os.path.join(GOLDEN, "qmatmul.npz"))
+    for name in z["quant_cases"]:
+        name = str(name)
+        N, K, M, has_bias, gelu = (int(v) for v in z[name + "_meta"])
+        yield name, z[name + "_blocks"], z[name + "_x"], (z[name + "_bias"] if has_bias else None), z[name + "_y"], N, K, M, gelu
+
+
+def test_truth_oracle_over_decoded_blocks_matches_gguf_py_plus_torch():
+    """GGUF blocks -> this oracle's decode -> this oracle's fp64 matmul (+ bias, + GELU), against the same blocks
+    through gguf-py's decoder and torch.matmul in float64: the expected values never touched this repository's code."""
+    for name, blocks, x, bias, want, N, K, M, gelu in _qmatmul_cases():
+        if name.startswith("q8"):
+            w = oracle.q8_dequantize_h(oracle.q8_transcode_gguf(blocks, 2), N * K).astype(np.float32)
+        else:
+            w = oracle.q4k_dequantize(blocks.reshape(-1), N * K)
+        truth = oracle.matmul_truth(w.reshape(N, K), x.astype(np.float32), None if bias is None else bias.astype(np.float32),
+                                    1, 1, 1, N, M, K, False, True, True, gelu)
+        got = oracle.f64_to_f16(truth).reshape(want.shape)
+        # one rounding on both sides: equal up to rare last-digit flips (the two GELUs evaluate tanh differently)
+        ulp = np.abs(got.view(np.int16).astype(np.int32) - want.view(np.int16).astype(np.int32))
+        assert ulp.max() <= 1 and (ulp != 0).mean() < 0.01, (name, int(ulp.max()), float((ulp != 0).mean()))
+
+
+def test_truth_oracle_f16_dense_matches_torch_half_matmul():
+    z = np.load(os.path.join(GOLDEN, "qmatmul.npz"))
+    for name in ("f16_a", "f16_b"):
+        a, b, c = z[name + "_a"], z[name + "_b"], z[name + "_c"]
+        B, M, K = a.shape
+        N = b.shape[2]
+        truth = oracle.matmul_truth(a.astype(np.float32), b.astype(np.float32), None, B, B, B, M, N, K, False, False, False)
+        got = oracle.f64_to_f16(truth).reshape(c.shape)
+        assert oracle.rel_l2(got.astype(np.float32), c.astype(np.float32)) <= 2e-4  # torch sums in f32

@@ -26,6 +26,30 @@ def test_library_exports_every_declared_symbol():
     assert "sm_100a" in _lib.load().rt_version().decode()
 
 
+def test_public_structs_have_the_layout_the_ctypes_mirror_assumes():
+    """sizeof / offsetof as the library was compiled against the ctypes Structures of _lib.py (the same check a
+    Rust -sys crate would make of its #[repr(C)] structs)."""
+    lib = _lib.load()
+    buf = (ctypes.c_uint64 * 64)()
+    n = lib.rt_abi_layout(buf, 64)
+    S, L = ctypes.sizeof, _lib
+    off = lambda t, f: getattr(t, f).offset
+    want = [
+        S(L.rt_shape), off(L.rt_shape, "dims"), S(L.rt_segment),
+        S(L.rt_matmul_desc), off(L.rt_matmul_desc, "lhs_shape"), off(L.rt_matmul_desc, "rhs_shape"), off(L.rt_matmul_desc, "bias_shape"),
+        off(L.rt_matmul_desc, "has_bias"), off(L.rt_matmul_desc, "epilogue"),
+        S(L.rt_gemm_spec), off(L.rt_gemm_spec, "out_dt"), off(L.rt_gemm_spec, "lhs_stack"), off(L.rt_gemm_spec, "dim_inner"), off(L.rt_gemm_spec, "is_gemv"),
+        S(L.rt_launch_opts), off(L.rt_launch_opts, "outs"), off(L.rt_launch_opts, "out_ld"), off(L.rt_launch_opts, "out_col"),
+        S(L.rt_dispatch), off(L.rt_dispatch, "opts"),
+        S(L.rt_gguf_value), off(L.rt_gguf_value, "str"),
+        S(L.rt_gguf_tensor_info), off(L.rt_gguf_tensor_info, "shape"), off(L.rt_gguf_tensor_info, "nbytes"),
+    ]
+    assert n == len(want)
+    assert [int(buf[i]) for i in range(n)] == want
+    # rt_dispatch embeds its options by value
+    assert off(L.rt_dispatch, "opts") + S(L.rt_launch_opts) == S(L.rt_dispatch)
+
+
 def test_no_device_is_a_loud_error_not_a_fallback():
     import torch
     if torch.cuda.is_available():

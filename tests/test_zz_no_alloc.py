@@ -41,7 +41,8 @@ def _static(gpu, w_t, x, bias, epilogue):
 
 
 def test_static_scratch_linear_matches_the_regular_path_twice(gpu):
-    cases = [((1536, 384), 1500, True, rb.EPILOGUE_GELU_TANH, 301), ((384, 1536), 777, False, rb.EPILOGUE_NONE, 302)]
+    # the second weight is smaller than the first: part of the first one's dequantised copy stays behind in the array
+    cases = [((1536, 384), 1500, True, rb.EPILOGUE_GELU_TANH, 301), ((256, 768), 777, False, rb.EPILOGUE_NONE, 302)]
     for (n, k), rows, has_bias, epilogue, seed in cases:
         w_cpu, wv = make_lhs(DType.Q8_0H, (n, k), np.random.default_rng(seed), 0.02)
         w_t = w_cpu.to(gpu)
@@ -59,6 +60,27 @@ def test_static_scratch_linear_matches_the_regular_path_twice(gpu):
         assert oracle.rel_l2(got.astype(np.float32).reshape(-1), oracle.f64_to_f16(truth).astype(np.float32)) <= 1e-3
 
 
+def test_static_scratch_calls_leave_free_device_memory_unchanged(gpu):
+    """The property the entry point exists for: with operands and output in place, calls through it take no device
+    memory (cudaMemGetInfo reads the same before and after)."""
+    import torch
+    lib = _lib.load()
+    n, k, rows = 512, 1024, 300
+    w_cpu, _ = make_lhs(DType.Q8_0H, (n, k), np.random.default_rng(311), 0.02)
+    w_t = w_cpu.to(gpu)
+    xd = Tensor.from_data(np.random.default_rng(312).standard_normal((rows, k)).astype(np.float16), gpu, DType.F16)
+    out = GpuBuffer(gpu, rows * n * 2)
+    call = lambda: _lib.check(lib.rt_linear_q8_0_static_scratch(gpu._h, w_t.ptr, xd.ptr, None, out.ptr, rows, n, k, 0, None))
+    call()       # the first call on a device looks the array's address up
+    gpu.sync()
+    free_before, _ = torch.cuda.mem_get_info(gpu.ordinal)
+    for _ in range(20):
+        call()
+    gpu.sync()
+    free_after, _ = torch.cuda.mem_get_info(gpu.ordinal)
+    assert free_after == free_before, (free_before, free_after)
+
+
 def test_static_scratch_refuses_weights_beyond_its_array(gpu):
     lib = _lib.load()
     n, k = 4096, 2048  # 16 MiB of f16 weights > the 8 MiB array
@@ -66,3 +88,6 @@ def test_static_scratch_refuses_weights_beyond_its_array(gpu):
     st = lib.rt_linear_q8_0_static_scratch(gpu._h, dummy.ptr, dummy.ptr + 4096, None, dummy.ptr + 8192, 16, n, k, 0, None)
     assert st == _lib.RT_ERR_UNSUPPORTED
     assert b"built-in array holds" in lib.rt_last_error()
+    # an inner extent beyond 32 bits is a shape error, not a wrapped size
+    st = lib.rt_linear_q8_0_static_scratch(gpu._h, dummy.ptr, dummy.ptr + 4096, None, dummy.ptr + 8192, 16, 1, 1 << 33, 0, None)
+    assert st == _lib.RT_ERR_SHAPE
