@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
             mbar_init(bar_sempty + 8 * a, 8);
         }
         *abort_flag = 0;
-        for (int i = 0; i < 10; i++) badmask[i] = 0u;
+        for (int i = 0; i < 12; i++) badmask[i] = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -280,6 +280,18 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
         int tg = 0, sbuf = 0, prev_x_off = 0, slot = 0;
         uint32_t sphase = 0, phase = 0;
         bool gave_up = false; // a wait of this warp ran out: it skips work but stays in step with the others up to the next barrier
+        // The eight warps leave together, and only at a node's last barrier.  Before it ONE thread copies the CTA's
+        // abort flag into one of two words (taken in turn, so that a thread still reading the last node's word is not
+        // overtaken); after the barrier all threads test that copy, hence take the same decision.  A warp whose own wait
+        // ran out (which raised the flag) skips its work, and every later wait of the CTA returns at once, until that
+        // barrier shows the flag to everybody.
+        volatile unsigned int *abort_seen = badmask + 10;
+        int barriers = 0;
+        auto sync_and_check = [&]() -> bool {
+            if (et == 0) abort_seen[barriers & 1] = (unsigned int)*abort_flag;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            return abort_seen[(barriers++) & 1] != 0u;
+        };
         for (int l = 0; l < cp.n_nodes; l++) {
             const ChainNodeInfo &nd = info[l & 1];
             const int split = nd.split, unit = (int)blockIdx.x / split, rank = (int)blockIdx.x % split;
@@ -401,9 +413,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
                 }
                 // the MMAs read the tiles through the async proxy
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                // xs visible to all epilogue warps; and the warps leave together (the barrier returns the OR of what every
-                // thread saw), so that none waits at a later barrier for one that has gone
-                if (bar_red_or(1, 256, gave_up || *abort_flag != 0)) break;
+                asm volatile("bar.sync 1, 256;" ::: "memory"); // xs visible to all epilogue warps
                 if (lane == 0) mbar_arrive(bar_x);
                 if (warp == 2 && l + 1 < cp.n_nodes) reinterpret_cast<int *>(info + ((l + 1) & 1))[lane] = next_word;
                 if (et < 4) badmask[((l + 1) & 1) * 4 + et] = 0u; // the next node's mask and flag (node l-1's readers are two barriers back)
@@ -475,7 +485,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
 #pragma unroll
                 for (int t = 0; t < MAX_TILES; t++)
                     if (mine[t]) part[half * (MAX_TILES * 128) + 128 * t + row_local] = acc[t];
-                if (bar_red_or(1, 256, gave_up || *abort_flag != 0)) break;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
                 const bool my_rows = et < rows_here; // from here on thread et of the first four warps owns row et
                 float sum = 0.f;
                 if (my_rows) {
@@ -562,7 +572,7 @@ __global__ void __launch_bounds__(THREADS, 1) q8_gemv_chain_kernel(const ChainPa
             }
             prev_x_off = nd.x_off;
             // every warp is done with node l's description, digits scales and sums before the next node's are written
-            if (bar_red_or(1, 256, gave_up || *abort_flag != 0)) break;
+            if (sync_and_check()) break;
         }
     }
 
