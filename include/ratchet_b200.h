@@ -63,7 +63,18 @@ typedef enum rt_epilogue {
      * fc1 -> full() -> gelu() -> cast() of crates/ratchet-models/src/whisper/mlp.rs:18-22
      * fused into the producing kernel.  bf16 outputs (which the reference does not have) are
      * the exception: bias and GELU act on the f32 accumulator and the result is rounded once. */
-    RT_EPILOGUE_GELU_TANH = 1
+    RT_EPILOGUE_GELU_TANH = 1,
+    /* The gate/up form of crates/ratchet-models/src/phi3/mlp.rs:31-39, for the Linear node
+     * W.gemm(x, b, false, true, true) only: W is [2*ff, K] with the gate rows first; the node's
+     * output is [.., ff] (out_shape has the last extent halved) and holds
+     *   up * cast(silu(full(gate)))      silu(v) = v * sigmoid(v), sigmoid as ops/unary.rs:121-131
+     * where gate and up are the two halves of the plain node's row, each rounded to the output
+     * dtype (bias added there) as the plain node would leave them; silu runs in f32 on the
+     * rounded gate, is rounded to the output dtype, and the product is rounded once more (bf16
+     * outputs, which the reference does not have, skip the rounding of silu).  The tensor-core GEMM
+     * computes both halves of a column in one tile and never writes the [.., 2*ff] tensor; the
+     * GEMV-shaped routes write it to plan scratch and run a second, elementwise launch. */
+    RT_EPILOGUE_SILU_MUL = 2
 } rt_epilogue;
 
 typedef struct rt_shape {
@@ -277,6 +288,67 @@ rt_status rt_executable_destroy(rt_executable *exe);
 int32_t rt_executable_launches(const rt_executable *exe);
 /* How the list is dispatched: "nodes", "graph", or the persistent kernel's name. */
 const char *rt_executable_kernel(const rt_executable *exe);
+
+/* ------------------------------------------------------------------ activation planner
+ * TensorUsageRecord (crates/ratchet-core/src/gpu/buffer_allocator/tensor_usage_record.rs): an
+ * intermediate's size and the positions, in execution order, of the node that produces it and of
+ * the last node that reads it. */
+typedef struct rt_usage_record {
+    uint64_t size;
+    int32_t producer;
+    int32_t last_consumer;
+} rt_usage_record;
+/* BufferAllocator::greedy_by_size (gpu/buffer_allocator/allocator.rs:209-271): records from the
+ * largest to the smallest; each takes the last shared object (in creation order) none of whose
+ * tenants is alive at the same time (two records are alive together when max(producers) <=
+ * min(last_consumers)), else opens a new object of its own size.  objects[i] = shared object of
+ * record i; the objects are laid end to end in one arena, each on an `alignment` boundary (a power
+ * of two): offsets[i] = byte offset of record i's object, *arena_bytes = the arena's size.  Any of
+ * the output pointers may be NULL.  Host only. */
+rt_status rt_arena_plan(const rt_usage_record *records, int32_t n, uint64_t alignment, int32_t *objects,
+                        uint64_t *offsets, int32_t *n_objects, uint64_t *arena_bytes);
+
+/* Which operands of a node are intermediates of the executable: -1 = the pointer in rt_dispatch,
+ * k >= 0 = intermediate k (the pointer in rt_dispatch is then ignored). */
+typedef struct rt_node_tensors {
+    int32_t lhs, rhs, bias, out;
+} rt_node_tensors;
+/* rt_executable_create for a node list whose intermediates the library places
+ * (Executable + BufferAllocator::allocate_cfg, executable.rs:13-54, allocator.rs:273-340):
+ * tensor_bytes[k] is the size of intermediate k; usage records are taken from the node list
+ * (producer = the first node writing k, last consumer = the last node touching it), every node's
+ * plan scratch is one more record alive during that node only, rt_arena_plan places them all, and
+ * ONE device allocation made here holds them: dispatches allocate nothing, and executables do not
+ * share scratch with each other or with direct launches of the same plans.  (Dequantised copies of
+ * weights flagged RT_LAUNCH_LHS_CONSTANT stay with their plans; they are weights, not
+ * activations.)  An intermediate must be produced by an earlier node than any that reads it
+ * (RT_ERR_ARG) and be large enough for its producer's output.  `ids` may be NULL: then only the
+ * plan scratch is placed.  rt_executable_create is this call with ids = NULL. */
+rt_status rt_executable_create_planned(rt_device *dev, const rt_dispatch *nodes, const rt_node_tensors *ids, int32_t n_nodes,
+                                       const uint64_t *tensor_bytes, int32_t n_tensors, int32_t use_graph,
+                                       rt_executable **exe);
+/* The executable's arena: its size, the number of shared objects in it and the sum of all its
+ * records' sizes (what separate allocations would have taken).  Any pointer may be NULL. */
+rt_status rt_executable_arena(const rt_executable *exe, uint64_t *arena_bytes, int32_t *n_objects, uint64_t *record_bytes);
+/* Device address of intermediate `id` (NULL when out of range): valid while the executable lives;
+ * its contents are defined only between its producer and its last consumer. */
+void *rt_executable_tensor(const rt_executable *exe, int32_t id);
+
+/* The MLP block as one executable (Module::schedule of crates/ratchet-models/src/phi2/mlp.rs:13-15,
+ * whisper/mlp.rs:18-22, phi3/mlp.rs:31-39): hidden = act(fc1(x)), out = fc2(hidden), where fc1's
+ * description carries the activation as its epilogue (RT_EPILOGUE_GELU_TANH: Phi-2 / Whisper /
+ * Moondream; RT_EPILOGUE_SILU_MUL: Phi-3, fc1 being the gate_up projection) and both are Linear
+ * nodes (trans_rhs, trans_out).  fc1's output shape must be fc2's rhs shape.  The hidden tensor is
+ * an intermediate placed by the planner; weights are taken as constant (RT_LAUNCH_LHS_CONSTANT).
+ * One row against Q8_0H weights becomes the persistent GEMV kernel over both nodes. */
+typedef struct rt_mlp_desc {
+    rt_matmul_desc fc1, fc2;
+    const void *w1, *b1; /* b1 / b2 NULL when the description has no bias */
+    const void *w2, *b2;
+    const void *x;
+    void *out;
+} rt_mlp_desc;
+rt_status rt_mlp_create(rt_device *dev, const rt_mlp_desc *mlp, int32_t use_graph, rt_executable **exe);
 
 /* Linear-shaped Q8_0 GEMM for callers that must not allocate device memory: out[rows][n] =
  * x[rows][k] . W[n][k]^T (+ bias[n]) (+ GELU), W as RT_Q8_0H, x / bias / out f16 -- the node

@@ -173,6 +173,44 @@ def gelu_f32(x: np.ndarray) -> np.ndarray:
     return y
 
 
+def silu_f32(v: np.ndarray) -> np.ndarray:
+    """silu(v) = v * sigmoid(v) in f32, with the reference's two-branch sigmoid
+    (crates/ratchet-core/src/ops/unary.rs:121-131,165-175): exp(v) / (1 + exp(v)) for v >= 0 (NaN once
+    exp(v) overflows), 1 / (1 + exp(-v)) below."""
+    v = np.asarray(v, dtype=np.float32)
+    one = np.float32(1)
+    with np.errstate(over="ignore", invalid="ignore"):
+        pos = np.exp(v) / (one + np.exp(v))
+        neg = one / (one + np.exp(-v))
+        return (v * np.where(v >= 0, pos, neg)).astype(np.float32)
+
+
+def silu_mul(full: np.ndarray, act_dt: str = "f16") -> np.ndarray:
+    """The Phi-3 gate/up fold, crates/ratchet-models/src/phi3/mlp.rs:31-39: `full` [..., 2*ff] is the gate_up
+    Linear's output (values of dtype `act_dt` held in f32), gate = [..., :ff], up = [..., ff:], result
+    up * cast(silu(full(gate))) with every tensor of the chain in `act_dt`.  bf16 (no reference counterpart)
+    rounds the product only."""
+    full = np.asarray(full, dtype=np.float32)
+    ff = full.shape[-1] // 2
+    gate, up = full[..., :ff], full[..., ff:]
+    sv = silu_f32(gate)
+    with np.errstate(over="ignore", invalid="ignore"):
+        if act_dt == "f16":
+            return (up.astype(np.float16) * sv.astype(np.float16)).astype(np.float32)
+        if act_dt == "bf16":
+            return bf16_bits_to_f32(f64_to_bf16_bits((up * sv).astype(np.float64))).reshape(up.shape)
+        return (up * sv).astype(np.float32)
+
+
+def silu_mul_truth(full64: np.ndarray) -> np.ndarray:
+    """The same fold in f64 without intermediate roundings."""
+    full64 = np.asarray(full64, dtype=np.float64)
+    ff = full64.shape[-1] // 2
+    gate, up = full64[..., :ff], full64[..., ff:]
+    with np.errstate(over="ignore"):
+        return up * gate / (1.0 + np.exp(-gate))
+
+
 def _mm_args(A, B, bias, stacks, a_stack, b_stack, M, N, K, ta, tb, to, epilogue):
     return [_i64(stacks), _i64(a_stack), _i64(b_stack), _i64(M), _i64(N), _i64(K),
             ctypes.c_int(int(ta)), ctypes.c_int(int(tb)), ctypes.c_int(int(to)),

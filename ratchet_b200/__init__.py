@@ -8,7 +8,8 @@ sm_100 device, the calls raise.
 from ._lib import InvariantError, RatchetError, ShapeError
 from ._lib import RT_EPILOGUE_GELU_TANH as EPILOGUE_GELU_TANH
 from ._lib import RT_EPILOGUE_NONE as EPILOGUE_NONE
-from .tensor import (Device, DeviceRequest, DType, Executable, GpuBuffer, Linear, Matmul, PinnedArray, Quantization, Quantizer,
+from ._lib import RT_EPILOGUE_SILU_MUL as EPILOGUE_SILU_MUL
+from .tensor import (Device, DeviceRequest, DType, Executable, GpuBuffer, Linear, Matmul, MLP, PinnedArray, Quantization, Quantizer,
                      Tensor, bf16_bits_to_f32, f32_to_bf16_bits, transcode_gguf_q8_0)
 
 from .sharded import Comm, ShardedLinear, shard_bounds, shard_rows
@@ -16,4 +17,4 @@ from .gguf import GGUF, TensorInfo
 
 __all__ = ["GGUF", "TensorInfo", "Comm", "ShardedLinear", "shard_bounds", "shard_rows", "Device", "DeviceRequest", "DType", "Executable", "GpuBuffer", "Linear", "Matmul", "PinnedArray", "Quantization",
            "Quantizer", "Tensor", "RatchetError", "ShapeError", "InvariantError", "EPILOGUE_NONE",
-           "EPILOGUE_GELU_TANH", "bf16_bits_to_f32", "f32_to_bf16_bits", "transcode_gguf_q8_0"]
+           "EPILOGUE_GELU_TANH", "EPILOGUE_SILU_MUL", "MLP", "bf16_bits_to_f32", "f32_to_bf16_bits", "transcode_gguf_q8_0"]

@@ -22,7 +22,7 @@ RT_OK, RT_ERR_SHAPE, RT_ERR_DTYPE, RT_ERR_INVARIANT, RT_ERR_ARG, RT_ERR_CUDA, RT
 # rt_dtype
 RT_F32, RT_F16, RT_BF16, RT_I32, RT_U32, RT_Q8_0H, RT_Q8_0F, RT_Q4_K = range(8)
 
-RT_EPILOGUE_NONE, RT_EPILOGUE_GELU_TANH = 0, 1
+RT_EPILOGUE_NONE, RT_EPILOGUE_GELU_TANH, RT_EPILOGUE_SILU_MUL = 0, 1, 2
 RT_LAUNCH_LHS_CONSTANT = 1
 
 
@@ -70,6 +70,19 @@ class rt_launch_opts(Structure):
 class rt_dispatch(Structure):
     _fields_ = [("plan", c_void_p), ("lhs", c_void_p), ("rhs", c_void_p), ("bias", c_void_p), ("out", c_void_p),
                 ("opts", rt_launch_opts)]
+
+
+class rt_usage_record(Structure):
+    _fields_ = [("size", c_uint64), ("producer", c_int32), ("last_consumer", c_int32)]
+
+
+class rt_node_tensors(Structure):
+    _fields_ = [("lhs", c_int32), ("rhs", c_int32), ("bias", c_int32), ("out", c_int32)]
+
+
+class rt_mlp_desc(Structure):
+    _fields_ = [("fc1", rt_matmul_desc), ("fc2", rt_matmul_desc), ("w1", c_void_p), ("b1", c_void_p),
+                ("w2", c_void_p), ("b2", c_void_p), ("x", c_void_p), ("out", c_void_p)]
 
 
 class rt_gguf_value(Structure):
@@ -154,6 +167,13 @@ def load() -> ctypes.CDLL:
         "rt_matmul_launch": (c_int32, [V, V, V, V, V, V]),
         "rt_matmul_launch_ex": (c_int32, [V, V, V, V, V, V, POINTER(rt_launch_opts)]),
         "rt_executable_create": (c_int32, [V, POINTER(rt_dispatch), c_int32, c_int32, POINTER(V)]),
+        "rt_executable_create_planned": (c_int32, [V, POINTER(rt_dispatch), POINTER(rt_node_tensors), c_int32,
+                                                   POINTER(c_uint64), c_int32, c_int32, POINTER(V)]),
+        "rt_executable_arena": (c_int32, [V, POINTER(c_uint64), POINTER(c_int32), POINTER(c_uint64)]),
+        "rt_executable_tensor": (V, [V, c_int32]),
+        "rt_mlp_create": (c_int32, [V, POINTER(rt_mlp_desc), c_int32, POINTER(V)]),
+        "rt_arena_plan": (c_int32, [POINTER(rt_usage_record), c_int32, c_uint64, POINTER(c_int32), POINTER(c_uint64),
+                                    POINTER(c_int32), POINTER(c_uint64)]),
         "rt_executable_dispatch": (c_int32, [V, V]),
         "rt_executable_destroy": (c_int32, [V]),
         "rt_executable_launches": (c_int32, [V]),

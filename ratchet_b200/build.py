@@ -18,6 +18,7 @@ INCLUDE = os.path.join(ROOT, "include")
 
 SOURCES = [
     "spec.cpp",
+    "arena.cpp",
     "quant_host.cpp",
     "gguf_reader.cpp",
     "comm.cpp",

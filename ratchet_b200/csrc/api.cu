@@ -7,12 +7,14 @@
 #include <cstddef>
 #include <cstdlib>
 #include <cstring>
+#include <memory>
 #include <mutex>
 #include <new>
 #include <string>
 #include <unordered_map>
 #include <vector>
 
+#include "arena.hpp"
 #include "kernels.hpp"
 #include "ratchet_b200.h"
 #include "spec.hpp"
@@ -91,6 +93,11 @@ struct rt_plan {
     uint64_t scratch_bytes = 0;
     void *act_scratch = nullptr; // bf16 activations cast to f16 (quantised weights only)
     uint64_t act_scratch_bytes = 0;
+    // RT_EPILOGUE_SILU_MUL on a route that does not fold the gate/up pairs itself: the plain node's [.., 2*ff] output
+    // goes here and an elementwise launch writes the [.., ff] result
+    bool pair = false;
+    void *pair_scratch = nullptr;
+    uint64_t pair_bytes = 0;
     int refs = 1;                // holders: the device's cache and every rt_matmul_plan call that returned this plan
     std::string key;             // its entry in the device's cache
     // Dequantised copies of weights the caller flagged RT_LAUNCH_LHS_CONSTANT, by weight pointer: the pre-pass then
@@ -98,9 +105,10 @@ struct rt_plan {
     std::mutex weights_mu;
     std::unordered_map<const void *, void *> kept_weights;
     ~rt_plan() {
-        if (scratch || act_scratch || !kept_weights.empty()) cudaSetDevice(dev->ordinal);
+        if (scratch || act_scratch || pair_scratch || !kept_weights.empty()) cudaSetDevice(dev->ordinal);
         if (scratch) cudaFree(scratch);
         if (act_scratch) cudaFree(act_scratch);
+        if (pair_scratch) cudaFree(pair_scratch);
         for (auto &kv : kept_weights) cudaFree(kv.second);
     }
 };
@@ -126,9 +134,21 @@ static std::string plan_key(const rt_matmul_desc &d) {
     return k;
 }
 
+// Scratch areas that take the place of a plan's own during one launch.
+struct ScratchSet {
+    void *scratch = nullptr, *act = nullptr, *pair = nullptr;
+};
+
 struct rt_executable {
     rt_device *dev = nullptr;
     std::vector<rt_dispatch> nodes;
+    // One allocation for every intermediate tensor and every node's plan scratch, placed by the activation planner
+    // (arena.cpp, the reference's BufferAllocator::greedy_by_size).
+    std::vector<ScratchSet> scratch; // per node: where its plan's scratch areas live in the arena
+    std::vector<void *> tensors;     // per intermediate: its address in the arena
+    void *arena = nullptr;
+    uint64_t arena_bytes = 0, record_bytes = 0;
+    int n_objects = 0;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     GemvChain *chain = nullptr; // the whole node list as one persistent kernel (gemv_q8_chain.cu)
@@ -136,6 +156,40 @@ struct rt_executable {
     std::string how = "nodes";
     int launches = 0;
 };
+
+// RT_KEEP_WEIGHTS=0: dequantise on every launch even for weights flagged constant (A/B timing, memory-tight callers).
+static bool keep_weights_enabled() {
+    const char *v = getenv("RT_KEEP_WEIGHTS");
+    return !(v && v[0] == '0');
+}
+
+// The dequantised copy the plan keeps of a constant weight, by weight pointer; *filled says whether an earlier
+// launch already wrote it.  A new weight gets its copy here unless the stream is capturing or memory is short
+// (nullptr: the caller uses scratch).
+static void *kept_weight_copy(rt_plan *plan, const void *lhs, cudaStream_t st, bool *filled) {
+    *filled = false;
+    if (!keep_weights_enabled()) return nullptr;
+    std::lock_guard<std::mutex> lk(plan->weights_mu);
+    auto it = plan->kept_weights.find(lhs);
+    if (it != plan->kept_weights.end()) {
+        *filled = true;
+        return it->second;
+    }
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    void *kept = nullptr;
+    if (cudaStreamIsCapturing(st, &cs) == cudaSuccess && cs == cudaStreamCaptureStatusNone &&
+        cudaMalloc(&kept, plan->scratch_bytes) == cudaSuccess) {
+        plan->kept_weights.emplace(lhs, kept);
+        std::lock_guard<std::mutex> dl(plan->dev->kept_mu);
+        plan->dev->kept_ptrs[lhs]++;
+        return kept;
+    }
+    cudaGetLastError(); // no room, or capturing
+    return nullptr;
+}
+
+static rt_status launch_node(rt_plan *plan, const void *lhs, const void *rhs, const void *bias, void *out, void *stream,
+                             const rt_launch_opts *opts, const ScratchSet *ov);
 
 #define CUDA_TRY(expr)                                                                              \
     do {                                                                                            \
@@ -252,6 +306,7 @@ rt_status rt_matmul_out_shape(const rt_matmul_desc *desc, rt_shape *out) {
     Status st = compute_c_shape(to_dims(desc->lhs_shape), to_dims(desc->rhs_shape), desc->trans_lhs != 0,
                                 desc->trans_rhs != 0, desc->trans_out != 0, &c);
     if (!st.ok()) return fail(st);
+    if (desc->epilogue == RT_EPILOGUE_SILU_MUL && !c.empty()) c.back() /= 2; // gate | up folded (see resolve_spec for the checks)
     if (!from_dims(c, out)) return fail(RT_ERR_SHAPE, "output rank exceeds RT_MAX_RANK");
     return RT_OK;
 }
@@ -452,11 +507,6 @@ static bool chain_enabled() {
 
 // RT_FORCE_KERNEL=simt keeps every node on the CUDA-core kernels (a debugging switch in the
 // spirit of the reference's RATCHET_* variables, gpu/device.rs:92-99).
-// RT_KEEP_WEIGHTS=0: dequantise on every launch even for weights flagged constant (A/B timing, memory-tight callers).
-static bool keep_weights_enabled() {
-    const char *v = getenv("RT_KEEP_WEIGHTS");
-    return !(v && v[0] == '0');
-}
 
 static bool force_simt() {
     const char *v = getenv("RT_FORCE_KERNEL");
@@ -714,6 +764,28 @@ static rt_status build_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan 
         pl->kernel = PK_GEMM_SIMT;
         pl->name = std::string("gemm_simt_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt);
     }
+    if (s.epilogue == RT_EPILOGUE_SILU_MUL) {
+        if (pl->kernel == PK_GEMM_UMMA && !pl->tf32x3) {
+            pl->name += "_silu_mul_paired_tiles"; // gate and up rows of a column meet in one tile
+        } else {
+            pl->pair = true;
+            pl->chain_ok = false;
+            p.epilogue = RT_EPILOGUE_NONE;
+            pl->pair_bytes = (uint64_t)(s.stacks * s.N * s.M) * dtype_size(s.out_dt);
+            if (pl->pair_bytes) {
+                cudaError_t e = cudaSetDevice(dev->ordinal);
+                if (e == cudaSuccess) e = cudaMalloc(&pl->pair_scratch, pl->pair_bytes);
+                if (e != cudaSuccess) {
+                    pl->pair_scratch = nullptr;
+                    delete pl;
+                    return fail(e == cudaErrorMemoryAllocation ? RT_ERR_NOMEM : RT_ERR_CUDA,
+                                std::string("plan scratch: ") + cudaGetErrorString(e));
+                }
+            }
+            pl->launches++;
+            pl->name += "+silu_mul";
+        }
+    }
     if (empty) pl->launches = 0;
     *plan = pl;
     return RT_OK;
@@ -744,7 +816,8 @@ rt_status rt_plan_forget_weights(rt_plan *plan) {
 // {sizeof(rt_shape), offsetof dims, sizeof(rt_segment), sizeof(rt_matmul_desc), offsetof lhs_shape, rhs_shape, bias_shape,
 //  has_bias, epilogue, sizeof(rt_gemm_spec), offsetof out_dt, lhs_stack, dim_inner, is_gemv, sizeof(rt_launch_opts), offsetof
 //  outs, out_ld, out_col, sizeof(rt_dispatch), offsetof opts, sizeof(rt_gguf_value), offsetof str,
-//  sizeof(rt_gguf_tensor_info), offsetof shape, nbytes}
+//  sizeof(rt_gguf_tensor_info), offsetof shape, nbytes, sizeof(rt_usage_record), offsetof producer, sizeof(rt_node_tensors),
+//  sizeof(rt_mlp_desc), offsetof fc2, w1, out}
 int32_t rt_abi_layout(uint64_t *out, int32_t n) {
     const uint64_t v[] = {
         sizeof(rt_shape), offsetof(rt_shape, dims), sizeof(rt_segment),
@@ -754,7 +827,9 @@ int32_t rt_abi_layout(uint64_t *out, int32_t n) {
         sizeof(rt_launch_opts), offsetof(rt_launch_opts, outs), offsetof(rt_launch_opts, out_ld), offsetof(rt_launch_opts, out_col),
         sizeof(rt_dispatch), offsetof(rt_dispatch, opts),
         sizeof(rt_gguf_value), offsetof(rt_gguf_value, str),
-        sizeof(rt_gguf_tensor_info), offsetof(rt_gguf_tensor_info, shape), offsetof(rt_gguf_tensor_info, nbytes)};
+        sizeof(rt_gguf_tensor_info), offsetof(rt_gguf_tensor_info, shape), offsetof(rt_gguf_tensor_info, nbytes),
+        sizeof(rt_usage_record), offsetof(rt_usage_record, producer), sizeof(rt_node_tensors),
+        sizeof(rt_mlp_desc), offsetof(rt_mlp_desc, fc2), offsetof(rt_mlp_desc, w1), offsetof(rt_mlp_desc, out)};
     const int32_t count = (int32_t)(sizeof(v) / sizeof(v[0]));
     for (int32_t i = 0; i < count && i < n; i++) out[i] = v[i];
     return count;
@@ -785,6 +860,14 @@ rt_status rt_matmul_launch(rt_plan *plan, const void *lhs, const void *rhs, cons
 
 rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, const void *bias, void *out, void *stream,
                               const rt_launch_opts *opts) {
+    return launch_node(plan, lhs, rhs, bias, out, stream, opts, nullptr);
+}
+
+} // extern "C"
+
+// One node's launches.  `ov` names scratch areas that take the place of the plan's own (an executable's arena).
+static rt_status launch_node(rt_plan *plan, const void *lhs, const void *rhs, const void *bias, void *out, void *stream,
+                             const rt_launch_opts *opts, const ScratchSet *ov) {
     if (!plan) return fail(RT_ERR_ARG, "rt_matmul_launch: null plan");
     const uint32_t flags = opts ? opts->flags : 0;
     const bool scatter = opts && opts->n_out > 0;
@@ -796,10 +879,17 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
             if (!opts->outs[d]) return fail(RT_ERR_ARG, "rt_matmul_launch_ex: null scatter destination");
     }
     const Spec &s = plan->spec;
+    if (scatter && s.epilogue == RT_EPILOGUE_SILU_MUL)
+        return fail(RT_ERR_UNSUPPORTED, "scattered outputs are not taken with RT_EPILOGUE_SILU_MUL");
     if (plan->launches == 0) return RT_OK; // empty output
-    if (!lhs || !rhs || (!out && !(opts && opts->n_out > 0)) || (s.has_bias && !bias))
+    void *const scratch = ov && ov->scratch ? ov->scratch : plan->scratch;
+    void *const act_scratch = ov && ov->act ? ov->act : plan->act_scratch;
+    void *const pair_scratch = ov && ov->pair ? ov->pair : plan->pair_scratch;
+    void *const user_out = out;
+    if (plan->pair) out = pair_scratch; // the plain node's [.., 2*ff] result; folded after the switch
+    if (!lhs || !rhs || (!user_out && !(opts && opts->n_out > 0)) || (s.has_bias && !bias))
         return fail(RT_ERR_ARG, "rt_matmul_launch: null operand");
-    if (out == lhs || out == rhs || (s.has_bias && out == bias))
+    if (user_out == lhs || user_out == rhs || (s.has_bias && user_out == bias))
         return fail(RT_ERR_INVARIANT, "Matmul is never in place: out aliases an operand");
     CUDA_TRY(cudaSetDevice(plan->dev->ordinal));
     cudaStream_t st = stream ? (cudaStream_t)stream : plan->dev->stream;
@@ -833,7 +923,7 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
         e = launch_matmul_simt(p, s.desc.lhs_dt, s.desc.rhs_dt, true, st);
         break;
     case PK_ROWVEC_MAT:
-        e = launch_rowvec_mat(p, s.desc.rhs_dt, plan->split, static_cast<float *>(plan->act_scratch), st);
+        e = launch_rowvec_mat(p, s.desc.rhs_dt, plan->split, static_cast<float *>(act_scratch), st);
         break;
     case PK_GEMM_SIMT:
         e = launch_matmul_simt(p, s.desc.lhs_dt, s.desc.rhs_dt, false, st);
@@ -843,13 +933,13 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
             if (scatter) return fail(RT_ERR_UNSUPPORTED, "scattered outputs are not taken by the f32 GEMM");
             const void *r32 = rhs;
             if (plan->rhs_transpose) {
-                e = launch_transpose(rhs, plan->act_scratch, (int)s.rhs_stack, (int)s.K, (int)s.N, (int)s.K, 4, st);
+                e = launch_transpose(rhs, act_scratch, (int)s.rhs_stack, (int)s.K, (int)s.N, (int)s.K, 4, st);
                 if (e != cudaSuccess) break;
-                r32 = plan->act_scratch;
+                r32 = act_scratch;
             }
             const void *P = plan->lhs_is_q ? r32 : lhs, *Q = plan->lhs_is_q ? lhs : r32;
             e = launch_gemm_umma_tf32x3(P, Q, out, plan->R, plan->S, (int)s.K, plan->u_stacks, plan->p_stack, plan->q_stack, p.bias,
-                                        p.bias_dt, s.has_bias ? BIAS_PER_N : BIAS_NONE, p.epilogue, plan->bn, plan->scratch,
+                                        p.bias_dt, s.has_bias ? BIAS_PER_N : BIAS_NONE, p.epilogue, plan->bn, plan->scratch ? scratch : nullptr,
                                         plan->dev->sm_count, st);
             break;
         }
@@ -857,36 +947,18 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
         rt_dtype w_dt = s.desc.lhs_dt;
         const int k_eff = plan->k_pad ? plan->k_pad : (int)s.K;
         if (plan->k_pad) {
-            e = launch_pad_rows16(lhs, plan->scratch, (long long)(s.lhs_stack * s.M), (int)s.K, plan->k_pad, plan->dev->sm_count, st);
+            e = launch_pad_rows16(lhs, scratch, (long long)(s.lhs_stack * s.M), (int)s.K, plan->k_pad, plan->dev->sm_count, st);
             if (e != cudaSuccess) break;
-            w = plan->scratch;
+            w = scratch;
         } else if (plan->scratch) {
             // A weight flagged constant is dequantised once and its f16 copy kept with the plan (the first launch with a
             // new weight allocates: make it outside any stream capture); any other lhs goes through the plan's own scratch
             // on every launch.
-            void *dst = plan->scratch;
+            void *dst = scratch;
             bool have = false;
-            if ((flags & RT_LAUNCH_LHS_CONSTANT) && keep_weights_enabled()) {
-                std::lock_guard<std::mutex> lk(plan->weights_mu);
-                auto it = plan->kept_weights.find(lhs);
-                if (it != plan->kept_weights.end()) {
-                    dst = it->second;
-                    have = true;
-                } else {
-                    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-                    void *kept = nullptr;
-                    if (cudaStreamIsCapturing(st, &cs) == cudaSuccess && cs == cudaStreamCaptureStatusNone &&
-                        cudaMalloc(&kept, plan->scratch_bytes) == cudaSuccess) {
-                        plan->kept_weights.emplace(lhs, kept);
-                        {
-                            std::lock_guard<std::mutex> dl(plan->dev->kept_mu);
-                            plan->dev->kept_ptrs[lhs]++;
-                        }
-                        dst = kept;
-                    } else {
-                        cudaGetLastError(); // no room, or capturing: this launch uses the plan's scratch
-                    }
-                }
+            if (flags & RT_LAUNCH_LHS_CONSTANT) {
+                void *kept = kept_weight_copy(plan, lhs, st, &have);
+                if (kept) dst = kept;
             }
             if (!have) {
                 e = launch_dequant(s.desc.lhs_dt, (long long)(s.lhs_stack * s.M * s.K), lhs, p.lhs_scales, dst, RT_F16,
@@ -899,13 +971,13 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
         const void *x = rhs;
         rt_dtype x_dt = s.desc.rhs_dt;
         if (plan->rhs_transpose) {
-            e = launch_transpose(rhs, plan->act_scratch, (int)s.rhs_stack, (int)s.K, (int)s.N, k_eff, 2, st);
+            e = launch_transpose(rhs, act_scratch, (int)s.rhs_stack, (int)s.K, (int)s.N, k_eff, 2, st);
             if (e != cudaSuccess) break;
-            x = plan->act_scratch;
+            x = act_scratch;
         } else if (plan->act_scratch) {
-            e = launch_cast_bf16_f16(rhs, plan->act_scratch, (long long)(s.rhs_stack * s.N * s.K), plan->dev->sm_count, st);
+            e = launch_cast_bf16_f16(rhs, act_scratch, (long long)(s.rhs_stack * s.N * s.K), plan->dev->sm_count, st);
             if (e != cudaSuccess) break;
-            x = plan->act_scratch;
+            x = act_scratch;
             x_dt = RT_F16;
         }
         const void *P = plan->lhs_is_q ? x : w, *Q = plan->lhs_is_q ? w : x;
@@ -925,36 +997,143 @@ rt_status rt_matmul_launch_ex(rt_plan *plan, const void *lhs, const void *rhs, c
         break;
     }
     }
+    if (e == cudaSuccess && plan->pair)
+        e = launch_silu_mul(pair_scratch, user_out, (long long)(s.stacks * s.N), (int)(s.M / 2), s.out_dt, plan->dev->sm_count, st);
     if (e != cudaSuccess) return fail(RT_ERR_CUDA, std::string("kernel launch (") + plan->name + "): " + cudaGetErrorString(e));
     return RT_OK;
 }
 
+extern "C" {
+
+
 static rt_status dispatch_nodes(rt_executable *exe, cudaStream_t st) {
-    for (auto &n : exe->nodes) {
-        rt_status s = rt_matmul_launch_ex(n.plan, n.lhs, n.rhs, n.bias, n.out, (void *)st, &n.opts);
+    for (size_t i = 0; i < exe->nodes.size(); i++) {
+        const rt_dispatch &n = exe->nodes[i];
+        rt_status s = launch_node(n.plan, n.lhs, n.rhs, n.bias, n.out, (void *)st, &n.opts, &exe->scratch[i]);
         if (s != RT_OK) return s;
     }
     return RT_OK;
 }
 
 rt_status rt_executable_create(rt_device *dev, const rt_dispatch *nodes, int32_t n_nodes, int32_t use_graph, rt_executable **exe) {
-    if (!dev || !exe || (n_nodes > 0 && !nodes) || n_nodes < 0) return fail(RT_ERR_ARG, "rt_executable_create: bad argument");
-    rt_executable *x = new (std::nothrow) rt_executable();
+    return rt_executable_create_planned(dev, nodes, nullptr, n_nodes, nullptr, 0, use_graph, exe);
+}
+
+rt_status rt_executable_create_planned(rt_device *dev, const rt_dispatch *nodes, const rt_node_tensors *ids, int32_t n_nodes,
+                                       const uint64_t *tensor_bytes, int32_t n_tensors, int32_t use_graph, rt_executable **exe) {
+    if (!dev || !exe || (n_nodes > 0 && !nodes) || n_nodes < 0 || n_tensors < 0 || (n_tensors > 0 && (!tensor_bytes || !ids)))
+        return fail(RT_ERR_ARG, "rt_executable_create: bad argument");
+    std::unique_ptr<rt_executable> x(new (std::nothrow) rt_executable());
     if (!x) return fail(RT_ERR_NOMEM, "out of host memory");
     x->dev = dev;
     for (int i = 0; i < n_nodes; i++) {
-        if (!nodes[i].plan || nodes[i].plan->dev != dev) {
-            delete x;
+        if (!nodes[i].plan || nodes[i].plan->dev != dev)
             return fail(RT_ERR_ARG, "rt_executable_create: node without a plan of this device");
-        }
-        if (nodes[i].out && (nodes[i].out == nodes[i].lhs || nodes[i].out == nodes[i].rhs ||
-                             (nodes[i].plan->spec.has_bias && nodes[i].out == nodes[i].bias))) {
-            delete x;
-            return fail(RT_ERR_INVARIANT, "Matmul is never in place: out aliases an operand");
-        }
         x->nodes.push_back(nodes[i]);
         x->launches += nodes[i].plan->launches;
     }
+    x->scratch.resize((size_t)n_nodes);
+    x->tensors.assign((size_t)n_tensors, nullptr);
+
+    // usage records (allocator.rs:168-207): intermediates first, then each node's scratch areas
+    std::vector<int> producer((size_t)n_tensors, -1), last((size_t)n_tensors, -1);
+    for (int i = 0; ids && i < n_nodes; i++) {
+        const rt_node_tensors &t = ids[i];
+        const int reads[3] = {t.lhs, t.rhs, x->nodes[(size_t)i].plan->spec.has_bias ? t.bias : -1};
+        for (int id : reads) {
+            if (id < 0) continue;
+            if (id >= n_tensors) return fail(RT_ERR_ARG, "rt_executable_create: intermediate id out of range");
+            if (producer[(size_t)id] < 0 || producer[(size_t)id] >= i)
+                return fail(RT_ERR_ARG, "rt_executable_create: node " + std::to_string(i) + " reads intermediate " +
+                                            std::to_string(id) + " before a node produced it");
+            last[(size_t)id] = i;
+        }
+        if (t.lhs >= 0 && (x->nodes[(size_t)i].opts.flags & RT_LAUNCH_LHS_CONSTANT))
+            return fail(RT_ERR_ARG, "rt_executable_create: an intermediate cannot be flagged RT_LAUNCH_LHS_CONSTANT");
+        if (t.out >= 0) {
+            if (t.out >= n_tensors) return fail(RT_ERR_ARG, "rt_executable_create: intermediate id out of range");
+            if (x->nodes[(size_t)i].opts.n_out > 0)
+                return fail(RT_ERR_ARG, "rt_executable_create: a scattered output cannot be an intermediate");
+            const Spec &sp = x->nodes[(size_t)i].plan->spec;
+            rt_segment seg[2];
+            int nseg = 0;
+            uint64_t need = 0;
+            Status st = dtype_segments(sp.out_dt, (uint64_t)numel(sp.out_shape), seg, &nseg);
+            if (!st.ok()) return fail(st);
+            for (int k = 0; k < nseg; k++) need += seg[k].size;
+            if (tensor_bytes[t.out] < need)
+                return fail(RT_ERR_ARG, "rt_executable_create: intermediate " + std::to_string(t.out) + " is smaller than node " +
+                                            std::to_string(i) + "'s output");
+            if (producer[(size_t)t.out] < 0) producer[(size_t)t.out] = i;
+            last[(size_t)t.out] = i;
+        }
+    }
+    // Weights flagged constant get their dequantised copy now (outside the capture below), filled on the device's
+    // stream and complete when this call returns; such a node then needs no dequantising scratch.
+    bool filled_any = false;
+    std::vector<bool> kept((size_t)n_nodes, false);
+    CUDA_TRY(cudaSetDevice(dev->ordinal));
+    for (int i = 0; i < n_nodes; i++) {
+        const rt_dispatch &n = x->nodes[(size_t)i];
+        rt_plan *pl = n.plan;
+        if (!(n.opts.flags & RT_LAUNCH_LHS_CONSTANT) || pl->kernel != PK_GEMM_UMMA || pl->tf32x3 || pl->k_pad || !pl->scratch ||
+            !n.lhs || pl->launches == 0)
+            continue;
+        bool filled = false;
+        void *copy = kept_weight_copy(pl, n.lhs, dev->stream, &filled);
+        if (!copy) continue;
+        if (!filled) {
+            const Spec &sp = pl->spec;
+            const void *scales = pl->lhs_scale_offset ? (const void *)((const char *)n.lhs + pl->lhs_scale_offset) : nullptr;
+            cudaError_t e = launch_dequant(sp.desc.lhs_dt, (long long)(sp.lhs_stack * sp.M * sp.K), n.lhs, scales, copy, RT_F16,
+                                           dev->sm_count, dev->stream);
+            if (e != cudaSuccess) return fail(RT_ERR_CUDA, std::string("dequantise (") + pl->name + "): " + cudaGetErrorString(e));
+            filled_any = true;
+        }
+        kept[(size_t)i] = true;
+    }
+    if (filled_any) CUDA_TRY(cudaStreamSynchronize(dev->stream));
+
+    std::vector<rt_usage_record> rec;
+    std::vector<void **> slot; // where each record's address goes
+    for (int k = 0; k < n_tensors; k++) {
+        if (producer[(size_t)k] < 0) continue; // never produced: never bound
+        rec.push_back({tensor_bytes[k], producer[(size_t)k], last[(size_t)k]});
+        slot.push_back(&x->tensors[(size_t)k]);
+    }
+    for (int i = 0; i < n_nodes; i++) {
+        const rt_plan *pl = x->nodes[(size_t)i].plan;
+        if (pl->launches == 0) continue;
+        ScratchSet &sc = x->scratch[(size_t)i];
+        if (pl->scratch_bytes && !kept[(size_t)i]) { rec.push_back({pl->scratch_bytes, i, i}); slot.push_back(&sc.scratch); }
+        if (pl->act_scratch_bytes) { rec.push_back({pl->act_scratch_bytes, i, i}); slot.push_back(&sc.act); }
+        if (pl->pair_bytes) { rec.push_back({pl->pair_bytes, i, i}); slot.push_back(&sc.pair); }
+    }
+    ArenaPlan ap;
+    Status pst = plan_arena(rec.data(), (int32_t)rec.size(), 256, &ap);
+    if (!pst.ok()) return fail(pst);
+    x->arena_bytes = ap.arena_bytes;
+    x->n_objects = (int)ap.object_bytes.size();
+    for (const rt_usage_record &r : rec) x->record_bytes += r.size;
+    if (ap.arena_bytes) {
+        cudaError_t e = cudaMalloc(&x->arena, ap.arena_bytes);
+        if (e != cudaSuccess) {
+            x->arena = nullptr;
+            return fail(e == cudaErrorMemoryAllocation ? RT_ERR_NOMEM : RT_ERR_CUDA, std::string("executable arena: ") + cudaGetErrorString(e));
+        }
+    }
+    for (size_t r = 0; r < rec.size(); r++) *slot[r] = (char *)x->arena + ap.offset[r];
+    for (int i = 0; ids && i < n_nodes; i++) {
+        rt_dispatch &n = x->nodes[(size_t)i];
+        if (ids[i].lhs >= 0) n.lhs = x->tensors[(size_t)ids[i].lhs];
+        if (ids[i].rhs >= 0) n.rhs = x->tensors[(size_t)ids[i].rhs];
+        if (ids[i].bias >= 0 && n.plan->spec.has_bias) n.bias = x->tensors[(size_t)ids[i].bias];
+        if (ids[i].out >= 0) n.out = x->tensors[(size_t)ids[i].out];
+    }
+    for (const rt_dispatch &n : x->nodes)
+        if (n.out && (n.out == n.lhs || n.out == n.rhs || (n.plan->spec.has_bias && n.out == n.bias)))
+            return fail(RT_ERR_INVARIANT, "Matmul is never in place: out aliases an operand");
+
     // A list of tensor-memory Q8_0 GEMVs over constant weights runs as one persistent kernel.
     if (use_graph && n_nodes >= 2 && chain_enabled()) {
         bool all = true;
@@ -970,27 +1149,24 @@ rt_status rt_executable_create(rt_device *dev, const rt_dispatch *nodes, int32_t
         if (all) {
             std::string why;
             cudaError_t e = gemv_chain_create(ps, dev->ordinal, dev->sm_count, &x->chain, &why);
-            if (e != cudaSuccess) {
-                delete x;
-                return fail(RT_ERR_CUDA, std::string("gemv_chain_create: ") + cudaGetErrorString(e));
-            }
+            if (e != cudaSuccess) return fail(RT_ERR_CUDA, std::string("gemv_chain_create: ") + cudaGetErrorString(e));
             if (x->chain) {
                 x->how = gemv_chain_name(x->chain);
                 x->launches = 1;
-                *exe = x;
+                *exe = x.release();
                 return RT_OK;
             }
         }
     }
     if (use_graph && x->launches > 0) {
         x->how = "graph";
-        cudaError_t e = cudaSetDevice(dev->ordinal);
+        cudaError_t e = cudaSuccess;
         cudaStream_t cap = nullptr;
-        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking);
+        e = cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking);
         if (e == cudaSuccess) e = cudaStreamBeginCapture(cap, cudaStreamCaptureModeRelaxed);
         rt_status rs = RT_OK;
         if (e == cudaSuccess) {
-            rs = dispatch_nodes(x, cap);
+            rs = dispatch_nodes(x.get(), cap);
             cudaError_t e2 = cudaStreamEndCapture(cap, &x->graph);
             if (rs == RT_OK) e = e2;
         }
@@ -998,13 +1174,68 @@ rt_status rt_executable_create(rt_device *dev, const rt_dispatch *nodes, int32_t
         if (cap) cudaStreamDestroy(cap);
         if (rs != RT_OK || e != cudaSuccess) {
             std::string msg = rs != RT_OK ? last_error() : std::string("graph capture: ") + cudaGetErrorString(e);
-            if (x->graph) cudaGraphDestroy(x->graph);
-            delete x;
             return fail(rs != RT_OK ? rs : RT_ERR_CUDA, msg);
         }
     }
-    *exe = x;
+    *exe = x.release();
     return RT_OK;
+}
+
+rt_status rt_executable_arena(const rt_executable *exe, uint64_t *arena_bytes, int32_t *n_objects, uint64_t *record_bytes) {
+    if (!exe) return fail(RT_ERR_ARG, "rt_executable_arena: null executable");
+    if (arena_bytes) *arena_bytes = exe->arena_bytes;
+    if (n_objects) *n_objects = exe->n_objects;
+    if (record_bytes) *record_bytes = exe->record_bytes;
+    return RT_OK;
+}
+
+void *rt_executable_tensor(const rt_executable *exe, int32_t id) {
+    if (!exe || id < 0 || (size_t)id >= exe->tensors.size()) return nullptr;
+    return exe->tensors[(size_t)id];
+}
+
+rt_status rt_mlp_create(rt_device *dev, const rt_mlp_desc *mlp, int32_t use_graph, rt_executable **exe) {
+    if (!dev || !mlp || !exe) return fail(RT_ERR_ARG, "rt_mlp_create: null argument");
+    for (const rt_matmul_desc *d : {&mlp->fc1, &mlp->fc2})
+        if (!(d->trans_rhs && d->trans_out && !d->trans_lhs))
+            return fail(RT_ERR_INVARIANT, "rt_mlp_create: fc1 and fc2 are Linear nodes (trans_rhs, trans_out)");
+    if (mlp->fc2.epilogue != RT_EPILOGUE_NONE) return fail(RT_ERR_ARG, "rt_mlp_create: fc2 carries no activation");
+    rt_plan *p1 = nullptr, *p2 = nullptr;
+    rt_status rs = rt_matmul_plan(dev, &mlp->fc1, &p1);
+    if (rs != RT_OK) return rs;
+    rs = rt_matmul_plan(dev, &mlp->fc2, &p2);
+    if (rs != RT_OK) {
+        rt_plan_destroy(p1);
+        return rs;
+    }
+    auto give_back = [&]() { rt_plan_destroy(p1); rt_plan_destroy(p2); };
+    // the hidden tensor is fc1's output and fc2's rhs
+    const Dims hid = p1->spec.out_shape, rhs2 = to_dims(mlp->fc2.rhs_shape);
+    if (hid != rhs2 || p1->spec.out_dt != mlp->fc2.rhs_dt) {
+        give_back();
+        return fail(RT_ERR_SHAPE, "rt_mlp_create: fc1 produces " + dims_str(hid) + " " + dtype_name(p1->spec.out_dt) + ", fc2 takes " +
+                                      dims_str(rhs2) + " " + dtype_name(mlp->fc2.rhs_dt));
+    }
+    rt_segment seg[2];
+    int nseg = 0;
+    uint64_t hidden_bytes = 0;
+    Status st = dtype_segments(p1->spec.out_dt, (uint64_t)numel(hid), seg, &nseg);
+    if (!st.ok()) {
+        give_back();
+        return fail(st);
+    }
+    for (int k = 0; k < nseg; k++) hidden_bytes += seg[k].size;
+    rt_dispatch nodes[2] = {};
+    nodes[0].plan = p1; nodes[0].lhs = mlp->w1; nodes[0].rhs = mlp->x; nodes[0].bias = mlp->b1;
+    nodes[0].opts.flags = RT_LAUNCH_LHS_CONSTANT;
+    nodes[1].plan = p2; nodes[1].lhs = mlp->w2; nodes[1].bias = mlp->b2; nodes[1].out = mlp->out;
+    nodes[1].opts.flags = RT_LAUNCH_LHS_CONSTANT;
+    const rt_node_tensors ids[2] = {{-1, -1, -1, 0}, {-1, 0, -1, -1}};
+    rs = rt_executable_create_planned(dev, nodes, ids, 2, &hidden_bytes, 1, use_graph, exe);
+    // The executable does not own plans; the device's cache keeps both alive until rt_device_destroy, so the
+    // holds taken here can go back at once.
+    give_back();
+    return rs;
 }
 
 rt_status rt_executable_dispatch(rt_executable *exe, void *stream) {
@@ -1034,6 +1265,10 @@ rt_status rt_executable_destroy(rt_executable *exe) {
     if (exe->exec) cudaGraphExecDestroy(exe->exec);
     if (exe->graph) cudaGraphDestroy(exe->graph);
     if (exe->chain) gemv_chain_destroy(exe->chain);
+    if (exe->arena) {
+        cudaSetDevice(exe->dev->ordinal);
+        cudaFree(exe->arena);
+    }
     delete exe;
     return RT_OK;
 }

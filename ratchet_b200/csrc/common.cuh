@@ -79,6 +79,24 @@ __device__ __forceinline__ OutT epilogue_value(float acc, bool has_bias, float b
     return v;
 }
 
+// sigmoid and silu of ops/unary.rs:121-131,165-175 in f32, branch for branch: exp(v) / (1 + exp(v)) for
+// v >= 0 (which is NaN once exp(v) overflows, v > 88.7, as it is in the reference's shader), 1 / (1 + exp(-v))
+// below zero.
+__device__ __forceinline__ float silu_ref_f32(float v) {
+    const float sg = v >= 0.f ? expf(v) / (1.0f + expf(v)) : 1.0f / (1.0f + expf(-v));
+    return v * sg;
+}
+
+// up * cast(silu(full(gate))) of crates/ratchet-models/src/phi3/mlp.rs:36 on values already rounded to the
+// output dtype: f16 rounds silu and then the product (the f32 product of two f16 values is exact, so one
+// rounding of it is the f16 multiply); f32 needs no rounding; bf16 (no reference counterpart) rounds the
+// product only.
+template <typename OutT> __device__ __forceinline__ OutT silu_mul_value(OutT gate, OutT up) {
+    const float sv = silu_ref_f32(to_f32(gate));
+    if (cuda::std::is_same<OutT, __half>::value) return from_f32<OutT>(to_f32(up) * to_f32(from_f32<OutT>(sv)));
+    return from_f32<OutT>(to_f32(up) * sv);
+}
+
 // Four int8 codes in a 32-bit word -> two half2 {c0,c1}, {c2,c3}, exact for every int8 value.
 // (code ^ 0x80) is the byte of 1024 + (code + 128) in binary16 (0x6400 | byte); subtracting 1152
 // leaves the signed code.

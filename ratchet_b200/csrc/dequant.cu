@@ -178,6 +178,35 @@ cudaError_t launch_pad_rows16(const void *src, void *dst, long long rows, int k,
     return launch_pdl(pad_rows16_kernel, dim3(blocks), dim3(256), 0, stream, (const uint16_t *)src, (uint4 *)dst, rows, k, k_pad);
 }
 
+// [rows][2*ff] (gate | up, as the plain Linear node leaves them) -> [rows][ff] = up * cast(silu(full(gate)))
+template <typename T>
+__global__ void __launch_bounds__(256) silu_mul_kernel(const T *__restrict__ full, T *__restrict__ out, long long rows, int ff) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const long long n = rows * ff, stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const long long r = i / ff;
+        const int c = (int)(i - r * ff);
+        const T *row = full + r * 2 * ff;
+        out[i] = silu_mul_value<T>(row[c], row[ff + c]);
+    }
+}
+
+cudaError_t launch_silu_mul(const void *full, void *out, long long rows, int ff, rt_dtype dt, int sm_count, cudaStream_t stream) {
+    const long long n = rows * ff;
+    if (n == 0) return cudaSuccess;
+    const long long want = (n + 255) / 256;
+    const int blocks = (int)(want < (long long)sm_count * 16 ? want : (long long)sm_count * 16);
+    switch (dt) {
+    case RT_F16: return launch_pdl(silu_mul_kernel<__half>, dim3(blocks), dim3(256), 0, stream, (const __half *)full, (__half *)out, rows, ff);
+    case RT_BF16:
+        return launch_pdl(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16 *)full,
+                          (__nv_bfloat16 *)out, rows, ff);
+    case RT_F32: return launch_pdl(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float *)full, (float *)out, rows, ff);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
 cudaError_t launch_cast_bf16_f16(const void *src, void *dst, long long numel, int sm_count, cudaStream_t stream) {
     if (numel == 0) return cudaSuccess;
     const long long n8 = numel / 8;

@@ -53,6 +53,11 @@ struct UmmaParams {
     const void *bias;
     int bias_dt, bias_mode; // BIAS_PER_N: index along S; BIAS_PER_M: index along R
     int epilogue;
+    // RT_EPILOGUE_SILU_MUL: Q is [2*ff][K], gate rows then up rows.  A tile's BN accumulator columns are BN/2 gate
+    // rows and the BN/2 up rows that pair with them (one 4-D copy whose third extent steps from the gate half to
+    // the up half), and the epilogue writes BN/2 output columns up * silu(gate): pair = 1, s_out = ff, and tiles
+    // advance by BN/2 output columns.  Otherwise pair = 0 and s_out = S.
+    int pair, s_out;
     int tiles_r, tiles_s;
     uint32_t idesc;
 };
@@ -109,6 +114,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, int c3, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
                  : "memory");
 }
 
@@ -217,14 +228,15 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
-                const int r0 = (rem % prm.tiles_r) * BM, s0 = (rem / prm.tiles_r) * BN;
+                const int r0 = (rem % prm.tiles_r) * BM, s0 = (rem / prm.tiles_r) * (prm.pair ? BN / 2 : BN);
                 const int bp = b % prm.p_stack, bq = b % prm.q_stack;
                 for (int kb = 0; kb < num_k; kb++) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, 1)) { ok = false; break; }
                     const uint32_t a_dst = smem_u32(tiles + stage * C::STAGE_BYTES);
                     mbar_expect_tx(bar_full + 8 * stage, C::STAGE_BYTES);
                     tma_load_3d(a_dst, &map_p, kb * BK, r0, bp, bar_full + 8 * stage);
-                    tma_load_3d(a_dst + C::A_BYTES, &map_q, kb * BK, s0, bq, bar_full + 8 * stage);
+                    if (prm.pair) tma_load_4d(a_dst + C::A_BYTES, &map_q, kb * BK, s0, 0, bq, bar_full + 8 * stage);
+                    else tma_load_3d(a_dst + C::A_BYTES, &map_q, kb * BK, s0, bq, bar_full + 8 * stage);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -264,8 +276,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
         const int ep_tid = threadIdx.x - 64;
         int acc = 0;
         uint32_t acc_phase = 0;
-        bool vec_ok = (prm.S % 8 == 0) && (prm.out_ld % 8 == 0) && (prm.out_col % 8 == 0) && (prm.out_batch_stride % 8 == 0);
-        bool pair_ok = (prm.S % 2 == 0) && (prm.out_ld % 2 == 0) && (prm.out_col % 2 == 0) && (prm.out_batch_stride % 2 == 0);
+        bool vec_ok = (prm.s_out % 8 == 0) && (prm.out_ld % 8 == 0) && (prm.out_col % 8 == 0) && (prm.out_batch_stride % 8 == 0);
+        bool pair_ok = (prm.s_out % 2 == 0) && (prm.out_ld % 2 == 0) && (prm.out_col % 2 == 0) && (prm.out_batch_stride % 2 == 0);
         for (int d = 0; d < prm.n_out; d++) {
             vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(prm.outs[d]) % 16 == 0);
             pair_ok = pair_ok && (reinterpret_cast<uintptr_t>(prm.outs[d]) % 4 == 0);
@@ -273,14 +285,18 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
         bool gave_up = false; // a wait of this warp ran out: it skips its work but stays in step with the other warps
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
-            const int r0 = (rem % prm.tiles_r) * BM, s0 = (rem / prm.tiles_r) * BN;
+            const int r0 = (rem % prm.tiles_r) * BM, s0 = (rem / prm.tiles_r) * (prm.pair ? BN / 2 : BN);
             // The eight warps leave together: the barrier hands every thread the OR of what each of them saw, so
             // none is left waiting at a barrier for a warp that has gone.
             if (bar_red_or(1, EPI_WARPS * 32, gave_up || *abort_flag != 0)) break;
             // bias values of this tile's columns, shared by the epilogue warps
             if (prm.bias_mode == BIAS_PER_N) {
-                for (int j = ep_tid; j < BN; j += EPI_WARPS * 32)
-                    bias_s[j] = (s0 + j < prm.S) ? load_bias(prm.bias, prm.bias_dt, s0 + j) : 0.f;
+                for (int j = ep_tid; j < BN; j += EPI_WARPS * 32) {
+                    // paired tiles: accumulator column j holds weight row (j / (BN/2)) * ff + s0 + j % (BN/2)
+                    const int jj = prm.pair ? j % (BN / 2) : j;
+                    const int wrow = prm.pair ? (j / (BN / 2)) * prm.s_out + s0 + jj : s0 + j;
+                    bias_s[j] = (s0 + jj < prm.s_out) ? load_bias(prm.bias, prm.bias_dt, wrow) : 0.f;
+                }
             }
             asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
             if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, 4)) { gave_up = true; continue; }
@@ -293,6 +309,69 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             // per-warp staging buffer so that global stores run along rows: 8 lanes x 16 B = one full
             // 128-byte line per row (this matters most when the destination is a peer GPU over NVLink)
             uint8_t *stg = stage_out + (warp - 2) * (32 * STG_ROW_BYTES);
+            if (prm.pair) {
+                // 32 output columns per round: the gate accumulators, the up accumulators BN/2 columns further on,
+                // up * silu(gate), then out through the staging rows (four 16-byte chunks each)
+#pragma unroll 1
+                for (int cc = half; cc < BN / 64; cc += 2) {
+                    const int colbase = s0 + cc * 32;
+                    uint32_t vg[32], vu[32];
+                    tmem_ld32(tmem_base + acc * BN + cc * 32 + ((uint32_t)(q * 32) << 16), vg);
+                    tmem_ld32(tmem_base + acc * BN + BN / 2 + cc * 32 + ((uint32_t)(q * 32) << 16), vu);
+                    if (cc + 2 >= BN / 64) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+                    }
+#pragma unroll
+                    for (int g = 0; g < 4; g++) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            float o[2];
+#pragma unroll
+                            for (int e = 0; e < 2; e++) {
+                                const int i = g * 8 + j * 2 + e;
+                                const float bg = has_bias ? bias_s[cc * 32 + i] : 0.f;
+                                const float bu = has_bias ? bias_s[BN / 2 + cc * 32 + i] : 0.f;
+                                const OutT gv = epilogue_value<OutT>(__uint_as_float(vg[i]), has_bias, bg, RT_EPILOGUE_NONE);
+                                const OutT uv = epilogue_value<OutT>(__uint_as_float(vu[i]), has_bias, bu, RT_EPILOGUE_NONE);
+                                o[e] = to_f32(silu_mul_value<OutT>(gv, uv));
+                            }
+                            w[j] = pack2<OutT>(o[0], o[1]);
+                        }
+                        *reinterpret_cast<uint4 *>(stg + lane * STG_ROW_BYTES + ((g ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                    __syncwarp();
+                    if (vec_ok) {
+                        const int colv = colbase + (lane & 3) * 8;
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const int rl = 8 * i + (lane >> 2);
+                            const int rg = r0 + q * 32 + rl;
+                            if (rg < prm.R && colv < prm.s_out) {
+                                const uint4 pk = *reinterpret_cast<const uint4 *>(stg + rl * STG_ROW_BYTES + (((lane & 3) ^ (rl & 7)) << 4));
+                                const long long off = (long long)b * prm.out_batch_stride + (long long)rg * prm.out_ld + prm.out_col + colv;
+                                for (int d = 0; d < prm.n_out; d++) *reinterpret_cast<uint4 *>(reinterpret_cast<OutT *>(prm.outs[d]) + off) = pk;
+                            }
+                        }
+                    } else {
+#pragma unroll 4
+                        for (int rl = 0; rl < 32; rl++) {
+                            const int rg = r0 + q * 32 + rl;
+                            if (rg >= prm.R) break;
+                            if (colbase + lane < prm.s_out) {
+                                const OutT o = *reinterpret_cast<const OutT *>(stg + rl * STG_ROW_BYTES + (((lane >> 3) ^ (rl & 7)) << 4) + (lane & 7) * 2);
+                                const long long off = (long long)b * prm.out_batch_stride + (long long)rg * prm.out_ld + prm.out_col + colbase + lane;
+                                for (int d = 0; d < prm.n_out; d++) reinterpret_cast<OutT *>(prm.outs[d])[off] = o;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                continue;
+            }
 #pragma unroll 1
             for (int cc = half; cc < BN / 64; cc += 2) {
                 const int colbase = s0 + cc * 64;
@@ -331,7 +410,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                     for (int i = 0; i < 8; i++) {
                         const int rl = 4 * i + (lane >> 3);
                         const int rg = r0 + q * 32 + rl;
-                        if (rg < prm.R && colv < prm.S) {
+                        if (rg < prm.R && colv < prm.s_out) {
                             const uint4 pk = *reinterpret_cast<const uint4 *>(stg + rl * STG_ROW_BYTES + (((lane & 7) ^ (rl & 7)) << 4));
                             const long long off = (long long)b * prm.out_batch_stride + (long long)rg * prm.out_ld + prm.out_col + colv;
                             for (int d = 0; d < prm.n_out; d++) *reinterpret_cast<uint4 *>(reinterpret_cast<OutT *>(prm.outs[d]) + off) = pk;
@@ -345,7 +424,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                         const int rg = r0 + q * 32 + rl;
                         if (rg >= prm.R) break;
                         const int col = 2 * lane;
-                        if (colbase + col < prm.S) {
+                        if (colbase + col < prm.s_out) {
                             const uint32_t o2 = *reinterpret_cast<const uint32_t *>(stg + rl * STG_ROW_BYTES + (((col >> 3) ^ (rl & 7)) << 4) + (col & 7) * 2);
                             const long long off = (long long)b * prm.out_batch_stride + (long long)rg * prm.out_ld + prm.out_col + colbase + col;
                             for (int d = 0; d < prm.n_out; d++) *reinterpret_cast<uint32_t *>(reinterpret_cast<OutT *>(prm.outs[d]) + off) = o2;
@@ -361,7 +440,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
 #pragma unroll
                         for (int k = 0; k < 2; k++) {
                             const int col = lane + 32 * k;
-                            if (colbase + col < prm.S) {
+                            if (colbase + col < prm.s_out) {
                                 const OutT o = *reinterpret_cast<const OutT *>(stg + rl * STG_ROW_BYTES + (((col >> 3) ^ (rl & 7)) << 4) + (col & 7) * 2);
                                 for (int d = 0; d < prm.n_out; d++) reinterpret_cast<OutT *>(prm.outs[d])[off + col] = o;
                             }
@@ -420,6 +499,21 @@ bool make_map(CUtensorMap *map, const void *base, rt_dtype dt, long long K, long
     return r == CUDA_SUCCESS;
 }
 
+// Q = [stack][2*ff][K] seen as [stack][2][ff][K]: one box of (64, box_rows, 2) brings box_rows gate rows and the
+// box_rows up rows ff further on, the gate rows first in shared memory; rows past ff read as zero
+bool make_pair_map(CUtensorMap *map, const void *base, rt_dtype dt, long long K, long long ff, long long stack, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[4] = {(cuuint64_t)K, (cuuint64_t)ff, 2, (cuuint64_t)stack};
+    cuuint64_t strides[3] = {(cuuint64_t)K * 2, (cuuint64_t)K * 2 * (cuuint64_t)ff, (cuuint64_t)K * 4 * (cuuint64_t)ff};
+    cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 2, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, dt == RT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 template <int BN, typename OutT>
 cudaError_t launch_bn(const CUtensorMap &mp, const CUtensorMap &mq, UmmaParams prm, int sm_count, cudaStream_t stream) {
     using C = Cfg<BN>;
@@ -430,7 +524,7 @@ cudaError_t launch_bn(const CUtensorMap &mp, const CUtensorMap &mq, UmmaParams p
         if (e != cudaSuccess) return e;
     }
     prm.tiles_r = (prm.R + BM - 1) / BM;
-    prm.tiles_s = (prm.S + BN - 1) / BN;
+    prm.tiles_s = prm.pair ? (prm.s_out + BN / 2 - 1) / (BN / 2) : (prm.S + BN - 1) / BN;
     // instruction descriptor: f32 accumulate, K-major A and B, N >> 3 at bit 17, M >> 4 at bit 24
     prm.idesc |= (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     const long long total = (long long)prm.tiles_r * prm.tiles_s * prm.stacks;
@@ -456,11 +550,16 @@ cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dty
     // kind::f16 wants one format for both operands: an instruction descriptor that mixes f16 and
     // bf16 is an illegal instruction on sm_100a
     if (p_dt != q_dt || (p_dt != RT_F16 && p_dt != RT_BF16)) return cudaErrorInvalidValue;
+    const bool pair = epilogue == RT_EPILOGUE_SILU_MUL;
+    if (pair && (S % 2 != 0 || bias_mode == BIAS_PER_M || (scatter && scatter->n_out > 0))) return cudaErrorInvalidValue;
     CUtensorMap mp, mq;
-    if (!make_map(&mp, P, p_dt, K, R, p_stack, BM) || !make_map(&mq, Q, q_dt, K, S, q_stack, bn))
+    if (!make_map(&mp, P, p_dt, K, R, p_stack, BM)) return cudaErrorInvalidValue;
+    if (!(pair ? make_pair_map(&mq, Q, q_dt, K, S / 2, q_stack, bn / 2) : make_map(&mq, Q, q_dt, K, S, q_stack, bn)))
         return cudaErrorInvalidValue;
     UmmaParams prm{};
     prm.R = R; prm.S = S; prm.K = K;
+    prm.pair = pair ? 1 : 0;
+    prm.s_out = pair ? S / 2 : S;
     prm.stacks = stacks; prm.p_stack = p_stack; prm.q_stack = q_stack;
     prm.out = out;
     if (scatter && scatter->n_out > 0) {
@@ -473,9 +572,9 @@ cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dty
     } else {
         prm.n_out = 1;
         prm.outs[0] = out;
-        prm.out_ld = S;
+        prm.out_ld = prm.s_out;
         prm.out_col = 0;
-        prm.out_batch_stride = (long long)R * S;
+        prm.out_batch_stride = (long long)R * prm.s_out;
     }
     prm.bias = bias; prm.bias_dt = bias_dt; prm.bias_mode = bias_mode;
     prm.epilogue = epilogue;

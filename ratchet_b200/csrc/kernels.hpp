@@ -115,6 +115,9 @@ cudaError_t launch_dequant(rt_dtype dt, long long numel, const void *src, const 
 
 // bf16 -> f16 (saturating) for the activations of a quantised-weight tensor-core GEMM.
 cudaError_t launch_cast_bf16_f16(const void *src, void *dst, long long numel, int sm_count, cudaStream_t stream);
+// [rows][2*ff] (gate | up) -> [rows][ff] = up * silu(gate), the second launch of a RT_EPILOGUE_SILU_MUL node on the routes
+// that do not fuse it
+cudaError_t launch_silu_mul(const void *full, void *out, long long rows, int ff, rt_dtype dt, int sm_count, cudaStream_t stream);
 // [stacks][rows][cols] -> [stacks][cols][dst_ld] (zero filled past `rows`), elements of 2 or 4 bytes: the pass that
 // makes an operand K-major; launch_pad_rows16 gives 16-bit rows a length that is a multiple of 8
 cudaError_t launch_transpose(const void *src, void *dst, int stacks, int rows, int cols, int dst_ld, int elem_size, cudaStream_t stream);

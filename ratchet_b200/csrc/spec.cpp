@@ -163,7 +163,7 @@ Status resolve_spec(const rt_matmul_desc &d, Spec *s) {
     if (d.lhs_shape.rank < 0 || d.lhs_shape.rank > RT_MAX_RANK || d.rhs_shape.rank < 0 ||
         d.rhs_shape.rank > RT_MAX_RANK)
         return Status::Err(RT_ERR_ARG, "rank out of range");
-    if (d.epilogue != RT_EPILOGUE_NONE && d.epilogue != RT_EPILOGUE_GELU_TANH)
+    if (d.epilogue != RT_EPILOGUE_NONE && d.epilogue != RT_EPILOGUE_GELU_TANH && d.epilogue != RT_EPILOGUE_SILU_MUL)
         return Status::Err(RT_ERR_ARG, "invalid epilogue");
     Dims a = to_dims(d.lhs_shape), b = to_dims(d.rhs_shape);
     bool tl = d.trans_lhs != 0, tr = d.trans_rhs != 0, to = d.trans_out != 0;
@@ -238,6 +238,15 @@ Status resolve_spec(const rt_matmul_desc &d, Spec *s) {
             o << "Bias length " << s->bias_len << " does not match the output dimension " << want;
             return Status::Err(RT_ERR_SHAPE, o.str());
         }
+    }
+    // gate/up pairs (phi3/mlp.rs:31-39): the Linear node's last output extent is the 2*ff rows of W, which the
+    // epilogue folds into ff
+    if (d.epilogue == RT_EPILOGUE_SILU_MUL) {
+        if (!(to && tr && !tl))
+            return Status::Err(RT_ERR_INVARIANT, "RT_EPILOGUE_SILU_MUL takes the Linear form (trans_rhs, trans_out) only");
+        if (s->M % 2 != 0)
+            return Status::Err(RT_ERR_SHAPE, "RT_EPILOGUE_SILU_MUL needs an even number of weight rows (gate | up)");
+        s->out_shape.back() = s->M / 2;
     }
     // block formats run along K inside a row (dtype/blocks.rs:61-74; gemm.rs:111,123)
     if ((d.lhs_dt == RT_Q8_0H || d.lhs_dt == RT_Q8_0F) && s->K % 32 != 0)

@@ -215,6 +215,48 @@ class Executable:
         self.launches = int(_lib.load().rt_executable_launches(self._h))
         self.kernel = _lib.load().rt_executable_kernel(self._h).decode()
 
+    @classmethod
+    def _adopt(cls, device: Device, handle: c_void_p, keep) -> "Executable":
+        self = cls.__new__(cls)
+        self.device, self._keep, self._h = device, list(keep), handle
+        self.launches = int(_lib.load().rt_executable_launches(handle))
+        self.kernel = _lib.load().rt_executable_kernel(handle).decode()
+        return self
+
+    @classmethod
+    def planned(cls, device: Device, nodes: Sequence[dict], tensor_bytes: Sequence[int], use_graph: bool = True,
+                keep=()) -> "Executable":
+        """An executable whose intermediates the library places in one arena (the reference's
+        BufferAllocator::allocate_cfg, allocator.rs:273-340).  Each node is a dict with `plan`
+        and, per operand lhs / rhs / bias / out, either a device pointer (int) or ("t", k) naming
+        intermediate k; `flags` optional."""
+        n = len(nodes)
+        arr = (_lib.rt_dispatch * n)()
+        ids = (_lib.rt_node_tensors * n)()
+        for i, nd in enumerate(nodes):
+            arr[i].plan = nd["plan"]
+            arr[i].opts.flags = int(nd.get("flags", 0))
+            for name in ("lhs", "rhs", "bias", "out"):
+                v = nd.get(name)
+                if isinstance(v, tuple):
+                    setattr(ids[i], name, int(v[1]))
+                else:
+                    setattr(ids[i], name, -1)
+                    setattr(arr[i], name, v)
+        sizes = (ctypes.c_uint64 * max(1, len(tensor_bytes)))(*[int(b) for b in tensor_bytes])
+        h = c_void_p()
+        check(_lib.load().rt_executable_create_planned(device._h, arr, ids, n, sizes, len(tensor_bytes), int(use_graph), byref(h)))
+        return cls._adopt(device, h, keep)
+
+    def arena(self) -> dict:
+        """Size of the executable's arena, the shared objects in it, and what its records add up to."""
+        a, o, r = ctypes.c_uint64(), ctypes.c_int32(), ctypes.c_uint64()
+        check(_lib.load().rt_executable_arena(self._h, byref(a), byref(o), byref(r)))
+        return {"arena_bytes": int(a.value), "objects": int(o.value), "record_bytes": int(r.value)}
+
+    def tensor_ptr(self, k: int) -> int:
+        return int(_lib.load().rt_executable_tensor(self._h, k) or 0)
+
     def dispatch(self) -> None:
         check(_lib.load().rt_executable_dispatch(self._h, None))
 
@@ -542,3 +584,61 @@ class Linear:
 
     def schedule(self, input: Tensor) -> Tensor:
         return self.w.gemm(input, self._bias_for(input.dt, input.device), False, True, True, self.epilogue)
+
+
+class MLP:
+    """The MLP block of the reference's models as ONE executable: hidden = act(fc1(x)), out = fc2(hidden).
+
+    `act` "gelu": Phi-2 `l2(l1(x).gelu())` (crates/ratchet-models/src/phi2/mlp.rs:13-15) and Whisper /
+    Moondream `fc2(fc1(x).full().gelu().cast())` (whisper/mlp.rs:18-22); `act` "silu_gate": Phi-3
+    `down(up * silu(gate.full()).cast())` with fc1 the gate_up projection (phi3/mlp.rs:31-39).
+    The hidden tensor is an intermediate of the executable placed by the activation planner."""
+
+    def __init__(self, fc1: Linear, fc2: Linear, act: str = "gelu"):
+        if act not in ("gelu", "silu_gate"):
+            raise ValueError(act)
+        self.fc1, self.fc2, self.act = fc1, fc2, act
+        self._exe = {}
+
+    def _desc(self, lin: Linear, x_shape, x_dt: DType, device: Device, epilogue: int) -> "_lib.rt_matmul_desc":
+        b = lin._bias_for(x_dt, device)
+        d = _lib.rt_matmul_desc()
+        d.lhs_dt, d.rhs_dt = int(lin.w.dt), int(x_dt)
+        d.lhs_shape, d.rhs_shape = _lib.rt_shape.of(lin.w.shape), _lib.rt_shape.of(x_shape)
+        d.has_bias = 0 if b is None else 1
+        if b is not None:
+            d.bias_dt, d.bias_shape = int(b.dt), _lib.rt_shape.of(b.shape)
+        d.trans_lhs, d.trans_rhs, d.trans_out, d.epilogue = 0, 1, 1, epilogue
+        return d
+
+    def bind(self, x: Tensor, use_graph: bool = True):
+        """(executable, out tensor) for this input tensor; the executable recomputes `out` from the
+        current contents of `x` at every dispatch."""
+        key = (x.ptr, tuple(x.shape), int(x.dt), use_graph)
+        if key in self._exe:
+            return self._exe[key]
+        dev = x.device
+        epi = _lib.RT_EPILOGUE_GELU_TANH if self.act == "gelu" else _lib.RT_EPILOGUE_SILU_MUL
+        m = _lib.rt_mlp_desc()
+        m.fc1 = self._desc(self.fc1, x.shape, x.dt, dev, epi)
+        hid = _lib.rt_shape()
+        check(_lib.load().rt_matmul_out_shape(byref(m.fc1), byref(hid)))
+        m.fc2 = self._desc(self.fc2, hid.tolist(), x.dt, dev, _lib.RT_EPILOGUE_NONE)
+        out_shape = _lib.rt_shape()
+        check(_lib.load().rt_matmul_out_shape(byref(m.fc2), byref(out_shape)))
+        out = Tensor(out_shape.tolist(), x.dt, dev, GpuBuffer(dev, x.dt.nbytes(int(np.prod(out_shape.tolist())))))
+        b1, b2 = self.fc1._bias_for(x.dt, dev), self.fc2._bias_for(x.dt, dev)
+        m.w1, m.w2, m.x, m.out = self.fc1.w.ptr, self.fc2.w.ptr, x.ptr, out.ptr
+        m.b1 = b1.ptr if b1 is not None else None
+        m.b2 = b2.ptr if b2 is not None else None
+        h = c_void_p()
+        check(_lib.load().rt_mlp_create(dev._h, byref(m), int(use_graph), byref(h)))
+        exe = Executable._adopt(dev, h, [x, out, b1, b2, self.fc1.w, self.fc2.w])
+        self._exe[key] = (exe, out)
+        return exe, out
+
+    def schedule(self, input: Tensor) -> Tensor:
+        """Module::schedule + resolve in one: dispatches the block and returns its output tensor."""
+        exe, out = self.bind(input)
+        exe.dispatch()
+        return out

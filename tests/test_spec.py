@@ -43,6 +43,8 @@ def test_public_structs_have_the_layout_the_ctypes_mirror_assumes():
         S(L.rt_dispatch), off(L.rt_dispatch, "opts"),
         S(L.rt_gguf_value), off(L.rt_gguf_value, "str"),
         S(L.rt_gguf_tensor_info), off(L.rt_gguf_tensor_info, "shape"), off(L.rt_gguf_tensor_info, "nbytes"),
+        S(L.rt_usage_record), off(L.rt_usage_record, "producer"), S(L.rt_node_tensors),
+        S(L.rt_mlp_desc), off(L.rt_mlp_desc, "fc2"), off(L.rt_mlp_desc, "w1"), off(L.rt_mlp_desc, "out"),
     ]
     assert n == len(want)
     assert [int(buf[i]) for i in range(n)] == want
@@ -285,3 +287,39 @@ def test_lazy_graph_shapes_without_a_device():
     z = rb.Linear(Tensor.from_data(np.ones((16, 64), dtype=np.float16))).schedule(y)
     assert z.shape == [2, 5, 16]
     assert z.execution_order()[-1] is z
+
+
+def test_silu_mul_epilogue_halves_the_linear_output_and_rejects_other_forms():
+    """RT_EPILOGUE_SILU_MUL (the gate/up fold of phi3/mlp.rs:31-39): only the Linear form takes it, the weight
+    has an even number of rows, and the node's output is [.., rows/2]."""
+    SILU = _lib.RT_EPILOGUE_SILU_MUL
+    st, s = _spec(_desc(DType.Q8_0H, DType.F16, [16384, 3072], [1, 7, 3072], False, True, True, epilogue=SILU))
+    assert st == _lib.RT_OK and s.out_shape.tolist() == [1, 7, 8192]
+    assert s.dim_lhs_outer == 16384 and s.dim_rhs_outer == 7 and s.dim_inner == 3072
+    out = _lib.rt_shape()
+    d = _desc(DType.F16, DType.F16, [64, 32], [5, 32], False, True, True, bias=[64], epilogue=SILU)
+    assert _lib.load().rt_matmul_out_shape(byref(d), byref(out)) == _lib.RT_OK and out.tolist() == [5, 32]
+    st, _ = _spec(_desc(DType.F16, DType.F16, [63, 32], [5, 32], False, True, True, epilogue=SILU))
+    assert st == _lib.RT_ERR_SHAPE
+    for trans in [(False, False, False), (False, True, False), (True, False, True)]:
+        a = [32, 64] if trans[0] else [64, 32]
+        b = [5, 32] if trans[1] else [32, 5]
+        st, _ = _spec(_desc(DType.F16, DType.F16, a, b, *trans, epilogue=SILU))
+        assert st == _lib.RT_ERR_INVARIANT, trans
+    st, _ = _spec(_desc(DType.F16, DType.F16, [64, 32], [5, 32], False, True, True, epilogue=3))
+    assert st == _lib.RT_ERR_ARG
+
+
+def test_oracle_silu_follows_the_two_branch_sigmoid():
+    """ops/unary.rs:121-131: exp(v)/(1+exp(v)) for v >= 0, which is NaN once exp(v) overflows; 1/(1+exp(-v)) below,
+    which underflows to -0 * ... = -0."""
+    import oracle
+    v = np.array([0.0, 1.0, -1.0, 20.0, -20.0, 88.0, 89.0, -100.0, 65504.0], dtype=np.float32)
+    s = oracle.silu_f32(v)
+    assert s[0] == 0.0 and abs(s[1] - 0.7310586) < 1e-6 and abs(s[2] + 0.26894143) < 1e-6
+    assert abs(s[3] - 20.0) < 1e-5 and abs(s[4]) < 1e-7 and abs(s[5] - 88.0) < 1e-4
+    assert np.isnan(s[6]) and np.isnan(s[8]) and s[7] == 0.0
+    full = np.array([[1.0, -2.0, 3.0, 0.5]], dtype=np.float32)  # gate = [1, -2], up = [3, 0.5]
+    got = oracle.silu_mul(full, "f16")
+    want = np.array([[3.0 * np.float16(0.7310586), 0.5 * np.float16(-2.0 * 0.11920292)]], dtype=np.float16)
+    assert np.array_equal(got.astype(np.float16), want)
