@@ -26,7 +26,7 @@ SOURCES = [
     "matmul_simt.cu",
     "gemv_q8_mma.cu",
     "gemv_q8_umma.cu", "gemv_q8_chain.cu",
-    "gemv_q4k_mma.cu",
+    "gemv_q4k_mma.cu", "gemv_q4k_umma.cu",
     "dequant.cu",
     "gemm_umma.cu", "gemm_umma_tf32.cu",
     "static_scratch.cu",

@@ -67,7 +67,7 @@ struct rt_buffer {
     uint64_t klass = 0; // bytes allocated
 };
 
-enum PlanKernel { PK_GEMM_SIMT, PK_GEMV_SIMT, PK_ROWVEC_MAT, PK_Q8_GEMV_MMA, PK_Q8_GEMV_UMMA, PK_Q4K_GEMV, PK_GEMM_UMMA };
+enum PlanKernel { PK_GEMM_SIMT, PK_GEMV_SIMT, PK_ROWVEC_MAT, PK_Q8_GEMV_MMA, PK_Q8_GEMV_UMMA, PK_Q4K_GEMV, PK_Q4K_GEMV_UMMA, PK_GEMM_UMMA };
 
 struct rt_plan {
     rt_device *dev = nullptr;
@@ -78,6 +78,7 @@ struct rt_plan {
     int split = 1;
     int nv = 1;
     GemvUmmaConfig gemv_umma{};
+    Q4kUmmaConfig q4k_umma{};
     int nv2 = 0;           // streaming Q8_0 kernel: vectors beyond the first launch's 8, taken 8 at a time (9..24 in all)
     bool chain_ok = false; // a Q8_0H x f16 GEMV the persistent chain kernel can take as a node
     MatmulParams params{}; // everything but the pointers
@@ -126,7 +127,7 @@ static std::string plan_key(const rt_matmul_desc &d) {
     put_shape(d.lhs_shape); put_shape(d.rhs_shape);
     if (d.has_bias) put_shape(d.bias_shape);
     put(d.has_bias != 0); put(d.trans_lhs != 0); put(d.trans_rhs != 0); put(d.trans_out != 0); put(d.epilogue);
-    for (const char *name : {"RT_FORCE_KERNEL", "RT_GEMV_UMMA", "RT_TF32_BN", "RT_TF32_PRESPLIT", "RT_Q4K_WALK_FROM", "RT_KEEP_WEIGHTS"}) {
+    for (const char *name : {"RT_FORCE_KERNEL", "RT_GEMV_UMMA", "RT_Q4K_UMMA", "RT_TF32_BN", "RT_TF32_PRESPLIT", "RT_Q4K_WALK_FROM", "RT_KEEP_WEIGHTS"}) {
         const char *v = getenv(name);
         k += '|';
         if (v) k += v;
@@ -376,6 +377,9 @@ rt_status rt_device_sync(rt_device *dev) {
         return fail(RT_ERR_CUDA, "a GEMV chain gave up a bounded wait (site " + std::to_string(site) + "): its outputs are incomplete");
     CUDA_TRY(gemv_q4k_take_error(&site, dev->stream));
     if (site != 0) return fail(RT_ERR_CUDA, "a Q4_K GEMV gave up waiting for its weight copies: its output is incomplete");
+    CUDA_TRY(gemv_q4k_umma_take_error(&site, dev->stream));
+    if (site != 0)
+        return fail(RT_ERR_CUDA, "a tensor-memory Q4_K GEMV gave up a bounded wait (site " + std::to_string(site) + "): its output is incomplete");
     CUDA_TRY(gemv_take_error(&site, dev->stream));
     if (site != 0) return fail(RT_ERR_CUDA, "a GEMV gave up waiting for its weight copies: its output is incomplete");
     return RT_OK;
@@ -507,6 +511,12 @@ static bool chain_enabled() {
 
 // RT_FORCE_KERNEL=simt keeps every node on the CUDA-core kernels (a debugging switch in the
 // spirit of the reference's RATCHET_* variables, gpu/device.rs:92-99).
+
+// RT_Q4K_UMMA=0 keeps Q4_K GEMVs on the warp-MMA kernel (A/B timing).
+static bool q4k_umma_enabled() {
+    const char *v = getenv("RT_Q4K_UMMA");
+    return !(v && v[0] == '0');
+}
 
 static bool force_simt() {
     const char *v = getenv("RT_FORCE_KERNEL");
@@ -647,6 +657,16 @@ static rt_status build_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan 
         pl->launches = 1 + (pl->nv2 + 7) / 8;
         pl->name = std::string("q8_gemv_mma_") + (desc->lhs_dt == RT_Q8_0H ? "h" : "f") + "_nv8+" + std::to_string(pl->nv2) +
                    "_split" + std::to_string(pl->split);
+    } else if (desc->lhs_dt == RT_Q4_K && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.N >= 1 && s.N <= 16 &&
+               (s.N == 1 || s.trans_rhs) && !empty && !force_simt() && s.stacks == 1 && q4k_umma_enabled() &&
+               (double)s.M * (double)s.K >= (double)(1 << 22) &&
+               q4k_gemv_umma_config(p.M, p.K, (int)s.N, dev->sm_count, &pl->q4k_umma)) {
+        // weights of a size that fills the machine: nibbles to int8 codes in shared memory, sums on the tensor cores
+        pl->kernel = PK_Q4K_GEMV_UMMA;
+        pl->nv = (int)s.N;
+        const Q4kUmmaConfig &c = pl->q4k_umma;
+        pl->name = std::string("q4k_gemv_umma_nv") + std::to_string(pl->nv) + "_rb" + std::to_string(c.rb) + "_split" + std::to_string(c.split) +
+                   "_ring" + std::to_string(c.raw_ring) + "x" + std::to_string(c.a_ring);
     } else if (desc->lhs_dt == RT_Q4_K && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.N >= 1 && s.N <= 16 &&
                (s.N == 1 || s.trans_rhs) && !empty && !force_simt() &&
                q4k_gemv_pick_split(p.M, p.K, (int)s.N, (int)s.stacks, dev->sm_count) > 0) {
@@ -913,6 +933,11 @@ static rt_status launch_node(rt_plan *plan, const void *lhs, const void *rhs, co
         if ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) % 16 != 0)
             return fail(RT_ERR_ARG, "rt_matmul_launch: lhs and rhs must be 16-byte aligned");
         e = launch_q4k_gemv(p, plan->nv, plan->split, (flags & RT_LAUNCH_LHS_CONSTANT) != 0, st);
+        break;
+    case PK_Q4K_GEMV_UMMA:
+        if ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) % 16 != 0)
+            return fail(RT_ERR_ARG, "rt_matmul_launch: lhs and rhs must be 16-byte aligned");
+        e = launch_q4k_gemv_umma(p, plan->nv, plan->q4k_umma, (flags & RT_LAUNCH_LHS_CONSTANT) != 0, st);
         break;
     case PK_Q8_GEMV_UMMA:
         if ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) % 16 != 0)

@@ -84,6 +84,16 @@ int q4k_gemv_pick_split(int M, int K, int nv, int stacks, int sm_count); // spli
 cudaError_t launch_q4k_gemv(const MatmulParams &p, int nv, int config, bool lhs_constant, cudaStream_t stream);
 cudaError_t gemv_q4k_take_error(int *site, cudaStream_t stream);
 
+// Q4_K GEMV / skinny GEMM through tensor memory (gemv_q4k_umma.cu): raw super-blocks by TMA, nibbles to int8 codes
+// in shared memory, tcgen05.mma kind::i8 against block-floating digits of the activations.
+struct Q4kUmmaConfig {
+    int split, clusters, rb, rb8, ks, raw_ring, a_ring, nvmax, b_bytes;
+    size_t smem_bytes;
+};
+bool q4k_gemv_umma_config(int M, int K, int nv, int sm_count, Q4kUmmaConfig *cfg);
+cudaError_t launch_q4k_gemv_umma(const MatmulParams &p, int nv, const Q4kUmmaConfig &cfg, bool lhs_constant, cudaStream_t stream);
+cudaError_t gemv_q4k_umma_take_error(int *site, cudaStream_t stream);
+
 // Dense f32 GEMM on the tensor cores, three TF32 MMAs per product (f32-class accuracy): D[R][S] = P[R][K] . Q[S][K]^T.
 bool umma_tf32_supported(long long K);
 int umma_tf32_pick_bn(int R, int S, int stacks, int sm_count);

@@ -131,14 +131,12 @@ class Device:
 
     def plan_for(self, desc: "_lib.rt_matmul_desc"):
         """The compiled-op cache: one plan per distinct node description (the KernelKey's role)."""
-        key = bytes(desc)
-        pl = self._plans.get(key)
-        if pl is None:
-            h = c_void_p()
-            check(_lib.load().rt_matmul_plan(self._h, byref(desc), byref(h)))
-            pl = h
-            self._plans[key] = pl
-        return pl
+        # the library keeps the cache (and keys it by the routing switches of the environment too); the hold this
+        # call takes goes straight back, the device's own keeps the plan alive as long as the device lives
+        h = c_void_p()
+        check(_lib.load().rt_matmul_plan(self._h, byref(desc), byref(h)))
+        check(_lib.load().rt_plan_destroy(h))
+        return h
 
     def __repr__(self):
         return "Device::CPU" if not self.is_gpu() else f"Device::GPU({self.ordinal})"

@@ -520,8 +520,9 @@ def test_q4k_phi3_shapes(gpu, M):
     check_problem(Problem(Q4K, F16, (8192, 3072), (1, M, 3072), (False, True, True), seed=104, w_std=0.02), gpu)
 
 
-def test_q4k_gemv_shapes_and_vectors(gpu):
+def test_q4k_gemv_shapes_and_vectors(gpu, monkeypatch):
     """The streaming Q4_K kernel: ragged rows, K slices over a cluster, 1..16 activation vectors, both output orders."""
+    monkeypatch.setenv("RT_Q4K_UMMA", "0")
     for N, K in [(16, 256), (37, 512), (1000, 1024), (3072, 8192), (5, 4096)]:
         _, kernel = check_problem(Problem(Q4K, F16, (N, K), (1, K), (False, True, True), bias=True, seed=N + K, w_std=0.02), gpu)
         assert kernel.startswith("q4k_gemv_mma"), kernel
@@ -534,10 +535,11 @@ def test_q4k_gemv_shapes_and_vectors(gpu):
     check_problem(Problem(Q4K, F16, (64, 512), (4, 1, 512), (False, True, True), seed=92, w_std=0.02), gpu)     # broadcast weight
 
 
-def test_q4k_skinny_gemm_walks_row_groups(gpu):
+def test_q4k_skinny_gemm_walks_row_groups(gpu, monkeypatch):
     """More row groups than SMs and 2..16 vectors: a CTA keeps the activations and walks several row
     groups (two at a time, one per half of its warps).  Ragged last group, a last CTA with fewer
     groups, both output orders, bias + GELU, K split over a cluster, batched weights."""
+    monkeypatch.setenv("RT_Q4K_UMMA", "0")
     for nv in (2, 5, 8, 9, 16):
         for to in (True, False):
             _, kernel = check_problem(Problem(Q4K, F16, (2405, 768), (1, nv, 768), (False, True, to), bias=True, epilogue=1,
@@ -549,6 +551,55 @@ def test_q4k_skinny_gemm_walks_row_groups(gpu):
     assert "walk4" in kernel, kernel
     _, kernel = check_problem(Problem(Q4K, F16, (8192, 3072), (1, 8, 3072), (False, True, True), seed=198, w_std=0.02), gpu)
     assert "nv8_split1_walk4x4buf" in kernel, kernel
+
+
+@pytest.mark.parametrize("wshape,nv,name", [
+    ((8192, 3072), 1, "nv1_rb111_split2"),     # Phi-3 decode: 74 clusters of two CTAs, 111 rows each
+    ((8192, 3072), 16, "nv16_rb111_split2"),
+    ((3072, 8192), 1, "nv1_rb84_split4"),      # the down projection: K = 8192 over clusters of four
+    ((3072, 8192), 5, "nv5_rb84_split4"),
+    ((16384, 3072), 3, "nv3_rb111_split1"),    # more rows than 148 x 111: one CTA per cluster
+    ((8191, 1024), 8, "nv8_"),                 # ragged last cluster
+    ((5000, 2048), 9, "nv9_"),
+    ((4100, 8192), 16, "nv16_"),
+])
+def test_q4k_gemv_through_tensor_memory(gpu, wshape, nv, name):
+    """Q4_K weights of a size that fills the machine: raw super-blocks by TMA, nibbles to int8 codes in shared
+    memory, tcgen05.mma against the activations' digits.  1..16 vectors, both output orders, bias and GELU."""
+    for to in ((True, False) if nv > 1 else (True,)):
+        _, kernel = check_problem(Problem(Q4K, F16, wshape, (1, nv, wshape[1]), (False, True, to), bias=True, epilogue=nv % 2,
+                                          seed=300 + nv + wshape[0], w_std=0.02), gpu)
+        assert kernel.startswith("q4k_gemv_umma") and name in kernel, kernel
+    if nv == 1:  # the vector form of the reference's GEMV call: rhs [K], no transposes
+        _, kernel = check_problem(Problem(Q4K, F16, wshape, (wshape[1],), (False, False, False), seed=77, w_std=0.02), gpu)
+        assert kernel.startswith("q4k_gemv_umma"), kernel
+
+
+def test_q4k_gemv_through_tensor_memory_matches_the_streaming_kernel_and_propagates_nan(gpu, monkeypatch):
+    """Same weights, same activations through both Q4_K kernels: within the bar of each other on finite inputs; a NaN
+    and infinities in the activations come out as IEEE arithmetic on the decoded weights gives them (0 * inf and
+    inf - inf are NaN, anything else with an infinity is that infinity)."""
+    M, K, nv = 8192, 3072, 4
+    w_t, wv = make_lhs(Q4K, (M, K), np.random.default_rng(411), 0.02)
+    x = round_to(F16, np.random.default_rng(412).standard_normal((nv, K)).astype(np.float32))
+    x[0, 5], x[1, 700], x[1, 701], x[2, 3000] = np.nan, np.inf, -np.inf, np.inf  # vector 3 stays finite
+    w_d, x_d = w_t.to(gpu), Tensor.from_data(x, gpu, F16)
+    node = w_d.gemm(x_d, None, False, True, True)
+    assert rb._lib.load().rt_plan_kernel(gpu.plan_for(node.op.desc)).decode().startswith("q4k_gemv_umma")
+    y_new = node.resolve().to(Device.CPU).to_f32().reshape(nv, M)
+    with np.errstate(invalid="ignore"):
+        want = (wv.astype(np.float64) @ x.astype(np.float64).T).T  # [nv][M]
+    assert np.array_equal(np.isnan(y_new), np.isnan(want))
+    assert np.all(np.isnan(y_new[0])) and np.isnan(y_new[1]).sum() > M // 4 and np.isinf(y_new[2]).sum() > M // 2
+    inf = np.isinf(want)
+    assert np.array_equal(np.isinf(y_new), inf) and np.array_equal(np.sign(y_new[inf]), np.sign(want[inf]))
+    fin = np.isfinite(want)
+    assert oracle.rel_l2(y_new[fin], oracle.f64_to_f16(want[fin]).astype(np.float32)) <= TOL[F16]
+    monkeypatch.setenv("RT_Q4K_UMMA", "0")
+    node_old = w_d.gemm(x_d, None, False, True, True)
+    assert rb._lib.load().rt_plan_kernel(gpu.plan_for(node_old.op.desc)).decode().startswith("q4k_gemv_mma")
+    y_old = node_old.resolve().to(Device.CPU).to_f32().reshape(nv, M)
+    assert oracle.rel_l2(y_new[3], y_old[3]) <= 2e-3
 
 
 def test_q4k_forms(gpu):
