@@ -64,7 +64,7 @@ def parse_args():
     ap.add_argument("--no-lazy", action="store_true", help="skip the node-by-node lazy-graph leg reported beside e2e")
     ap.add_argument("--no-sharded", action="store_true", help="with --gpus > 1: skip the N-sharded prefill GEMM section")
     ap.add_argument("--extras", default="all", help="comma list of the other workloads to time on one GPU and "
-                    "report under \"extras\": c1,c3,c4,c5,c5long, all (default) or none")
+                    "report under \"extras\": c1,c3,c4,c5,c5long,mlp, all (default) or none")
     return ap.parse_args()
 
 
@@ -270,6 +270,32 @@ def run_extras(which, gpu, stream):
             nbytes = 14155776 + 2 * M * 3072 + 2 * M * 8192
             record(f"c4_q4_k_phi3_m{M}", us, k, l, 2 * M * 8192 * 3072, nbytes, "tensor" if M == 512 else "hbm",
                    "rotating 20 weight copies")
+    if "mlp" in which:
+        # Phi-3 mini MLP block as ONE executable (rt_mlp_create): gate_up [16384,3072] -> up * silu(gate) -> down [3072,8192]
+        copies = 3  # 3 x 80 MB of weights: larger than L2
+        blocks = [rb.MLP(rb.Linear(weight((16384, 3072), DType.Q8_0H, 1201 + c).to(gpu)),
+                         rb.Linear(weight((3072, 8192), DType.Q8_0H, 1301 + c).to(gpu)), act="silu_gate") for c in range(copies)]
+        import torch
+        for M in (1, 16, 512):
+            x = act((1, M, 3072), DType.F16, 1400 + M).to(gpu)
+            bound = [blk.bind(x) for blk in blocks]
+            for exe, _ in bound:
+                exe.dispatch()
+            gpu.sync()
+            reps = 20 if M < 512 else 10
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                for exe, _ in bound:
+                    exe.dispatch()
+            e1.record(stream)
+            gpu.sync()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / reps / copies
+            wbytes = (16384 * 3072 + 3072 * 8192) * 34 // 32
+            record(f"mlp_phi3_q8_0_block_m{M}", us, bound[0][0].kernel, bound[0][0].launches,
+                   2 * M * (16384 * 3072 + 3072 * 8192), wbytes + 2 * M * (3072 + 3072), "tensor" if M == 512 else "hbm",
+                   "gate_up + SiLU*mul + down as one executable, hidden tensor in the executable's arena; rotating 3 weight sets")
     for name, rows in (("c5", 2048), ("c5long", 8192)):
         if name not in which:
             continue
@@ -415,18 +441,23 @@ def cpu_step(weights_raw, x16, layers):
 
 
 def time_cpu(weights_raw, x16, budget_s: float, max_layers: int):
-    """Times a bounded sample: as many whole layers as fit the budget, at least one."""
+    """Times a bounded sample of the workload: whole decode steps (all `max_layers` layers) repeated until about
+    `budget_s` seconds of CPU work are done; when one step alone is longer than the budget, as many of its layers as
+    fit.  Returns GB/s, the layers per pass, the passes and the seconds."""
     import oracle
     oracle.lib()
+    cpu_step(weights_raw, x16, 1)  # warm-up (threads start, pages fault in)
     t0 = time.perf_counter()
-    cpu_step(weights_raw, x16, 1)  # warm-up, and a cost estimate per layer
+    cpu_step(weights_raw, x16, 1)  # cost estimate per layer
     per_layer = time.perf_counter() - t0
     layers = int(max(1, min(max_layers, budget_s / max(per_layer, 1e-6))))
+    passes = int(max(1, budget_s / max(per_layer * layers, 1e-6)))
     t0 = time.perf_counter()
-    cpu_step(weights_raw, x16, layers)
+    for _ in range(passes):
+        cpu_step(weights_raw, x16, layers)
     dt = time.perf_counter() - t0
-    gbs = layers * 2 * BYTES_PER_GEMV / dt / 1e9
-    return gbs, layers, dt
+    gbs = passes * layers * 2 * BYTES_PER_GEMV / dt / 1e9
+    return gbs, layers, passes, dt
 
 
 def base_config(layers):
@@ -673,13 +704,14 @@ def main():
             import oracle
             oracle.use_all_cores()
             raw = [(a.to_numpy(), b.to_numpy()) for a, b in host_w]
-            gbs, l_used, dt = time_cpu(raw, x_pin.array.reshape(-1).copy(), budget_s=15.0, max_layers=layers)
+            gbs, l_used, passes, dt = time_cpu(raw, x_pin.array.reshape(-1).copy(), budget_s=15.0, max_layers=layers)
             line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
-                                    "sample": f"{l_used} of {layers} layers of one decode step ({2 * l_used} GEMVs) in {dt:.2f} s, C oracle with OpenMP"}
+                                    "sample": f"{passes} passes over {l_used} of the {layers} layers of one decode step "
+                                              f"({passes * 2 * l_used} GEMVs, {dt:.1f} s of CPU work), C oracle with OpenMP"}
         if sharded is not None:
             line["sharded"] = sharded
         if args.extras != "none" and world == 1:
-            which = {"c1", "c3", "c4", "c5", "c5long"} if args.extras == "all" else set(args.extras.split(","))
+            which = {"c1", "c3", "c4", "c5", "c5long", "mlp"} if args.extras == "all" else set(args.extras.split(","))
             line["extras"] = run_extras(which, gpu, stream)
         print(json.dumps(line), flush=True)
     if world > 1:

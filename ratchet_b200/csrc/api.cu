@@ -512,10 +512,13 @@ static bool chain_enabled() {
 // RT_FORCE_KERNEL=simt keeps every node on the CUDA-core kernels (a debugging switch in the
 // spirit of the reference's RATCHET_* variables, gpu/device.rs:92-99).
 
-// RT_Q4K_UMMA=0 keeps Q4_K GEMVs on the warp-MMA kernel (A/B timing).
+// RT_Q4K_UMMA=1 sends large Q4_K GEMVs through tensor memory (gemv_q4k_umma.cu).  Off by default: measured on
+// [8192,3072] it is faster than the warp-MMA kernel only with two vectors (10.1 against 11.1 us; 9.0 against 8.3 us with
+// one, 26 against 17 us with sixteen): unpacking nibbles to int8 codes moves 5.5 bytes through shared memory per weight
+// byte, and a CTA that needs the SM to itself cannot overlap the next launch's prologue with this one's tail.
 static bool q4k_umma_enabled() {
     const char *v = getenv("RT_Q4K_UMMA");
-    return !(v && v[0] == '0');
+    return v && v[0] == '1';
 }
 
 static bool force_simt() {

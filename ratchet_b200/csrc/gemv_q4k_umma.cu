@@ -46,16 +46,36 @@ namespace {
 
 using namespace umma_gemv;
 
-constexpr int UNPACK_WARPS = 8, EPI_WARPS = 8;
-constexpr int THREADS = 64 + 32 * (UNPACK_WARPS + EPI_WARPS); // warp 0 producer, warp 1 MMA issuer, 2..9 unpack, 10..17 epilogue
+constexpr int N_ISSUE = 2;      // MMA-issuing warps: warp 1 takes the first 128 values of every super-block, warp 2 the second
+constexpr int UNPACK_WARPS = 8; // warps 4..11
+constexpr int FIRST_UNPACK = 4, FIRST_EPI = FIRST_UNPACK + UNPACK_WARPS;
 constexpr int SB_BYTES = 144;
-constexpr int TMEM_COLS = 512;
 constexpr int MAX_KS = 4096; // K elements per CTA at most (128 blocks: four mask words per vector)
+
+// Epilogue warps: four (one per tensor-memory lane quarter, all eight sub-blocks each) up to eight vectors, eight
+// (two per quarter, four sub-blocks each) beyond.
+template <int NV> struct Roles {
+    static constexpr int EPI_WARPS = NV <= 8 ? 4 : 8;
+    static constexpr int THREADS = 32 * (FIRST_EPI + EPI_WARPS);
+    static constexpr int BLOCKS_PER_WARP = 32 / EPI_WARPS; // sub-blocks of a super-block one epilogue warp takes
+    static constexpr int NB = NV <= 8 ? 16 : 32;           // N of the MMA = accumulator columns per sub-block
+    // Digit rows stored per 128 bytes of K: up to four vectors fill one 8-row group, which the MMA reads twice (group
+    // stride 0: its columns 8..15 repeat 0..7 and are never read).
+    static constexpr int B_ROWS = NV <= 4 ? 8 : NB;
+    // Up to four vectors a CTA takes half of an SM's tensor memory (two super-blocks in flight) and, up to two, at most
+    // half of its shared memory and registers, so that the next launch's CTA is resident beside it with its first
+    // weights loaded while this one computes.
+    static constexpr int TMEM_COLS = NV <= 4 ? 256 : 512;
+    static constexpr int CTAS_PER_SM = NV <= 2 ? 2 : 1;
+    static constexpr int LD_COLS = 2 * NV < 16 ? 2 * NV : 16;   // columns per tensor-memory load
+    static constexpr int LOADS = 2 * NV / LD_COLS;              // loads per sub-block (two for sixteen vectors)
+    // sub-blocks whose sums a warp fetches before it waits once and does their arithmetic: 32 registers' worth
+    static constexpr int BATCH = (32 / (2 * NV) < 1 ? 1 : 32 / (2 * NV)) < BLOCKS_PER_WARP ? (32 / (2 * NV) < 1 ? 1 : 32 / (2 * NV)) : BLOCKS_PER_WARP;
+};
 
 struct Q4kUmmaParams {
     MatmulParams p;
     int nv;            // activation vectors, 1..16
-    int nb;            // digit rows of the MMA's B operand: 16 (nv <= 8) or 32
     int rb, rb8;       // rows per cluster, rounded up to 8
     int ks, nsb;       // K elements per CTA, super-blocks per CTA
     int split;         // cluster size along K
@@ -67,8 +87,29 @@ struct Q4kUmmaParams {
     int lhs_constant;
 };
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site) {
+__device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site) {
     return mbar_wait_flag(bar, parity, abort_flag, site, &g_gemv_q4k_umma_error);
+}
+
+// Bounded wait.  The waiting warp sleeps between tries: a spinning warp's tries go through the same shared-memory
+// instruction queue as the loads and stores of the warps that unpack nibbles, and take issue slots from the MMA
+// issuers, whose instruction chains are this kernel's pace-makers.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = wait_clock();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 64; i++) {
+            __nanosleep(32);
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (*abort_flag) return false;
+        if (wait_clock() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            atomicCAS(&g_gemv_q4k_umma_error, 0, site);
+            return false;
+        }
+    }
 }
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
@@ -76,11 +117,22 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, int *v) { // sixteen columns, no wait
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-                 : "r"(taddr) : "memory");
+// N consecutive accumulator columns of this warp's 32 lanes into v[0..N), no wait (N = 2, 4, 8 or 16).
+template <int N> __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, int *v) {
+    if constexpr (N == 2) {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(v[0]), "=r"(v[1]) : "r"(taddr) : "memory");
+    } else if constexpr (N == 4) {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(taddr) : "memory");
+    } else if constexpr (N == 8) {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "r"(taddr) : "memory");
+    } else {
+        static_assert(N == 16, "column count");
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                       "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                     : "r"(taddr) : "memory");
+    }
 }
 
 // An s32 of magnitude below 2^22 as a float, without the (quarter-rate) conversion instruction: the integer is
@@ -88,11 +140,11 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, int *v) { // sixteen
 __device__ __forceinline__ float small_int_to_float(int v) { return __int_as_float(0x4B400000 + v) - 12582912.0f; }
 
 // Shared-memory map (offsets from a 1024-byte aligned base):
-//   [code ring: a_ring x {chunk 0: rb8 x 128, chunk 1: rb8 x 128}][digit tiles: (ks/128) x nb rows x 128; at least
+//   [code ring: a_ring x {chunk 0: rb8 x 128, chunk 1: rb8 x 128}][digit tiles: (ks/128) x 2 NV rows x 128; at least
 //   (128 - rb8) x 128 bytes, because every MMA reads 128 rows][raw ring: raw_ring x rb8 x 144][headers: a_ring x
-//   rb8 x 16][xs: nv x ks/32][sumx: nv x ks/32][part: 2 x NV x 128][red: split x NV x 128][mask][barriers]
+//   rb8 x 16][xs: NV x 128][sumx: NV x 128][part: 2 x NV x 128][red: split x NV x 128][mask][barriers]
 template <int NV>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(Roles<NV>::THREADS, Roles<NV>::CTAS_PER_SM)
 q4k_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const Q4kUmmaParams up) {
     extern __shared__ uint8_t smem_raw[];
     const MatmulParams &p = up.p;
@@ -102,7 +154,9 @@ q4k_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const Q4kUmmaPar
     const int row_begin = cluster_id * up.rb;
     if (row_begin >= p.M) return; // the whole cluster leaves together: nothing has been set up yet
 
-    constexpr int NB = NV * 2;              // digit rows = accumulator columns per sub-block
+    constexpr int EPI_WARPS = Roles<NV>::EPI_WARPS, BPW = Roles<NV>::BLOCKS_PER_WARP;
+    constexpr int NB = Roles<NV>::NB, B_ROWS = Roles<NV>::B_ROWS, TMEM_COLS = Roles<NV>::TMEM_COLS;
+    constexpr int LD_COLS = Roles<NV>::LD_COLS, LOADS = Roles<NV>::LOADS, BATCH = Roles<NV>::BATCH;
     constexpr int TG_COLS = 8 * NB;         // one super-block's sums
     constexpr int TGROUPS = TMEM_COLS / TG_COLS;
     const int nblk = up.ks / 32, nv = up.nv;
@@ -134,10 +188,10 @@ q4k_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const Q4kUmmaPar
         }
         for (int s = 0; s < up.a_ring; s++) {
             mbar_init(bar_afull + 8 * s, UNPACK_WARPS);
-            mbar_init(bar_aempty + 8 * s, 1 + EPI_WARPS); // the MMAs' commit and the epilogue warps (they read the stage's headers)
+            mbar_init(bar_aempty + 8 * s, N_ISSUE + EPI_WARPS); // the issuers' commits and the epilogue warps (they read the stage's headers)
         }
         for (int a = 0; a < TGROUPS; a++) {
-            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tfull + 8 * a, N_ISSUE);
             mbar_init(bar_tempty + 8 * a, EPI_WARPS);
         }
         mbar_init(bar_x, EPI_WARPS);
@@ -175,67 +229,71 @@ q4k_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const Q4kUmmaPar
                 if (++slot == up.raw_ring) { slot = 0; phase ^= 1; }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp <= N_ISSUE) {
+        // ------------------------------------------------------------------ MMA issuers (warps 1, 2): one 128-value chunk each
         if (lane == 0) {
+            const int c = warp - 1;
             // instruction descriptor: s32 accumulate, signed 8-bit A and B, K-major, N = NB, M = 128
             const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((128u >> 4) << 24);
-            const uint64_t a_desc_ring = umma_desc_sw128(smem_u32(a_ring), 1024), b_desc_base = umma_desc_sw128(smem_u32(b_tiles), 1024);
+            const uint64_t a_desc_ring = umma_desc_sw128(smem_u32(a_ring) + c * up.rb8 * 128, 1024);
+            const uint64_t b_desc_base = umma_desc_sw128(smem_u32(b_tiles) + c * B_ROWS * 128, B_ROWS == 8 ? 0 : 1024);
             bool ok = mbar_wait(bar_x, 0, abort_flag, 2);
             int slot = 0, tg = 0;
             uint32_t phase = 0, tphase = 0;
             for (int s = 0; s < up.nsb && ok; s++) {
-                if (!mbar_wait(bar_tempty + 8 * tg, tphase ^ 1, abort_flag, 3)) break;
-                if (!mbar_wait(bar_afull + 8 * slot, phase, abort_flag, 4)) break;
+                if (!mbar_wait_hot(bar_tempty + 8 * tg, tphase ^ 1, abort_flag, 3)) break;
+                if (!mbar_wait_hot(bar_afull + 8 * slot, phase, abort_flag, 4)) break;
                 tc_fence_after();
-                const uint64_t a_desc = a_desc_ring + (uint64_t)((uint32_t)(slot * up.a_stage_bytes) >> 4);
-                const uint64_t b_desc = b_desc_base + (uint64_t)((uint32_t)(s * 2 * NB * 128) >> 4);
-                const uint32_t d0 = tmem_base + tg * TG_COLS;
+                const uint64_t ak = a_desc_ring + (uint64_t)((uint32_t)(slot * up.a_stage_bytes) >> 4);
+                const uint64_t bk = b_desc_base + (uint64_t)((uint32_t)(s * 2 * B_ROWS * 128) >> 4);
+                const uint32_t d0 = tmem_base + tg * TG_COLS + c * 4 * NB;
+                // sub-block j of the chunk: 32 bytes further along K in both operands; its NB sums get their own columns
 #pragma unroll
-                for (int c = 0; c < 2; c++) {
-                    const uint64_t ak = a_desc + (uint64_t)((uint32_t)(c * up.rb8 * 128) >> 4), bk = b_desc + (uint64_t)((uint32_t)(c * NB * 128) >> 4);
-                    // sub-block j of the chunk: 32 bytes further along K in both operands; its NB sums get their own columns
-#pragma unroll
-                    for (int j = 0; j < 4; j++) umma_i8(d0 + (c * 4 + j) * NB, ak + 2 * j, bk + 2 * j, idesc);
-                }
+                for (int j = 0; j < 4; j++) umma_i8(d0 + j * NB, ak + 2 * j, bk + 2 * j, idesc);
                 umma_commit(bar_aempty + 8 * slot);
                 umma_commit(bar_tfull + 8 * tg);
                 if (++slot == up.a_ring) { slot = 0; phase ^= 1; }
                 if (++tg == TGROUPS) { tg = 0; tphase ^= 1; }
             }
         }
-    } else if (warp < 2 + UNPACK_WARPS) {
-        // ------------------------------------------------------------------ nibbles -> int8 codes (warps 2..9)
-        const int ut = threadIdx.x - 64; // 0..255
-        const int items = 9 * up.rb8;    // per row: eight 16-byte groups of nibbles and the header
+    } else if (warp < FIRST_UNPACK) {
+        // warp 3: no role (keeps the unpacking and epilogue warps spread evenly over the four schedulers)
+    } else if (warp < FIRST_EPI) {
+        // ------------------------------------------------------------------ nibbles -> int8 codes (warps 4..11)
+        // Warp t takes the t-th 16-byte group of nibbles of every row (rows lane, lane + 32, ..): no index arithmetic
+        // beyond a row stride, and eight consecutive lanes touch eight consecutive rows, which are 144 bytes apart in
+        // the raw stage and 128 bytes apart (16-byte chunks XOR-swizzled by row) in the tile: no bank conflicts on
+        // either side.  Warps 0..3 also copy the rows' 16-byte headers.
+        const int t = warp - FIRST_UNPACK;
+        // group g = t / 2 of 64 values: bytes 16 (t % 2) .. of its 32 hold values 64 g + 16 (t % 2) .. in their low
+        // nibbles and the values 32 further on in their high nibbles
+        const int g = t >> 1, unit = (g & 1) * 4 + (t & 1);
+        const int lo_off = (unit ^ (lane & 7)) << 4, hi_off = ((unit + 2) ^ (lane & 7)) << 4; // row & 7 == lane & 7
+        const int chunk_off = (g >> 1) * (up.rb8 * 128);
         int rslot = 0, aslot = 0;
         uint32_t rphase = 0, aphase = 0;
         for (int s = 0; s < up.nsb; s++) {
-            if (!mbar_wait(bar_rfull + 8 * rslot, rphase, abort_flag, 5)) break;
-            if (!mbar_wait(bar_aempty + 8 * aslot, aphase ^ 1, abort_flag, 6)) break;
-            const uint8_t *raw = raw_ring + (size_t)rslot * up.raw_stage_bytes;
-            uint8_t *a_st = a_ring + (size_t)aslot * up.a_stage_bytes;
-            uint8_t *h_st = hdr + (size_t)aslot * up.rb8 * 16;
-#pragma unroll 4
-            for (int idx = ut; idx < items; idx += 32 * UNPACK_WARPS) {
-                // eight consecutive lanes take the same group of eight consecutive rows: rows are 144 bytes apart in
-                // the raw stage and 128 bytes apart (chunks XOR-swizzled by row) in the tile, so neither side has bank
-                // conflicts
-                const int t = (idx * up.inv_rb8_q20) >> 20, row = idx - t * up.rb8;
-                if (t == 8) {
-                    *reinterpret_cast<uint4 *>(h_st + row * 16) = *reinterpret_cast<const uint4 *>(raw + row * SB_BYTES);
-                    continue;
+            if (!mbar_wait_hot(bar_rfull + 8 * rslot, rphase, abort_flag, 5)) break;
+            if (!mbar_wait_hot(bar_aempty + 8 * aslot, aphase ^ 1, abort_flag, 6)) break;
+            const uint8_t *raw = raw_ring + (size_t)rslot * up.raw_stage_bytes + lane * SB_BYTES;
+            uint8_t *a_st = a_ring + (size_t)aslot * up.a_stage_bytes + chunk_off + lane * 128;
+            uint8_t *h_st = hdr + (size_t)aslot * up.rb8 * 16 + lane * 16;
+            uint4 w[4], hd = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int i = 0; i < 4; i++) // all loads first: one trip through shared memory, not four
+                w[i] = lane + 32 * i < up.rb8 ? *reinterpret_cast<const uint4 *>(raw + i * 32 * SB_BYTES + 16 + t * 16) : make_uint4(0u, 0u, 0u, 0u);
+            if (t < 4 && lane + 32 * t < up.rb8) hd = *reinterpret_cast<const uint4 *>(raw + t * 32 * SB_BYTES);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                if (lane + 32 * i < up.rb8) {
+                    const uint4 lo = make_uint4(w[i].x & 0x0F0F0F0Fu, w[i].y & 0x0F0F0F0Fu, w[i].z & 0x0F0F0F0Fu, w[i].w & 0x0F0F0F0Fu);
+                    const uint4 hi = make_uint4((w[i].x >> 4) & 0x0F0F0F0Fu, (w[i].y >> 4) & 0x0F0F0F0Fu, (w[i].z >> 4) & 0x0F0F0F0Fu,
+                                                (w[i].w >> 4) & 0x0F0F0F0Fu);
+                    *reinterpret_cast<uint4 *>(a_st + i * 32 * 128 + lo_off) = lo;
+                    *reinterpret_cast<uint4 *>(a_st + i * 32 * 128 + hi_off) = hi;
                 }
-                const uint4 w = *reinterpret_cast<const uint4 *>(raw + row * SB_BYTES + 16 + t * 16);
-                // group g = t / 2 of 64 values: bytes 16 (t % 2) .. of its 32 hold values 64 g + 16 (t % 2) .. in their low
-                // nibbles and the values 32 further on in their high nibbles
-                const uint4 lo = make_uint4(w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, w.z & 0x0F0F0F0Fu, w.w & 0x0F0F0F0Fu);
-                const uint4 hi = make_uint4((w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu, (w.z >> 4) & 0x0F0F0F0Fu, (w.w >> 4) & 0x0F0F0F0Fu);
-                const int g = t >> 1, unit = (g & 1) * 4 + (t & 1);
-                uint8_t *dst = a_st + (g >> 1) * (up.rb8 * 128) + row * 128;
-                *reinterpret_cast<uint4 *>(dst + ((unit ^ (row & 7)) << 4)) = lo;
-                *reinterpret_cast<uint4 *>(dst + (((unit + 2) ^ (row & 7)) << 4)) = hi;
             }
+            if (t < 4 && lane + 32 * t < up.rb8) *reinterpret_cast<uint4 *>(h_st + t * 32 * 16) = hd;
             // the MMAs read the tile through the async proxy
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
@@ -247,17 +305,17 @@ q4k_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const Q4kUmmaPar
             if (++aslot == up.a_ring) { aslot = 0; aphase ^= 1; }
         }
     } else {
-        // ------------------------------------------------------------------ digits, then epilogue (warps 10..17)
-        const int et = threadIdx.x - 64 - 32 * UNPACK_WARPS; // 0..255
-        const int q = warp & 3;                               // tensor-memory lane quarter of this warp
-        const int half = (warp - 2 - UNPACK_WARPS) >> 2;      // sub-blocks 0..3 or 4..7 of every super-block
+        // ------------------------------------------------------------------ digits, then epilogue (warps 12..)
+        const int et = threadIdx.x - 32 * FIRST_EPI;  // 0 .. 32 EPI_WARPS - 1
+        const int q = warp & 3;                        // tensor-memory lane quarter of this warp
+        const int half = (warp - FIRST_EPI) >> 2;      // with eight warps: sub-blocks 0..3 or 4..7 of every super-block
         // the activations are the stream predecessor's output
         asm volatile("griddepcontrol.wait;" ::: "memory");
         {
             const int sub = et & 3; // 4 threads per block of 32 elements, 8 elements each
             const int n_items = nv * nblk; // a multiple of 8: a warp's eight quads stay together
 #pragma unroll 2
-            for (int i = et >> 2; i < n_items; i += 64) {
+            for (int i = et >> 2; i < n_items; i += 8 * EPI_WARPS) {
                 const int v = i / nblk, blk = i - v * nblk;
                 const uint4 raw = *reinterpret_cast<const uint4 *>((const __half *)p.rhs + (size_t)v * p.K + k_begin + blk * 32 + sub * 8);
                 uint2 hi8, lo8;
@@ -269,7 +327,7 @@ q4k_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const Q4kUmmaPar
                          __dp4a((int)lo8.x, 0x01010101, 0) + __dp4a((int)lo8.y, 0x01010101, 0);
                 sm += __shfl_xor_sync(0xffffffffu, sm, 1);
                 sm += __shfl_xor_sync(0xffffffffu, sm, 2);
-                uint8_t *tile = b_tiles + (size_t)(blk >> 2) * (NB * 128) + ((2 * v) >> 3) * 1024;
+                uint8_t *tile = b_tiles + (size_t)(blk >> 2) * (B_ROWS * 128) + ((2 * v) >> 3) * 1024;
                 const int kpos = (blk & 3) * 32 + sub * 8;
                 store_digits8(tile, (2 * v) & 7, kpos, hi8);
                 store_digits8(tile, ((2 * v) & 7) + 1, kpos, lo8);
@@ -298,41 +356,50 @@ q4k_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const Q4kUmmaPar
             const uint4 h = *reinterpret_cast<const uint4 *>(hdr + (size_t)slot * up.rb8 * 16 + min(row_local, up.rb8 - 1) * 16);
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_aempty + 8 * slot);
-            // this warp's four sub-blocks: (d * sc, dmin * m), each one f32 rounding as the decoders form them
             const __half2 dd = *reinterpret_cast<const __half2 *>(&h.x);
             const float d = __low2float(dd), dmin = __high2float(dd);
-            float dsc[4], dmn[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                // get_scale_min_k4 of the format for sub-block half * 4 + j: bytes j of the three words of packed scales
-                const unsigned int b0 = (h.y >> (8 * j)) & 0xFFu, b1 = (h.z >> (8 * j)) & 0xFFu, b2 = (h.w >> (8 * j)) & 0xFFu;
-                const int sc = half == 0 ? (int)(b0 & 63u) : (int)((b2 & 0x0Fu) | ((b0 >> 6) << 4));
-                const int m = half == 0 ? (int)(b1 & 63u) : (int)((b2 >> 4) | ((b1 >> 6) << 4));
-                dsc[j] = __fmul_rn(d, (float)sc);
-                dmn[j] = __fmul_rn(dmin, (float)m);
-            }
             if (!mbar_wait(bar_tfull + 8 * tg, tphase, abort_flag, 8)) break;
             tc_fence_after();
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                int dv[NB];
-                const uint32_t taddr = tmem_base + tg * TG_COLS + (half * 4 + j) * NB + ((uint32_t)(q * 32) << 16);
-                tmem_ld_x16(taddr, dv);
-                if (NB == 32) tmem_ld_x16(taddr + 16, dv + (NB == 32 ? 16 : 0));
+            for (int j0 = 0; j0 < BPW; j0 += BATCH) {
+                // the batch's sums first (one wait for all of them), then their arithmetic
+                int dv[BATCH][2 * NV];
+#pragma unroll
+                for (int jj = 0; jj < BATCH; jj++) {
+                    const int jb = (BPW == 8 ? 0 : half * 4) + j0 + jj; // sub-block of the super-block
+                    const uint32_t taddr = tmem_base + tg * TG_COLS + jb * NB + ((uint32_t)(q * 32) << 16);
+#pragma unroll
+                    for (int l = 0; l < LOADS; l++) tmem_ld_cols<LD_COLS>(taddr + l * LD_COLS, &dv[jj][l * LD_COLS]);
+                }
                 tmem_ld_wait();
-                if (j == 3) {
+                if (j0 + BATCH >= BPW) {
                     // this warp has read its part of the stage's sums
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_tempty + 8 * tg);
                 }
-                const int blk = s * 8 + half * 4 + j;
 #pragma unroll
-                for (int v = 0; v < NV; v++) {
-                    if (v < nv) {
-                        const float t = fmaf(256.0f, small_int_to_float(dv[2 * v]), small_int_to_float(dv[2 * v + 1]));
-                        acc[v] = fmaf(dsc[j] * xs[v * (MAX_KS / 32) + blk], t, acc[v]);
-                        acc[v] = fmaf(-dmn[j], sumx[v * (MAX_KS / 32) + blk], acc[v]);
+                for (int jj = 0; jj < BATCH; jj++) {
+                    const int jw = j0 + jj, jb = (BPW == 8 ? 0 : half * 4) + jw;
+                    float dsc, dmn; // (d * sc, dmin * m), each one f32 rounding as the decoders form them
+                    {
+                        // get_scale_min_k4 of the format: bytes jb % 4 of the three words of packed scales
+                        const int j = jw & 3;
+                        const bool upper = BPW == 8 ? jw >= 4 : half != 0;
+                        const unsigned int b0 = (h.y >> (8 * j)) & 0xFFu, b1 = (h.z >> (8 * j)) & 0xFFu, b2 = (h.w >> (8 * j)) & 0xFFu;
+                        const int sc = !upper ? (int)(b0 & 63u) : (int)((b2 & 0x0Fu) | ((b0 >> 6) << 4));
+                        const int m = !upper ? (int)(b1 & 63u) : (int)((b2 >> 4) | ((b1 >> 6) << 4));
+                        dsc = __fmul_rn(d, small_int_to_float(sc));
+                        dmn = __fmul_rn(dmin, small_int_to_float(m));
+                    }
+                    const int blk = s * 8 + jb;
+#pragma unroll
+                    for (int v = 0; v < NV; v++) {
+                        if (v < nv) {
+                            const float t = fmaf(256.0f, small_int_to_float(dv[jj][2 * v]), small_int_to_float(dv[jj][2 * v + 1]));
+                            acc[v] = fmaf(dsc * xs[v * (MAX_KS / 32) + blk], t, acc[v]);
+                            acc[v] = fmaf(-dmn, sumx[v * (MAX_KS / 32) + blk], acc[v]);
+                        }
                     }
                 }
             }
@@ -343,7 +410,9 @@ q4k_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const Q4kUmmaPar
         // products from the decoded weights, in f32
         if (badmask[NV * 4] && half == 0 && row_local < rows_here) {
             const long long row = row_begin + row_local;
-            for (int v = 0; v < nv; v++) {
+#pragma unroll
+            for (int v = 0; v < NV; v++) { // unrolled: a runtime index would put the accumulators into local memory
+                if (v >= nv) continue;
                 for (int w = 0; w < (nblk + 31) / 32; w++) {
                     unsigned int m = badmask[v * 4 + w];
                     while (m) {
@@ -358,12 +427,17 @@ q4k_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const Q4kUmmaPar
                 }
             }
         }
+        if (EPI_WARPS == 8) {
 #pragma unroll
-        for (int v = 0; v < NV; v++) part[(half * NV + v) * 128 + row_local] = acc[v];
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
-        if (half == 0) {
+            for (int v = 0; v < NV; v++) part[(half * NV + v) * 128 + row_local] = acc[v];
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
+            if (half == 0) {
 #pragma unroll
-            for (int v = 0; v < NV; v++) red[v * 128 + row_local] = part[v * 128 + row_local] + part[(NV + v) * 128 + row_local];
+                for (int v = 0; v < NV; v++) red[v * 128 + row_local] = part[v * 128 + row_local] + part[(NV + v) * 128 + row_local];
+            }
+        } else {
+#pragma unroll
+            for (int v = 0; v < NV; v++) red[v * 128 + row_local] = acc[v];
         }
     }
 
@@ -421,18 +495,20 @@ q4k_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const Q4kUmmaPar
     }
 }
 
-int b_region_bytes(int ks, int rb8, int nb) {
-    int b = (ks / 128) * nb * 128;
+int b_region_bytes(int ks, int rb8, int b_rows) {
+    int b = (ks / 128) * b_rows * 128;
     const int guard = (128 - rb8) * 128;
     if (b < guard) b = guard;
     return (b + 1023) & ~1023;
 }
 
+int b_rows_for(int nvmax) { return nvmax <= 4 ? 8 : nvmax <= 8 ? 16 : 32; }
+
 size_t smem_for(int ks, int rb8, int nvmax, int split, int raw_ring, int a_ring) {
-    const int nb = 2 * nvmax, tgroups = TMEM_COLS / (8 * nb);
-    return 1024 + (size_t)a_ring * 2 * rb8 * 128 + b_region_bytes(ks, rb8, nb) + (size_t)raw_ring * rb8 * SB_BYTES + (size_t)a_ring * rb8 * 16 +
-           (size_t)2 * nvmax * (MAX_KS / 32) * 4 + (size_t)2 * nvmax * 128 * 4 + (size_t)split * nvmax * 128 * 4 + (size_t)(nvmax * 4 + 2) * 4 +
-           (size_t)(2 * raw_ring + 2 * a_ring + 2 * tgroups + 2) * 8 + 64;
+    const int nb = nvmax <= 8 ? 16 : 32, tgroups = (nvmax <= 4 ? 256 : 512) / (8 * nb);
+    return 1024 + (size_t)a_ring * 2 * rb8 * 128 + b_region_bytes(ks, rb8, b_rows_for(nvmax)) + (size_t)raw_ring * rb8 * SB_BYTES +
+           (size_t)a_ring * rb8 * 16 + (size_t)2 * nvmax * (MAX_KS / 32) * 4 + (size_t)2 * nvmax * 128 * 4 + (size_t)split * nvmax * 128 * 4 +
+           (size_t)(nvmax * 4 + 2) * 4 + (size_t)(2 * raw_ring + 2 * a_ring + 2 * tgroups + 2) * 8 + 64;
 }
 
 } // namespace
@@ -441,7 +517,7 @@ size_t smem_for(int ks, int rb8, int nvmax, int split, int raw_ring, int a_ring)
 // depths.  False when the shape is not one this kernel takes (the plan then uses gemv_q4k_mma.cu).
 bool q4k_gemv_umma_config(int M, int K, int nv, int sm_count, Q4kUmmaConfig *cfg) {
     if (M < 1 || K < 256 || K % 256 != 0 || nv < 1 || nv > 16 || !encode_tiled_fn()) return false;
-    const int nvmax = nv <= 8 ? 8 : 16;
+    const int nvmax = nv <= 1 ? 1 : nv <= 2 ? 2 : nv <= 4 ? 4 : nv <= 8 ? 8 : 16; // the kernel's template parameter
     // the split whose clusters own the most rows (fullest MMAs) among those that fit
     int best = 0, best_rb = 0;
     for (int split = 1; split <= 8; split *= 2) {
@@ -456,17 +532,21 @@ bool q4k_gemv_umma_config(int M, int K, int nv, int sm_count, Q4kUmmaConfig *cfg
     }
     if (!best) return false;
     const int split = best, rb = best_rb, rb8 = (rb + 7) & ~7, ks = K / split, nsb = ks / 256;
-    int raw_ring = std::min(8, nsb), a_ring = std::min(4, nsb);
-    if (raw_ring < 2) raw_ring = 2;
-    if (a_ring < 2) a_ring = 2;
-    while (smem_for(ks, rb8, nvmax, split, raw_ring, a_ring) > 227 * 1024) {
-        if (raw_ring > 2) raw_ring--;
-        else if (a_ring > 2) a_ring--;
-        else return false;
+    int raw_ring, a_ring = 2;
+    if (nvmax <= 2 && smem_for(ks, rb8, nvmax, split, 2, 2) <= 113 * 1024) {
+        // two CTAs per SM (this launch's and the next one's): two stages of each ring, a third raw one if it fits
+        raw_ring = nsb > 2 && smem_for(ks, rb8, nvmax, split, 3, 2) <= 113 * 1024 ? 3 : 2;
+    } else {
+        // the SM to itself: all of the CTA's weights are requested at once when they fit (nothing waits for a slot), two
+        // stages of codes suffice, a third takes what is left
+        raw_ring = std::max(2, std::min(12, nsb));
+        while (raw_ring > 2 && smem_for(ks, rb8, nvmax, split, raw_ring, a_ring) > 227 * 1024) raw_ring--;
+        if (smem_for(ks, rb8, nvmax, split, raw_ring, a_ring) > 227 * 1024) return false;
+        if (nsb > 2 && smem_for(ks, rb8, nvmax, split, raw_ring, 3) <= 227 * 1024) a_ring = 3;
     }
     cfg->split = split; cfg->clusters = sm_count / split; cfg->rb = rb; cfg->rb8 = rb8; cfg->ks = ks;
     cfg->raw_ring = raw_ring; cfg->a_ring = a_ring; cfg->nvmax = nvmax;
-    cfg->b_bytes = b_region_bytes(ks, rb8, 2 * nvmax);
+    cfg->b_bytes = b_region_bytes(ks, rb8, b_rows_for(nvmax));
     cfg->smem_bytes = smem_for(ks, rb8, nvmax, split, raw_ring, a_ring);
     return true;
 }
@@ -486,7 +566,7 @@ cudaError_t launch_q4k_gemv_umma(const MatmulParams &p, int nv, const Q4kUmmaCon
     }
     Q4kUmmaParams up{};
     up.p = p;
-    up.nv = nv; up.nb = 2 * cfg.nvmax;
+    up.nv = nv;
     up.rb = cfg.rb; up.rb8 = cfg.rb8; up.ks = cfg.ks; up.nsb = cfg.ks / 256; up.split = cfg.split;
     up.raw_ring = cfg.raw_ring; up.a_ring = cfg.a_ring;
     up.raw_stage_bytes = cfg.rb8 * SB_BYTES;
@@ -494,15 +574,24 @@ cudaError_t launch_q4k_gemv_umma(const MatmulParams &p, int nv, const Q4kUmmaCon
     up.b_bytes = cfg.b_bytes;
     up.inv_rb8_q20 = ((1 << 20) + cfg.rb8 - 1) / cfg.rb8;
     up.lhs_constant = lhs_constant ? 1 : 0;
-    static SmemAttr smem_attr[2];
-    auto kernel = cfg.nvmax == 8 ? q4k_gemv_umma_kernel<8> : q4k_gemv_umma_kernel<16>;
+    static SmemAttr smem_attr[5];
+    void (*kernel)(CUtensorMap, Q4kUmmaParams) = nullptr;
+    int slot = 0, threads = 0;
+    switch (cfg.nvmax) {
+    case 1: kernel = q4k_gemv_umma_kernel<1>; slot = 0; threads = Roles<1>::THREADS; break;
+    case 2: kernel = q4k_gemv_umma_kernel<2>; slot = 1; threads = Roles<2>::THREADS; break;
+    case 4: kernel = q4k_gemv_umma_kernel<4>; slot = 2; threads = Roles<4>::THREADS; break;
+    case 8: kernel = q4k_gemv_umma_kernel<8>; slot = 3; threads = Roles<8>::THREADS; break;
+    case 16: kernel = q4k_gemv_umma_kernel<16>; slot = 4; threads = Roles<16>::THREADS; break;
+    default: return cudaErrorInvalidValue;
+    }
     {
-        cudaError_t e = smem_attr[cfg.nvmax == 8 ? 0 : 1].ensure(kernel, cfg.smem_bytes);
+        cudaError_t e = smem_attr[slot].ensure(kernel, cfg.smem_bytes);
         if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(cfg.clusters * cfg.split);
-    lc.blockDim = dim3(THREADS);
+    lc.blockDim = dim3(threads);
     lc.dynamicSmemBytes = cfg.smem_bytes;
     lc.stream = stream;
     cudaLaunchAttribute attr[2];

@@ -563,9 +563,11 @@ def test_q4k_skinny_gemm_walks_row_groups(gpu, monkeypatch):
     ((5000, 2048), 9, "nv9_"),
     ((4100, 8192), 16, "nv16_"),
 ])
-def test_q4k_gemv_through_tensor_memory(gpu, wshape, nv, name):
-    """Q4_K weights of a size that fills the machine: raw super-blocks by TMA, nibbles to int8 codes in shared
-    memory, tcgen05.mma against the activations' digits.  1..16 vectors, both output orders, bias and GELU."""
+def test_q4k_gemv_through_tensor_memory(gpu, monkeypatch, wshape, nv, name):
+    """Q4_K weights of a size that fills the machine (opt-in route, RT_Q4K_UMMA=1): raw super-blocks by TMA, nibbles to
+    int8 codes in shared memory, tcgen05.mma against the activations' digits.  1..16 vectors, both output orders, bias
+    and GELU."""
+    monkeypatch.setenv("RT_Q4K_UMMA", "1")
     for to in ((True, False) if nv > 1 else (True,)):
         _, kernel = check_problem(Problem(Q4K, F16, wshape, (1, nv, wshape[1]), (False, True, to), bias=True, epilogue=nv % 2,
                                           seed=300 + nv + wshape[0], w_std=0.02), gpu)
@@ -580,6 +582,7 @@ def test_q4k_gemv_through_tensor_memory_matches_the_streaming_kernel_and_propaga
     and infinities in the activations come out as IEEE arithmetic on the decoded weights gives them (0 * inf and
     inf - inf are NaN, anything else with an infinity is that infinity)."""
     M, K, nv = 8192, 3072, 4
+    monkeypatch.setenv("RT_Q4K_UMMA", "1")
     w_t, wv = make_lhs(Q4K, (M, K), np.random.default_rng(411), 0.02)
     x = round_to(F16, np.random.default_rng(412).standard_normal((nv, K)).astype(np.float32))
     x[0, 5], x[1, 700], x[1, 701], x[2, 3000] = np.nan, np.inf, -np.inf, np.inf  # vector 3 stays finite
