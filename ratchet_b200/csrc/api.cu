@@ -127,7 +127,7 @@ static std::string plan_key(const rt_matmul_desc &d) {
     put_shape(d.lhs_shape); put_shape(d.rhs_shape);
     if (d.has_bias) put_shape(d.bias_shape);
     put(d.has_bias != 0); put(d.trans_lhs != 0); put(d.trans_rhs != 0); put(d.trans_out != 0); put(d.epilogue);
-    for (const char *name : {"RT_FORCE_KERNEL", "RT_GEMV_UMMA", "RT_Q4K_UMMA", "RT_TF32_BN", "RT_TF32_PRESPLIT", "RT_Q4K_WALK_FROM", "RT_KEEP_WEIGHTS"}) {
+    for (const char *name : {"RT_FORCE_KERNEL", "RT_GEMV_UMMA", "RT_Q4K_UMMA", "RT_GEMM_PAIR", "RT_TF32_BN", "RT_TF32_PRESPLIT", "RT_Q4K_WALK_FROM", "RT_KEEP_WEIGHTS"}) {
         const char *v = getenv(name);
         k += '|';
         if (v) k += v;
@@ -521,6 +521,12 @@ static bool q4k_umma_enabled() {
     return v && v[0] == '1';
 }
 
+// RT_GEMM_PAIR=0 keeps the tensor-core GEMM on one CTA per tile (A/B timing).
+static bool gemm_pair_enabled() {
+    const char *v = getenv("RT_GEMM_PAIR");
+    return !(v && v[0] == '0');
+}
+
 static bool force_simt() {
     const char *v = getenv("RT_FORCE_KERNEL");
     return v && std::string(v) == "simt";
@@ -712,6 +718,10 @@ static rt_status build_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan 
         pl->tf32x3 = desc->rhs_dt == RT_F32;
         pl->bn = pl->tf32x3 ? umma_tf32_pick_bn(pl->R, pl->S, pl->u_stacks, dev->sm_count)
                             : umma_pick_bn(pl->R, pl->S, pl->u_stacks, dev->sm_count);
+        // problems with at least two 256 x 256 tiles per pair of SMs: two CTAs per tile (tcgen05 cta_group::2)
+        if (!pl->tf32x3 && s.epilogue != RT_EPILOGUE_SILU_MUL && gemm_pair_enabled() && dev->sm_count >= 2 &&
+            (long long)((pl->R + 255) / 256) * ((pl->S + 255) / 256) * pl->u_stacks >= dev->sm_count)
+            pl->bn = UMMA_BN_PAIR;
         pl->launches = 1;
         if (!s.trans_rhs) {
             pl->rhs_transpose = true;
@@ -777,8 +787,8 @@ static rt_status build_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan 
                 pl->launches = 3;
             }
         }
-        pl->name = std::string(pl->tf32x3 ? "gemm_umma_tf32x3_" : "gemm_umma_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt) + "_bn" +
-                   std::to_string(pl->bn) + (pl->scratch && !pl->k_pad ? (pl->tf32x3 ? "_presplit" : "_dequant_prepass") : "") +
+        pl->name = std::string(pl->tf32x3 ? "gemm_umma_tf32x3_" : "gemm_umma_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt) +
+                   (pl->bn == UMMA_BN_PAIR ? std::string("_pair256x256") : "_bn" + std::to_string(pl->bn)) + (pl->scratch && !pl->k_pad ? (pl->tf32x3 ? "_presplit" : "_dequant_prepass") : "") +
                    (pl->rhs_transpose ? "_rhs_transposed" : "") + (pl->k_pad ? "_kpad" + std::to_string(pl->k_pad) : "");
     } else if (s.N == 1 && !s.trans_lhs) {
         pl->kernel = PK_GEMV_SIMT;

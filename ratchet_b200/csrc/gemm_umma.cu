@@ -21,6 +21,8 @@
 // reads the flag at the next rt_device_sync.
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.hpp"
 
@@ -171,6 +173,98 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
     __nv_bfloat162 h = __halves2bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(b));
     return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// The plain epilogue of one accumulator tile (128 rows x BN columns of this CTA's tensor memory at `tmem_acc`): 64
+// columns per round: two tensor-memory loads, the epilogue arithmetic, then through a per-warp staging buffer so that
+// global stores run along rows: 8 lanes x 16 B = one full 128-byte line per row (this matters most when the destination
+// is a peer GPU over NVLink).  `bar_done` (a shared::cluster address: this CTA's barrier, or the leading CTA's for a CTA
+// pair) gets one arrival per warp once the warp has read its part of the accumulator.
+__device__ __forceinline__ void arrive_cluster(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+template <int BN, typename OutT>
+__device__ __forceinline__ void epilogue_tile(const UmmaParams &prm, uint32_t tmem_acc, uint32_t bar_done, int r0, int s0, int b, int q, int half,
+                                              int lane, uint8_t *stg, const float *bias_s, bool has_bias, float row_bias, bool vec_ok,
+                                              bool pair_ok) {
+#pragma unroll 1
+    for (int cc = half; cc < BN / 64; cc += 2) {
+        const int colbase = s0 + cc * 64;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int c = cc * 2 + h;
+            uint32_t v[32];
+            tmem_ld32(tmem_acc + c * 32 + ((uint32_t)(q * 32) << 16), v);
+            if (cc + 2 >= BN / 64 && h == 1) {
+                // the accumulator has been read completely: hand it back to the MMA warp now
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) arrive_cluster(bar_done);
+            }
+            {
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const int i0 = g * 8 + j * 2;
+                        const float b0 = prm.bias_mode == BIAS_PER_N ? bias_s[c * 32 + i0] : row_bias;
+                        const float b1 = prm.bias_mode == BIAS_PER_N ? bias_s[c * 32 + i0 + 1] : row_bias;
+                        const OutT o0 = epilogue_value<OutT>(__uint_as_float(v[i0]), has_bias, b0, prm.epilogue);
+                        const OutT o1 = epilogue_value<OutT>(__uint_as_float(v[i0 + 1]), has_bias, b1, prm.epilogue);
+                        w[j] = pack2<OutT>(to_f32(o0), to_f32(o1));
+                    }
+                    *reinterpret_cast<uint4 *>(stg + lane * STG_ROW_BYTES + (((h * 4 + g) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+        __syncwarp();
+        if (vec_ok) {
+            const int colv = colbase + (lane & 7) * 8;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int rl = 4 * i + (lane >> 3);
+                const int rg = r0 + q * 32 + rl;
+                if (rg < prm.R && colv < prm.s_out) {
+                    const uint4 pk = *reinterpret_cast<const uint4 *>(stg + rl * STG_ROW_BYTES + (((lane & 7) ^ (rl & 7)) << 4));
+                    const long long off = (long long)b * prm.out_batch_stride + (long long)rg * prm.out_ld + prm.out_col + colv;
+                    for (int d = 0; d < prm.n_out; d++) *reinterpret_cast<uint4 *>(reinterpret_cast<OutT *>(prm.outs[d]) + off) = pk;
+                }
+            }
+        } else if (pair_ok) {
+            // rows that start on 4-byte but not on 16-byte boundaries: a warp writes the round's 64
+            // columns of one row as 32 element pairs per instruction
+#pragma unroll 4
+            for (int rl = 0; rl < 32; rl++) {
+                const int rg = r0 + q * 32 + rl;
+                if (rg >= prm.R) break;
+                const int col = 2 * lane;
+                if (colbase + col < prm.s_out) {
+                    const uint32_t o2 = *reinterpret_cast<const uint32_t *>(stg + rl * STG_ROW_BYTES + (((col >> 3) ^ (rl & 7)) << 4) + (col & 7) * 2);
+                    const long long off = (long long)b * prm.out_batch_stride + (long long)rg * prm.out_ld + prm.out_col + colbase + col;
+                    for (int d = 0; d < prm.n_out; d++) *reinterpret_cast<uint32_t *>(reinterpret_cast<OutT *>(prm.outs[d]) + off) = o2;
+                }
+            }
+        } else {
+            // any other row alignment: element stores, still along the rows
+#pragma unroll 4
+            for (int rl = 0; rl < 32; rl++) {
+                const int rg = r0 + q * 32 + rl;
+                if (rg >= prm.R) break;
+                const long long off = (long long)b * prm.out_batch_stride + (long long)rg * prm.out_ld + prm.out_col + colbase;
+#pragma unroll
+                for (int k = 0; k < 2; k++) {
+                    const int col = lane + 32 * k;
+                    if (colbase + col < prm.s_out) {
+                        const OutT o = *reinterpret_cast<const OutT *>(stg + rl * STG_ROW_BYTES + (((col >> 3) ^ (rl & 7)) << 4) + (col & 7) * 2);
+                        for (int d = 0; d < prm.n_out; d++) reinterpret_cast<OutT *>(prm.outs[d])[off + col] = o;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
 }
 
 template <int BN, typename OutT>
@@ -372,83 +466,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
                 continue;
             }
-#pragma unroll 1
-            for (int cc = half; cc < BN / 64; cc += 2) {
-                const int colbase = s0 + cc * 64;
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const int c = cc * 2 + h;
-                    uint32_t v[32];
-                    tmem_ld32(tmem_base + acc * BN + c * 32 + ((uint32_t)(q * 32) << 16), v);
-                    if (cc + 2 >= BN / 64 && h == 1) {
-                        // the accumulator has been read completely: hand it back to the MMA warp now
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
-                    }
-                    {
-#pragma unroll
-                        for (int g = 0; g < 4; g++) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                const int i0 = g * 8 + j * 2;
-                                const float b0 = prm.bias_mode == BIAS_PER_N ? bias_s[c * 32 + i0] : row_bias;
-                                const float b1 = prm.bias_mode == BIAS_PER_N ? bias_s[c * 32 + i0 + 1] : row_bias;
-                                const OutT o0 = epilogue_value<OutT>(__uint_as_float(v[i0]), has_bias, b0, prm.epilogue);
-                                const OutT o1 = epilogue_value<OutT>(__uint_as_float(v[i0 + 1]), has_bias, b1, prm.epilogue);
-                                w[j] = pack2<OutT>(to_f32(o0), to_f32(o1));
-                            }
-                            *reinterpret_cast<uint4 *>(stg + lane * STG_ROW_BYTES + (((h * 4 + g) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
-                    }
-                }
-                __syncwarp();
-                if (vec_ok) {
-                    const int colv = colbase + (lane & 7) * 8;
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const int rl = 4 * i + (lane >> 3);
-                        const int rg = r0 + q * 32 + rl;
-                        if (rg < prm.R && colv < prm.s_out) {
-                            const uint4 pk = *reinterpret_cast<const uint4 *>(stg + rl * STG_ROW_BYTES + (((lane & 7) ^ (rl & 7)) << 4));
-                            const long long off = (long long)b * prm.out_batch_stride + (long long)rg * prm.out_ld + prm.out_col + colv;
-                            for (int d = 0; d < prm.n_out; d++) *reinterpret_cast<uint4 *>(reinterpret_cast<OutT *>(prm.outs[d]) + off) = pk;
-                        }
-                    }
-                } else if (pair_ok) {
-                    // rows that start on 4-byte but not on 16-byte boundaries: a warp writes the round's 64
-                    // columns of one row as 32 element pairs per instruction
-#pragma unroll 4
-                    for (int rl = 0; rl < 32; rl++) {
-                        const int rg = r0 + q * 32 + rl;
-                        if (rg >= prm.R) break;
-                        const int col = 2 * lane;
-                        if (colbase + col < prm.s_out) {
-                            const uint32_t o2 = *reinterpret_cast<const uint32_t *>(stg + rl * STG_ROW_BYTES + (((col >> 3) ^ (rl & 7)) << 4) + (col & 7) * 2);
-                            const long long off = (long long)b * prm.out_batch_stride + (long long)rg * prm.out_ld + prm.out_col + colbase + col;
-                            for (int d = 0; d < prm.n_out; d++) *reinterpret_cast<uint32_t *>(reinterpret_cast<OutT *>(prm.outs[d]) + off) = o2;
-                        }
-                    }
-                } else {
-                    // any other row alignment: element stores, still along the rows
-#pragma unroll 4
-                    for (int rl = 0; rl < 32; rl++) {
-                        const int rg = r0 + q * 32 + rl;
-                        if (rg >= prm.R) break;
-                        const long long off = (long long)b * prm.out_batch_stride + (long long)rg * prm.out_ld + prm.out_col + colbase;
-#pragma unroll
-                        for (int k = 0; k < 2; k++) {
-                            const int col = lane + 32 * k;
-                            if (colbase + col < prm.s_out) {
-                                const OutT o = *reinterpret_cast<const OutT *>(stg + rl * STG_ROW_BYTES + (((col >> 3) ^ (rl & 7)) << 4) + (col & 7) * 2);
-                                for (int d = 0; d < prm.n_out; d++) reinterpret_cast<OutT *>(prm.outs[d])[off + col] = o;
-                            }
-                        }
-                    }
-                }
-                __syncwarp();
-            }
+            epilogue_tile<BN, OutT>(prm, tmem_base + acc * BN, bar_tempty + 8 * acc, r0, s0, b, q, half, lane, stg, bias_s, has_bias, row_bias,
+                                    vec_ok, pair_ok);
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
     }
@@ -464,6 +483,202 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------ CTA pairs
+// The same GEMM with two CTAs (a cluster of two SMs) on one 256 x 256 tile: tcgen05.mma cta_group::2.  Each CTA
+// stages its own 128 rows of P and HALF of the tile's 256 rows of Q (every copy is a plain TMA load into the CTA's own
+// shared memory whose completion is counted on the leading CTA's barrier; no copy is multicast), the leading CTA's
+// thread issues one MMA for both SMs, which read both halves of Q, and each SM's tensor memory receives its own 128 rows
+// of the tile.  Per MMA cycle an SM then takes 64 bytes of operands from shared memory instead of 96, and a stage is 32 KB
+// instead of 48: six stages in flight instead of four.
+//   full[s]      leading CTA: its producer's arrival with the byte count of both CTAs' copies
+//   empty[s]     both CTAs: the leading CTA's tcgen05.commit, multicast to both
+//   tmem_full    both CTAs: the same commit after a tile's last MMA
+//   tmem_empty   leading CTA: one arrival per epilogue warp of both CTAs
+constexpr int P2_STAGES = 6;
+constexpr int P2_BN = 256;
+constexpr int P2_A_BYTES = BM * BK * 2, P2_B_BYTES = (P2_BN / 2) * BK * 2, P2_STAGE_BYTES = P2_A_BYTES + P2_B_BYTES;
+constexpr int P2_SMEM_BYTES = P2_STAGES * P2_STAGE_BYTES + 1024 + 256 + P2_BN * 4 + EPI_WARPS * 32 * STG_ROW_BYTES;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// A tile into this CTA's shared memory, its bytes counted on the barrier at `bar_cluster` (the leading CTA's)
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar_cluster) {
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar_cluster)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+// arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far are complete
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("{\n\t.reg .b16 m;\n\tmov.b16 m, 3;\n\t"
+                 "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}\n" ::"r"(bar)
+                 : "memory");
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const UmmaParams prm) {
+    constexpr int BN = P2_BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *tiles = smem;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + P2_STAGES * P2_STAGE_BYTES);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * P2_STAGES + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *bias_s = reinterpret_cast<float *>(smem + P2_STAGES * P2_STAGE_BYTES + 256);
+    uint8_t *stage_out = smem + P2_STAGES * P2_STAGE_BYTES + 256 + BN * 4;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank(); // 0: the leading CTA
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + P2_STAGES);
+    const uint32_t bar_tfull = smem_u32(bars + 2 * P2_STAGES), bar_tempty = smem_u32(bars + 2 * P2_STAGES + 2);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P2_STAGES; s++) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tempty + 8 * a, 2 * EPI_WARPS); // the epilogue warps of both CTAs
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) { // the same warp of both CTAs: the allocation is one operation of the pair
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(2 * P2_BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all(); // both CTAs' barriers exist before either signals the other's
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    const int num_k = (prm.K + BK - 1) / BK;
+    const int tiles_per_batch = prm.tiles_r * prm.tiles_s; // tiles of 256 x 256
+    const int total_tiles = tiles_per_batch * prm.stacks;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+                const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+                const int r0 = (rem % prm.tiles_r) * 2 * BM + (int)rank * BM, s0 = (rem / prm.tiles_r) * BN + (int)rank * (BN / 2);
+                const int bp = b % prm.p_stack, bq = b % prm.q_stack;
+                for (int kb = 0; kb < num_k; kb++) {
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, 1)) { ok = false; break; }
+                    const uint32_t a_dst = smem_u32(tiles + stage * P2_STAGE_BYTES);
+                    if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * P2_STAGE_BYTES);
+                    const uint32_t full0 = map_to_cta(bar_full + 8 * stage, 0);
+                    tma_load_3d_pair(a_dst, &map_p, kb * BK, r0, bp, full0);
+                    tma_load_3d_pair(a_dst + P2_A_BYTES, &map_q, kb * BK, s0, bq, full0);
+                    if (++stage == P2_STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer (the leading CTA only)
+        if (lane == 0 && rank == 0) {
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+                if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, 2)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_k; kb++) {
+                    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + stage * P2_STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + P2_A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        umma_f16_pair(d_tmem, umma_desc_sw128(a_addr + k * UMMA_K * 2), umma_desc_sw128(b_addr + k * UMMA_K * 2), prm.idesc,
+                                      (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit_pair(bar_empty + 8 * stage); // both CTAs' stages are reusable once these MMAs have read them
+                    if (++stage == P2_STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit_pair(bar_tfull + 8 * acc); // both CTAs' accumulators are complete
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..9 of both CTAs)
+        const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int ep_tid = threadIdx.x - 64;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool vec_ok = (prm.s_out % 8 == 0) && (prm.out_ld % 8 == 0) && (prm.out_col % 8 == 0) && (prm.out_batch_stride % 8 == 0);
+        bool pair_ok = (prm.s_out % 2 == 0) && (prm.out_ld % 2 == 0) && (prm.out_col % 2 == 0) && (prm.out_batch_stride % 2 == 0);
+        for (int d = 0; d < prm.n_out; d++) {
+            vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(prm.outs[d]) % 16 == 0);
+            pair_ok = pair_ok && (reinterpret_cast<uintptr_t>(prm.outs[d]) % 4 == 0);
+        }
+        const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
+        bool gave_up = false;
+        for (int tile = pair; tile < total_tiles; tile += num_pairs) {
+            const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+            const int r0 = (rem % prm.tiles_r) * 2 * BM + (int)rank * BM, s0 = (rem / prm.tiles_r) * BN;
+            if (bar_red_or(1, EPI_WARPS * 32, gave_up || *abort_flag != 0)) break;
+            if (prm.bias_mode == BIAS_PER_N) {
+                for (int j = ep_tid; j < BN; j += EPI_WARPS * 32)
+                    bias_s[j] = (s0 + j < prm.S) ? load_bias(prm.bias, prm.bias_dt, s0 + j) : 0.f;
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+            if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, 4)) { gave_up = true; continue; }
+            tc_fence_after();
+            const int row = r0 + q * 32 + lane;
+            const bool has_bias = prm.bias_mode != BIAS_NONE;
+            float row_bias = 0.f;
+            if (prm.bias_mode == BIAS_PER_M && row < prm.R) row_bias = load_bias(prm.bias, prm.bias_dt, row);
+            uint8_t *stg = stage_out + (warp - 2) * (32 * STG_ROW_BYTES);
+            epilogue_tile<BN, OutT>(prm, tmem_base + acc * BN, tempty0 + 8 * acc, r0, s0, b, q, half, lane, stg, bias_s, has_bias, row_bias, vec_ok,
+                                    pair_ok);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all(); // neither CTA leaves while the other may still signal its barriers or read its shared memory
+    if (*abort_flag) {
+        const unsigned long long t0 = wait_clock();
+        while (wait_clock() - t0 < 400000ull) __nanosleep(1000);
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(2 * P2_BN) : "memory");
     }
 }
 
@@ -532,6 +747,37 @@ cudaError_t launch_bn(const CUtensorMap &mp, const CUtensorMap &mq, UmmaParams p
     return launch_pdl(kernel, dim3(grid), dim3(NUM_THREADS), C::SMEM_BYTES, stream, mp, mq, prm);
 }
 
+template <typename OutT>
+cudaError_t launch_pair(const CUtensorMap &mp, const CUtensorMap &mq, UmmaParams prm, int sm_count, cudaStream_t stream) {
+    static SmemAttr smem_attr;
+    auto kernel = gemm_umma_pair_kernel<OutT>;
+    {
+        cudaError_t e = smem_attr.ensure(kernel, P2_SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+    }
+    prm.tiles_r = (prm.R + 2 * BM - 1) / (2 * BM);
+    prm.tiles_s = (prm.S + P2_BN - 1) / P2_BN;
+    // instruction descriptor: f32 accumulate, K-major A and B, N = 256, M = 256 over the two CTAs
+    prm.idesc |= (1u << 4) | ((uint32_t)(P2_BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+    const long long total = (long long)prm.tiles_r * prm.tiles_s * prm.stacks;
+    const int pairs = (int)std::min<long long>(total, sm_count / 2);
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(2 * pairs);
+    lc.blockDim = dim3(NUM_THREADS);
+    lc.dynamicSmemBytes = P2_SMEM_BYTES;
+    lc.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 2;
+    return cudaLaunchKernelEx(&lc, kernel, mp, mq, prm);
+}
+
 } // namespace
 
 bool umma_gemm_supported(long long K) { return K >= 8 && K % 8 == 0 && encode_fn() != nullptr; }
@@ -554,7 +800,9 @@ cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dty
     if (pair && (S % 2 != 0 || bias_mode == BIAS_PER_M || (scatter && scatter->n_out > 0))) return cudaErrorInvalidValue;
     CUtensorMap mp, mq;
     if (!make_map(&mp, P, p_dt, K, R, p_stack, BM)) return cudaErrorInvalidValue;
-    if (!(pair ? make_pair_map(&mq, Q, q_dt, K, S / 2, q_stack, bn / 2) : make_map(&mq, Q, q_dt, K, S, q_stack, bn)))
+    if (bn == UMMA_BN_PAIR && pair) return cudaErrorInvalidValue; // the CTA-pair kernel has no gate/up fold
+    if (!(pair ? make_pair_map(&mq, Q, q_dt, K, S / 2, q_stack, bn / 2)
+               : make_map(&mq, Q, q_dt, K, S, q_stack, bn == UMMA_BN_PAIR ? P2_BN / 2 : bn)))
         return cudaErrorInvalidValue;
     UmmaParams prm{};
     prm.R = R; prm.S = S; prm.K = K;
@@ -579,6 +827,11 @@ cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dty
     prm.bias = bias; prm.bias_dt = bias_dt; prm.bias_mode = bias_mode;
     prm.epilogue = epilogue;
     prm.idesc = ((p_dt == RT_BF16 ? 1u : 0u) << 7) | ((q_dt == RT_BF16 ? 1u : 0u) << 10);
+    if (bn == UMMA_BN_PAIR) {
+        if (out_dt == RT_F16) return launch_pair<__half>(mp, mq, prm, sm_count, stream);
+        if (out_dt == RT_BF16) return launch_pair<__nv_bfloat16>(mp, mq, prm, sm_count, stream);
+        return cudaErrorInvalidValue;
+    }
     if (out_dt == RT_F16)
         return bn == 256 ? launch_bn<256, __half>(mp, mq, prm, sm_count, stream) : launch_bn<128, __half>(mp, mq, prm, sm_count, stream);
     if (out_dt == RT_BF16)

@@ -111,6 +111,8 @@ struct UmmaScatter {
     long long out_ld, out_col;
 };
 bool umma_gemm_supported(long long K);
+// Tile width: 128 or 256 columns on one CTA per SM, or UMMA_BN_PAIR: 256 x 256 tiles on pairs of CTAs (cta_group::2)
+constexpr int UMMA_BN_PAIR = 512;
 int umma_pick_bn(long long R, long long S, long long stacks, int sm_count);
 cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dtype q_dt, void *out, rt_dtype out_dt,
                              int R, int S, int K, int stacks, int p_stack, int q_stack, const void *bias, int bias_dt,

@@ -725,6 +725,39 @@ def test_umma_takes_the_prefill_configs(gpu):
         assert lib.rt_plan_kernel(gpu.plan_for(node.op.desc)).decode().startswith("gemm_umma"), (lhs_dt, wshape)
 
 
+@pytest.mark.parametrize("lhs_dt,act,wshape,xshape,bias,epi", [
+    (Q8H, F16, (5120, 512), (1, 2048, 512), True, 1),      # 8 x 20 tiles of 256 x 256
+    (F16, F16, (5000, 256), (2, 1000, 256), True, 0),      # ragged rows and columns, two batches over one weight
+    (BF16, BF16, (4096, 320), (1, 2560, 320), False, 1),   # K = 5 blocks of 64
+    (Q8H, BF16, (10240, 512), (1, 1030, 512), True, 1),    # rows that end in a pair's first CTA
+    (Q4K, F16, (8192, 512), (1, 1200, 512), False, 0),
+])
+def test_gemm_on_cta_pairs_matches_the_oracle_and_the_single_cta_kernel(gpu, monkeypatch, lhs_dt, act, wshape, xshape, bias, epi):
+    """Large GEMMs run 256 x 256 tiles on pairs of CTAs (tcgen05 cta_group::2: each CTA stages its 128 rows of the
+    activations and half of the tile's weight rows): the result meets the bar against the oracle on sampled rows and
+    has the bits of the one-CTA kernel (same products, same order of the K blocks)."""
+    rng = np.random.default_rng(sum(wshape) + sum(xshape))
+    w_t, wv = make_lhs(lhs_dt, wshape, np.random.default_rng(5 + wshape[0]), 0.05)
+    x = round_to(act, rng.standard_normal(xshape).astype(np.float32))
+    bdt = F16 if act == BF16 else act
+    b = round_to(bdt, rng.standard_normal(wshape[0]).astype(np.float32) * 0.1) if bias else None
+    w_d, x_d = w_t.to(gpu), Tensor.from_data(x, gpu, act)
+    b_d = Tensor.from_data(b, gpu, bdt) if bias else None
+    node = w_d.gemm(x_d, b_d, False, True, True, epilogue=epi)
+    assert "pair256x256" in rb._lib.load().rt_plan_kernel(gpu.plan_for(node.op.desc)).decode()
+    got = node.resolve().to(Device.CPU)
+    monkeypatch.setenv("RT_GEMM_PAIR", "0")
+    node1 = w_d.gemm(x_d, b_d, False, True, True, epilogue=epi)
+    assert "pair" not in rb._lib.load().rt_plan_kernel(gpu.plan_for(node1.op.desc)).decode()
+    assert np.array_equal(got.to_numpy().reshape(-1), node1.resolve().to(Device.CPU).to_numpy().reshape(-1))
+    N, K = wshape
+    rows_total = int(np.prod(xshape[:-1]))
+    rows = np.unique(np.concatenate([[0, 127, 128, 255, 256, rows_total - 1], np.random.default_rng(1).integers(0, rows_total, size=40)]))
+    truth = oracle.matmul_truth(wv, x.reshape(rows_total, K)[rows], b, 1, 1, 1, N, len(rows), K, False, True, True, epi)
+    truth_r = (oracle.bf16_bits_to_f32(oracle.f64_to_bf16_bits(truth)) if act == BF16 else oracle.f64_to_f16(truth).astype(np.float32))
+    assert oracle.rel_l2(got.to_f32().reshape(rows_total, N)[rows], truth_r.reshape(len(rows), N)) <= TOL[act]
+
+
 @pytest.mark.parametrize("M", [2048, 8192], ids=["4x2048", "4x8192"])
 def test_q8_bf16_prefill_full_size_sampled(gpu, M):
     """The sharded prefill workload at full size on one GPU: A bf16 [4,M,2560], W Q8_0H [10240,2560], f16 bias,
