@@ -406,6 +406,7 @@ def run_sharded(rank, world, gpu, stream, dist, torch, rows_per_batch=2048, iter
 
     us_compute = timed(compute_only)
     us_nccl = timed(lambda: lin.launch_nccl(x, comm, local, gathered))
+    us_comm = timed(lambda: comm.all_gather(local.ptr, gathered.ptr, rows * per * 2))  # the all-gather of ready slices alone
     # the NCCL leg gathers [world][rows][N / world]: rank r's column window of row i
     g = Tensor([world, rows, per], DType.BF16, gpu, gathered).to(Device.CPU).to_numpy()
     parity_nccl = sharded_parity(np.ascontiguousarray(np.transpose(g, (1, 0, 2))).reshape(rows, N), sample, w.to_numpy(), b16, x_vals, N, K)
@@ -414,17 +415,21 @@ def run_sharded(rank, world, gpu, stream, dist, torch, rows_per_batch=2048, iter
     dist.barrier()
     full = out_t.to(Device.CPU).to_numpy().reshape(rows, N)
     parity_peer = sharded_parity(full, sample, w.to_numpy(), b16, x_vals, N, K)
-    par = torch.tensor([parity_nccl, parity_peer], device=f"cuda:{gpu.ordinal}", dtype=torch.float64)
-    dist.all_reduce(par, op=dist.ReduceOp.MAX)  # the worst rank's
+    pars = exchange((float(parity_nccl), float(parity_peer)))  # every rank's; the worst is reported
+    par = [max(p[0] for p in pars), max(p[1] for p in pars)]
     dist.barrier()
     lin.close_peers()
     comm.close()
     link_bytes = rows * N * 2 * (world - 1) / world  # what every GPU has to receive
-    res.update({"compute_only_us": us_compute, "gemm_plus_nccl_all_gather_us": us_nccl, "peer_store_epilogue_us": us_peer,
+    res.update({"compute_only_us": us_compute, "nccl_all_gather_only_us": us_comm, "gemm_plus_nccl_all_gather_us": us_nccl,
+                "peer_store_epilogue_us": us_peer,
+                # how much of the smaller of the two legs the fused form hides: 1 = the whole of it, 0 = nothing
+                "peer_store_overlap": (us_compute + us_comm - us_peer) / max(min(us_compute, us_comm), 1e-3),
+                "link_bound_us_at_measured_770_gbs": rows * N * 2 * (world - 1) / world / 770e3,
                 "tflops_compute_only": flops / us_compute / 1e6, "tflops_nccl": flops / us_nccl / 1e6, "tflops_peer": flops / us_peer / 1e6,
                 "link_ingress_bytes_per_gpu": link_bytes, "link_ingress_gbs_peer": link_bytes / us_peer / 1e3,
                 "link_ingress_gbs_nccl": link_bytes / max(us_nccl - us_compute, 1e-3) / 1e3,
-                "parity_rel_l2": float(par[1].item()), "parity_rel_l2_nccl": float(par[0].item()),
+                "parity_rel_l2": par[1], "parity_rel_l2_nccl": par[0],
                 "kernel": lib.rt_plan_kernel(plan).decode()})
     return res
 

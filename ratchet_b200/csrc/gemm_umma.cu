@@ -843,7 +843,10 @@ cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dty
     if (scatter && scatter->n_out > 0) {
         if (scatter->n_out > RT_MAX_PEERS) return cudaErrorInvalidValue;
         prm.n_out = scatter->n_out;
-        for (int d = 0; d < scatter->n_out; d++) prm.outs[d] = scatter->outs[d];
+        // The destinations are written in an order that starts at this shard's own index (out_col / S for equal shards):
+        // at any moment the GPUs of a group then store to different peers, instead of all to GPU 0, then all to GPU 1, ..
+        const int first = S > 0 ? (int)((scatter->out_col / S) % scatter->n_out) : 0;
+        for (int d = 0; d < scatter->n_out; d++) prm.outs[d] = scatter->outs[(first + d) % scatter->n_out];
         prm.out_ld = scatter->out_ld;
         prm.out_col = scatter->out_col;
         prm.out_batch_stride = (long long)R * scatter->out_ld;
