@@ -94,6 +94,8 @@ struct rt_plan {
     uint64_t scratch_bytes = 0;
     void *act_scratch = nullptr; // bf16 activations cast to f16 (quantised weights only)
     uint64_t act_scratch_bytes = 0;
+    void *wdq = nullptr;         // f32 GEMM over Q8_0F weights: the weights as f32 ((i8)q * d, quant.rs:114-120)
+    uint64_t wdq_bytes = 0;
     // RT_EPILOGUE_SILU_MUL on a route that does not fold the gate/up pairs itself: the plain node's [.., 2*ff] output
     // goes here and an elementwise launch writes the [.., ff] result
     bool pair = false;
@@ -106,7 +108,8 @@ struct rt_plan {
     std::mutex weights_mu;
     std::unordered_map<const void *, void *> kept_weights;
     ~rt_plan() {
-        if (scratch || act_scratch || pair_scratch || !kept_weights.empty()) cudaSetDevice(dev->ordinal);
+        if (scratch || act_scratch || pair_scratch || wdq || !kept_weights.empty()) cudaSetDevice(dev->ordinal);
+        if (wdq) cudaFree(wdq);
         if (scratch) cudaFree(scratch);
         if (act_scratch) cudaFree(act_scratch);
         if (pair_scratch) cudaFree(pair_scratch);
@@ -137,7 +140,7 @@ static std::string plan_key(const rt_matmul_desc &d) {
 
 // Scratch areas that take the place of a plan's own during one launch.
 struct ScratchSet {
-    void *scratch = nullptr, *act = nullptr, *pair = nullptr;
+    void *scratch = nullptr, *act = nullptr, *pair = nullptr, *wdq = nullptr;
 };
 
 struct rt_executable {
@@ -167,7 +170,7 @@ static bool keep_weights_enabled() {
 // The dequantised copy the plan keeps of a constant weight, by weight pointer; *filled says whether an earlier
 // launch already wrote it.  A new weight gets its copy here unless the stream is capturing or memory is short
 // (nullptr: the caller uses scratch).
-static void *kept_weight_copy(rt_plan *plan, const void *lhs, cudaStream_t st, bool *filled) {
+static void *kept_weight_copy(rt_plan *plan, const void *lhs, cudaStream_t st, bool *filled, uint64_t bytes) {
     *filled = false;
     if (!keep_weights_enabled()) return nullptr;
     std::lock_guard<std::mutex> lk(plan->weights_mu);
@@ -179,7 +182,7 @@ static void *kept_weight_copy(rt_plan *plan, const void *lhs, cudaStream_t st, b
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
     void *kept = nullptr;
     if (cudaStreamIsCapturing(st, &cs) == cudaSuccess && cs == cudaStreamCaptureStatusNone &&
-        cudaMalloc(&kept, plan->scratch_bytes) == cudaSuccess) {
+        cudaMalloc(&kept, bytes) == cudaSuccess) {
         plan->kept_weights.emplace(lhs, kept);
         std::lock_guard<std::mutex> dl(plan->dev->kept_mu);
         plan->dev->kept_ptrs[lhs]++;
@@ -547,7 +550,8 @@ static bool umma_eligible(const rt_matmul_desc &d, const Spec &s) {
         if (d.rhs_dt == RT_F32 && s.M < 16) return false;
     }
     if (d.rhs_dt == RT_F32) {
-        if (d.lhs_dt != RT_F32 || !umma_tf32_supported(s.K)) return false;
+        // dense f32, or the reference's default pair (Q8_0F, F32) in the Linear form with the weights dequantised to f32
+        if ((d.lhs_dt != RT_F32 && d.lhs_dt != RT_Q8_0F) || !umma_tf32_supported(s.K)) return false;
     } else {
         if (d.rhs_dt != RT_F16 && d.rhs_dt != RT_BF16) return false;
         const bool dense = d.lhs_dt == d.rhs_dt;
@@ -762,7 +766,17 @@ static rt_status build_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan 
                 pl->launches++;
             }
         }
-        if (is_quantized(desc->lhs_dt)) {
+        if (is_quantized(desc->lhs_dt) && pl->tf32x3) {
+            pl->wdq_bytes = (uint64_t)(s.lhs_stack * s.M * s.K) * 4;
+            cudaError_t e = cudaSetDevice(dev->ordinal);
+            if (e == cudaSuccess) e = cudaMalloc(&pl->wdq, pl->wdq_bytes);
+            if (e != cudaSuccess) {
+                pl->wdq = nullptr;
+                delete pl;
+                return fail(e == cudaErrorMemoryAllocation ? RT_ERR_NOMEM : RT_ERR_CUDA, std::string("plan scratch: ") + cudaGetErrorString(e));
+            }
+            pl->launches++;
+        } else if (is_quantized(desc->lhs_dt)) {
             pl->scratch_bytes = (uint64_t)(s.lhs_stack * s.M * s.K) * 2;
             cudaError_t e = cudaSetDevice(dev->ordinal);
             if (e == cudaSuccess) e = cudaMalloc(&pl->scratch, pl->scratch_bytes);
@@ -788,7 +802,7 @@ static rt_status build_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan 
             }
         }
         pl->name = std::string(pl->tf32x3 ? "gemm_umma_tf32x3_" : "gemm_umma_") + dtype_name(desc->lhs_dt) + "_" + dtype_name(desc->rhs_dt) +
-                   (pl->bn == UMMA_BN_PAIR ? std::string("_pair256x256") : "_bn" + std::to_string(pl->bn)) + (pl->scratch && !pl->k_pad ? (pl->tf32x3 ? "_presplit" : "_dequant_prepass") : "") +
+                   (pl->bn == UMMA_BN_PAIR ? std::string("_pair256x256") : "_bn" + std::to_string(pl->bn)) + (pl->scratch && !pl->k_pad ? (pl->tf32x3 ? "_presplit" : "_dequant_prepass") : "") + (pl->wdq ? "_dequant_prepass" : "") +
                    (pl->rhs_transpose ? "_rhs_transposed" : "") + (pl->k_pad ? "_kpad" + std::to_string(pl->k_pad) : "");
     } else if (s.N == 1 && !s.trans_lhs) {
         pl->kernel = PK_GEMV_SIMT;
@@ -975,7 +989,23 @@ static rt_status launch_node(rt_plan *plan, const void *lhs, const void *rhs, co
                 if (e != cudaSuccess) break;
                 r32 = act_scratch;
             }
-            const void *P = plan->lhs_is_q ? r32 : lhs, *Q = plan->lhs_is_q ? lhs : r32;
+            const void *wl = lhs;
+            if (plan->wdq_bytes) {
+                // Q8_0F weights as f32; a weight flagged constant keeps its copy with the plan, as the 16-bit route does
+                void *dst = ov && ov->wdq ? ov->wdq : plan->wdq;
+                bool have = false;
+                if (flags & RT_LAUNCH_LHS_CONSTANT) {
+                    void *kept = kept_weight_copy(plan, lhs, st, &have, plan->wdq_bytes);
+                    if (kept) dst = kept;
+                }
+                if (!have) {
+                    e = launch_dequant(s.desc.lhs_dt, (long long)(s.lhs_stack * s.M * s.K), lhs, p.lhs_scales, dst, RT_F32,
+                                       plan->dev->sm_count, st);
+                    if (e != cudaSuccess) break;
+                }
+                wl = dst;
+            }
+            const void *P = plan->lhs_is_q ? r32 : wl, *Q = plan->lhs_is_q ? wl : r32;
             e = launch_gemm_umma_tf32x3(P, Q, out, plan->R, plan->S, (int)s.K, plan->u_stacks, plan->p_stack, plan->q_stack, p.bias,
                                         p.bias_dt, s.has_bias ? BIAS_PER_N : BIAS_NONE, p.epilogue, plan->bn, plan->scratch ? scratch : nullptr,
                                         plan->dev->sm_count, st);
@@ -995,7 +1025,7 @@ static rt_status launch_node(rt_plan *plan, const void *lhs, const void *rhs, co
             void *dst = scratch;
             bool have = false;
             if (flags & RT_LAUNCH_LHS_CONSTANT) {
-                void *kept = kept_weight_copy(plan, lhs, st, &have);
+                void *kept = kept_weight_copy(plan, lhs, st, &have, plan->scratch_bytes);
                 if (kept) dst = kept;
             }
             if (!have) {
@@ -1114,17 +1144,17 @@ rt_status rt_executable_create_planned(rt_device *dev, const rt_dispatch *nodes,
     for (int i = 0; i < n_nodes; i++) {
         const rt_dispatch &n = x->nodes[(size_t)i];
         rt_plan *pl = n.plan;
-        if (!(n.opts.flags & RT_LAUNCH_LHS_CONSTANT) || pl->kernel != PK_GEMM_UMMA || pl->tf32x3 || pl->k_pad || !pl->scratch ||
-            !n.lhs || pl->launches == 0)
-            continue;
+        const bool f32_route = pl->kernel == PK_GEMM_UMMA && pl->tf32x3 && pl->wdq_bytes;
+        const bool f16_route = pl->kernel == PK_GEMM_UMMA && !pl->tf32x3 && !pl->k_pad && pl->scratch;
+        if (!(n.opts.flags & RT_LAUNCH_LHS_CONSTANT) || !(f32_route || f16_route) || !n.lhs || pl->launches == 0) continue;
         bool filled = false;
-        void *copy = kept_weight_copy(pl, n.lhs, dev->stream, &filled);
+        void *copy = kept_weight_copy(pl, n.lhs, dev->stream, &filled, f32_route ? pl->wdq_bytes : pl->scratch_bytes);
         if (!copy) continue;
         if (!filled) {
             const Spec &sp = pl->spec;
             const void *scales = pl->lhs_scale_offset ? (const void *)((const char *)n.lhs + pl->lhs_scale_offset) : nullptr;
-            cudaError_t e = launch_dequant(sp.desc.lhs_dt, (long long)(sp.lhs_stack * sp.M * sp.K), n.lhs, scales, copy, RT_F16,
-                                           dev->sm_count, dev->stream);
+            cudaError_t e = launch_dequant(sp.desc.lhs_dt, (long long)(sp.lhs_stack * sp.M * sp.K), n.lhs, scales, copy,
+                                           f32_route ? RT_F32 : RT_F16, dev->sm_count, dev->stream);
             if (e != cudaSuccess) return fail(RT_ERR_CUDA, std::string("dequantise (") + pl->name + "): " + cudaGetErrorString(e));
             filled_any = true;
         }
@@ -1143,7 +1173,9 @@ rt_status rt_executable_create_planned(rt_device *dev, const rt_dispatch *nodes,
         const rt_plan *pl = x->nodes[(size_t)i].plan;
         if (pl->launches == 0) continue;
         ScratchSet &sc = x->scratch[(size_t)i];
-        if (pl->scratch_bytes && !kept[(size_t)i]) { rec.push_back({pl->scratch_bytes, i, i}); slot.push_back(&sc.scratch); }
+        // (the f32 route's `scratch` is the activations' hi / lo split, needed at every dispatch; its kept copy is `wdq`)
+        if (pl->scratch_bytes && !(kept[(size_t)i] && !pl->tf32x3)) { rec.push_back({pl->scratch_bytes, i, i}); slot.push_back(&sc.scratch); }
+        if (pl->wdq_bytes && !kept[(size_t)i]) { rec.push_back({pl->wdq_bytes, i, i}); slot.push_back(&sc.wdq); }
         if (pl->act_scratch_bytes) { rec.push_back({pl->act_scratch_bytes, i, i}); slot.push_back(&sc.act); }
         if (pl->pair_bytes) { rec.push_back({pl->pair_bytes, i, i}); slot.push_back(&sc.pair); }
     }

@@ -504,6 +504,31 @@ def test_q8_gemm_forms(gpu):
                           w_std=0.03, bias_dt=F16), gpu)
 
 
+@pytest.mark.parametrize("wshape,xshape,bias,epi", [
+    ((1536, 384), (1, 1500, 384), True, 1),      # Whisper fc1 in the reference's default dtypes
+    ((10240, 2560), (1, 128, 2560), True, 0),    # Phi-2 fc1, 128 rows
+    ((520, 352), (3, 33, 352), False, 0),        # ragged, batched rows over one weight
+])
+def test_q8f_f32_prefill_takes_the_tf32x3_gemm(gpu, wshape, xshape, bias, epi):
+    """The reference's default pair (Q8_0F weights, f32 activations; dtype/mod.rs:77-83) in the Linear form: weights
+    dequantised to f32 as (i8)q * d (quant.rs:114-120), then the 3 x TF32 tensor-core GEMM; the f32 bar holds."""
+    err, kernel = check_problem(Problem(Q8F, F32, wshape, xshape, (False, True, True), bias=bias, epilogue=epi, seed=wshape[0] + xshape[1],
+                                        w_std=0.02), gpu)
+    assert kernel.startswith("gemm_umma_tf32x3_Q8_0F_F32") and "dequant_prepass" in kernel, kernel
+    assert err <= 1e-5
+    # as an executable with the weight flagged constant: the f32 copy is kept, dispatch after dispatch gives the same bits
+    w_t, _ = make_lhs(Q8F, wshape, np.random.default_rng(9), 0.02)
+    x = Tensor.from_data(np.random.default_rng(10).standard_normal(xshape).astype(np.float32), gpu, F32)
+    node = w_t.to(gpu).gemm(x, None, False, True, True)
+    first = node.resolve().to(Device.CPU).to_numpy().copy()
+    exe = rb.Executable(gpu, [node])
+    node.write(np.zeros(node.numel(), dtype=np.float32))
+    exe.dispatch()
+    exe.dispatch()
+    gpu.sync()
+    assert np.array_equal(node.to(Device.CPU).to_numpy(), first)
+
+
 def test_dense_f32_phi2_fc1(gpu):
     """Dense f32 Phi-2 fc1 prefill: A f32 [1,128,2560], W f32 [10240,2560] N(0,0.02) rhs-transposed, b f32."""
     err, kernel = check_problem(Problem(F32, F32, (10240, 2560), (1, 128, 2560), (False, True, True), bias=True, seed=101,
