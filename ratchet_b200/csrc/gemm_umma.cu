@@ -193,13 +193,13 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
 // The plain epilogue of one accumulator tile (128 rows x BN columns of this CTA's tensor memory at `tmem_acc`): 64
 // columns per round: two tensor-memory loads, the epilogue arithmetic, then through a per-warp staging buffer so that
 // global stores run along rows: 8 lanes x 16 B = one full 128-byte line per row (this matters most when the destination
-// is a peer GPU over NVLink).  `bar_done` (a shared::cluster address: this CTA's barrier, or the leading CTA's for a CTA
-// pair) gets one arrival per warp once the warp has read its part of the accumulator.
+// is a peer GPU over NVLink).  `bar_done` (this CTA's barrier, or with REMOTE_DONE the shared::cluster address of the
+// leading CTA's) gets one arrival per warp once the warp has read its part of the accumulator.
 __device__ __forceinline__ void arrive_cluster(uint32_t bar_cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
-template <int BN, typename OutT>
+template <int BN, typename OutT, bool REMOTE_DONE>
 __device__ __forceinline__ void epilogue_tile(const UmmaParams &prm, uint32_t tmem_acc, uint32_t bar_done, int r0, int s0, int b, int q, int half,
                                               int lane, uint8_t *stg, const float *bias_s, bool has_bias, float row_bias, bool vec_ok,
                                               bool pair_ok) {
@@ -215,7 +215,10 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams &prm, uint32_t tm
                 // the accumulator has been read completely: hand it back to the MMA warp now
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) arrive_cluster(bar_done);
+                if (lane == 0) {
+                    if (REMOTE_DONE) arrive_cluster(bar_done);
+                    else mbar_arrive(bar_done);
+                }
             }
             {
 #pragma unroll
@@ -282,7 +285,8 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams &prm, uint32_t tm
     }
 }
 
-template <int BN, typename OutT>
+// PAIR: the gate/up fold of RT_EPILOGUE_SILU_MUL (see UmmaParams::pair), compiled only into the kernels that run it
+template <int BN, typename OutT, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const UmmaParams prm) {
     using C = Cfg<BN>;
@@ -339,14 +343,14 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                 const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
                 int tr, ts;
                 tile_coords(rem, prm.tiles_r, prm.tiles_s, prm.group_r, tr, ts);
-                const int r0 = tr * BM, s0 = ts * (prm.pair ? BN / 2 : BN);
+                const int r0 = tr * BM, s0 = ts * (PAIR ? BN / 2 : BN);
                 const int bp = b % prm.p_stack, bq = b % prm.q_stack;
                 for (int kb = 0; kb < num_k; kb++) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, 1)) { ok = false; break; }
                     const uint32_t a_dst = smem_u32(tiles + stage * C::STAGE_BYTES);
                     mbar_expect_tx(bar_full + 8 * stage, C::STAGE_BYTES);
                     tma_load_3d(a_dst, &map_p, kb * BK, r0, bp, bar_full + 8 * stage);
-                    if (prm.pair) tma_load_4d(a_dst + C::A_BYTES, &map_q, kb * BK, s0, 0, bq, bar_full + 8 * stage);
+                    if (PAIR) tma_load_4d(a_dst + C::A_BYTES, &map_q, kb * BK, s0, 0, bq, bar_full + 8 * stage);
                     else tma_load_3d(a_dst + C::A_BYTES, &map_q, kb * BK, s0, bq, bar_full + 8 * stage);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -398,7 +402,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             const int b = tile / tiles_per_batch, rem = tile % tiles_per_batch;
             int tr, ts;
             tile_coords(rem, prm.tiles_r, prm.tiles_s, prm.group_r, tr, ts);
-            const int r0 = tr * BM, s0 = ts * (prm.pair ? BN / 2 : BN);
+            const int r0 = tr * BM, s0 = ts * (PAIR ? BN / 2 : BN);
             // The eight warps leave together: the barrier hands every thread the OR of what each of them saw, so
             // none is left waiting at a barrier for a warp that has gone.
             if (bar_red_or(1, EPI_WARPS * 32, gave_up || *abort_flag != 0)) break;
@@ -406,8 +410,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             if (prm.bias_mode == BIAS_PER_N) {
                 for (int j = ep_tid; j < BN; j += EPI_WARPS * 32) {
                     // paired tiles: accumulator column j holds weight row (j / (BN/2)) * ff + s0 + j % (BN/2)
-                    const int jj = prm.pair ? j % (BN / 2) : j;
-                    const int wrow = prm.pair ? (j / (BN / 2)) * prm.s_out + s0 + jj : s0 + j;
+                    const int jj = PAIR ? j % (BN / 2) : j;
+                    const int wrow = PAIR ? (j / (BN / 2)) * prm.s_out + s0 + jj : s0 + j;
                     bias_s[j] = (s0 + jj < prm.s_out) ? load_bias(prm.bias, prm.bias_dt, wrow) : 0.f;
                 }
             }
@@ -422,7 +426,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             // per-warp staging buffer so that global stores run along rows: 8 lanes x 16 B = one full
             // 128-byte line per row (this matters most when the destination is a peer GPU over NVLink)
             uint8_t *stg = stage_out + (warp - 2) * (32 * STG_ROW_BYTES);
-            if (prm.pair) {
+            if (PAIR) {
                 // 32 output columns per round: the gate accumulators, the up accumulators BN/2 columns further on,
                 // up * silu(gate), then out through the staging rows (four 16-byte chunks each)
 #pragma unroll 1
@@ -485,7 +489,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
                 continue;
             }
-            epilogue_tile<BN, OutT>(prm, tmem_base + acc * BN, bar_tempty + 8 * acc, r0, s0, b, q, half, lane, stg, bias_s, has_bias, row_bias,
+            epilogue_tile<BN, OutT, false>(prm, tmem_base + acc * BN, bar_tempty + 8 * acc, r0, s0, b, q, half, lane, stg, bias_s, has_bias, row_bias,
                                     vec_ok, pair_ok);
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
@@ -685,7 +689,7 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_co
             float row_bias = 0.f;
             if (prm.bias_mode == BIAS_PER_M && row < prm.R) row_bias = load_bias(prm.bias, prm.bias_dt, row);
             uint8_t *stg = stage_out + (warp - 2) * (32 * STG_ROW_BYTES);
-            epilogue_tile<BN, OutT>(prm, tmem_base + acc * BN, tempty0 + 8 * acc, r0, s0, b, q, half, lane, stg, bias_s, has_bias, row_bias, vec_ok,
+            epilogue_tile<BN, OutT, true>(prm, tmem_base + acc * BN, tempty0 + 8 * acc, r0, s0, b, q, half, lane, stg, bias_s, has_bias, row_bias, vec_ok,
                                     pair_ok);
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
@@ -761,9 +765,10 @@ template <int BN, typename OutT>
 cudaError_t launch_bn(const CUtensorMap &mp, const CUtensorMap &mq, UmmaParams prm, int sm_count, cudaStream_t stream) {
     using C = Cfg<BN>;
     static SmemAttr smem_attr;
-    auto kernel = gemm_umma_kernel<BN, OutT>;
+    static SmemAttr smem_attr_pair;
+    auto kernel = prm.pair ? gemm_umma_kernel<BN, OutT, true> : gemm_umma_kernel<BN, OutT, false>;
     {
-        cudaError_t e = smem_attr.ensure(kernel, C::SMEM_BYTES);
+        cudaError_t e = (prm.pair ? smem_attr_pair : smem_attr).ensure(kernel, C::SMEM_BYTES);
         if (e != cudaSuccess) return e;
     }
     prm.tiles_r = (prm.R + BM - 1) / BM;
