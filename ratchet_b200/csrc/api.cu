@@ -130,7 +130,7 @@ static std::string plan_key(const rt_matmul_desc &d) {
     put_shape(d.lhs_shape); put_shape(d.rhs_shape);
     if (d.has_bias) put_shape(d.bias_shape);
     put(d.has_bias != 0); put(d.trans_lhs != 0); put(d.trans_rhs != 0); put(d.trans_out != 0); put(d.epilogue);
-    for (const char *name : {"RT_FORCE_KERNEL", "RT_GEMV_UMMA", "RT_Q4K_UMMA", "RT_GEMM_PAIR", "RT_TF32_BN", "RT_TF32_PRESPLIT", "RT_Q4K_WALK_FROM", "RT_KEEP_WEIGHTS"}) {
+    for (const char *name : {"RT_FORCE_KERNEL", "RT_GEMV_UMMA", "RT_Q4K_UMMA", "RT_GEMM_PAIR", "RT_GEMM_PAIR_MIN", "RT_TF32_BN", "RT_TF32_PRESPLIT", "RT_Q4K_WALK_FROM", "RT_KEEP_WEIGHTS"}) {
         const char *v = getenv(name);
         k += '|';
         if (v) k += v;
@@ -530,6 +530,14 @@ static bool gemm_pair_enabled() {
     return !(v && v[0] == '0');
 }
 
+// fewest 256 x 256 tiles at which the CTA-pair kernel is taken (RT_GEMM_PAIR_MIN overrides: A/B timing)
+static long long gemm_pair_min_tiles(int sm_count) {
+    const char *v = getenv("RT_GEMM_PAIR_MIN");
+    // from four fifths of a wave of pairs (measured: 64 tiles on 74 pairs, Q4_K [8192,3072] x 512 rows: 27.2 -> 25.1 us;
+    // 36 tiles, the Whisper MLP: 22.7 -> 30.9 us)
+    return v ? atoll(v) : (long long)(sm_count / 2) * 4 / 5;
+}
+
 static bool force_simt() {
     const char *v = getenv("RT_FORCE_KERNEL");
     return v && std::string(v) == "simt";
@@ -722,9 +730,9 @@ static rt_status build_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan 
         pl->tf32x3 = desc->rhs_dt == RT_F32;
         pl->bn = pl->tf32x3 ? umma_tf32_pick_bn(pl->R, pl->S, pl->u_stacks, dev->sm_count)
                             : umma_pick_bn(pl->R, pl->S, pl->u_stacks, dev->sm_count);
-        // problems with at least two 256 x 256 tiles per pair of SMs: two CTAs per tile (tcgen05 cta_group::2)
+        // problems that fill most of a wave of SM pairs with 256 x 256 tiles: two CTAs per tile (tcgen05 cta_group::2)
         if (!pl->tf32x3 && s.epilogue != RT_EPILOGUE_SILU_MUL && gemm_pair_enabled() && dev->sm_count >= 2 &&
-            (long long)((pl->R + 255) / 256) * ((pl->S + 255) / 256) * pl->u_stacks >= dev->sm_count)
+            (long long)((pl->R + 255) / 256) * ((pl->S + 255) / 256) * pl->u_stacks >= gemm_pair_min_tiles(dev->sm_count))
             pl->bn = UMMA_BN_PAIR;
         pl->launches = 1;
         if (!s.trans_rhs) {
