@@ -81,6 +81,11 @@ def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
     return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
 
 
+# environment switches that change which kernel a plan takes (the library's cache key holds them too)
+_ROUTING_SWITCHES = ("RT_FORCE_KERNEL", "RT_GEMV_UMMA", "RT_Q4K_UMMA", "RT_GEMM_PAIR", "RT_GEMM_PAIR_MIN", "RT_TF32_BN",
+                     "RT_TF32_PRESPLIT", "RT_Q4K_WALK_FROM", "RT_KEEP_WEIGHTS")
+
+
 class DeviceRequest(enum.Enum):
     CPU = "cpu"
     GPU = "gpu"
@@ -131,11 +136,16 @@ class Device:
 
     def plan_for(self, desc: "_lib.rt_matmul_desc"):
         """The compiled-op cache: one plan per distinct node description (the KernelKey's role)."""
-        # the library keeps the cache (and keys it by the routing switches of the environment too); the hold this
-        # call takes goes straight back, the device's own keeps the plan alive as long as the device lives
-        h = c_void_p()
-        check(_lib.load().rt_matmul_plan(self._h, byref(desc), byref(h)))
-        check(_lib.load().rt_plan_destroy(h))
+        # The library keeps the cache (keyed by the description and by the routing switches of the environment); this
+        # memo only saves the two calls per node on the lazy path.  The hold rt_matmul_plan takes goes straight back:
+        # the device's own keeps the plan alive as long as the device lives.
+        key = (bytes(desc), tuple(os.environ.get(n) for n in _ROUTING_SWITCHES))
+        h = self._plans.get(key)
+        if h is None:
+            h = c_void_p()
+            check(_lib.load().rt_matmul_plan(self._h, byref(desc), byref(h)))
+            check(_lib.load().rt_plan_destroy(h))
+            self._plans[key] = h
         return h
 
     def __repr__(self):
