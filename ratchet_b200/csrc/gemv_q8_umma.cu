@@ -43,10 +43,11 @@ __device__ int g_gemv_umma_error = 0;
 
 namespace {
 
-constexpr int THREADS = 224;          // warp 0: TMA producer, warps 1 and 6: MMA issuers, warps 2-5: digits + epilogue
+constexpr int THREADS = 288;          // warp 0: TMA producer, warps 1, 6, 7, 8: MMA issuers, warps 2-5: digits + epilogue
+constexpr int N_ISSUE = 4;
 constexpr int STAGE_K = 256;          // bytes of K per ring stage = 8 Q8_0 blocks = two 128-byte swizzle rows
 constexpr int TMEM_COLS = 256;        // half of an SM's tensor memory
-constexpr int TG_COLS = 64;           // tensor-memory columns per stage: 32 per issuing thread (see the MMA issuers)
+constexpr int TG_COLS = 128;          // tensor-memory columns per stage: 32 per issuing thread (see the MMA issuers)
 constexpr int TGROUPS = TMEM_COLS / TG_COLS;
 
 struct UmmaGemvParams {
@@ -101,10 +102,10 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (threadIdx.x == 0) {
         for (int s = 0; s < up.ring; s++) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 6); // the two issuers' commits + the four epilogue warps (they read the stage's scales)
+            mbar_init(bar_empty + 8 * s, N_ISSUE + 4); // the issuers' commits + the four epilogue warps (they read the stage's scales)
         }
         for (int a = 0; a < TGROUPS; a++) {
-            mbar_init(bar_tfull + 8 * a, 2);
+            mbar_init(bar_tfull + 8 * a, N_ISSUE);
             mbar_init(bar_tempty + 8 * a, 4);
         }
         mbar_init(bar_x, 4);
@@ -147,12 +148,13 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (++slot == up.ring) { slot = 0; phase ^= 1; }
             }
         }
-    } else if (warp == 1 || warp == 6) {
-        // ------------------------------------------------------------------ MMA issuers: each takes one of a stage's two
-        // 128-byte sub-tiles.  One thread issues a tcgen05.mma about every 130 cycles beside the other warps of two resident
-        // CTAs (70 on an idle SM), which for the 80 MMAs of a Phi-2 sized share was most of the launch.
+    } else if (warp == 1 || warp >= 6) {
+        // ------------------------------------------------------------------ MMA issuers: each takes two of a stage's eight
+        // blocks.  One thread issues a tcgen05.mma about every 130 cycles beside the other warps of two resident CTAs (70
+        // on an idle SM), which for the 80 MMAs of a Phi-2 sized share was most of the launch.
         if (lane == 0) {
-            const int kk = warp == 1 ? 0 : 1;
+            const int issuer = warp == 1 ? 0 : warp - 5; // 0..3
+            const int kk = issuer >> 1, j0 = (issuer & 1) * 2; // sub-tile, first block of the sub-tile
             // instruction descriptor: s32 accumulate, signed 8-bit A and B, K-major, N = 16, M = 128
             const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
             const uint64_t a_desc_ring = umma_desc_sw128(smem_u32(ring), 1024), b_desc_base = umma_desc_sw128(smem_u32(b_tiles), 0);
@@ -170,13 +172,12 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const uint32_t d0 = tmem_base + tg * TG_COLS;
                 {
                     const uint64_t ak = a_desc + (uint64_t)((uint32_t)(kk * up.rb8 * 128) >> 4), bk = b_desc + (uint64_t)(kk * (1024 >> 4));
-                    // Block j of this thread's sub-tile writes columns [2j, 2j+16) of the thread's half of the stage's
-                    // group: its two sums (the hi and lo digit rows of B) followed by columns it does not need.  MMAs
-                    // of one thread execute in issue order and block j+1 starts two columns later, so the last writer
-                    // of column c < 8 is block c/2: after the fourth block the half's first eight columns hold hi0,
-                    // lo0, .. hi3, lo3.  The other thread's MMAs are not ordered against these, hence the halves.
+                    // Each MMA writes 16 columns: a block's two sums (the hi and lo digit rows of B) followed by columns it
+                    // does not need.  MMAs of one thread execute in issue order and this thread's second block starts two
+                    // columns after its first, so its quarter of the stage's group begins hi, lo, hi, lo.  The other
+                    // threads' MMAs are not ordered against these, hence a quarter of 32 columns per thread.
 #pragma unroll
-                    for (int j = 0; j < 4; j++) umma_i8(d0 + kk * 32 + j * 2, ak + 2 * j, bk + 2 * j, idesc);
+                    for (int j = 0; j < 2; j++) umma_i8(d0 + issuer * 32 + j * 2, ak + 2 * (j0 + j), bk + 2 * (j0 + j), idesc);
                 }
                 umma_commit(bar_empty + 8 * slot);
                 umma_commit(bar_tfull + 8 * tg);
@@ -230,9 +231,9 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
             if (!mbar_wait(bar_tfull + 8 * tg, tphase, abort_flag, 6)) break;
             tc_fence_after();
-            int dva[8], dvb[8]; // the two sub-tiles' sums: hi, lo of blocks 0..3 and of blocks 4..7
-            tmem_ld8_nowait(tmem_base + tg * TG_COLS + ((uint32_t)(q * 32) << 16), dva);
-            tmem_ld8_nowait(tmem_base + tg * TG_COLS + 32 + ((uint32_t)(q * 32) << 16), dvb);
+            int dq[N_ISSUE][8]; // per issuing thread: hi, lo of its two blocks (the upper four values are not loaded)
+#pragma unroll
+            for (int i = 0; i < N_ISSUE; i++) tmem_ld4_nowait(tmem_base + tg * TG_COLS + 32 * i + ((uint32_t)(q * 32) << 16), dq[i]);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
@@ -243,7 +244,7 @@ q8_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 const float d = (j & 1) ? __high2float(d2[j >> 1]) : __low2float(d2[j >> 1]);
-                acc = add_block(acc, d, xsv[j], j < 4 ? dva[2 * j] : dvb[2 * (j - 4)], j < 4 ? dva[2 * j + 1] : dvb[2 * (j - 4) + 1]);
+                acc = add_block(acc, d, xsv[j], dq[j >> 1][2 * (j & 1)], dq[j >> 1][2 * (j & 1) + 1]); // block j: issuer j / 2
             }
             if (++slot == up.ring) { slot = 0; phase ^= 1; }
             if (++tg == TGROUPS) { tg = 0; tphase ^= 1; }
