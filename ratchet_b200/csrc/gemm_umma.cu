@@ -22,6 +22,8 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 #include "kernels.hpp"
@@ -63,6 +65,7 @@ struct UmmaParams {
     int pair, s_out;
     int tiles_r, tiles_s;
     int group_r; // tile rows per group of the tile order (tile_coords); tiles_r: plain order, tile rows fastest
+    int tma_store; // CTA-pair kernel: the epilogue hands its staged 32 x 64 blocks to TMA stores (one per destination)
     uint32_t idesc;
 };
 
@@ -199,13 +202,28 @@ __device__ __forceinline__ void arrive_cluster(uint32_t bar_cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
-template <int BN, typename OutT, bool REMOTE_DONE>
+// One tensor map per destination of the output ([stacks][R][window end] of 16-bit values, 128-byte swizzle, boxes of 64
+// columns x 32 rows: what one epilogue warp stages per round).
+struct OutMaps {
+    CUtensorMap m[RT_MAX_PEERS];
+};
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, int c0, int c1, int c2, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(src) : "memory");
+}
+
+template <int BN, typename OutT, bool REMOTE_DONE, bool TMA_STORE = false>
 __device__ __forceinline__ void epilogue_tile(const UmmaParams &prm, uint32_t tmem_acc, uint32_t bar_done, int r0, int s0, int b, int q, int half,
                                               int lane, uint8_t *stg, const float *bias_s, bool has_bias, float row_bias, bool vec_ok,
-                                              bool pair_ok) {
+                                              bool pair_ok, const OutMaps *omaps = nullptr) {
 #pragma unroll 1
     for (int cc = half; cc < BN / 64; cc += 2) {
         const int colbase = s0 + cc * 64;
+        if (TMA_STORE && prm.tma_store) {
+            // the stores of the previous round have read the staging block
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            __syncwarp();
+        }
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const int c = cc * 2 + h;
@@ -238,7 +256,18 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams &prm, uint32_t tm
             }
         }
         __syncwarp();
-        if (vec_ok) {
+        if (TMA_STORE && prm.tma_store) {
+            // The staged block is the image a 128-byte-swizzled TMA box wants (16-byte chunks XOR the row index, the
+            // warp's block on a 1024-byte boundary): one bulk store per destination, clipped by the map at the tensor's
+            // last row and at the end of this shard's column window.
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                for (int d = 0; d < prm.n_out; d++)
+                    tma_store_3d(&omaps->m[d], (int)prm.out_col + colbase, r0 + q * 32, b, smem_u32(stg));
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+        } else if (vec_ok) {
             const int colv = colbase + (lane & 7) * 8;
 #pragma unroll
             for (int i = 0; i < 8; i++) {
@@ -560,16 +589,18 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 
 template <typename OutT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const UmmaParams prm) {
+gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const __grid_constant__ OutMaps omaps,
+                      const UmmaParams prm) {
     constexpr int BN = P2_BN;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *tiles = smem;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + P2_STAGES * P2_STAGE_BYTES);
+    // the store staging follows the ring, so each warp's 4 KB block sits on a 1024-byte boundary (the TMA stores' swizzle)
+    uint8_t *stage_out = smem + P2_STAGES * P2_STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(stage_out + EPI_WARPS * 32 * STG_ROW_BYTES);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * P2_STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    float *bias_s = reinterpret_cast<float *>(smem + P2_STAGES * P2_STAGE_BYTES + 256);
-    uint8_t *stage_out = smem + P2_STAGES * P2_STAGE_BYTES + 256 + BN * 4;
+    float *bias_s = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(bars) + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank(); // 0: the leading CTA
@@ -689,10 +720,12 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_co
             float row_bias = 0.f;
             if (prm.bias_mode == BIAS_PER_M && row < prm.R) row_bias = load_bias(prm.bias, prm.bias_dt, row);
             uint8_t *stg = stage_out + (warp - 2) * (32 * STG_ROW_BYTES);
-            epilogue_tile<BN, OutT, true>(prm, tmem_base + acc * BN, tempty0 + 8 * acc, r0, s0, b, q, half, lane, stg, bias_s, has_bias, row_bias, vec_ok,
-                                    pair_ok);
+            epilogue_tile<BN, OutT, true, true>(prm, tmem_base + acc * BN, tempty0 + 8 * acc, r0, s0, b, q, half, lane, stg, bias_s, has_bias, row_bias,
+                                                vec_ok, pair_ok, &omaps);
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
+        // the warp's bulk stores are complete (written, not only read) before the CTA goes
+        if (prm.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     // ---------------------------------------------------------------- teardown
@@ -781,8 +814,27 @@ cudaError_t launch_bn(const CUtensorMap &mp, const CUtensorMap &mq, UmmaParams p
     return launch_pdl(kernel, dim3(grid), dim3(NUM_THREADS), C::SMEM_BYTES, stream, mp, mq, prm);
 }
 
+// The output as the epilogue's TMA stores see it: [stacks][R][columns up to the end of this launch's window].
+bool make_out_maps(OutMaps *om, const UmmaParams &prm, rt_dtype dt) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    if (prm.out_ld % 8 != 0 || prm.out_col % 8 != 0 || prm.out_batch_stride % 8 != 0) return false;
+    for (int d = 0; d < prm.n_out; d++) {
+        if (reinterpret_cast<uintptr_t>(prm.outs[d]) % 16 != 0) return false;
+        cuuint64_t dims[3] = {(cuuint64_t)(prm.out_col + prm.s_out), (cuuint64_t)prm.R, (cuuint64_t)prm.stacks};
+        cuuint64_t strides[2] = {(cuuint64_t)prm.out_ld * 2, (cuuint64_t)prm.out_batch_stride * 2};
+        cuuint32_t box[3] = {64, 32, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        if (fn(&om->m[d], dt == RT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, prm.outs[d], dims, strides, box,
+               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+    }
+    return true;
+}
+
 template <typename OutT>
-cudaError_t launch_pair(const CUtensorMap &mp, const CUtensorMap &mq, UmmaParams prm, int sm_count, cudaStream_t stream) {
+cudaError_t launch_pair(const CUtensorMap &mp, const CUtensorMap &mq, UmmaParams prm, int sm_count, cudaStream_t stream, rt_dtype out_dt) {
     static SmemAttr smem_attr;
     auto kernel = gemm_umma_pair_kernel<OutT>;
     {
@@ -810,7 +862,12 @@ cudaError_t launch_pair(const CUtensorMap &mp, const CUtensorMap &mq, UmmaParams
     attr[1].val.clusterDim.z = 1;
     lc.attrs = attr;
     lc.numAttrs = 2;
-    return cudaLaunchKernelEx(&lc, kernel, mp, mq, prm);
+    // RT_GEMM_TMA_STORE=0 keeps the epilogue on the SM's own stores (A/B timing)
+    static const bool tma_store_wanted = [] { const char *v = getenv("RT_GEMM_TMA_STORE"); return !(v && v[0] == '0'); }();
+    OutMaps om;
+    memset(&om, 0, sizeof(om));
+    prm.tma_store = tma_store_wanted && make_out_maps(&om, prm, out_dt) ? 1 : 0;
+    return cudaLaunchKernelEx(&lc, kernel, mp, mq, om, prm);
 }
 
 } // namespace
@@ -866,8 +923,8 @@ cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dty
     prm.epilogue = epilogue;
     prm.idesc = ((p_dt == RT_BF16 ? 1u : 0u) << 7) | ((q_dt == RT_BF16 ? 1u : 0u) << 10);
     if (bn == UMMA_BN_PAIR) {
-        if (out_dt == RT_F16) return launch_pair<__half>(mp, mq, prm, sm_count, stream);
-        if (out_dt == RT_BF16) return launch_pair<__nv_bfloat16>(mp, mq, prm, sm_count, stream);
+        if (out_dt == RT_F16) return launch_pair<__half>(mp, mq, prm, sm_count, stream, out_dt);
+        if (out_dt == RT_BF16) return launch_pair<__nv_bfloat16>(mp, mq, prm, sm_count, stream, out_dt);
         return cudaErrorInvalidValue;
     }
     if (out_dt == RT_F16)
