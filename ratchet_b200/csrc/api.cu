@@ -159,6 +159,15 @@ struct rt_executable {
     bool chain_refused = false; // its launch was refused once: dispatch node by node from then on
     std::string how = "nodes";
     int launches = 0;
+    ~rt_executable() { // also what a failed rt_executable_create leaves behind
+        if (exec) cudaGraphExecDestroy(exec);
+        if (graph) cudaGraphDestroy(graph);
+        if (chain) gemv_chain_destroy(chain);
+        if (arena) {
+            cudaSetDevice(dev->ordinal);
+            cudaFree(arena);
+        }
+    }
 };
 
 // RT_KEEP_WEIGHTS=0: dequantise on every launch even for weights flagged constant (A/B timing, memory-tight callers).
@@ -1340,13 +1349,6 @@ rt_status rt_executable_dispatch(rt_executable *exe, void *stream) {
 
 rt_status rt_executable_destroy(rt_executable *exe) {
     if (!exe) return RT_OK;
-    if (exe->exec) cudaGraphExecDestroy(exe->exec);
-    if (exe->graph) cudaGraphDestroy(exe->graph);
-    if (exe->chain) gemv_chain_destroy(exe->chain);
-    if (exe->arena) {
-        cudaSetDevice(exe->dev->ordinal);
-        cudaFree(exe->arena);
-    }
     delete exe;
     return RT_OK;
 }
