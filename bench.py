@@ -456,11 +456,14 @@ def time_cpu(weights_raw, x16, budget_s: float, max_layers: int):
     cpu_step(weights_raw, x16, 1)  # cost estimate per layer
     per_layer = time.perf_counter() - t0
     layers = int(max(1, min(max_layers, budget_s / max(per_layer, 1e-6))))
-    passes = int(max(1, budget_s / max(per_layer * layers, 1e-6)))
+    passes = 0
     t0 = time.perf_counter()
-    for _ in range(passes):
+    while True:  # whole passes until the budget is used (the per-layer estimate above is only good for choosing `layers`)
         cpu_step(weights_raw, x16, layers)
-    dt = time.perf_counter() - t0
+        passes += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s or dt + dt / passes > 1.5 * budget_s:
+            break
     gbs = passes * layers * 2 * BYTES_PER_GEMV / dt / 1e9
     return gbs, layers, passes, dt
 
