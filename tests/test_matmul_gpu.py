@@ -783,6 +783,43 @@ def test_gemm_on_cta_pairs_matches_the_oracle_and_the_single_cta_kernel(gpu, mon
     assert oracle.rel_l2(got.to_f32().reshape(rows_total, N)[rows], truth_r.reshape(len(rows), N)) <= TOL[act]
 
 
+@pytest.mark.parametrize("N,K,rows,widths,kernel_part", [
+    (10240, 512, 1536, [3424, 3408, 3408], "pair256x256"),   # windows that end inside a 64-column block: the TMA stores clip
+    (768, 256, 200, [272, 256, 240], "bn"),                   # the one-CTA kernel's scatter
+])
+def test_scattered_outputs_on_one_gpu(gpu, N, K, rows, widths, kernel_part):
+    """The N-sharded prefill form with every shard on ONE GPU: each shard's GEMM writes its column window into TWO
+    full-width output buffers (rt_matmul_launch_ex with n_out = 2, the peer-store epilogue with local "peers").  Both
+    buffers end up holding the unsharded Linear's result, bit for bit, and nothing outside a window is touched."""
+    from ctypes import byref
+    lib = rb._lib.load()
+    w_t, wv = make_lhs(Q8H, (N, K), np.random.default_rng(31), 0.03)
+    b = round_to(F16, np.random.default_rng(32).standard_normal(N).astype(np.float32) * 0.1)
+    x = round_to(BF16, np.random.default_rng(33).standard_normal((rows, K)).astype(np.float32))
+    x_d = Tensor.from_data(x, gpu, BF16)
+    whole = w_t.to(gpu).gemm(x_d, Tensor.from_data(b, gpu, F16), False, True, True, epilogue=rb.EPILOGUE_GELU_TANH)
+    want = whole.resolve().to(Device.CPU).to_numpy().reshape(rows, N)
+    outs = [Tensor([rows, N], BF16, gpu, rb.GpuBuffer(gpu, rows * N * 2)) for _ in range(2)]
+    for o in outs:
+        o.write(np.full(rows * N, 0x7FC0, dtype=np.uint16))  # bf16 NaN: an unwritten element would show
+    c0 = 0
+    for wd in widths:
+        shard = rb.shard_rows(w_t, c0, c0 + wd).to(gpu)
+        bias = Tensor.from_data(np.ascontiguousarray(b[c0:c0 + wd]), gpu, F16)
+        node = shard.gemm(x_d, bias, False, True, True, epilogue=rb.EPILOGUE_GELU_TANH)
+        plan = gpu.plan_for(node.op.desc)
+        assert kernel_part in lib.rt_plan_kernel(plan).decode(), lib.rt_plan_kernel(plan).decode()
+        opts = rb._lib.rt_launch_opts()
+        opts.flags, opts.n_out = rb._lib.RT_LAUNCH_LHS_CONSTANT, 2
+        opts.outs[0], opts.outs[1] = outs[0].ptr, outs[1].ptr
+        opts.out_ld, opts.out_col = N, c0
+        rb._lib.check(lib.rt_matmul_launch_ex(plan, shard.ptr, x_d.ptr, bias.ptr, None, None, byref(opts)))
+        c0 += wd
+    gpu.sync()
+    for o in outs:
+        assert np.array_equal(o.to(Device.CPU).to_numpy().reshape(rows, N), want)
+
+
 @pytest.mark.parametrize("M", [2048, 8192], ids=["4x2048", "4x8192"])
 def test_q8_bf16_prefill_full_size_sampled(gpu, M):
     """The sharded prefill workload at full size on one GPU: A bf16 [4,M,2560], W Q8_0H [10240,2560], f16 bias,
