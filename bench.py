@@ -195,12 +195,59 @@ def time_nodes(gpu, stream, nodes, reps: int, warmup: int = 3):
     return e0.elapsed_time(e1) * 1e3 / reps, kernels, exe.launches
 
 
-def time_node(gpu, stream, make_node, copies: int, iters: int, warmup: int = 3):
+def time_node(gpu, stream, make_node, copies: int, iters: int, warmup: int = 3, keep=None):
     """Times one Matmul node: `copies` independent operand sets are rotated inside one executable so
-    that a memory-bound node never finds its weights in L2.  Returns microseconds per node."""
+    that a memory-bound node never finds its weights in L2.  Returns microseconds per node.  `keep`, a list, receives
+    the first copy's node (its output is what the parity check reads)."""
     nodes = [make_node(i) for i in range(copies)]
     us, kernels, launches = time_nodes(gpu, stream, nodes, max(1, iters // copies), warmup)
+    if keep is not None:
+        keep.append(nodes[0])
     return us / copies, kernels[0], launches // copies
+
+
+def mlp_parity(out_t, w1_host, b1_host, w2_host, b2_host, x_host, act, n_rows=6):
+    """rel-L2 of sampled rows of an MLP block's f16 output against the fp64 oracle (hidden rounded to f16 between the
+    nodes, as the reference's graph holds it); act: "gelu" or "silu_gate"."""
+    import oracle
+    from ratchet_b200 import Device
+    n1, k1 = w1_host.shape
+    n2, k2 = w2_host.shape
+    xv = x_host.to_f32().reshape(-1, k1)
+    rows = np.unique(np.concatenate([[0, xv.shape[0] - 1], np.random.default_rng(7).integers(0, xv.shape[0], size=n_rows)]))
+    b1 = b1_host.to_f32().reshape(-1) if b1_host is not None else None
+    b2 = b2_host.to_f32().reshape(-1) if b2_host is not None else None
+    h = oracle.matmul_truth(w1_host.to_f32().reshape(n1, k1), xv[rows], b1, 1, 1, 1, n1, len(rows), k1, False, True, True,
+                            1 if act == "gelu" else 0).reshape(len(rows), n1)
+    if act == "silu_gate":
+        h = oracle.silu_mul_truth(h)
+    h16 = oracle.f64_to_f16(h).astype(np.float32)
+    t = oracle.matmul_truth(w2_host.to_f32().reshape(n2, k2), h16, b2, 1, 1, 1, n2, len(rows), k2, False, True, True, 0).reshape(len(rows), n2)
+    have = out_t.to(Device.CPU).to_numpy().reshape(-1, n2)[rows].astype(np.float32)
+    return oracle.rel_l2(have, oracle.f64_to_f16(t).astype(np.float32))
+
+
+def linear_parity(node, w_host, x_host, b_host, epilogue, n_rows=8):
+    """rel-L2 of sampled rows of a Linear node's output against the fp64 oracle over the weight's exact values (the
+    oracle is the checker here, after and outside every timed region)."""
+    import oracle
+    from ratchet_b200 import Device, DType, Quantizer
+    N, K = w_host.shape
+    wv = (Quantizer.dequantize_bytes(w_host.to_numpy(), w_host.dt, N * K) if w_host.dt.is_quantized() else w_host.to_f32()).reshape(N, K)
+    xv = x_host.to_f32().reshape(-1, K)
+    rows = np.unique(np.concatenate([[0, xv.shape[0] - 1], np.random.default_rng(7).integers(0, xv.shape[0], size=n_rows)]))
+    bv = b_host.to_f32().reshape(-1) if b_host is not None else None
+    truth = oracle.matmul_truth(wv, xv[rows], bv, 1, 1, 1, N, len(rows), K, False, True, True, epilogue).reshape(len(rows), N)
+    got = node.to(Device.CPU)
+    raw = got.to_numpy().reshape(-1, N)[rows]  # only the sampled rows are converted
+    if got.dt == DType.F16:
+        want, have = oracle.f64_to_f16(truth).astype(np.float32), raw.astype(np.float32)
+    elif got.dt == DType.BF16:
+        want = oracle.bf16_bits_to_f32(oracle.f64_to_bf16_bits(truth)).reshape(truth.shape)
+        have = oracle.bf16_bits_to_f32(np.ascontiguousarray(raw).reshape(-1)).reshape(truth.shape)
+    else:
+        want, have = truth.astype(np.float32), raw.astype(np.float32)
+    return oracle.rel_l2(have, want)
 
 
 # measured DRAM bytes per call (ncu dram__bytes_read.sum + dram__bytes_write.sum, profiles/), where a capture exists
@@ -231,7 +278,7 @@ def run_extras(which, gpu, stream):
     def act(shape, dt, seed):
         return Tensor.from_data(np.random.default_rng(seed).standard_normal(shape, dtype=np.float32), dt=dt)
 
-    def record(name, us, kernel, launches, flops, nbytes, bound, note=""):
+    def record(name, us, kernel, launches, flops, nbytes, bound, note="", parity=None):
         tfs, gbs = flops / us / 1e6, nbytes / us / 1e3
         peak = tf_burst if bound == "tensor" else hbm
         ach = tfs if bound == "tensor" else gbs
@@ -241,43 +288,50 @@ def run_extras(which, gpu, stream):
                                  "unit": "TFLOP/s" if bound == "tensor" else "GB/s", "frac": ach / peak,
                                  "peak_kind": f"of {tf_kind if bound == 'tensor' else hbm_kind}",
                                  "traffic": NCU_TRAFFIC.get(name)}, "note": note})
+        if parity is not None:
+            out[-1]["parity_rel_l2"] = parity
 
     def linear_node(w_dev, x_dev, b_dev, epilogue=0):
         return w_dev.gemm(x_dev, b_dev, False, True, True, epilogue=epilogue)
 
     if "c1" in which:
-        w = weight((10240, 2560), DType.F32, 1101).to(gpu)
-        b = weight((10240,), DType.F32, 2101).to(gpu)
-        x = act((1, 128, 2560), DType.F32, 101).to(gpu)
-        us, k, l = time_node(gpu, stream, lambda i: linear_node(w, x, b), 1, 20)
-        record("c1_dense_f32_phi2_fc1_m128", us, k, l, 2 * 128 * 10240 * 2560, 111452160, "hbm", "weights L2-resident between calls")
+        wh, bh, xh = weight((10240, 2560), DType.F32, 1101), weight((10240,), DType.F32, 2101), act((1, 128, 2560), DType.F32, 101)
+        w, b, x = wh.to(gpu), bh.to(gpu), xh.to(gpu)
+        kept = []
+        us, k, l = time_node(gpu, stream, lambda i: linear_node(w, x, b), 1, 20, keep=kept)
+        record("c1_dense_f32_phi2_fc1_m128", us, k, l, 2 * 128 * 10240 * 2560, 111452160, "hbm", "weights L2-resident between calls",
+               parity=linear_parity(kept[0], wh, xh, bh, 0))
     if "c3" in which:
-        w1, w2 = weight((1536, 384), DType.Q8_0H, 1103).to(gpu), weight((384, 1536), DType.Q8_0H, 1104).to(gpu)
-        b1, b2 = weight((1536,), DType.F16, 2103).to(gpu), weight((384,), DType.F16, 2104).to(gpu)
-        x = act((1, 1500, 384), DType.F16, 103).to(gpu)
+        w1h, w2h = weight((1536, 384), DType.Q8_0H, 1103), weight((384, 1536), DType.Q8_0H, 1104)
+        b1h, b2h, xh = weight((1536,), DType.F16, 2103), weight((384,), DType.F16, 2104), act((1, 1500, 384), DType.F16, 103)
+        w1, w2, b1, b2, x = w1h.to(gpu), w2h.to(gpu), b1h.to(gpu), b2h.to(gpu), xh.to(gpu)
         h = linear_node(w1, x, b1, rb.EPILOGUE_GELU_TANH)
         y = linear_node(w2, h, b2)
         us, ks, l = time_nodes(gpu, stream, [h, y], 200)
         record("c3_whisper_tiny_mlp_q8_0_m1500", us, " + ".join(ks), l, 2 * 1500 * 384 * 1536 * 2, 12777216,
-               "tensor", "fc1+GELU then fc2 as one executable; latency-bound (one wave)")
+               "tensor", "fc1+GELU then fc2 as one executable; latency-bound (one wave)",
+               parity=mlp_parity(y, w1h, b1h, w2h, b2h, xh, "gelu"))
     if "c4" in which:
         hw = weight((8192, 3072), DType.Q4_K, 1104)
         copies = 20  # 20 x 14.2 MB of weights: larger than L2
         ws = [hw.to(gpu) for _ in range(copies)]
         for M in (1, 16, 512):
-            x = act((1, M, 3072), DType.F16, 104).to(gpu)
-            us, k, l = time_node(gpu, stream, lambda i: linear_node(ws[i], x, None), copies, 200 if M < 512 else 60)
+            xh = act((1, M, 3072), DType.F16, 104)
+            x = xh.to(gpu)
+            kept = []
+            us, k, l = time_node(gpu, stream, lambda i: linear_node(ws[i], x, None), copies, 200 if M < 512 else 60, keep=kept)
             nbytes = 14155776 + 2 * M * 3072 + 2 * M * 8192
             record(f"c4_q4_k_phi3_m{M}", us, k, l, 2 * M * 8192 * 3072, nbytes, "tensor" if M == 512 else "hbm",
-                   "rotating 20 weight copies")
+                   "rotating 20 weight copies", parity=linear_parity(kept[0], hw, xh, None, 0))
     if "mlp" in which:
         # Phi-3 mini MLP block as ONE executable (rt_mlp_create): gate_up [16384,3072] -> up * silu(gate) -> down [3072,8192]
         copies = 3  # 3 x 80 MB of weights: larger than L2
-        blocks = [rb.MLP(rb.Linear(weight((16384, 3072), DType.Q8_0H, 1201 + c).to(gpu)),
-                         rb.Linear(weight((3072, 8192), DType.Q8_0H, 1301 + c).to(gpu)), act="silu_gate") for c in range(copies)]
+        host_blocks = [(weight((16384, 3072), DType.Q8_0H, 1201 + c), weight((3072, 8192), DType.Q8_0H, 1301 + c)) for c in range(copies)]
+        blocks = [rb.MLP(rb.Linear(a.to(gpu)), rb.Linear(b_.to(gpu)), act="silu_gate") for a, b_ in host_blocks]
         import torch
         for M in (1, 16, 512):
-            x = act((1, M, 3072), DType.F16, 1400 + M).to(gpu)
+            xh = act((1, M, 3072), DType.F16, 1400 + M)
+            x = xh.to(gpu)
             bound = [blk.bind(x) for blk in blocks]
             for exe, _ in bound:
                 exe.dispatch()
@@ -295,16 +349,19 @@ def run_extras(which, gpu, stream):
             wbytes = (16384 * 3072 + 3072 * 8192) * 34 // 32
             record(f"mlp_phi3_q8_0_block_m{M}", us, bound[0][0].kernel, bound[0][0].launches,
                    2 * M * (16384 * 3072 + 3072 * 8192), wbytes + 2 * M * (3072 + 3072), "tensor" if M == 512 else "hbm",
-                   "gate_up + SiLU*mul + down as one executable, hidden tensor in the executable's arena; rotating 3 weight sets")
+                   "gate_up + SiLU*mul + down as one executable, hidden tensor in the executable's arena; rotating 3 weight sets",
+                   parity=mlp_parity(bound[0][1], host_blocks[0][0], None, host_blocks[0][1], None, xh, "silu_gate"))
     for name, rows in (("c5", 2048), ("c5long", 8192)):
         if name not in which:
             continue
-        w = weight((10240, 2560), DType.Q8_0H, 1105).to(gpu)
-        b = weight((10240,), DType.F16, 2105).to(gpu)
-        x = act((4, rows, 2560), DType.BF16, 105).to(gpu)
-        us, k, l = time_node(gpu, stream, lambda i: linear_node(w, x, b, rb.EPILOGUE_GELU_TANH), 1, 10)
+        wh, bh, xh = weight((10240, 2560), DType.Q8_0H, 1105), weight((10240,), DType.F16, 2105), act((4, rows, 2560), DType.BF16, 105)
+        w, b, x = wh.to(gpu), bh.to(gpu), xh.to(gpu)
+        kept = []
+        us, k, l = time_node(gpu, stream, lambda i: linear_node(w, x, b, rb.EPILOGUE_GELU_TANH), 1, 10, keep=kept)
         record(f"{name}_q8_0_prefill_bf16_4x{rows}", us, k, l, 2 * 4 * rows * 10240 * 2560,
-               4 * rows * 2560 * 2 + 27852800 + 4 * rows * 10240 * 2, "tensor", "bias + fused GELU, 1 GPU")
+               4 * rows * 2560 * 2 + 27852800 + 4 * rows * 10240 * 2, "tensor", "bias + fused GELU, 1 GPU",
+               parity=linear_parity(kept[0], wh, xh, bh, 1))
+        del kept, w, x
     return out
 
 
