@@ -9,7 +9,8 @@
 //
 //  * the int8 codes go from HBM to shared memory by TMA (128-byte swizzle) and are consumed there
 //    by tcgen05.mma kind::i8 (M = 128 weight rows, N = 16, K = 32 = one Q8_0 block), one
-//    instruction per block, s32 accumulators in tensor memory;
+//    instruction per block, issued by four threads (two blocks of every stage each), s32 accumulators in
+//    tensor memory;
 //  * the activation vector is turned once per CTA into block-floating-point int8 digits: per block
 //    of 32 a power-of-two scale xs and a 15-bit integer m = hi*256 + lo per element, stored as
 //    two int8 rows (hi, lo) of the MMA's B operand; |x - m*xs| <= 2^-15 of the block's largest
