@@ -22,6 +22,9 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <unordered_map>
+#include <string>
+#include <mutex>
 #include <cstdlib>
 #include <cstring>
 
@@ -760,6 +763,39 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// A tensor map is a pure function of its description, and a step launches the same few descriptions again and again
+// (the reference compiles a node once and dispatches it many times, op.rs:304-362): the encoded maps are kept, so a launch
+// outside a CUDA graph does not pay the driver's encoder each time.
+CUresult encode_cached(CUtensorMap *map, CUtensorMapDataType dt, cuuint32_t rank, void *base, const cuuint64_t *dims, const cuuint64_t *strides,
+                       const cuuint32_t *box, CUtensorMapL2promotion l2) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return CUDA_ERROR_NOT_SUPPORTED;
+    std::string key;
+    auto put = [&key](unsigned long long v) { key.append(reinterpret_cast<const char *>(&v), sizeof(v)); };
+    put((unsigned long long)dt); put(rank); put((unsigned long long)(uintptr_t)base); put((unsigned long long)l2);
+    for (cuuint32_t i = 0; i < rank; i++) { put(dims[i]); put(box[i]); }
+    for (cuuint32_t i = 0; i + 1 < rank; i++) put(strides[i]);
+    static std::mutex mu;
+    static std::unordered_map<std::string, CUtensorMap> cache;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) {
+            *map = it->second;
+            return CUDA_SUCCESS;
+        }
+    }
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    const CUresult r = fn(map, dt, rank, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, l2,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) {
+        std::lock_guard<std::mutex> lk(mu);
+        if (cache.size() >= 8192) cache.clear(); // bounded: addresses of freed buffers would otherwise pile up
+        cache.emplace(std::move(key), *map);
+    }
+    return r;
+}
+
 // [stack][rows][K] 16-bit row-major -> boxes of box_rows x 64 elements, 128-byte swizzle, zero fill
 bool make_map(CUtensorMap *map, const void *base, rt_dtype dt, long long K, long long rows, long long stack, int box_rows) {
     EncodeTiledFn fn = encode_fn();
@@ -767,11 +803,8 @@ bool make_map(CUtensorMap *map, const void *base, rt_dtype dt, long long K, long
     cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)stack};
     cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)K * 2 * (cuuint64_t)rows};
     cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = fn(map, dt == RT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
+    return encode_cached(map, dt == RT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base),
+                         dims, strides, box, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) == CUDA_SUCCESS;
 }
 
 // Q = [stack][2*ff][K] seen as [stack][2][ff][K]: one box of (64, box_rows, 2) brings box_rows gate rows and the
@@ -782,11 +815,8 @@ bool make_pair_map(CUtensorMap *map, const void *base, rt_dtype dt, long long K,
     cuuint64_t dims[4] = {(cuuint64_t)K, (cuuint64_t)ff, 2, (cuuint64_t)stack};
     cuuint64_t strides[3] = {(cuuint64_t)K * 2, (cuuint64_t)K * 2 * (cuuint64_t)ff, (cuuint64_t)K * 4 * (cuuint64_t)ff};
     cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 2, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = fn(map, dt == RT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
+    return encode_cached(map, dt == RT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(base),
+                         dims, strides, box, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) == CUDA_SUCCESS;
 }
 
 // The grouped tile order pays when the row operand does not stay in L2 across a sweep of the tile columns (measured:
@@ -824,10 +854,8 @@ bool make_out_maps(OutMaps *om, const UmmaParams &prm, rt_dtype dt) {
         cuuint64_t dims[3] = {(cuuint64_t)(prm.out_col + prm.s_out), (cuuint64_t)prm.R, (cuuint64_t)prm.stacks};
         cuuint64_t strides[2] = {(cuuint64_t)prm.out_ld * 2, (cuuint64_t)prm.out_batch_stride * 2};
         cuuint32_t box[3] = {64, 32, 1};
-        cuuint32_t estr[3] = {1, 1, 1};
-        if (fn(&om->m[d], dt == RT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, prm.outs[d], dims, strides, box,
-               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        if (encode_cached(&om->m[d], dt == RT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, prm.outs[d], dims,
+                          strides, box, CU_TENSOR_MAP_L2_PROMOTION_NONE) != CUDA_SUCCESS)
             return false;
     }
     return true;
