@@ -756,6 +756,7 @@ def test_umma_takes_the_prefill_configs(gpu):
     (BF16, BF16, (4096, 320), (1, 2560, 320), False, 1),   # K = 5 blocks of 64
     (Q8H, BF16, (10240, 512), (1, 1030, 512), True, 1),    # rows that end in a pair's first CTA
     (Q4K, F16, (8192, 512), (1, 1200, 512), False, 0),
+    (F16, F16, (3, 2048, 256), (3, 1000, 256), False, 0),  # a weight per batch: three stacks of ragged row tiles
 ])
 def test_gemm_on_cta_pairs_matches_the_oracle_and_the_single_cta_kernel(gpu, monkeypatch, lhs_dt, act, wshape, xshape, bias, epi):
     """Large GEMMs run 256 x 256 tiles on pairs of CTAs (tcgen05 cta_group::2: each CTA stages its 128 rows of the
@@ -775,6 +776,14 @@ def test_gemm_on_cta_pairs_matches_the_oracle_and_the_single_cta_kernel(gpu, mon
     node1 = w_d.gemm(x_d, b_d, False, True, True, epilogue=epi)
     assert "pair" not in rb._lib.load().rt_plan_kernel(gpu.plan_for(node1.op.desc)).decode()
     assert np.array_equal(got.to_numpy().reshape(-1), node1.resolve().to(Device.CPU).to_numpy().reshape(-1))
+    if len(wshape) == 3:  # batched weights: check batch 1 against its own weight
+        N, K = wshape[1:]
+        rows_total = xshape[1]
+        got_f = got.to_f32().reshape(wshape[0], rows_total, N)[1]
+        rows = np.unique(np.concatenate([[0, 127, 128, 255, 256, rows_total - 1], np.random.default_rng(1).integers(0, rows_total, size=40)]))
+        truth = oracle.matmul_truth(wv[1], x[1][rows], None, 1, 1, 1, N, len(rows), K, False, True, True, epi)
+        assert oracle.rel_l2(got_f[rows], oracle.f64_to_f16(truth).astype(np.float32).reshape(len(rows), N)) <= TOL[act]
+        return
     N, K = wshape
     rows_total = int(np.prod(xshape[:-1]))
     rows = np.unique(np.concatenate([[0, 127, 128, 255, 256, rows_total - 1], np.random.default_rng(1).integers(0, rows_total, size=40)]))
