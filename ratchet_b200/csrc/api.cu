@@ -94,6 +94,7 @@ struct rt_plan {
     uint64_t scratch_bytes = 0;
     void *act_scratch = nullptr; // bf16 activations cast to f16 (quantised weights only)
     uint64_t act_scratch_bytes = 0;
+    uint64_t act_scale_off = 0; // bf16 cast: where the per-row factors (f32) start inside act_scratch
     void *wdq = nullptr;         // f32 GEMM over Q8_0F weights: the weights as f32 ((i8)q * d, quant.rs:114-120)
     uint64_t wdq_bytes = 0;
     // RT_EPILOGUE_SILU_MUL on a route that does not fold the gate/up pairs itself: the plain node's [.., 2*ff] output
@@ -805,9 +806,11 @@ static rt_status build_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan 
             }
             pl->launches = 2;
             // tcgen05.mma kind::f16 takes one 16-bit format for both operands: the dequantised weights
-            // are f16 (bf16 would drop 3 of their 11 significant bits), so bf16 activations are cast
+            // are f16 (bf16 would drop 3 of their 11 significant bits), so bf16 activations are cast, each row
+            // with a power-of-two factor that brings it into f16's range and that the epilogue puts back
             if (desc->rhs_dt == RT_BF16) {
-                pl->act_scratch_bytes = (uint64_t)(s.rhs_stack * s.N * s.K) * 2;
+                pl->act_scale_off = ((uint64_t)(s.rhs_stack * s.N * s.K) * 2 + 255) / 256 * 256;
+                pl->act_scratch_bytes = pl->act_scale_off + (uint64_t)(s.rhs_stack * s.N) * 4;
                 e = cudaMalloc(&pl->act_scratch, pl->act_scratch_bytes);
                 if (e != cudaSuccess) {
                     pl->act_scratch = nullptr;
@@ -1055,12 +1058,14 @@ static rt_status launch_node(rt_plan *plan, const void *lhs, const void *rhs, co
         }
         const void *x = rhs;
         rt_dtype x_dt = s.desc.rhs_dt;
+        float *x_scale = nullptr;
         if (plan->rhs_transpose) {
             e = launch_transpose(rhs, act_scratch, (int)s.rhs_stack, (int)s.K, (int)s.N, k_eff, 2, st);
             if (e != cudaSuccess) break;
             x = act_scratch;
         } else if (plan->act_scratch) {
-            e = launch_cast_bf16_f16(rhs, act_scratch, (long long)(s.rhs_stack * s.N * s.K), plan->dev->sm_count, st);
+            x_scale = reinterpret_cast<float *>(static_cast<char *>(act_scratch) + plan->act_scale_off);
+            e = launch_cast_bf16_f16_rows(rhs, act_scratch, x_scale, (long long)(s.rhs_stack * s.N), (int)s.K, plan->dev->sm_count, st);
             if (e != cudaSuccess) break;
             x = act_scratch;
             x_dt = RT_F16;
@@ -1078,7 +1083,8 @@ static rt_status launch_node(rt_plan *plan, const void *lhs, const void *rhs, co
         }
         e = launch_gemm_umma(P, p_dt, Q, q_dt, out, s.out_dt, plan->R, plan->S, k_eff, plan->u_stacks, plan->p_stack,
                              plan->q_stack, p.bias, p.bias_dt, s.has_bias ? BIAS_PER_N : BIAS_NONE, p.epilogue, plan->bn,
-                             plan->dev->sm_count, st, scatter ? &sc : nullptr);
+                             plan->dev->sm_count, st, scatter ? &sc : nullptr, plan->lhs_is_q ? x_scale : nullptr,
+                             plan->lhs_is_q ? nullptr : x_scale);
         break;
     }
     }

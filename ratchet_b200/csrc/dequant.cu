@@ -39,9 +39,6 @@ __global__ void __launch_bounds__(256) dequant_q8h_f16_vec_kernel(const uint4 *c
     }
 }
 
-// bf16 -> f16, eight values per thread.  Exact for 2^-14 <= |x| <= 65504 (bf16 has 8 significant
-// bits, f16 has 11); larger magnitudes saturate to +-65504, smaller ones round into the f16
-// subnormals (absolute error below 2^-25).
 // Q4_K -> f16, sixteen quant bytes per thread: their low nibbles are sixteen values of sub-block 2p, their
 // high nibbles sixteen values of sub-block 2p + 1 (GGUF block_q4_K: d, dmin, 12 bytes of 6-bit scales and
 // mins, 128 bytes of nibbles).  Same arithmetic, value by value, as q4k_element: (d * sc) * q - dmin * m
@@ -89,28 +86,89 @@ __global__ void __launch_bounds__(256) dequant_q4k_f16_vec_kernel(const uint8_t 
     }
 }
 
-__global__ void __launch_bounds__(256) cast_bf16_f16_kernel(const uint4 *src, uint4 *dst, long long n8) {
+// the largest finite magnitude among eight bf16 values (0 when none is finite)
+__device__ __forceinline__ float finite_amax8(const uint4 v) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    float m = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float lo = fabsf(__uint_as_float(w[j] << 16)), hi = fabsf(__uint_as_float(w[j] & 0xFFFF0000u));
+        if (lo <= 3.0e38f) m = fmaxf(m, lo); // false for infinities and NaNs
+        if (hi <= 3.0e38f) m = fmaxf(m, hi);
+    }
+    return m;
+}
+// eight bf16 values times a power of two, as f16
+__device__ __forceinline__ uint4 scaled_f16x8(const uint4 v, float down) {
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+        w[j] = h2_as_u32(__floats2half2_rn(__uint_as_float(w[j] << 16) * down, __uint_as_float(w[j] & 0xFFFF0000u) * down));
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// bf16 rows to f16 rows with one power-of-two factor per row.  f16 keeps every bit of a bf16 mantissa but not its
+// exponent range, so each row is first multiplied by 2^-sh, sh chosen from the row's largest finite magnitude m so
+// that m * 2^-sh lies in [2^14, 2^15): nothing saturates, and only elements more than 2^29 below the row's largest lose
+// bits (in the f16 subnormals).  scale[row] = 2^sh goes back onto the f32 accumulators in the GEMM's epilogue: both
+// multiplications are exact.  Infinities and NaNs pass through as they are; a row without a finite non-zero element
+// has the factor 1.
+__global__ void __launch_bounds__(256) cast_bf16_f16_rows_kernel(const __nv_bfloat16 *__restrict__ src, __half *__restrict__ dst,
+                                                                 float *__restrict__ scale, long long rows, int K) {
     // the next kernel may start its prologue now; this one's stream predecessor may still be reading what it writes
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
-        uint4 v = __ldg(src + i);
-        uint32_t *w = reinterpret_cast<uint32_t *>(&v);
+    // One warp per row: the row's largest magnitude needs shuffles only, and rows of up to 4096 values (16 loads of
+    // 16 bytes per lane, all in flight together) stay in registers between the two steps; longer rows are read a
+    // second time, out of L2.
+    constexpr int HOLD = 16;
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * 8 + (threadIdx.x >> 5), n_warps = (long long)gridDim.x * 8;
+    const bool vec = (K % 8) == 0; // then every row starts on a 16-byte boundary
+    const int n8 = vec ? K / 8 : 0;
+    const bool held = n8 <= HOLD * 32;
+    for (long long r = warp; r < rows; r += n_warps) {
+        const __nv_bfloat16 *s = src + r * K;
+        __half *d = dst + r * K;
+        float m = 0.f;
+        uint4 keep[HOLD];
+        if (held) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float lo = fminf(fmaxf(__uint_as_float(w[j] << 16), -65504.f), 65504.f);
-            const float hi = fminf(fmaxf(__uint_as_float(w[j] & 0xFFFF0000u), -65504.f), 65504.f);
-            const __half2 h = __floats2half2_rn(lo, hi);
-            w[j] = h2_as_u32(h);
+            for (int j = 0; j < HOLD; j++) {
+                const int i = lane + 32 * j;
+                keep[j] = i < n8 ? __ldg(reinterpret_cast<const uint4 *>(s) + i) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int j = 0; j < HOLD; j++) m = fmaxf(m, finite_amax8(keep[j]));
+        } else {
+            for (int i = lane; i < n8; i += 32) m = fmaxf(m, finite_amax8(__ldg(reinterpret_cast<const uint4 *>(s) + i)));
         }
-        dst[i] = v;
+        for (int i = n8 * 8 + lane; i < K; i += 32) {
+            const float a = fabsf(__bfloat162float(s[i]));
+            if (a <= 3.0e38f) m = fmaxf(m, a);
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        int sh = 0;
+        if (m > 0.f) {
+            int e;
+            frexpf(m, &e); // m = f * 2^e, f in [0.5, 1)
+            sh = min(max(e - 15, -126), 112); // 2^126 and 2^-126 are still normal f32 values
+        }
+        const float down = ldexpf(1.f, -sh);
+        if (held) {
+#pragma unroll
+            for (int j = 0; j < HOLD; j++) {
+                const int i = lane + 32 * j;
+                if (i < n8) reinterpret_cast<uint4 *>(d)[i] = scaled_f16x8(keep[j], down);
+            }
+        } else {
+            for (int i = lane; i < n8; i += 32)
+                reinterpret_cast<uint4 *>(d)[i] = scaled_f16x8(__ldg(reinterpret_cast<const uint4 *>(s) + i), down);
+        }
+        for (int i = n8 * 8 + lane; i < K; i += 32) d[i] = __float2half_rn(__bfloat162float(s[i]) * down);
+        if (lane == 0) scale[r] = ldexpf(1.f, sh);
     }
-}
-
-__global__ void __launch_bounds__(256) cast_bf16_f16_tail_kernel(const __nv_bfloat16 *src, __half *dst, long long begin, long long n) {
-    const long long i = begin + (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) dst[i] = __float2half_rn(fminf(fmaxf(__bfloat162float(src[i]), -65504.f), 65504.f));
 }
 
 // [stack][rows][cols] -> [stack][cols][dst_ld], 32 x 32 tiles through padded shared memory so that both
@@ -207,18 +265,11 @@ cudaError_t launch_silu_mul(const void *full, void *out, long long rows, int ff,
     }
 }
 
-cudaError_t launch_cast_bf16_f16(const void *src, void *dst, long long numel, int sm_count, cudaStream_t stream) {
-    if (numel == 0) return cudaSuccess;
-    const long long n8 = numel / 8;
-    if (n8 > 0) {
-        const long long want = (n8 + 255) / 256;
-        const int blocks = (int)(want < (long long)sm_count * 16 ? want : (long long)sm_count * 16);
-        cudaError_t e = launch_pdl(cast_bf16_f16_kernel, dim3(blocks), dim3(256), 0, stream, (const uint4 *)src, (uint4 *)dst, n8);
-        if (e != cudaSuccess) return e;
-    }
-    if (numel % 8)
-        cast_bf16_f16_tail_kernel<<<1, 256, 0, stream>>>((const __nv_bfloat16 *)src, (__half *)dst, n8 * 8, numel);
-    return cudaGetLastError();
+cudaError_t launch_cast_bf16_f16_rows(const void *src, void *dst, float *scale, long long rows, int K, int sm_count, cudaStream_t stream) {
+    if (rows == 0 || K == 0) return cudaSuccess;
+    const long long want = (rows + 7) / 8; // eight rows (warps) per block
+    const int blocks = (int)(want < (long long)sm_count * 8 ? want : (long long)sm_count * 8);
+    return launch_pdl(cast_bf16_f16_rows_kernel, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16 *)src, (__half *)dst, scale, rows, K);
 }
 
 cudaError_t launch_dequant(rt_dtype dt, long long numel, const void *src, const void *scales, void *dst, rt_dtype out_dt,

@@ -70,6 +70,9 @@ struct UmmaParams {
     int group_r; // tile rows per group of the tile order (tile_coords); tiles_r: plain order, tile rows fastest
     int tma_store; // CTA-pair kernel: the epilogue hands its staged 32 x 64 blocks to TMA stores (one per destination)
     uint32_t idesc;
+    // Factors that were taken out of an operand's rows before the product (bf16 activations brought into f16's range):
+    // p_scale [p_stack][R], q_scale [q_stack][S], either may be null; they go back onto the f32 accumulators.
+    const float *p_scale, *q_scale;
 };
 
 template <int BN> struct Cfg {
@@ -215,10 +218,14 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, int c0, int
                  ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(src) : "memory");
 }
 
+// Operand factors (UmmaParams::p_scale, q_scale) exist for bf16 activations only, and those have bf16 outputs: the
+// f16 kernels carry none of that code.
+template <typename OutT> constexpr bool HAS_OPERAND_FACTORS = !cuda::std::is_same<OutT, __half>::value;
+
 template <int BN, typename OutT, bool REMOTE_DONE, bool TMA_STORE = false>
 __device__ __forceinline__ void epilogue_tile(const UmmaParams &prm, uint32_t tmem_acc, uint32_t bar_done, int r0, int s0, int b, int q, int half,
-                                              int lane, uint8_t *stg, const float *bias_s, bool has_bias, float row_bias, bool vec_ok,
-                                              bool pair_ok, const OutMaps *omaps = nullptr) {
+                                              int lane, uint8_t *stg, const float *bias_s, bool has_bias, float row_bias, float row_mul,
+                                              bool vec_ok, bool pair_ok, const OutMaps *omaps = nullptr) {
 #pragma unroll 1
     for (int cc = half; cc < BN / 64; cc += 2) {
         const int colbase = s0 + cc * 64;
@@ -232,6 +239,15 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams &prm, uint32_t tm
             const int c = cc * 2 + h;
             uint32_t v[32];
             tmem_ld32(tmem_acc + c * 32 + ((uint32_t)(q * 32) << 16), v);
+            if (HAS_OPERAND_FACTORS<OutT>) {
+#pragma unroll
+                for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * row_mul); // 1 where P has no factors
+                if (prm.q_scale) {
+                    const float *qs = prm.q_scale + (long long)(b % prm.q_stack) * prm.S;
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * __ldg(qs + min(s0 + c * 32 + i, prm.S - 1)));
+                }
+            }
             if (cc + 2 >= BN / 64 && h == 1) {
                 // the accumulator has been read completely: hand it back to the MMA warp now
                 tc_fence_before();
@@ -454,6 +470,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             const bool has_bias = prm.bias_mode != BIAS_NONE;
             float row_bias = 0.f;
             if (prm.bias_mode == BIAS_PER_M && row < prm.R) row_bias = load_bias(prm.bias, prm.bias_dt, row);
+            const float row_mul = (HAS_OPERAND_FACTORS<OutT> && prm.p_scale && row < prm.R) ? __ldg(prm.p_scale + (long long)(b % prm.p_stack) * prm.R + row) : 1.f;
             // 64 columns per round: two tensor-memory loads, the epilogue arithmetic, then through a
             // per-warp staging buffer so that global stores run along rows: 8 lanes x 16 B = one full
             // 128-byte line per row (this matters most when the destination is a peer GPU over NVLink)
@@ -483,8 +500,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                                 const int i = g * 8 + j * 2 + e;
                                 const float bg = has_bias ? bias_s[cc * 32 + i] : 0.f;
                                 const float bu = has_bias ? bias_s[BN / 2 + cc * 32 + i] : 0.f;
-                                const OutT gv = epilogue_value<OutT>(__uint_as_float(vg[i]), has_bias, bg, RT_EPILOGUE_NONE);
-                                const OutT uv = epilogue_value<OutT>(__uint_as_float(vu[i]), has_bias, bu, RT_EPILOGUE_NONE);
+                                const float ga = HAS_OPERAND_FACTORS<OutT> ? __uint_as_float(vg[i]) * row_mul : __uint_as_float(vg[i]);
+                                const float ua = HAS_OPERAND_FACTORS<OutT> ? __uint_as_float(vu[i]) * row_mul : __uint_as_float(vu[i]);
+                                const OutT gv = epilogue_value<OutT>(ga, has_bias, bg, RT_EPILOGUE_NONE);
+                                const OutT uv = epilogue_value<OutT>(ua, has_bias, bu, RT_EPILOGUE_NONE);
                                 o[e] = to_f32(silu_mul_value<OutT>(gv, uv));
                             }
                             w[j] = pack2<OutT>(o[0], o[1]);
@@ -522,7 +541,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                 continue;
             }
             epilogue_tile<BN, OutT, false>(prm, tmem_base + acc * BN, bar_tempty + 8 * acc, r0, s0, b, q, half, lane, stg, bias_s, has_bias, row_bias,
-                                    vec_ok, pair_ok);
+                                    row_mul, vec_ok, pair_ok);
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
     }
@@ -722,9 +741,10 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_co
             const bool has_bias = prm.bias_mode != BIAS_NONE;
             float row_bias = 0.f;
             if (prm.bias_mode == BIAS_PER_M && row < prm.R) row_bias = load_bias(prm.bias, prm.bias_dt, row);
+            const float row_mul = (HAS_OPERAND_FACTORS<OutT> && prm.p_scale && row < prm.R) ? __ldg(prm.p_scale + (long long)(b % prm.p_stack) * prm.R + row) : 1.f;
             uint8_t *stg = stage_out + (warp - 2) * (32 * STG_ROW_BYTES);
             epilogue_tile<BN, OutT, true, true>(prm, tmem_base + acc * BN, tempty0 + 8 * acc, r0, s0, b, q, half, lane, stg, bias_s, has_bias, row_bias,
-                                                vec_ok, pair_ok, &omaps);
+                                                row_mul, vec_ok, pair_ok, &omaps);
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
         // the warp's bulk stores are complete (written, not only read) before the CTA goes
@@ -912,7 +932,8 @@ int umma_pick_bn(long long R, long long S, long long stacks, int sm_count) {
 // P: [p_stack][R][K] of p_dt, Q: [q_stack][S][K] of q_dt (f16 or bf16 each); out [stacks][R][S] of out_dt.
 cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dtype q_dt, void *out, rt_dtype out_dt,
                              int R, int S, int K, int stacks, int p_stack, int q_stack, const void *bias, int bias_dt,
-                             int bias_mode, int epilogue, int bn, int sm_count, cudaStream_t stream, const UmmaScatter *scatter) {
+                             int bias_mode, int epilogue, int bn, int sm_count, cudaStream_t stream, const UmmaScatter *scatter,
+                             const float *p_scale, const float *q_scale) {
     // kind::f16 wants one format for both operands: an instruction descriptor that mixes f16 and
     // bf16 is an illegal instruction on sm_100a
     if (p_dt != q_dt || (p_dt != RT_F16 && p_dt != RT_BF16)) return cudaErrorInvalidValue;
@@ -949,6 +970,9 @@ cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dty
     }
     prm.bias = bias; prm.bias_dt = bias_dt; prm.bias_mode = bias_mode;
     prm.epilogue = epilogue;
+    prm.p_scale = p_scale; prm.q_scale = q_scale;
+    if (pair && q_scale) return cudaErrorInvalidValue; // the gate/up fold has the weights as Q
+    if ((p_scale || q_scale) && out_dt != RT_BF16) return cudaErrorInvalidValue; // only those kernels hold the code
     prm.idesc = ((p_dt == RT_BF16 ? 1u : 0u) << 7) | ((q_dt == RT_BF16 ? 1u : 0u) << 10);
     if (bn == UMMA_BN_PAIR) {
         if (out_dt == RT_F16) return launch_pair<__half>(mp, mq, prm, sm_count, stream, out_dt);

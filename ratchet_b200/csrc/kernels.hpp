@@ -104,7 +104,8 @@ cudaError_t launch_gemm_umma_tf32x3(const void *P, const void *Q, void *out, int
 cudaError_t umma_tf32_take_error(int *site, cudaStream_t stream);
 
 // Tensor-core GEMM (tcgen05): D[R][S] = P[R][K] . Q[S][K]^T, 16-bit K-major operands, bias along S.
-// Several destinations for one result: see UmmaParams in gemm_umma.cu.
+// Several destinations for one result: see UmmaParams in gemm_umma.cu.  p_scale [p_stack][R] / q_scale [q_stack][S]:
+// optional f32 factors per row of P / of Q, multiplied onto the accumulators before bias and epilogue.
 struct UmmaScatter {
     int n_out;
     void *outs[RT_MAX_PEERS];
@@ -117,7 +118,7 @@ int umma_pick_bn(long long R, long long S, long long stacks, int sm_count);
 cudaError_t launch_gemm_umma(const void *P, rt_dtype p_dt, const void *Q, rt_dtype q_dt, void *out, rt_dtype out_dt,
                              int R, int S, int K, int stacks, int p_stack, int q_stack, const void *bias, int bias_dt,
                              int bias_mode, int epilogue, int bn, int sm_count, cudaStream_t stream,
-                             const UmmaScatter *scatter = nullptr);
+                             const UmmaScatter *scatter = nullptr, const float *p_scale = nullptr, const float *q_scale = nullptr);
 // Reads and clears the device flag a kernel sets when one of its bounded waits expires.
 cudaError_t umma_take_error(int *site, cudaStream_t stream);
 
@@ -125,8 +126,9 @@ cudaError_t umma_take_error(int *site, cudaStream_t stream);
 cudaError_t launch_dequant(rt_dtype dt, long long numel, const void *src, const void *scales, void *dst, rt_dtype out_dt,
                            int sm_count, cudaStream_t stream);
 
-// bf16 -> f16 (saturating) for the activations of a quantised-weight tensor-core GEMM.
-cudaError_t launch_cast_bf16_f16(const void *src, void *dst, long long numel, int sm_count, cudaStream_t stream);
+// bf16 [rows][K] -> f16 [rows][K] * 2^-sh(row) with scale[row] = 2^sh(row): the activations of a quantised-weight
+// tensor-core GEMM, brought into f16's exponent range row by row (nothing saturates; infinities and NaNs pass through).
+cudaError_t launch_cast_bf16_f16_rows(const void *src, void *dst, float *scale, long long rows, int K, int sm_count, cudaStream_t stream);
 // [rows][2*ff] (gate | up) -> [rows][ff] = up * silu(gate), the second launch of a RT_EPILOGUE_SILU_MUL node on the routes
 // that do not fuse it
 cudaError_t launch_silu_mul(const void *full, void *out, long long rows, int ff, rt_dtype dt, int sm_count, cudaStream_t stream);

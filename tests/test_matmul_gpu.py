@@ -876,3 +876,89 @@ def test_repeated_dispatch_is_bitwise_stable(gpu):
             if first is None:
                 first = got
             assert np.array_equal(got, first), (lhs_dt, lsh)
+
+
+# ----------------------------------------------------------------------------- a seeded sweep over the routing boundaries
+
+@pytest.mark.parametrize("lhs_dt,act", [(Q8H, F16), (Q8F, F32), (Q8F, F16), (Q8H, BF16), (Q4K, F16), (Q4K, BF16), (F16, F16), (BF16, BF16), (F32, F32)])
+def test_seeded_sweep_of_linear_forms_across_the_routing_boundaries(gpu, lhs_dt, act):
+    """Row counts on both sides of every switch between kernels (1 | 2..8 | 9..24 | 25.. | whole 128- and 256-row tiles),
+    weight rows that are no multiple of any tile, with and without bias and GELU, flattened batches; every case
+    against the oracle at the activation type's tolerance, and every kernel name collected so that the sweep is known
+    to have crossed the boundaries."""
+    rng = np.random.default_rng(int(lhs_dt) * 31 + int(act))
+    kstep = 256 if lhs_dt == Q4K else 32
+    rows_pool = [1, 2, 3, 8, 9, 16, 17, 24, 25, 31, 32, 33, 100, 127, 128, 129, 255, 256, 257, 300, 513]
+    seen = set()
+    for case in range(len(rows_pool)):
+        rows = rows_pool[case]
+        N = int(rng.choice([8, 24, 40, 128, 136, 200, 520, 1000, 1544]))
+        K = int(rng.integers(1, 9)) * kstep if case % 3 else int(rng.choice([1, 4, 10])) * 256
+        batch = int(rng.choice([1, 1, 2, 3])) if rows <= 130 else 1
+        bias = bool(rng.integers(0, 2))
+        epi = int(rng.integers(0, 2)) if bias else 0
+        bias_dt = F16 if (act == BF16 and lhs_dt != BF16) else None
+        kw = dict(bias=bias, epilogue=epi, seed=1000 + case, w_std=0.03)
+        if bias_dt is not None:
+            kw["bias_dt"] = bias_dt
+        prob = Problem(lhs_dt, act, (N, K), (batch, rows, K), (False, True, True), **kw)
+        if lhs_dt == Q4K and act == BF16:
+            # Q4_K weights are rounded to f16 for the tensor cores (2^-12 relative).  Against a truth that is itself
+            # rounded to bf16 that shows as whole-ulp flips (2^-8 each) on a few percent of the elements, which puts
+            # the rel-L2 of rounded against rounded near 9e-4 with a sample spread that crosses 1e-3 on small outputs.
+            # The statement that does not depend on where the truth happens to fall between two bf16 values: the
+            # result is as close to the exact product as the correctly rounded one is, within 10 %.
+            got, truth_r, truth, _, kernel = run_problem(prob, gpu)
+            assert np.all(np.isfinite(got))
+            exact = truth.reshape(-1)
+            assert oracle.rel_l2(got, exact) <= 1.10 * oracle.rel_l2(truth_r, exact), (kernel, prob)
+            assert oracle.rel_l2(got, truth_r) <= 1.5e-3, (kernel, prob)
+        else:
+            _, kernel = check_problem(prob, gpu)
+        seen.add(kernel.split("<")[0].split("(")[0])
+    assert len(seen) >= 2, seen
+
+
+# ----------------------------------------------------------------------------- bf16 activations outside f16's range
+
+@pytest.mark.parametrize("lhs_dt", [Q8H, Q4K])
+@pytest.mark.parametrize("trans_out", [True, False])
+def test_bf16_activations_outside_the_f16_range_against_quantised_weights(gpu, lhs_dt, trans_out):
+    """The tensor-core GEMM multiplies f16 weights by activations cast from bf16 to f16; the cast takes a power of two
+    out of every activation row and the epilogue puts it back, so rows of any bf16 magnitude come out at the tolerance
+    of ordinary ones, and infinities and NaNs arrive where the exact product has them."""
+    N, K, rows = 264, 512, 70
+    w_t, wv = make_lhs(lhs_dt, (N, K), np.random.default_rng(5), 0.03)
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal((rows, K)).astype(np.float32)
+    mags = {0: 1e6, 1: 3e38 / 16, 2: 1e-20, 3: 1e-33, 4: 70000.0, 5: 1.0}
+    for r, m in mags.items():
+        x[r] *= np.float32(m)
+    x[6, :] = 0.0                     # a row of zeros: factor 1
+    x[7, 10] = np.inf                 # one infinity among ordinary values
+    x[8, 11] = np.nan                 # one NaN
+    x[9, :] *= np.float32(1e-30)
+    x[9, 5] = np.float32(1e30)        # 2^200 between the largest and the rest of the row: the rest underflows, harmlessly
+    x = round_to(BF16, x)
+    xt = Tensor.from_data(x.reshape(1, rows, K), gpu, BF16)
+    out = w_t.to(gpu).gemm(xt, None, False, True, trans_out)
+    kernel = rb._lib.load().rt_plan_kernel(gpu.plan_for(out.op.desc)).decode()
+    assert kernel.startswith("gemm_umma_"), kernel
+    got = out.resolve().to(Device.CPU).to_f32().reshape((rows, N) if trans_out else (N, rows))
+    if not trans_out:
+        got = got.T
+    with np.errstate(all="ignore"):
+        truth = x.astype(np.float64) @ wv.astype(np.float64).T
+        truth_r = oracle.bf16_bits_to_f32(oracle.f64_to_bf16_bits(truth)).reshape(rows, N)
+    for r in range(rows):
+        if r == 6:
+            assert np.all(got[r] == 0.0)
+        elif r == 7:
+            assert np.array_equal(got[r], truth_r[r], equal_nan=True), "one infinity: +-inf by the sign of its weight"
+            assert np.all(np.isinf(got[r]) | np.isnan(got[r]))
+        elif r == 8:
+            assert np.all(np.isnan(got[r]))
+        else:
+            fin = np.isfinite(truth_r[r])  # 3e38/16 times a sum of 512 terms may leave bf16's range in the truth too
+            assert np.array_equal(np.isfinite(got[r]), fin), r
+            assert oracle.rel_l2(got[r][fin], truth_r[r][fin]) <= (2e-3 if lhs_dt == Q4K else 1e-3), (r, kernel)
