@@ -95,6 +95,17 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
                  : "memory");
 }
 
+// hi = the value with its 13 low mantissa bits cleared (what a TF32 operand keeps), lo = value - hi.  An infinity goes
+// into lo alone (hi = 0): with hi = inf, lo would be inf - inf, and hi would meet the other operand's lo part, whose
+// sign is arbitrary.  As lo it meets only the other operand's hi part, so inf * w comes out +-inf by w's sign (NaN
+// against w = 0), as in one f32 product.  (Two infinities at the same k on both sides meet a zero hi part each: NaN.)
+__device__ __forceinline__ void split_tf32(float v, float &h, float &l) {
+    const uint32_t bits = __float_as_uint(v);
+    const bool inf = (bits << 1) == 0xFF000000u;
+    h = __uint_as_float(inf ? 0u : bits & 0xFFFFE000u);
+    l = inf ? v : v - h;
+}
+
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}\n"
@@ -288,6 +299,16 @@ gemm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
                         h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
                         h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
                         h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
+                        // P (the activations of a Linear) gets the careful split; Q (its weights) is split by
+                        // every CTA of a tile column in this loop, which is what bounds the kernel, so an infinite
+                        // value of Q comes out as NaN (hi = inf, lo = inf - inf)
+                        const float probe = op == 0 ? (l.x + l.y) + (l.z + l.w) : 0.f;
+                        if (op == 0 && probe != probe) { // an infinity (lo = inf - inf) or a NaN among the four
+                            split_tf32(v.x, h.x, l.x);
+                            split_tf32(v.y, h.y, l.y);
+                            split_tf32(v.z, h.z, l.z);
+                            split_tf32(v.w, h.w, l.w);
+                        }
                         raw[idx] = h;
                         lo[idx] = l;
                     }
@@ -363,10 +384,10 @@ __global__ void split_tf32_kernel(const float4 *__restrict__ in, float4 *__restr
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
         const float4 v = in[i];
         float4 h, l;
-        h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
-        h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
-        h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
-        h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
+        split_tf32(v.x, h.x, l.x);
+        split_tf32(v.y, h.y, l.y);
+        split_tf32(v.z, h.z, l.z);
+        split_tf32(v.w, h.w, l.w);
         hi[i] = h;
         lo[i] = l;
     }

@@ -89,6 +89,18 @@ __host__ __device__ inline Q4kLayout layout(int nsb, int nv, int nbuf) {
 // each with its own header table, partial sums and named barrier, sharing the activations and the
 // buffers (like two CTAs per SM, without staging the activations twice); not with SPLIT, whose
 // cluster barrier needs the whole CTA.
+// n consecutive Q4_K values of one row (from global memory, starting at a super-block) against one staged activation
+// vector, element by element in f32: IEEE's rules for infinities and NaNs decide the result, not the order of the sum.
+// Kept out of line so that the kernel's registers are those of its main path.
+__device__ __forceinline__ float exact_dot(const uint8_t *row, const __half *xv, int n) {
+    float acc = 0.f;
+    for (int k = 0; k < n; k++) {
+        const int pos = (k & ~7) | ((0x75643120u >> (4 * (k & 7))) & 7); // the staged order 0,2,1,3,4,6,5,7
+        acc += q4k_element(row, k) * __half2float(xv[pos]);
+    }
+    return acc;
+}
+
 template <int NVG, bool SPLIT, int WARPS, int HALVES>
 __global__ void __launch_bounds__(WARPS * 32) q4k_gemv_kernel(MatmulParams p, int nv, int sb_per_cta, int lhs_constant, int gpc, int nbuf) {
     static_assert(HALVES == 1 || !SPLIT, "the cluster barrier needs every thread");
@@ -331,6 +343,11 @@ __global__ void __launch_bounds__(WARPS * 32) q4k_gemv_kernel(MatmulParams p, in
 #pragma unroll
         for (int w8 = 0; w8 < WH; w8++) sum += red[(w8 * ROWS + r) * COLS + v];
     }
+    // An infinity among the activations makes s1 * sum((1024+q) x) - s3 * sum(x) = inf - inf: a NaN here is either
+    // the product's own or that one, so the slice is summed again for this (row, vector), element by element.
+    if (sum != sum && ok && v < nv && row_base + r < p.M)
+        sum = exact_dot(w + ((long long)(row_base + r) * nsb_total + sb_begin) * SB_BYTES,
+                        x_s + (long long)v * x_stride(sb_per_cta), nsb * 256);
     bool writer = true;
     if (SPLIT) {
         cg::cluster_group cluster = cg::this_cluster();

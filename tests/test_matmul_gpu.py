@@ -962,3 +962,52 @@ def test_bf16_activations_outside_the_f16_range_against_quantised_weights(gpu, l
             fin = np.isfinite(truth_r[r])  # 3e38/16 times a sum of 512 terms may leave bf16's range in the truth too
             assert np.array_equal(np.isfinite(got[r]), fin), r
             assert oracle.rel_l2(got[r][fin], truth_r[r][fin]) <= (2e-3 if lhs_dt == Q4K else 1e-3), (r, kernel)
+
+
+# ----------------------------------------------------------------------------- infinities and NaNs on every route
+
+@pytest.mark.parametrize("lhs_dt,act,N,K,rows", [
+    (Q8H, F16, 256, 512, 4),      # streaming GEMV kernel, several vectors
+    (Q8H, F16, 256, 512, 20),     # the same in passes
+    (Q8H, F16, 264, 512, 70),     # tensor-core GEMM
+    (Q8F, F32, 264, 512, 70),     # 3 x TF32
+    (F32, F32, 264, 512, 70),
+    (F16, F16, 264, 512, 70),
+    (BF16, BF16, 264, 512, 70),
+    (Q8H, BF16, 264, 512, 70),
+    (Q4K, F16, 264, 512, 1),
+    (Q4K, F16, 264, 512, 12),
+    (Q4K, F16, 264, 512, 70),
+    (F32, F32, 24, 32, 5),        # below every tensor-core threshold
+    (Q8F, F32, 24, 32, 5),
+])
+def test_infinities_and_nans_stay_in_their_rows(gpu, lhs_dt, act, N, K, rows):
+    """One activation row holds an infinity, one a NaN: those output rows are what the exact product has there
+    (+-inf by the weight's sign, NaN against a zero weight; all NaN), and every other row is bit for bit what it is
+    without the two."""
+    w_t, wv = make_lhs(lhs_dt, (N, K), np.random.default_rng(15), 0.03)
+    x = round_to(act, np.random.default_rng(16).standard_normal((rows, K)).astype(np.float32))
+    r_inf, r_nan = (0, rows - 1) if rows > 1 else (0, None)
+    xs = x.copy()
+    xs[r_inf, 7] = np.inf
+    if r_nan is not None and r_nan != r_inf:
+        xs[r_nan, 9] = np.nan
+
+    def run(a):
+        out = w_t.to(gpu).gemm(Tensor.from_data(a.reshape(1, rows, K), gpu, act), None, False, True, True)
+        name = rb._lib.load().rt_plan_kernel(gpu.plan_for(out.op.desc)).decode()
+        return out.resolve().to(Device.CPU).to_f32().reshape(rows, N), name
+
+    clean, kernel = run(x)
+    got, _ = run(xs)
+    assert np.all(np.isfinite(clean)), kernel
+    for r in range(rows):
+        if r == r_inf:
+            w7 = wv[:, 7]
+            want_nan = w7 == 0
+            assert np.array_equal(np.isnan(got[r]), want_nan), kernel
+            assert np.array_equal(got[r][~want_nan], np.where(w7 > 0, np.inf, -np.inf)[~want_nan].astype(np.float32)), kernel
+        elif r == r_nan:
+            assert np.all(np.isnan(got[r])), kernel
+        else:
+            assert np.array_equal(got[r], clean[r]), (kernel, r)
