@@ -1001,6 +1001,9 @@ static rt_status launch_node(rt_plan *plan, const void *lhs, const void *rhs, co
         e = launch_matmul_simt(p, s.desc.lhs_dt, s.desc.rhs_dt, false, st);
         break;
     case PK_GEMM_UMMA: {
+        // tensor maps want 16-byte aligned bases, and the pre-passes (dequantise, cast, pad) read 16 bytes per load
+        if ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) % 16 != 0)
+            return fail(RT_ERR_ARG, "rt_matmul_launch: lhs and rhs must be 16-byte aligned");
         if (plan->tf32x3) {
             if (scatter) return fail(RT_ERR_UNSUPPORTED, "scattered outputs are not taken by the f32 GEMM");
             const void *r32 = rhs;

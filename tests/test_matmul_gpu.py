@@ -188,6 +188,28 @@ def test_streaming_gemv_rejects_misaligned_operands(gpu):
     gpu.sync()
 
 
+@pytest.mark.parametrize("lhs_dt,act", [(Q8H, F16), (Q8H, BF16), (Q4K, F16), (F32, F32), (F16, F16)])
+def test_tensor_core_gemm_rejects_misaligned_operands(gpu, lhs_dt, act):
+    """Its tensor maps and its dequantise / cast pre-passes need 16-byte aligned operands: refused with an error code
+    before anything is launched."""
+    lib = rb._lib.load()
+    w, _ = make_lhs(lhs_dt, (512, 512), np.random.default_rng(1), 0.02)
+    w = w.to(gpu)
+    np_dt = np.float32 if act == F32 else np.float16
+    x = Tensor.from_data(np.zeros((1, 130, 512), dtype=np.float32), gpu, act)
+    node = w.gemm(x, None, False, True, True)
+    plan = gpu.plan_for(node.op.desc)
+    assert lib.rt_plan_kernel(plan).decode().startswith("gemm_umma"), lib.rt_plan_kernel(plan)
+    out = rb.GpuBuffer(gpu, 130 * 512 * 4 + 64)
+    assert lib.rt_matmul_launch(plan, w.ptr, x.ptr + 4, None, out.ptr, None) == rb._lib.RT_ERR_ARG
+    assert lib.rt_matmul_launch(plan, w.ptr + 8, x.ptr, None, out.ptr, None) == rb._lib.RT_ERR_ARG
+    assert b"16-byte aligned" in lib.rt_last_error()
+    # an output that is only element-aligned is fine: the epilogue falls back to narrower stores
+    assert lib.rt_matmul_launch(plan, w.ptr, x.ptr, None, out.ptr + x.dt.size_of(), None) == rb._lib.RT_OK
+    assert lib.rt_matmul_launch(plan, w.ptr, x.ptr, None, out.ptr, None) == rb._lib.RT_OK
+    gpu.sync()
+
+
 def test_plans_are_cached_by_the_library_and_kept_weights_follow_their_buffers(gpu):
     """rt_matmul_plan hands equal descriptions the same plan (the KernelKey cache's role).  A quantised weight
     flagged constant is dequantised once and the copy kept by pointer; when the weight's buffer is freed and its
