@@ -101,8 +101,11 @@ __device__ __forceinline__ float exact_dot(const uint8_t *row, const __half *xv,
     return acc;
 }
 
+// Registers: a walking CTA (512 threads) is given all the registers one CTA per SM can have (70 .. 96 are used): held to
+// 64 for two CTAs per SM it was up to 7 % slower with 9 .. 16 vectors and no faster with fewer.  The one-row-group CTAs
+// keep the compiler's own choice (64 or fewer: four per SM).
 template <int NVG, bool SPLIT, int WARPS, int HALVES>
-__global__ void __launch_bounds__(WARPS * 32) q4k_gemv_kernel(MatmulParams p, int nv, int sb_per_cta, int lhs_constant, int gpc, int nbuf) {
+__global__ void __launch_bounds__(WARPS * 32, WARPS == WARPS_WALK ? 1 : 0) q4k_gemv_kernel(MatmulParams p, int nv, int sb_per_cta, int lhs_constant, int gpc, int nbuf) {
     static_assert(HALVES == 1 || !SPLIT, "the cluster barrier needs every thread");
     constexpr int THREADS = WARPS * 32;
     constexpr int WH = WARPS / HALVES, TH = WH * 32; // warps and threads that share a row group
