@@ -676,18 +676,21 @@ static rt_status build_plan(rt_device *dev, const rt_matmul_desc *desc, rt_plan 
         pl->name = std::string("q8_gemv_mma_") + (desc->lhs_dt == RT_Q8_0H ? "h" : "f") + "_nv" + std::to_string(pl->nv) +
                    "_split" + std::to_string(pl->split);
     } else if (gemv_split > 0 && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.trans_rhs && s.trans_out && s.N >= 9 && s.N <= 24 &&
-               s.stacks == 1 && s.K > 0 && !empty) {
-        // 9..24 vectors against Q8_0: two or three passes of the streaming kernel, 8 vectors at a time.  The
-        // weights are read again by each pass (from L2 where they fit), which still is well under the
-        // dequantise + tensor-core GEMM route ([10240,2560] x 12 rows: 37 -> 15.6 us); with trans_out each
+               s.stacks == 1 && s.K > 0 && !empty &&
+               // two passes over weights of 32 Mi values or more cost more than the tensor-core GEMM even when that has to
+               // dequantise first ([16384,3072] x 17..24 rows: 52 .. 55 us against 24 us with a kept f16 copy, ~50 without)
+               !(s.N > 16 && (double)s.M * (double)s.K >= (double)(1 << 25) && umma_eligible(*desc, s))) {
+        // 9..24 vectors against Q8_0: the streaming kernel with two groups of eight MMA columns takes up to 16 in one
+        // pass over the weights; 17..24 are a pass of 16 and a pass of the rest (the weights are read again, from L2
+        // where they fit), which still is under the dequantise + tensor-core GEMM route; with trans_out each
         // vector's outputs are contiguous, so a later pass is the same problem on offset pointers.
         pl->kernel = PK_Q8_GEMV_MMA;
-        pl->nv = 8;
-        pl->nv2 = (int)s.N - 8;
+        pl->nv = (int)std::min<int64_t>(s.N, 16);
+        pl->nv2 = (int)s.N - pl->nv;
         pl->split = gemv_split;
-        pl->launches = 1 + (pl->nv2 + 7) / 8;
-        pl->name = std::string("q8_gemv_mma_") + (desc->lhs_dt == RT_Q8_0H ? "h" : "f") + "_nv8+" + std::to_string(pl->nv2) +
-                   "_split" + std::to_string(pl->split);
+        pl->launches = 1 + (pl->nv2 > 0 ? 1 : 0);
+        pl->name = std::string("q8_gemv_mma_") + (desc->lhs_dt == RT_Q8_0H ? "h" : "f") + "_nv" + std::to_string(pl->nv) +
+                   (pl->nv2 ? "+" + std::to_string(pl->nv2) : std::string()) + "_split" + std::to_string(pl->split);
     } else if (desc->lhs_dt == RT_Q4_K && desc->rhs_dt == RT_F16 && !s.trans_lhs && s.N >= 1 && s.N <= 16 &&
                (s.N == 1 || s.trans_rhs) && !empty && !force_simt() && s.stacks == 1 && q4k_umma_enabled() &&
                (double)s.M * (double)s.K >= (double)(1 << 22) &&
@@ -968,11 +971,11 @@ static rt_status launch_node(rt_plan *plan, const void *lhs, const void *rhs, co
         if ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) % 16 != 0)
             return fail(RT_ERR_ARG, "rt_matmul_launch: lhs and rhs must be 16-byte aligned");
         e = launch_q8_gemv_mma(p, s.desc.lhs_dt == RT_Q8_0F, plan->nv, plan->split, (flags & RT_LAUNCH_LHS_CONSTANT) != 0, st);
-        for (int done = plan->nv; e == cudaSuccess && done < plan->nv + plan->nv2; done += 8) {
+        for (int done = plan->nv; e == cudaSuccess && done < plan->nv + plan->nv2; done += 16) {
             MatmulParams p2 = p; // vectors done.. : rhs rows and (trans_out) output rows of the same problem
             p2.rhs = (const char *)rhs + (size_t)done * (size_t)s.K * 2;
             p2.out = (char *)out + (size_t)done * (size_t)s.M * 2;
-            const int nv = std::min(8, plan->nv + plan->nv2 - done);
+            const int nv = std::min(16, plan->nv + plan->nv2 - done);
             e = launch_q8_gemv_mma(p2, s.desc.lhs_dt == RT_Q8_0F, nv, plan->split, (flags & RT_LAUNCH_LHS_CONSTANT) != 0, st);
         }
         break;
@@ -1185,6 +1188,7 @@ rt_status rt_executable_create_planned(rt_device *dev, const rt_dispatch *nodes,
             filled_any = true;
         }
         kept[(size_t)i] = true;
+        x->launches -= 1; // this node's dispatches go without the dequantising pass
     }
     if (filled_any) CUDA_TRY(cudaStreamSynchronize(dev->stream));
 

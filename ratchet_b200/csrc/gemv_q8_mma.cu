@@ -1,4 +1,4 @@
-// Q8_0 GEMV / skinny GEMM for f16 activations: y[v][r] = sum_k W[r][k] * x[v][k], 1..8 vectors.
+// Q8_0 GEMV / skinny GEMM for f16 activations: y[v][r] = sum_k W[r][k] * x[v][k], 1..16 vectors.
 //
 // Takes the role of the reference's subgroup GEMV (crates/ratchet-core/src/ops/gemv.rs:333-558)
 // for the (Q8_0H, F16) pair, and of its GEMM (ops/gemm.rs:342-492) when op(rhs) has at most 8
@@ -70,17 +70,19 @@ __host__ __device__ inline int scale_row_stride(int nblk_slice) { return nblk_sl
 
 // Shared memory: [codes 16 x cstride][scales 16 x sstride][mbarrier]; the first 4 KB double as the
 // cross-warp reduction buffer once the codes have been consumed (the mbarrier lies beyond it).
-__host__ __device__ inline size_t bar_offset(int blocks_per_cta, int scale_size) {
+__host__ __device__ inline size_t bar_offset(int blocks_per_cta, int scale_size, int cols) {
     const size_t codes = (size_t)ROWS * code_row_stride(blocks_per_cta * 32);
     const size_t scales = ((size_t)ROWS * scale_row_stride(blocks_per_cta) * scale_size + 15) & ~(size_t)15;
-    const size_t red = (size_t)WARPS * ROWS * 8 * sizeof(float);
+    const size_t red = (size_t)WARPS * ROWS * cols * sizeof(float);
     return codes + scales < red ? red : codes + scales;
 }
 
-// ScaleT: __half (Q8_0H) or float (Q8_0F).  NV: number of activation vectors (1..8).
-// SPLIT: K is split over a cluster of gridDim.y CTAs.
+// ScaleT: __half (Q8_0H) or float (Q8_0F).  NV: number of activation vectors, 1..8, or 16 = two groups of eight
+// MMA columns holding nv_rt (9..16) vectors.  SPLIT: K is split over a cluster of gridDim.y CTAs.
 template <typename ScaleT, int NV, bool SPLIT>
-__global__ void __launch_bounds__(THREADS, 5) q8_gemv_bulk_kernel(MatmulParams p, int blocks_per_cta, int lhs_constant) {
+__global__ void __launch_bounds__(THREADS, 5) q8_gemv_bulk_kernel(MatmulParams p, int blocks_per_cta, int lhs_constant, int nv_rt) {
+    constexpr int NVG = NV > 8 ? 2 : 1, COLS = NVG * 8;
+    const int nvv = NV > 8 ? nv_rt : NV;
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__(THREADS, 5) q8_gemv_bulk_kernel(MatmulParams p
     const int sstride = scale_row_stride(blocks_per_cta);
     uint8_t *codes_s = smem;
     ScaleT *scales_s = reinterpret_cast<ScaleT *>(smem + ROWS * cstride);
-    uint64_t *bar = reinterpret_cast<uint64_t *>(smem + bar_offset(blocks_per_cta, (int)sizeof(ScaleT)));
+    uint64_t *bar = reinterpret_cast<uint64_t *>(smem + bar_offset(blocks_per_cta, (int)sizeof(ScaleT), COLS));
     const uint32_t bar_addr = smem_u32(bar);
 
     const int row_base = blockIdx.x * ROWS;
@@ -133,13 +135,17 @@ __global__ void __launch_bounds__(THREADS, 5) q8_gemv_bulk_kernel(MatmulParams p
     if (lhs_constant) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- activations: written by the stream predecessor, so only touched after the wait
-    const int vec = NV == 1 ? 0 : min(g, NV - 1);
     const long long rbatch = batch % p.rhs_stack;
-    const __half *x = (const __half *)p.rhs + rbatch * (long long)p.K * NV + (long long)vec * p.K + (long long)blk_begin * 32 + c * 8;
+    const __half *x[NVG]; // MMA column g of group j is vector j*8 + g (clamped: columns past the last vector repeat it)
+#pragma unroll
+    for (int j = 0; j < NVG; j++) {
+        const int vec = NV == 1 ? 0 : min(j * 8 + g, nvv - 1);
+        x[j] = (const __half *)p.rhs + rbatch * (long long)p.K * nvv + (long long)vec * p.K + (long long)blk_begin * 32 + c * 8;
+    }
     {
         // warm L1 with this CTA's slice of x while the weights are still on their way
-        const char *xb = (const char *)((const __half *)p.rhs + rbatch * (long long)p.K * NV + (long long)blk_begin * 32);
-        for (int v = 0; v < NV; v++)
+        const char *xb = (const char *)((const __half *)p.rhs + rbatch * (long long)p.K * nvv + (long long)blk_begin * 32);
+        for (int v = 0; v < nvv; v++)
             for (int off = threadIdx.x * 128; off < blk_cnt * 64; off += THREADS * 128)
                 asm volatile("prefetch.global.L1 [%0];" ::"l"(xb + (long long)v * p.K * 2 + off));
     }
@@ -158,7 +164,11 @@ __global__ void __launch_bounds__(THREADS, 5) q8_gemv_bulk_kernel(MatmulParams p
         }
     }
 
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[NVG][4];
+#pragma unroll
+    for (int j = 0; j < NVG; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[j][i] = 0.f;
     if (ok) {
         const uint8_t *qa = codes_s + g * cstride + c * 8;
         const uint8_t *qb = codes_s + (g + 8) * cstride + c * 8;
@@ -167,58 +177,64 @@ __global__ void __launch_bounds__(THREADS, 5) q8_gemv_bulk_kernel(MatmulParams p
         for (int blk = warp; blk < blk_cnt; blk += WARPS) {
             const uint2 wa = *reinterpret_cast<const uint2 *>(qa + blk * 32);
             const uint2 wb = *reinterpret_cast<const uint2 *>(qb + blk * 32);
-            const uint4 xv = *reinterpret_cast<const uint4 *>(x + blk * 32);
             const float da = scale_to_f32(sa[blk]), db = scale_to_f32(sb[blk]);
             __half2 a01, a23, a45, a67, b01, b23, b45, b67;
             codes4_to_half2(wa.x, a01, a23);
             codes4_to_half2(wa.y, a45, a67);
             codes4_to_half2(wb.x, b01, b23);
             codes4_to_half2(wb.y, b45, b67);
-            float t[4] = {0.f, 0.f, 0.f, 0.f};
             // The k index inside a block is permuted identically for W and x: lane c owns
             // elements c*8..c*8+7; the first MMA consumes 0..3 of them, the second 4..7.
             const uint32_t fa[4] = {h2_as_u32(a01), h2_as_u32(b01), h2_as_u32(a23), h2_as_u32(b23)};
-            mma_m16n8k16_f16(t, fa, xv.x, xv.y);
             const uint32_t fb[4] = {h2_as_u32(a45), h2_as_u32(b45), h2_as_u32(a67), h2_as_u32(b67)};
-            mma_m16n8k16_f16(t, fb, xv.z, xv.w);
-            acc[0] = fmaf(da, t[0], acc[0]);
-            acc[1] = fmaf(da, t[1], acc[1]);
-            acc[2] = fmaf(db, t[2], acc[2]);
-            acc[3] = fmaf(db, t[3], acc[3]);
+#pragma unroll
+            for (int j = 0; j < NVG; j++) {
+                const uint4 xv = *reinterpret_cast<const uint4 *>(x[j] + blk * 32);
+                float t[4] = {0.f, 0.f, 0.f, 0.f};
+                mma_m16n8k16_f16(t, fa, xv.x, xv.y);
+                mma_m16n8k16_f16(t, fb, xv.z, xv.w);
+                acc[j][0] = fmaf(da, t[0], acc[j][0]);
+                acc[j][1] = fmaf(da, t[1], acc[j][1]);
+                acc[j][2] = fmaf(db, t[2], acc[j][2]);
+                acc[j][3] = fmaf(db, t[3], acc[j][3]);
+            }
         }
     }
     __syncthreads(); // every warp is done with the staged codes: the region becomes the reduction buffer
 
     // C fragment: acc[0],acc[1] -> (row g, cols 2c,2c+1); acc[2],acc[3] -> (row g+8, same cols)
-    float *red = reinterpret_cast<float *>(smem); // [WARPS][ROWS][8]
-    red[(warp * ROWS + g) * 8 + 2 * c] = acc[0];
-    red[(warp * ROWS + g) * 8 + 2 * c + 1] = acc[1];
-    red[(warp * ROWS + g + 8) * 8 + 2 * c] = acc[2];
-    red[(warp * ROWS + g + 8) * 8 + 2 * c + 1] = acc[3];
+    float *red = reinterpret_cast<float *>(smem); // [WARPS][ROWS][COLS]
+#pragma unroll
+    for (int j = 0; j < NVG; j++) {
+        red[(warp * ROWS + g) * COLS + j * 8 + 2 * c] = acc[j][0];
+        red[(warp * ROWS + g) * COLS + j * 8 + 2 * c + 1] = acc[j][1];
+        red[(warp * ROWS + g + 8) * COLS + j * 8 + 2 * c] = acc[j][2];
+        red[(warp * ROWS + g + 8) * COLS + j * 8 + 2 * c + 1] = acc[j][3];
+    }
     __syncthreads();
 
-    const int r = threadIdx.x >> 3, v = threadIdx.x & 7; // first 128 threads: one (row, vector) each
+    const int r = threadIdx.x / COLS, v = threadIdx.x % COLS; // the first ROWS * COLS threads: one (row, vector) each
     float sum = 0.f;
-    if (threadIdx.x < ROWS * 8) {
+    if (threadIdx.x < ROWS * COLS) {
 #pragma unroll
-        for (int w = 0; w < WARPS; w++) sum += red[(w * ROWS + r) * 8 + v];
+        for (int w = 0; w < WARPS; w++) sum += red[(w * ROWS + r) * COLS + v];
     }
     if (SPLIT) {
         cg::cluster_group cluster = cg::this_cluster();
         __syncthreads();
-        if (threadIdx.x < ROWS * 8) red[r * 8 + v] = sum;
+        if (threadIdx.x < ROWS * COLS) red[r * COLS + v] = sum;
         cluster.sync();
-        if (cluster.block_rank() == 0 && threadIdx.x < ROWS * 8) {
+        if (cluster.block_rank() == 0 && threadIdx.x < ROWS * COLS) {
             const unsigned n = cluster.num_blocks();
             for (unsigned k = 1; k < n; k++) {
                 const float *remote = cluster.map_shared_rank(red, k);
-                sum += remote[r * 8 + v];
+                sum += remote[r * COLS + v];
             }
         }
         cluster.sync(); // keep every CTA's shared memory alive until rank 0 has read it
         if (cluster.block_rank() != 0) return;
     }
-    if (threadIdx.x < ROWS * 8 && v < NV) {
+    if (threadIdx.x < ROWS * COLS && v < nvv) {
         const int row = row_base + r;
         if (row < p.M) {
             const bool has_bias = p.bias_mode != BIAS_NONE;
@@ -226,20 +242,20 @@ __global__ void __launch_bounds__(THREADS, 5) q8_gemv_bulk_kernel(MatmulParams p
             if (has_bias) bias = load_bias(p.bias, p.bias_dt, p.bias_mode == BIAS_PER_M ? row : v);
             __half o = epilogue_value<__half>(sum, has_bias, bias, p.epilogue);
             // out is [stacks][M][NV] or, transposed, [stacks][NV][M]
-            const long long ob = (long long)batch * p.M * NV;
-            const long long idx = p.trans_out ? ob + (long long)v * p.M + row : ob + (long long)row * NV + v;
+            const long long ob = (long long)batch * p.M * nvv;
+            const long long idx = p.trans_out ? ob + (long long)v * p.M + row : ob + (long long)row * nvv + v;
             ((__half *)p.out)[idx] = o;
         }
     }
 }
 
-size_t smem_bytes(int blocks_per_cta, int scale_size) { return bar_offset(blocks_per_cta, scale_size) + 16; }
+size_t smem_bytes(int blocks_per_cta, int scale_size, int cols = 8) { return bar_offset(blocks_per_cta, scale_size, cols) + 16; }
 
 template <typename ScaleT, int NV>
-cudaError_t launch_nv(const MatmulParams &p, int split, bool lhs_constant, cudaStream_t stream) {
+cudaError_t launch_nv(const MatmulParams &p, int nv, int split, bool lhs_constant, cudaStream_t stream) {
     const int nblk = p.K / 32;
     const int bpc = (nblk + split - 1) / split;
-    const size_t smem = smem_bytes(bpc, (int)sizeof(ScaleT));
+    const size_t smem = smem_bytes(bpc, (int)sizeof(ScaleT), NV > 8 ? 16 : 8);
     auto kernel = split == 1 ? q8_gemv_bulk_kernel<ScaleT, NV, false> : q8_gemv_bulk_kernel<ScaleT, NV, true>;
     static SmemAttr smem_attr[2];
     if (smem > 48 * 1024) {
@@ -265,21 +281,22 @@ cudaError_t launch_nv(const MatmulParams &p, int split, bool lhs_constant, cudaS
     }
     cfg.attrs = attr;
     cfg.numAttrs = n;
-    return cudaLaunchKernelEx(&cfg, kernel, p, bpc, lhs_constant ? 1 : 0);
+    return cudaLaunchKernelEx(&cfg, kernel, p, bpc, lhs_constant ? 1 : 0, nv);
 }
 
 template <typename ScaleT>
 cudaError_t launch_scale(const MatmulParams &p, int nv, int split, bool lhs_constant, cudaStream_t stream) {
     switch (nv) {
-    case 1: return launch_nv<ScaleT, 1>(p, split, lhs_constant, stream);
-    case 2: return launch_nv<ScaleT, 2>(p, split, lhs_constant, stream);
-    case 3: return launch_nv<ScaleT, 3>(p, split, lhs_constant, stream);
-    case 4: return launch_nv<ScaleT, 4>(p, split, lhs_constant, stream);
-    case 5: return launch_nv<ScaleT, 5>(p, split, lhs_constant, stream);
-    case 6: return launch_nv<ScaleT, 6>(p, split, lhs_constant, stream);
-    case 7: return launch_nv<ScaleT, 7>(p, split, lhs_constant, stream);
-    case 8: return launch_nv<ScaleT, 8>(p, split, lhs_constant, stream);
+    case 1: return launch_nv<ScaleT, 1>(p, nv, split, lhs_constant, stream);
+    case 2: return launch_nv<ScaleT, 2>(p, nv, split, lhs_constant, stream);
+    case 3: return launch_nv<ScaleT, 3>(p, nv, split, lhs_constant, stream);
+    case 4: return launch_nv<ScaleT, 4>(p, nv, split, lhs_constant, stream);
+    case 5: return launch_nv<ScaleT, 5>(p, nv, split, lhs_constant, stream);
+    case 6: return launch_nv<ScaleT, 6>(p, nv, split, lhs_constant, stream);
+    case 7: return launch_nv<ScaleT, 7>(p, nv, split, lhs_constant, stream);
+    case 8: return launch_nv<ScaleT, 8>(p, nv, split, lhs_constant, stream);
     }
+    if (nv >= 9 && nv <= 16) return launch_nv<ScaleT, 16>(p, nv, split, lhs_constant, stream);
     return cudaErrorInvalidValue;
 }
 

@@ -750,8 +750,8 @@ def test_short_prompts_take_the_tensor_core_gemm(gpu):
             for to in (True, False):
                 _, kernel = check_problem(Problem(lhs, dt, (1000, 512), (1, nv, 512), (False, True, to), bias=True,
                                                   epilogue=0 if dt == F32 else 1, seed=200 + nv, w_std=0.02), gpu)
-                if lhs == Q8H and to:  # the Linear form: two passes of the streaming kernel, 8 vectors then the rest
-                    assert kernel.startswith(f"q8_gemv_mma_h_nv8+{nv - 8}"), kernel
+                if lhs == Q8H and to:  # the Linear form: one pass of the streaming kernel, two groups of eight MMA columns
+                    assert kernel.startswith(f"q8_gemv_mma_h_nv{nv}_"), kernel
                 else:
                     assert kernel.startswith("gemm_umma"), kernel
     # the same at a decode shape, with bias and GELU, f32 scales too
@@ -759,7 +759,17 @@ def test_short_prompts_take_the_tensor_core_gemm(gpu):
         for nv in (9, 12, 16, 17, 24):
             _, kernel = check_problem(Problem(lhs, F16, (10240, 2560), (1, nv, 2560), (False, True, True), bias=True, epilogue=1,
                                               seed=230 + nv, w_std=0.02), gpu)
-            assert "_nv8+" in kernel, kernel
+            assert (f"_nv{nv}_" if nv <= 16 else f"_nv16+{nv - 16}_") in kernel, kernel  # 17..24: a pass of 16, then the rest
+
+
+def test_skinny_q8_routes_by_vectors_and_weight_size(gpu):
+    """9..16 vectors: one pass of the streaming kernel; 17..24: a pass of 16 and a pass of the rest, except against
+    weights of 32 Mi values or more, where two passes cost more than the tensor-core GEMM."""
+    lib = rb._lib.load()
+    for (wshape, nv, want) in [((16384, 3072), 16, "q8_gemv_mma_h_nv16_"), ((16384, 3072), 17, "gemm_umma_Q8_0H_F16"),
+                               ((10240, 2560), 24, "q8_gemv_mma_h_nv16+8_"), ((3072, 8192), 20, "q8_gemv_mma_h_nv16+4_")]:
+        _, kernel = check_problem(Problem(Q8H, F16, wshape, (1, nv, wshape[1]), (False, True, True), bias=True, seed=nv, w_std=0.02), gpu)
+        assert kernel.startswith(want), kernel
 
 
 def test_umma_takes_the_prefill_configs(gpu):
