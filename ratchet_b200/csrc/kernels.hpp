@@ -52,7 +52,7 @@ cudaError_t launch_matmul_simt(const MatmulParams &p, rt_dtype lhs_dt, rt_dtype 
 int rowvec_mat_chunks(int N, int K, int stacks, int sm_count); // CTAs that share the k rows (1: no partial sums)
 cudaError_t launch_rowvec_mat(const MatmulParams &p, rt_dtype dt, int chunks, float *partial, cudaStream_t stream);
 
-// Q8_0 x f16 GEMV / skinny GEMM on warp MMAs.  nv = columns of op(rhs), 1..8 (rhs stored [nv][K]).
+// Q8_0 x f16 GEMV / skinny GEMM on warp MMAs.  nv = columns of op(rhs), 1..16 (rhs stored [nv][K]).
 // pick_split returns the K split (cluster size), or 0 when the shape does not fit the kernel.
 // lhs_constant: the weight bytes are not written by any work in flight on the stream, so the
 // kernel may request them before it waits for its stream predecessor.
