@@ -199,6 +199,42 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
+// epilogue_value over 32 accumulator columns of one row, results into the row's staging line (chunk h*4+g, XOR-swizzled
+// by the row).  BIAS: 0 none, 1 per column (bias32 = this round's 32 values in shared memory), 2 per row.  The f16
+// form is epilogue_value<__half> step by step (round the accumulator, add the bias in f32 and round, GELU in f32 and
+// round) on pairs, so that each rounding is one packed conversion; the bf16 form rounds once, at the end.
+template <typename OutT, int BIAS, bool GELU>
+__device__ __forceinline__ void epilogue_math32(const uint32_t (&v)[32], const float *bias32, float row_bias, uint8_t *row_stg, int h, int lane) {
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int i0 = g * 8 + j * 2;
+            float2 f = make_float2(__uint_as_float(v[i0]), __uint_as_float(v[i0 + 1]));
+            float2 b = make_float2(row_bias, row_bias);
+            if (BIAS == 1) b = *reinterpret_cast<const float2 *>(bias32 + i0);
+            if (cuda::std::is_same<OutT, __half>::value) {
+                __half2 hh = __floats2half2_rn(f.x, f.y);
+                if (BIAS != 0) {
+                    f = __half22float2(hh);
+                    hh = __floats2half2_rn(f.x + b.x, f.y + b.y);
+                }
+                if (GELU) {
+                    f = __half22float2(hh);
+                    hh = __floats2half2_rn(gelu_tanh_f32(f.x), gelu_tanh_f32(f.y));
+                }
+                w[j] = *reinterpret_cast<uint32_t *>(&hh);
+            } else {
+                if (BIAS != 0) { f.x += b.x; f.y += b.y; }
+                if (GELU) { f.x = gelu_tanh_f32(f.x); f.y = gelu_tanh_f32(f.y); }
+                w[j] = pack2<OutT>(f.x, f.y);
+            }
+        }
+        *reinterpret_cast<uint4 *>(row_stg + (((h * 4 + g) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
 // The plain epilogue of one accumulator tile (128 rows x BN columns of this CTA's tensor memory at `tmem_acc`): 64
 // columns per round: two tensor-memory loads, the epilogue arithmetic, then through a per-warp staging buffer so that
 // global stores run along rows: 8 lanes x 16 B = one full 128-byte line per row (this matters most when the destination
@@ -234,7 +270,9 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams &prm, uint32_t tm
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             __syncwarp();
         }
-#pragma unroll
+        // not unrolled: a CTA with one tile runs this code once, straight from a cold instruction cache (a fifth of the
+        // warps' stall cycles of a one-tile launch were instruction fetches), so half the code is half of those misses
+#pragma unroll 1
         for (int h = 0; h < 2; h++) {
             const int c = cc * 2 + h;
             uint32_t v[32];
@@ -258,19 +296,19 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams &prm, uint32_t tm
                 }
             }
             {
-#pragma unroll
-                for (int g = 0; g < 4; g++) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const int i0 = g * 8 + j * 2;
-                        const float b0 = prm.bias_mode == BIAS_PER_N ? bias_s[c * 32 + i0] : row_bias;
-                        const float b1 = prm.bias_mode == BIAS_PER_N ? bias_s[c * 32 + i0 + 1] : row_bias;
-                        const OutT o0 = epilogue_value<OutT>(__uint_as_float(v[i0]), has_bias, b0, prm.epilogue);
-                        const OutT o1 = epilogue_value<OutT>(__uint_as_float(v[i0 + 1]), has_bias, b1, prm.epilogue);
-                        w[j] = pack2<OutT>(to_f32(o0), to_f32(o1));
-                    }
-                    *reinterpret_cast<uint4 *>(stg + lane * STG_ROW_BYTES + (((h * 4 + g) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                // the arithmetic of 32 columns, compiled once per (bias, GELU) form: with the two switches tested for every
+                // element the eight epilogue warps took 0.8 us per 32 columns without GELU and 2.1 us with it, which is
+                // most of a one-tile launch
+                uint8_t *row_stg = stg + lane * STG_ROW_BYTES;
+                const float *b32 = bias_s + c * 32;
+                const int form = (has_bias ? (prm.bias_mode == BIAS_PER_N ? 2 : 4) : 0) | (prm.epilogue == RT_EPILOGUE_GELU_TANH ? 1 : 0);
+                switch (form) {
+                case 0: epilogue_math32<OutT, 0, false>(v, b32, row_bias, row_stg, h, lane); break;
+                case 1: epilogue_math32<OutT, 0, true>(v, b32, row_bias, row_stg, h, lane); break;
+                case 2: epilogue_math32<OutT, 1, false>(v, b32, row_bias, row_stg, h, lane); break;
+                case 3: epilogue_math32<OutT, 1, true>(v, b32, row_bias, row_stg, h, lane); break;
+                case 4: epilogue_math32<OutT, 2, false>(v, b32, row_bias, row_stg, h, lane); break;
+                default: epilogue_math32<OutT, 2, true>(v, b32, row_bias, row_stg, h, lane); break;
                 }
             }
         }
