@@ -44,7 +44,12 @@ typedef enum rt_status {
 
 /* crates/ratchet-core/src/dtype/mod.rs:10-20 (DType).  RT_BF16 as a matmul operand and
  * RT_Q4_K are extensions the reference declares but does not implement
- * (dtype/mod.rs:12, crates/ratchet-loader/src/k_quants.rs:95-103). */
+ * (dtype/mod.rs:12, crates/ratchet-loader/src/k_quants.rs:95-103).
+ * Values outside the ordinary: an infinite or NaN activation gives what the product has by
+ * IEEE's rules (+-inf by the weight's sign, NaN against a zero weight or for a NaN) in its own
+ * output row and touches no other row, on every route; bf16 activations of any magnitude are
+ * taken as they are (against quantised weights they are brought into f16's range row by row
+ * with a power of two that is multiplied back onto the accumulator). */
 typedef enum rt_dtype {
     RT_F32 = 0,
     RT_F16 = 1,
