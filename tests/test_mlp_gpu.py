@@ -36,6 +36,12 @@ def _kernel_of(gpu, node):
 @pytest.mark.parametrize("lhs_dt,act,wshape,xshape,bias,route", [
     (Q8H, F16, (16384, 3072), (1, 1, 3072), False, "+silu_mul"),             # Phi-3 gate_up, decode
     (Q8H, F16, (16384, 3072), (1, 16, 3072), False, "+silu_mul"),            # 16 rows: two streaming passes
+    (Q8H, F16, (2048, 1024), (1, 9, 1024), True, "+silu_mul"),               # one streaming pass with two groups of MMA columns
+    (Q8H, F16, (2048, 1024), (1, 17, 1024), True, "+silu_mul"),              # a pass of 16 and a pass of one
+    (Q8H, F16, (2048, 1024), (1, 24, 1024), False, "+silu_mul"),
+    (Q8H, F16, (2048, 1024), (1, 25, 1024), True, "paired_tiles"),           # the first row count of the tensor-core GEMM
+    (Q4K, F16, (2048, 1024), (1, 16, 1024), True, "+silu_mul"),
+    (Q4K, F16, (2048, 1024), (1, 17, 1024), True, "paired_tiles"),
     (Q8H, F16, (16384, 3072), (1, 512, 3072), False, "paired_tiles"),        # prefill: the tensor-core GEMM folds the pairs
     (Q8H, F16, (512, 256), (3, 40, 256), True, "paired_tiles"),              # batched rows over one weight, bias on both halves
     (F16, F16, (200, 64), (1, 300, 64), True, "paired_tiles"),               # ff = 100: not a multiple of 8, ragged tiles
