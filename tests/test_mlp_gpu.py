@@ -172,6 +172,41 @@ def test_whisper_mlp_block(gpu):
     assert np.array_equal(lazy.to(Device.CPU).to_numpy().reshape(-1), out.to(Device.CPU).to_numpy().reshape(-1))
 
 
+def test_bf16_mlp_block_with_rows_beyond_the_f16_range(gpu):
+    """A GELU block on bf16 activations against Q8_0H weights as one planned executable: the cast of each node's
+    activations (to f16, with a power of two per row) and its factors live in the executable's arena.  Rows of
+    magnitude 1e5 and 1e-6 come out as accurately as ordinary ones; the hidden tensor is bf16 between the nodes."""
+    rows = 96
+    w1_t, w1 = make_lhs(Q8H, (1024, 256), np.random.default_rng(9101), 0.03)
+    w2_t, w2 = make_lhs(Q8H, (256, 1024), np.random.default_rng(9102), 0.03)
+    b1 = round_to(BF16, np.random.default_rng(9103).standard_normal(1024) * 0.02)  # Linear casts its bias to the input dtype
+    b2 = round_to(BF16, np.random.default_rng(9104).standard_normal(256) * 0.02)
+    x = np.random.default_rng(9105).standard_normal((1, rows, 256)).astype(np.float32)
+    x[0, 0] *= 1e5
+    x[0, 1] *= 1e-6
+    x = round_to(BF16, x)
+    fc1 = Linear(w1_t.to(gpu), Tensor.from_data(b1, gpu, BF16))
+    fc2 = Linear(w2_t.to(gpu), Tensor.from_data(b2, gpu, BF16))
+    exe, out = MLP(fc1, fc2, act="gelu").bind(Tensor.from_data(x, gpu, BF16))
+    assert exe.arena()["arena_bytes"] > 0
+    for _ in range(2):  # the second dispatch reuses the arena's cast areas
+        exe.dispatch()
+    gpu.sync()
+    got = out.to(Device.CPU).to_f32().reshape(rows, 256)
+    x2 = x.reshape(rows, 256).astype(np.float64)
+    with np.errstate(all="ignore"):
+        h = oracle.matmul_truth(w1, x2, b1, 1, 1, 1, 1024, rows, 256, False, True, True, 1).reshape(rows, 1024)
+        h_r = oracle.bf16_bits_to_f32(oracle.f64_to_bf16_bits(h)).reshape(rows, 1024)
+        t = oracle.matmul_truth(w2, h_r, b2, 1, 1, 1, 256, rows, 1024, False, True, True, 0).reshape(rows, 256)
+        want = oracle.bf16_bits_to_f32(oracle.f64_to_bf16_bits(t)).reshape(rows, 256)
+    assert np.all(np.isfinite(got))
+    for r in (0, 1, 2, rows - 1):
+        # two bf16 roundings in sequence (hidden, output) against a truth with the same two: whole-ulp flips of the hidden
+        # tensor carry through, so the bar per row is twice the single node's
+        assert oracle.rel_l2(got[r], want[r]) <= 2e-3, r
+    assert oracle.rel_l2(got, want) <= 2e-3
+
+
 def test_phi2_decode_mlp_block_is_the_persistent_gemv_kernel(gpu):
     """Phi-2 decode: x f16 [1,1,2560] -> Q8_0H [10240,2560] + b -> GELU -> Q8_0H [2560,10240] + b
     (phi2/mlp.rs:13-15): the two nodes of the block run as one launch."""
