@@ -319,3 +319,53 @@ def test_executables_own_their_scratch(gpu):
     gpu.sync()
     for out, want in zip(outs, wants):
         assert oracle.rel_l2(out.to(Device.CPU).to_f32().reshape(-1), want) <= TOL[F16]
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_seeded_planned_chains_match_the_lazy_graph_bit_for_bit(gpu, seed):
+    """Chains of three to six Linear nodes of mixed weight formats, with and without bias and GELU, weights flagged
+    constant or not, as planned executables (intermediates, dequantising scratch, cast areas and paired rows all placed
+    in the one arena): every chain gives exactly what its nodes give when resolved one by one into buffers of their own,
+    on the first dispatch and on the third."""
+    rng = np.random.default_rng(4200 + seed)
+    act = [F16, BF16, F32][seed % 3]
+    weights = {F16: [Q8H, Q4K, F16], BF16: [Q8H, Q4K, BF16], F32: [Q8F, F32]}[act]
+    rows = int(rng.choice([4, 12, 20, 40, 130]))
+    n_nodes = int(rng.integers(3, 7))
+    widths = [int(rng.choice([256, 512, 768, 1024])) for _ in range(n_nodes + 1)]
+    x = round_to(act, rng.standard_normal((rows, widths[0])).astype(np.float32))
+    x_d = Tensor.from_data(x, gpu, act)
+    ws, bs, epis, flags = [], [], [], []
+    for i in range(n_nodes):
+        w_t, _ = make_lhs(weights[int(rng.integers(0, len(weights)))], (widths[i + 1], widths[i]), np.random.default_rng(seed * 100 + i), 0.04)
+        ws.append(w_t.to(gpu))
+        has_b = bool(rng.integers(0, 2))
+        bs.append(Tensor.from_data(round_to(act, rng.standard_normal(widths[i + 1]).astype(np.float32) * 0.05), gpu, act) if has_b else None)
+        epis.append(int(rng.integers(0, 2)) if i < n_nodes - 1 else 0)
+        flags.append(_lib.RT_LAUNCH_LHS_CONSTANT if rng.integers(0, 2) else 0)
+    h = x_d
+    for w, b, e in zip(ws, bs, epis):
+        h = w.gemm(h, b, False, True, True, epilogue=e)
+    want = h.resolve().to(Device.CPU).to_numpy().reshape(-1)
+
+    esz = act.size_of()
+    out = Tensor([rows, widths[-1]], act, gpu, rb.GpuBuffer(gpu, rows * widths[-1] * esz))
+    nodes = []
+    for i, (w, b, e) in enumerate(zip(ws, bs, epis)):
+        d = _lib.rt_matmul_desc()
+        d.lhs_dt, d.rhs_dt = int(w.dt), int(act)
+        d.lhs_shape, d.rhs_shape = _lib.rt_shape.of(w.shape), _lib.rt_shape.of([rows, widths[i]])
+        d.trans_rhs = d.trans_out = 1
+        d.epilogue = e
+        if b is not None:
+            d.has_bias, d.bias_dt, d.bias_shape = 1, int(act), _lib.rt_shape.of([widths[i + 1]])
+        nodes.append({"plan": gpu.plan_for(d), "lhs": w.ptr, "rhs": x_d.ptr if i == 0 else ("t", i - 1),
+                      "bias": b.ptr if b is not None else None,
+                      "out": out.ptr if i == n_nodes - 1 else ("t", i), "flags": flags[i]})
+    sizes = [rows * widths[i + 1] * esz for i in range(n_nodes - 1)]
+    exe = Executable.planned(gpu, nodes, sizes, use_graph=bool(seed & 1), keep=[x_d, out] + ws + [b for b in bs if b is not None])
+    for rep in range(3):
+        exe.dispatch()
+        gpu.sync()
+        got = out.to(Device.CPU).to_numpy().reshape(-1)
+        assert np.array_equal(got, want, equal_nan=True), (rep, act, [w.dt for w in ws], rows, widths, epis, flags, exe.kernel)
