@@ -1043,3 +1043,36 @@ def test_infinities_and_nans_stay_in_their_rows(gpu, lhs_dt, act, N, K, rows):
             assert np.all(np.isnan(got[r])), kernel
         else:
             assert np.array_equal(got[r], clean[r]), (kernel, r)
+
+
+# ----------------------------------------------------------------------------- a seeded sweep over decode chains
+
+@pytest.mark.parametrize("seed", range(6))
+def test_seeded_decode_chains_against_the_oracle(gpu, seed):
+    """Decode chains of two to six Q8_0H GEMVs with widths drawn from the models' (and a few that are no multiple of
+    the kernel's row groups), bias on some nodes, GELU on every second: whatever form the executable takes (the
+    persistent kernel where every node is eligible, else a graph of single launches), every node's output meets the
+    bar against the fp64 oracle fed with the previous node's actual output, twice in a row."""
+    rng = np.random.default_rng(5200 + seed)
+    dims = [2560, 10240, 3072, 8192, 4096, 5120, 3200, 6400, 2048]
+    n = int(rng.integers(2, 7))
+    widths = [int(rng.choice(dims)) for _ in range(n + 1)]
+    shapes = [(widths[i + 1], widths[i]) for i in range(n)]
+    x_dev, nodes, host = _decode_chain(gpu, shapes, 5300 + seed, [bool(rng.integers(0, 2)) for _ in range(n)])
+    nodes[-1].resolve()
+    exe = rb.Executable(gpu, nodes, use_graph=True)
+    for trial in range(2):
+        x = np.random.default_rng(5400 + seed + trial).standard_normal(shapes[0][1]).astype(np.float16)
+        x_dev.write(x)
+        for nd in nodes:
+            nd.write(np.zeros(nd.numel(), dtype=np.float16))
+        exe.dispatch()
+        gpu.sync()
+        h = x.astype(np.float32)
+        for i, (w_vals, b_vals, epi) in enumerate(host):
+            M, K = shapes[i]
+            got = nodes[i].to(Device.CPU).to_numpy().reshape(-1).astype(np.float32)
+            truth = oracle.matmul_truth(w_vals, h, b_vals, 1, 1, 1, M, 1, K, False, True, True, epi)
+            assert np.all(np.isfinite(got)), (exe.kernel, shapes, i)
+            assert oracle.rel_l2(got, oracle.f64_to_f16(truth).astype(np.float32)) <= TOL[F16], (exe.kernel, shapes, i)
+            h = got
