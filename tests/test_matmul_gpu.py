@@ -90,6 +90,28 @@ def test_sgemm_property_space(gpu):
         check_problem(Problem(dt, dt, lhs, rhs, (tl, tr, to), bias=bool(rng.integers(0, 2)), seed=100 + case), gpu)
 
 
+def test_sgemm_property_space_at_tensor_core_sizes(gpu):
+    """The same space with extents up to 700 x 1600 x 700 (most cases reach the tensor-core GEMMs, with ragged last
+    tiles, inner dimensions that need padding, and an rhs that has to be transposed first), bf16 as a third dtype, and
+    one operand's batch broadcast against the other's."""
+    rng = np.random.default_rng(23)
+    kinds = list(TRANS_KINDS.values())
+    seen = set()
+    for case in range(36):
+        B = int(rng.integers(1, 4))
+        M, N = (int(v) for v in rng.integers(1, 701, size=2))
+        K = int(rng.integers(1, 1601))
+        tl, tr, to = kinds[case % 6]
+        dt = [F32, F16, BF16][case % 3]
+        bl, br = (B, B) if case % 4 else ((1, B) if case % 8 else (B, 1))
+        lhs = (bl, K, M) if tl else (bl, M, K)
+        rhs = (br, N, K) if tr else (br, K, N)
+        _, kernel = check_problem(Problem(dt, dt, lhs, rhs, (tl, tr, to), bias=bool(rng.integers(0, 2)), seed=300 + case,
+                                          w_std=1.0 / np.sqrt(K)), gpu)
+        seen.add(kernel.split("_")[0] + "_" + kernel.split("_")[1])
+    assert any(k.startswith("gemm_umma") for k in seen), seen
+
+
 def test_reference_regression_shapes(gpu):
     # debug_gemm (matmul.rs:854-890): transposed lhs, broadcast batch, extents not multiples of 32
     check_problem(Problem(F32, F32, (2, 222, 252), (1, 222, 238), (True, False, False), bias=True, seed=31), gpu)
