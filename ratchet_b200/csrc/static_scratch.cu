@@ -47,6 +47,9 @@ extern "C" rt_status rt_linear_q8_0_static_scratch(rt_device *dev, const void *w
     const int ordinal = rt_device_ordinal(dev), sm_count = rt_device_sm_count(dev);
     if (ordinal < 0 || ordinal >= MAX_DEVICES) return fail(RT_ERR_ARG, "device ordinal out of range");
     if (out == w || out == x || out == bias) return fail(RT_ERR_INVARIANT, "Matmul is never in place: out aliases an operand");
+    // the dequantising pass and the GEMM's tensor maps read 16 bytes at a time
+    if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) % 16 != 0)
+        return fail(RT_ERR_ARG, "rt_linear_q8_0_static_scratch: w and x must be 16-byte aligned");
     cudaError_t e = cudaSetDevice(ordinal);
     if (e != cudaSuccess) return fail(RT_ERR_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(e));
     void *scratch = nullptr;

@@ -91,3 +91,8 @@ def test_static_scratch_refuses_weights_beyond_its_array(gpu):
     # an inner extent beyond 32 bits is a shape error, not a wrapped size
     st = lib.rt_linear_q8_0_static_scratch(gpu._h, dummy.ptr, dummy.ptr + 4096, None, dummy.ptr + 8192, 16, 1, 1 << 33, 0, None)
     assert st == _lib.RT_ERR_SHAPE
+    # operands that are not 16-byte aligned are refused before anything is launched
+    st = lib.rt_linear_q8_0_static_scratch(gpu._h, dummy.ptr + 2, dummy.ptr + 4096, None, dummy.ptr + 8192, 16, 64, 64, 0, None)
+    assert st == _lib.RT_ERR_ARG
+    st = lib.rt_linear_q8_0_static_scratch(gpu._h, dummy.ptr, dummy.ptr + 4096 + 4, None, dummy.ptr + 8192, 16, 64, 64, 0, None)
+    assert st == _lib.RT_ERR_ARG and b"16-byte aligned" in lib.rt_last_error()
